@@ -1,0 +1,26 @@
+/*
+ * conv.cuh -- internal interface of the fused convolution kernels (conv_igemm.cu).
+ */
+#pragma once
+
+#include "common.cuh"
+
+namespace mb200
+{
+	/* True when an input tensor can be consumed by the fused 3x3 kernel (dtype, channel count, alignment). */
+	bool conv_fused_input_supported(const mlTensor_t &x);
+	/* True when y = act(conv3x3(x, w) + bias + ext) can run as the fused kernel. */
+	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act);
+	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
+			mlActivationType_t act);
+} /* namespace mb200 */
+
+namespace mb200
+{
+	/* Hooks of the deferred int8 sequence im2row -> int8 GEMM -> scale_shift_act (src/layers/Conv2D.cpp:214-239).
+	 * Each returns true when it consumed the call. */
+	bool im2row_defer(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &input_shape, void *output, const void *input, int kernel_size,
+			bool invert, const void *padding);
+	bool requant_complete_fused(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &shape, void *output, mlQuantizationData_t output_qd,
+			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd);
+} /* namespace mb200 */

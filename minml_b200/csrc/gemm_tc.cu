@@ -1,0 +1,525 @@
+/*
+ * gemm_tc.cu -- the tensor-core GEMM of the backend: D[b] = epilogue(alpha * A[b] * B[b]^T + beta * C[b]).
+ *
+ * Serves every 'n','t' matrix product of the inference path (reference call sites: the 36 batched Winograd
+ * products of Conv2D::forward, src/layers/Conv2D.cpp:371; 1x1 convolutions and dense layers through gemm_ex,
+ * src/core/math.cpp:682-702; the int8 -> int32 product of the quantised path, src/layers/Conv2D.cpp:232),
+ * which the reference sends to cuBLAS (src/backend/cuda/gemms.cpp:99-259).
+ *
+ * Design (one CTA per SM, persistent over output tiles of 128 x BN):
+ *   warp 0      TMA producer: A and B tiles (128 bytes of K per row, 128B swizzle) into a ring of shared-memory stages
+ *   warp 1      issues tcgen05.mma (one elected lane); owns the tensor-memory allocation
+ *   warps 2-5   epilogue: tcgen05.ld of the fp32 / s32 accumulators, alpha/beta/bias/activation or requantisation,
+ *               vectorised stores.  Two accumulator buffers in tensor memory let the epilogue of tile i overlap the
+ *               main loop of tile i+1.
+ * Both operands are K-major (row-major A[M,K] and B[N,K]); K tails and M/N tails are zero-filled by TMA.
+ */
+#include "common.cuh"
+#include "tc.cuh"
+#include "gemm.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+
+namespace mb200
+{
+	bool encode_tensor_map(void *ctx, CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
+			const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swizzle)
+	{
+		typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+				const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+				CUtensorMapFloatOOBfill);
+		static encode_fn fn = []() -> encode_fn
+		{
+			void *ptr = nullptr;
+			cudaDriverEntryPointQueryResult result;
+			if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess || ptr == nullptr)
+			{
+				cudaGetLastError();
+				return nullptr;
+			}
+			return reinterpret_cast<encode_fn>(ptr);
+		}();
+		if (fn == nullptr)
+		{
+			record_error(ctx, "cuTensorMapEncodeTiled is not available from the driver");
+			return false;
+		}
+		cuuint32_t element_strides[5] = { 1, 1, 1, 1, 1 };
+		cuuint64_t gdims[5];
+		cuuint64_t gstrides[5];
+		cuuint32_t gbox[5];
+		for (int i = 0; i < rank; i++)
+		{
+			gdims[i] = dims[i];
+			gbox[i] = box[i];
+			if (i + 1 < rank)
+				gstrides[i] = strides_bytes[i];
+		}
+		const CUresult status = fn(map, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox, element_strides,
+				CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+		if (status != CUDA_SUCCESS)
+		{
+			record_error(ctx, "cuTensorMapEncodeTiled failed with code %d (rank %d, dims %llu x %llu)", static_cast<int>(status), rank,
+					static_cast<unsigned long long>(dims[0]), static_cast<unsigned long long>(rank > 1 ? dims[1] : 0));
+			return false;
+		}
+		return true;
+	}
+
+	namespace
+	{
+		using namespace tc;
+
+		constexpr int BM = 128;
+		constexpr int BK_BYTES = 128; // one swizzle row: 64 fp16 or 128 int8
+		constexpr int NUM_THREADS = 192;
+
+		template<int BN>
+		struct Tiling
+		{
+				static constexpr int stage_bytes = BM * BK_BYTES + BN * BK_BYTES;
+				static constexpr int stages = (BN == 256) ? 4 : 6;
+				static constexpr int smem_bytes = stages * stage_bytes + 1024;
+				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
+		};
+
+		struct Barriers
+		{
+				uint64_t full[6];
+				uint64_t empty[6];
+				uint64_t tmem_full[2];
+				uint64_t tmem_empty[2];
+				uint32_t tmem_base;
+				int abort_flag;
+		};
+
+		__device__ __forceinline__ float requant_prepare(int acc, float scale, float shift)
+		{
+			return static_cast<float>(acc) * scale + shift;
+		}
+
+		template<int KIND, int BN>
+		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
+				const __grid_constant__ CUtensorMap map_b, const GemmTcParams p)
+		{
+			using T = Tiling<BN>;
+			extern __shared__ uint8_t smem_raw[];
+			__shared__ Barriers bars;
+
+			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+			const int warp = threadIdx.x / 32;
+			const int lane = threadIdx.x % 32;
+
+			const int m_tiles = (p.M + BM - 1) / BM;
+			const int n_tiles = (p.N + BN - 1) / BN;
+			const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * p.batch;
+			const int elems_per_kblock = (KIND == 0) ? 64 : 128;
+			const int k_blocks = (p.K + elems_per_kblock - 1) / elems_per_kblock;
+
+			if (threadIdx.x == 0)
+			{
+				for (int s = 0; s < T::stages; s++)
+				{
+					mbar_init(smem_u32(&bars.full[s]), 1);
+					mbar_init(smem_u32(&bars.empty[s]), 1);
+				}
+				for (int a = 0; a < 2; a++)
+				{
+					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
+					mbar_init(smem_u32(&bars.tmem_empty[a]), 4);
+				}
+				bars.abort_flag = 0;
+				fence_mbar_init();
+			}
+			if (warp == 1)
+			{
+				tmem_alloc(smem_u32(&bars.tmem_base), T::tmem_columns);
+				tmem_relinquish();
+			}
+			tcgen05_fence_before();
+			__syncthreads();
+			tcgen05_fence_after();
+			const uint32_t tmem_base = bars.tmem_base;
+			volatile int *abort_flag = &bars.abort_flag;
+
+			if (warp == 0)
+			{ /* ------------------------------------------------ TMA producer */
+				if (elect_one())
+				{
+					prefetch_tensormap(&map_a);
+					prefetch_tensormap(&map_b);
+					uint32_t it = 0;
+					bool ok = true;
+					for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+					{
+						const int nt = static_cast<int>(tile % n_tiles);
+						const int mt = static_cast<int>((tile / n_tiles) % m_tiles);
+						const int b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+						for (int kb = 0; kb < k_blocks; kb++, it++)
+						{
+							const int s = it % T::stages;
+							const uint32_t parity = ((it / T::stages) & 1u) ^ 1u;
+							if (!mbar_wait(smem_u32(&bars.empty[s]), parity, abort_flag))
+							{
+								ok = false;
+								break;
+							}
+							const uint32_t full = smem_u32(&bars.full[s]);
+							mbar_arrive_expect_tx(full, T::stage_bytes);
+							const uint32_t dst_a = smem_base + s * T::stage_bytes;
+							const uint32_t dst_b = dst_a + BM * BK_BYTES;
+							tma_load_3d(dst_a, &map_a, full, kb * elems_per_kblock, mt * BM, p.a_broadcast ? 0 : b);
+							tma_load_3d(dst_b, &map_b, full, kb * elems_per_kblock, nt * BN, p.b_broadcast ? 0 : b);
+						}
+					}
+				}
+				__syncwarp();
+			}
+			else if (warp == 1)
+			{ /* ------------------------------------------- MMA issuer */
+				if (elect_one())
+				{
+					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN);
+					uint32_t it = 0;
+					uint32_t local_tile = 0;
+					bool ok = true;
+					for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local_tile++)
+					{
+						const uint32_t acc = local_tile & 1u;
+						const uint32_t acc_parity = ((local_tile >> 1) & 1u) ^ 1u;
+						if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_parity, abort_flag))
+							break;
+						tcgen05_fence_after();
+						const uint32_t tmem_d = tmem_base + acc * BN;
+						for (int kb = 0; kb < k_blocks; kb++, it++)
+						{
+							const int s = it % T::stages;
+							const uint32_t parity = (it / T::stages) & 1u;
+							if (!mbar_wait(smem_u32(&bars.full[s]), parity, abort_flag))
+							{
+								ok = false;
+								break;
+							}
+							tcgen05_fence_after();
+							const uint32_t addr_a = smem_base + s * T::stage_bytes;
+							const uint32_t addr_b = addr_a + BM * BK_BYTES;
+							const uint64_t desc_a = make_desc_k_sw128(addr_a);
+							const uint64_t desc_b = make_desc_k_sw128(addr_b);
+#pragma unroll
+							for (int k = 0; k < 4; k++) // 4 x 32 bytes of K per stage; +2 in descriptor units of 16 bytes
+								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+							mma_commit(smem_u32(&bars.empty[s]));
+						}
+						if (ok)
+							mma_commit(smem_u32(&bars.tmem_full[acc]));
+					}
+				}
+				__syncwarp();
+			}
+			else
+			{ /* ------------------------------------------------------------ epilogue */
+				const int q = warp % 4; // tensor-memory lane quarter this warp may read
+				uint32_t local_tile = 0;
+				for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
+				{
+					const int nt = static_cast<int>(tile % n_tiles);
+					const int mt = static_cast<int>((tile / n_tiles) % m_tiles);
+					const int b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+					const uint32_t acc = local_tile & 1u;
+					const uint32_t acc_parity = (local_tile >> 1) & 1u;
+					if (!mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag))
+						break;
+					tcgen05_fence_after();
+
+					const int row = mt * BM + q * 32 + lane;
+					const bool row_ok = row < p.M;
+					const long long d_off = static_cast<long long>(b) * p.stride_d + static_cast<long long>(row) * p.ldd;
+					const long long c_off = static_cast<long long>(b) * p.stride_c + static_cast<long long>(row) * p.ldc;
+					const int n_valid_tile = min(BN, p.N - nt * BN);
+
+					for (int c = 0; c < BN / 32; c++)
+					{
+						if (c * 32 >= n_valid_tile)
+							break; // warp-uniform
+						uint32_t r[32];
+						tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+						tmem_wait_ld();
+						if (!row_ok)
+							continue;
+						const int n0 = nt * BN + c * 32;
+						const int n_valid = min(32, p.N - n0);
+						float v[32];
+						if (KIND == 0)
+						{
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = __uint_as_float(r[j]) * p.alpha;
+							if (p.beta != 0.0f && p.C != nullptr)
+							{
+								if (p.out_dtype == DTYPE_FLOAT16)
+								{
+									const __half *cp = reinterpret_cast<const __half*>(p.C) + c_off + n0;
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											v[j] += p.beta * __half2float(cp[j]);
+								}
+								else
+								{
+									const float *cp = reinterpret_cast<const float*>(p.C) + c_off + n0;
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											v[j] += p.beta * cp[j];
+								}
+							}
+							if (p.bias != nullptr)
+							{
+								if (p.out_dtype == DTYPE_FLOAT16)
+								{
+									const __half *bp = reinterpret_cast<const __half*>(p.bias) + n0;
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											v[j] += __half2float(bp[j]);
+								}
+								else
+								{
+									const float *bp = reinterpret_cast<const float*>(p.bias) + n0;
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											v[j] += bp[j];
+								}
+							}
+							if (p.act != ACTIVATION_LINEAR)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									v[j] = apply_activation(v[j], p.act);
+							}
+						}
+						else if (p.out_dtype != DTYPE_INT32)
+						{ // fused requantisation: x = acc * scale[n] + shift[n] (+ dequantised ext), activation
+							const int8_t *ep = (p.ext != nullptr) ? p.ext + c_off + n0 : nullptr;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+								{
+									float x = requant_prepare(static_cast<int>(r[j]), p.scales[n0 + j], p.shifts[n0 + j]);
+									if (ep != nullptr)
+										x += static_cast<float>(ep[j]) * p.ext_scale + p.ext_shift;
+									v[j] = (p.act == ACTIVATION_LEAKY_RELU || p.act == ACTIVATION_EXP) ? x : apply_activation(x, p.act);
+								}
+						}
+
+						if (p.out_dtype == DTYPE_FLOAT16)
+						{
+							__half *dp = reinterpret_cast<__half*>(p.D) + d_off + n0;
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j += 8)
+								{
+									uint4 pk;
+									__half2 h0 = __floats2half2_rn(v[j + 0], v[j + 1]);
+									__half2 h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+									__half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]);
+									__half2 h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+									pk.x = *reinterpret_cast<uint32_t*>(&h0);
+									pk.y = *reinterpret_cast<uint32_t*>(&h1);
+									pk.z = *reinterpret_cast<uint32_t*>(&h2);
+									pk.w = *reinterpret_cast<uint32_t*>(&h3);
+									*reinterpret_cast<uint4*>(dp + j) = pk;
+								}
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = __float2half_rn(v[j]);
+							}
+						}
+						else if (p.out_dtype == DTYPE_FLOAT32)
+						{
+							float *dp = reinterpret_cast<float*>(p.D) + d_off + n0;
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j += 4)
+									*reinterpret_cast<float4*>(dp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = v[j];
+							}
+						}
+						else if (p.out_dtype == DTYPE_INT32)
+						{
+							int *dp = reinterpret_cast<int*>(p.D) + d_off + n0;
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j += 4)
+									*reinterpret_cast<uint4*>(dp + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = static_cast<int>(r[j]);
+							}
+						}
+						else if (p.out_dtype == DTYPE_INT8)
+						{
+							int8_t *dp = reinterpret_cast<int8_t*>(p.D) + d_off + n0;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+									dp[j] = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, roundf((v[j] - p.out_shift) / p.out_scale))));
+						}
+					}
+					tcgen05_fence_before();
+					__syncwarp();
+					if (lane == 0)
+						mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
+				}
+			}
+
+			/* ---------------------------------------------------------------- teardown */
+			tcgen05_fence_before();
+			__syncthreads();
+			if (bars.abort_flag != 0)
+			{
+				if (threadIdx.x == 0 && p.status != nullptr)
+					atomicExch(p.status, 1);
+				__nanosleep(1000000); // give copies that are still in flight time to land before the CTA retires
+			}
+			if (warp == 1)
+			{
+				tcgen05_fence_after();
+				tmem_dealloc(tmem_base, T::tmem_columns);
+			}
+		}
+
+		template<int KIND, int BN>
+		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const GemmTcParams &p, int sm_count)
+		{
+			using T = Tiling<BN>;
+			static bool configured = false;
+			if (!configured)
+			{
+				if (!check_cuda(ctx,
+						cudaFuncSetAttribute(kernel_gemm_tc<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::smem_bytes),
+						"gemm_tc: shared memory opt-in"))
+					return false;
+				configured = true;
+			}
+			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
+			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+			kernel_gemm_tc<KIND, BN> <<<grid, NUM_THREADS, T::smem_bytes, stream>>>(map_a, map_b, p);
+			MB200_COUNT_LAUNCH();
+			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
+		}
+	}
+
+	bool gemm_tc_supported(const GemmTcProblem &g)
+	{
+		if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0)
+			return false;
+		const int elem = (g.kind == 0) ? 2 : 1;
+		// TMA: 16-byte aligned bases and row strides
+		if (!aligned_to(g.A, 16) || !aligned_to(g.B, 16))
+			return false;
+		if ((static_cast<long long>(g.lda) * elem) % 16 != 0 || (static_cast<long long>(g.ldb) * elem) % 16 != 0)
+			return false;
+		if (g.batch > 1)
+		{
+			if (g.stride_a != 0 && (g.stride_a * elem) % 16 != 0)
+				return false;
+			if (g.stride_b != 0 && (g.stride_b * elem) % 16 != 0)
+				return false;
+		}
+		if (g.kind == 0 && g.out_dtype != DTYPE_FLOAT16 && g.out_dtype != DTYPE_FLOAT32)
+			return false;
+		if (g.kind == 1 && g.out_dtype != DTYPE_INT32 && g.out_dtype != DTYPE_INT8 && g.out_dtype != DTYPE_FLOAT16
+				&& g.out_dtype != DTYPE_FLOAT32)
+			return false;
+		return true;
+	}
+
+	bool gemm_tc_run(mlContext_t ctx, const GemmTcProblem &g)
+	{
+		Context *c = get(ctx);
+		cudaStream_t stream = use_stream(ctx);
+		const int elem = (g.kind == 0) ? 2 : 1;
+		const CUtensorMapDataType dt = (g.kind == 0) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+		const int bn = (g.N > 128) ? 256 : 128;
+		const uint32_t box_k = (g.kind == 0) ? 64 : 128;
+
+		const bool a_bcast = (g.batch > 1 && g.stride_a == 0);
+		const bool b_bcast = (g.batch > 1 && g.stride_b == 0);
+		CUtensorMap map_a, map_b;
+		{
+			const uint64_t dims[3] = { static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M), static_cast<uint64_t>(
+					(a_bcast || g.batch == 1) ? 1 : g.batch) };
+			const uint64_t strides[2] = { static_cast<uint64_t>(g.lda) * elem, (a_bcast || g.batch == 1) ? static_cast<uint64_t>(g.lda) * elem
+					* g.M : static_cast<uint64_t>(g.stride_a) * elem };
+			const uint32_t box[3] = { box_k, static_cast<uint32_t>(BM), 1 };
+			if (!encode_tensor_map(ctx, &map_a, dt, 3, g.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+				return false;
+		}
+		{
+			const uint64_t dims[3] = { static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.N), static_cast<uint64_t>(
+					(b_bcast || g.batch == 1) ? 1 : g.batch) };
+			const uint64_t strides[2] = { static_cast<uint64_t>(g.ldb) * elem, (b_bcast || g.batch == 1) ? static_cast<uint64_t>(g.ldb) * elem
+					* g.N : static_cast<uint64_t>(g.stride_b) * elem };
+			const uint32_t box[3] = { box_k, static_cast<uint32_t>(bn), 1 };
+			if (!encode_tensor_map(ctx, &map_b, dt, 3, g.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+				return false;
+		}
+		GemmTcParams p;
+		std::memset(&p, 0, sizeof(p));
+		p.M = g.M;
+		p.N = g.N;
+		p.K = g.K;
+		p.batch = g.batch;
+		p.a_broadcast = a_bcast ? 1 : 0;
+		p.b_broadcast = b_bcast ? 1 : 0;
+		p.D = g.D;
+		p.ldd = g.ldd;
+		p.stride_d = g.stride_d;
+		p.C = g.C;
+		p.ldc = g.ldc;
+		p.stride_c = g.stride_c;
+		p.bias = g.bias;
+		p.alpha = g.alpha;
+		p.beta = g.beta;
+		p.act = g.act;
+		p.out_dtype = g.out_dtype;
+		p.scales = g.scales;
+		p.shifts = g.shifts;
+		p.ext = g.ext;
+		p.ext_scale = g.ext_scale;
+		p.ext_shift = g.ext_shift;
+		p.out_scale = g.out_scale;
+		p.out_shift = g.out_shift;
+		p.status = c->dev_status;
+		c->kernels_with_waits = true;
+
+		if (g.kind == 0)
+			return (bn == 256) ? launch<0, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128>(ctx, stream, map_a, map_b, p,
+							c->sm_count);
+		else
+			return (bn == 256) ? launch<1, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<1, 128>(ctx, stream, map_a, map_b, p,
+							c->sm_count);
+	}
+} /* namespace mb200 */

@@ -1,0 +1,230 @@
+/*
+ * quantized.cu -- eager entry points of the int8 path: requantisation of int32 accumulators, im2row, dequantise.
+ *
+ * Replaces src/backend/cuda/kernels/quantized.cu:219-262,563-645 of the reference.
+ *
+ *   scale_shift_act:  x = acc[i, c] * scales[c] + bias[c] (+ ext[i, c] * ext_qd.scale + ext_qd.shift);
+ *                     activation in {linear, sigmoid, tanh, relu} (anything else is left linear, as in the reference);
+ *                     output fp16 / fp32 / fp64, or int8 = clamp(round((x - out_qd.shift) / out_qd.scale), -128, 127)
+ *                     with round-half-away-from-zero.
+ *   im2row:           [b, h, w, c] -> [b*h*w, k*k*c], columns ordered (kh, kw, c), taps outside the image filled with
+ *                     *padding (zero when the pointer is null).  Unlike the reference's active code path this one
+ *                     handles int8 and honours `padding`, which the host's int8 3x3 convolution needs
+ *                     (src/layers/Conv2D.cpp:227-232).
+ */
+#include "common.cuh"
+#include "conv.cuh"
+
+#include <cstring>
+
+namespace mb200
+{
+	namespace
+	{
+		template<typename T> __device__ __forceinline__ void store_value(T *p, float x, float inv_unused, float scale, float shift);
+		template<> __device__ __forceinline__ void store_value<float>(float *p, float x, float, float, float) { *p = x; }
+		template<> __device__ __forceinline__ void store_value<double>(double *p, float x, float, float, float) { *p = x; }
+		template<> __device__ __forceinline__ void store_value<__half>(__half *p, float x, float, float, float) { *p = __float2half_rn(x); }
+		template<> __device__ __forceinline__ void store_value<int8_t>(int8_t *p, float x, float, float scale, float shift)
+		{
+			*p = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, roundf((x - shift) / scale))));
+		}
+
+		template<typename T>
+		__global__ void __launch_bounds__(256) kernel_scale_shift_act(T *__restrict__ output, const int *__restrict__ input,
+				const float *__restrict__ scales, const float *__restrict__ bias, const int8_t *__restrict__ ext, long long rows, int channels,
+				int act, float out_scale, float out_shift, float ext_scale, float ext_shift)
+		{
+			const long long total = rows * channels;
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+			{
+				const int c = static_cast<int>(i % channels);
+				float x = static_cast<float>(input[i]) * scales[c] + bias[c];
+				if (ext != nullptr)
+					x += static_cast<float>(ext[i]) * ext_scale + ext_shift;
+				if (act == ACTIVATION_SIGMOID || act == ACTIVATION_TANH || act == ACTIVATION_RELU)
+					x = apply_activation(x, act);
+				store_value<T>(output + i, x, 0.0f, out_scale, out_shift);
+			}
+		}
+
+		template<typename T>
+		__global__ void __launch_bounds__(256) kernel_dequantize(T *__restrict__ output, const int8_t *__restrict__ input, long long elements,
+				float scale, float shift)
+		{
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < elements; i += stride)
+				store_value<T>(output + i, static_cast<float>(input[i]) * scale + shift, 0.0f, 1.0f, 0.0f);
+		}
+
+		/* One thread moves one packet of VB bytes of one tap of one output position. */
+		template<int VB> struct PacketOf;
+		template<> struct PacketOf<1> { using type = uint8_t; };
+		template<> struct PacketOf<2> { using type = uint16_t; };
+		template<> struct PacketOf<4> { using type = uint32_t; };
+		template<> struct PacketOf<8> { using type = uint2; };
+		template<> struct PacketOf<16> { using type = uint4; };
+
+		template<int VB>
+		__global__ void __launch_bounds__(256) kernel_im2row(void *__restrict__ output, const void *__restrict__ input, int batch, int height,
+				int width, int row_bytes, int kernel, bool invert, typename PacketOf<VB>::type pad)
+		{
+			using P = typename PacketOf<VB>::type;
+			const int packets = row_bytes / VB; // per (position, tap)
+			const int pad_hw = (kernel - 1) / 2;
+			const long long total = static_cast<long long>(batch) * height * width * kernel * kernel * packets;
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			const P *src = reinterpret_cast<const P*>(input);
+			P *dst = reinterpret_cast<P*>(output);
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+			{
+				const int pk = static_cast<int>(i % packets);
+				long long t = i / packets;
+				const int kw = static_cast<int>(t % kernel);
+				t /= kernel;
+				const int kh = static_cast<int>(t % kernel);
+				t /= kernel;
+				const int w = static_cast<int>(t % width);
+				t /= width;
+				const int h = static_cast<int>(t % height);
+				const int b = static_cast<int>(t / height);
+				const int ih = h - pad_hw + (invert ? (kernel - 1 - kh) : kh);
+				const int iw = w - pad_hw + (invert ? (kernel - 1 - kw) : kw);
+				P v = pad;
+				if (ih >= 0 && ih < height && iw >= 0 && iw < width)
+					v = src[((static_cast<long long>(b) * height + ih) * width + iw) * packets + pk];
+				dst[i] = v;
+			}
+		}
+		template<int VB>
+		void launch_im2row(cudaStream_t stream, int grid, void *output, const void *input, int batch, int height, int width, int row_bytes,
+				int kernel, bool invert, const uint8_t (&pattern)[16])
+		{
+			typename PacketOf<VB>::type pad;
+			std::memcpy(&pad, pattern, VB);
+			kernel_im2row<VB> <<<grid, 256, 0, stream>>>(output, input, batch, height, width, row_bytes, kernel, invert, pad);
+			MB200_COUNT_LAUNCH();
+		}
+	}
+} /* namespace mb200 */
+
+using namespace mb200;
+
+extern "C"
+{
+	void cuda_quantized_scale_shift_act(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *output, mlQuantizationData_t output_qd,
+			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd)
+	{
+		MB200_REQUIRE(context, context != nullptr, "cuda_quantized_scale_shift_act: null context");
+		MB200_REQUIRE(context, output != nullptr && input != nullptr && scales != nullptr && bias != nullptr,
+				"cuda_quantized_scale_shift_act: null pointer");
+		if (requant_complete_fused(context, dtype, shape, output, output_qd, input, scales, bias, act, ext, ext_qd))
+			return;
+		flush_pending(context);
+		const long long rows = volume_without_last_dim(shape);
+		const int channels = last_dim(shape);
+		if (rows == 0 || channels == 0)
+			return;
+		cudaStream_t stream = use_stream(context);
+		const int grid = static_cast<int>(std::min<long long>((rows * channels + 255) / 256, static_cast<long long>(get(context)->sm_count) * 16));
+#define ARGS(T) reinterpret_cast<T*>(output), reinterpret_cast<const int*>(input), reinterpret_cast<const float*>(scales), \
+		reinterpret_cast<const float*>(bias), reinterpret_cast<const int8_t*>(ext), rows, channels, static_cast<int>(act), \
+		output_qd.scale, output_qd.shift, ext_qd.scale, ext_qd.shift
+		switch (dtype)
+		{
+			case DTYPE_FLOAT16:
+				kernel_scale_shift_act<__half> <<<grid, 256, 0, stream>>>(ARGS(__half));
+				break;
+			case DTYPE_FLOAT32:
+				kernel_scale_shift_act<float> <<<grid, 256, 0, stream>>>(ARGS(float));
+				break;
+			case DTYPE_FLOAT64:
+				kernel_scale_shift_act<double> <<<grid, 256, 0, stream>>>(ARGS(double));
+				break;
+			case DTYPE_INT8:
+				kernel_scale_shift_act<int8_t> <<<grid, 256, 0, stream>>>(ARGS(int8_t));
+				break;
+			default:
+				record_error(context, "cuda_quantized_scale_shift_act: output dtype %d not supported", static_cast<int>(dtype));
+				return;
+		}
+#undef ARGS
+		MB200_COUNT_LAUNCH();
+		check_cuda(context, cudaGetLastError(), "cuda_quantized_scale_shift_act");
+	}
+	void cuda_dequantize(mlContext_t context, mlDataType_t dtype, const void *input, void *output, int elements, float scale, float shift)
+	{
+		MB200_REQUIRE(context, context != nullptr, "cuda_dequantize: null context");
+		if (elements <= 0)
+			return;
+		MB200_REQUIRE(context, input != nullptr && output != nullptr, "cuda_dequantize: null pointer");
+		flush_pending(context);
+		cudaStream_t stream = use_stream(context);
+		const int grid = static_cast<int>(std::min<long long>((elements + 255) / 256, static_cast<long long>(get(context)->sm_count) * 16));
+		switch (dtype)
+		{
+			case DTYPE_FLOAT16:
+				kernel_dequantize<__half> <<<grid, 256, 0, stream>>>(reinterpret_cast<__half*>(output), reinterpret_cast<const int8_t*>(input),
+						elements, scale, shift);
+				break;
+			case DTYPE_FLOAT32:
+				kernel_dequantize<float> <<<grid, 256, 0, stream>>>(reinterpret_cast<float*>(output), reinterpret_cast<const int8_t*>(input),
+						elements, scale, shift);
+				break;
+			case DTYPE_FLOAT64:
+				kernel_dequantize<double> <<<grid, 256, 0, stream>>>(reinterpret_cast<double*>(output), reinterpret_cast<const int8_t*>(input),
+						elements, scale, shift);
+				break;
+			default:
+				record_error(context, "cuda_dequantize: output dtype %d not supported", static_cast<int>(dtype));
+				return;
+		}
+		MB200_COUNT_LAUNCH();
+		check_cuda(context, cudaGetLastError(), "cuda_dequantize");
+	}
+	void cuda_im2row(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, void *output, const void *input, int kernel_size, bool invert,
+			const void *padding)
+	{
+		MB200_REQUIRE(context, context != nullptr, "cuda_im2row: null context");
+		MB200_REQUIRE(context, input_shape.rank == 4 && output != nullptr && input != nullptr, "cuda_im2row: needs a rank-4 input and buffers");
+		MB200_REQUIRE(context, kernel_size >= 1 && kernel_size % 2 == 1, "cuda_im2row: kernel size %d must be odd", kernel_size);
+		const int elem = size_of(dtype);
+		MB200_REQUIRE(context, elem > 0, "cuda_im2row: dtype %d not supported", static_cast<int>(dtype));
+		const int batch = input_shape.dim[0], height = input_shape.dim[1], width = input_shape.dim[2], channels = input_shape.dim[3];
+		if (batch == 0 || height == 0 || width == 0 || channels == 0)
+			return;
+		if (im2row_defer(context, dtype, input_shape, output, input, kernel_size, invert, padding))
+			return;
+		flush_pending(context);
+		const int row_bytes = channels * elem;
+		uint8_t pattern[16];
+		for (int i = 0; i < 16; i++)
+			pattern[i] = (padding == nullptr) ? 0 : reinterpret_cast<const uint8_t*>(padding)[i % elem];
+		int vb = 16;
+		while (vb > elem && (row_bytes % vb != 0 || !aligned_to(input, vb) || !aligned_to(output, vb)))
+			vb /= 2;
+		cudaStream_t stream = use_stream(context);
+		const long long total = static_cast<long long>(batch) * height * width * kernel_size * kernel_size * (row_bytes / vb);
+		const int grid = static_cast<int>(std::min<long long>((total + 255) / 256, static_cast<long long>(get(context)->sm_count) * 32));
+		switch (vb)
+		{
+			case 16:
+				launch_im2row<16>(stream, grid, output, input, batch, height, width, row_bytes, kernel_size, invert, pattern);
+				break;
+			case 8:
+				launch_im2row<8>(stream, grid, output, input, batch, height, width, row_bytes, kernel_size, invert, pattern);
+				break;
+			case 4:
+				launch_im2row<4>(stream, grid, output, input, batch, height, width, row_bytes, kernel_size, invert, pattern);
+				break;
+			case 2:
+				launch_im2row<2>(stream, grid, output, input, batch, height, width, row_bytes, kernel_size, invert, pattern);
+				break;
+			default:
+				launch_im2row<1>(stream, grid, output, input, batch, height, width, row_bytes, kernel_size, invert, pattern);
+				break;
+		}
+		check_cuda(context, cudaGetLastError(), "cuda_im2row");
+	}
+}

@@ -1,0 +1,208 @@
+/*
+ * tc.cuh -- inline-PTX wrappers for the Blackwell (sm_100a) tensor path: mbarrier, TMA (cp.async.bulk.tensor),
+ * tensor memory (tcgen05.alloc / ld / dealloc) and tcgen05.mma with shared-memory operand descriptors.
+ *
+ * Every wait in here is bounded: after SPIN_LIMIT failed polls the waiter raises the CTA-wide abort flag and
+ * returns false, so a kernel built from these pieces always terminates and reports through its status word.
+ */
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace mb200
+{
+	namespace tc
+	{
+		constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+		__device__ __forceinline__ uint32_t smem_u32(const void *ptr)
+		{
+			return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+		}
+		__device__ __forceinline__ bool elect_one()
+		{
+			uint32_t pred = 0;
+			asm volatile(
+					"{\n\t"
+					".reg .pred P;\n\t"
+					"elect.sync _|P, 0xffffffff;\n\t"
+					"selp.u32 %0, 1, 0, P;\n\t"
+					"}\n" : "=r"(pred));
+			return pred != 0;
+		}
+
+		/* ---------------------------------------------------------------- mbarrier */
+		__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+		{
+			asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+		}
+		__device__ __forceinline__ void fence_mbar_init()
+		{
+			asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+		}
+		__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+		{
+			asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+		}
+		__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+		{
+			asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+		}
+		__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+		{
+			uint32_t done;
+			asm volatile(
+					"{\n\t"
+					".reg .pred P;\n\t"
+					"mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+					"selp.u32 %0, 1, 0, P;\n\t"
+					"}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+			return done != 0;
+		}
+		/* Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles of the CTA. */
+		__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+		{
+			for (uint32_t it = 0; it < SPIN_LIMIT; ++it)
+			{
+				if (mbar_try_wait(bar, parity))
+					return true;
+				if ((it & 255u) == 255u && *abort_flag != 0)
+					return false;
+			}
+			*abort_flag = 1;
+			return false;
+		}
+
+		/* ---------------------------------------------------------------- TMA */
+		__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
+		{
+			asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(map)) : "memory");
+		}
+		__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+		}
+		__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+		}
+		/* Makes generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05.mma operand reads). */
+		__device__ __forceinline__ void fence_proxy_async_smem()
+		{
+			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+		}
+
+		/* ---------------------------------------------------------------- tensor memory */
+		__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t columns)
+		{
+			asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_result), "r"(columns) : "memory");
+		}
+		__device__ __forceinline__ void tmem_relinquish()
+		{
+			asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+		}
+		__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns)
+		{
+			asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(columns) : "memory");
+		}
+		__device__ __forceinline__ void tcgen05_fence_before()
+		{
+			asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+		}
+		__device__ __forceinline__ void tcgen05_fence_after()
+		{
+			asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+		}
+		__device__ __forceinline__ void tmem_wait_ld()
+		{
+			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+		}
+		/* 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives row (lane base + t). */
+		__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
+		{
+			asm volatile(
+					"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+					"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+					"%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+					: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+					"=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+					"=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+					"=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+					: "r"(taddr) : "memory");
+		}
+		__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
+		{
+			asm volatile(
+					"tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+					"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+					: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+					"=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+					: "r"(taddr) : "memory");
+		}
+		__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8])
+		{
+			asm volatile(
+					"tcgen05.ld.sync.aligned.32x32b.x8.b32 "
+					"{%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+					: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+					: "r"(taddr) : "memory");
+		}
+
+		/* ---------------------------------------------------------------- tcgen05.mma */
+		/* Shared-memory operand descriptor for a K-major tile stored with the 128-byte swizzle: rows of 128 bytes,
+		 * 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor version 1. */
+		__device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr)
+		{
+			uint64_t desc = 0;
+			desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+			desc |= static_cast<uint64_t>(1) << 16;
+			desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+			desc |= static_cast<uint64_t>(1) << 46;
+			desc |= static_cast<uint64_t>(2) << 61;
+			return desc;
+		}
+		/* Instruction descriptors: D fp32 <- fp16 x fp16, and D s32 <- s8 x s8; both operands K-major, M = 128. */
+		__host__ __device__ constexpr uint32_t make_idesc_f16(int n)
+		{
+			return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+		}
+		__host__ __device__ constexpr uint32_t make_idesc_i8(int n)
+		{
+			return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+		}
+		template<int KIND> // 0: kind::f16, 1: kind::i8
+		__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+		{
+			if (KIND == 0)
+				asm volatile(
+						"{\n\t"
+						".reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+			else
+				asm volatile(
+						"{\n\t"
+						".reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+		}
+		/* The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has completed. */
+		__device__ __forceinline__ void mma_commit(uint32_t bar)
+		{
+			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+		}
+	} /* namespace tc */
+
+	/* Host side: cuTensorMapEncodeTiled fetched through the runtime so the library has no link-time dependency
+	 * on libcuda.  Returns false (and records an error on ctx) when the driver entry point is unavailable. */
+	bool encode_tensor_map(void *ctx, CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
+			const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swizzle);
+} /* namespace mb200 */
