@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Throughput of the ResNet-trunk inference path on B200, through the backend's C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c3|c1] [--impl ours|reference]
+
+One "step" is one forward pass of the trunk over one batch of synthetic positions (bit-packed planes in, policy and
+value out).  Default workload: BASELINE config 3 -- 20x20 board, 32 input planes (Bernoulli p = 0.3), stem 3x3 32 -> 256,
+20 residual blocks of two 3x3 256 -> 256 convolutions with bias and ReLU, 1x1 policy head, global-average-pool + dense
+value head, fp16, batch 1024 per GPU, He-normal random weights.  With N > 1 (launched by torch.distributed.run) every
+rank runs the same per-GPU batch on its own GPU: weak scaling, no collective on the forward path.
+
+The JSON line printed by rank 0 carries:
+  value       positions/s with the packed input already resident in HBM (device time, CUDA events, max over ranks)
+  e2e         positions/s through the C ABI with HOST buffers: pinned host -> device copy of the packed planes,
+              forward, device -> host copy of policy and value, inside the timed region
+  roofline    the dominant kernel of a 256 -> 256 layer, timed alone with CUDA events on the context's stream
+  cpu_baseline  minml's own CPU backend (oracle/_ref, else the C port) on the host cores, on a bounded sample
+`--impl reference` times only that CPU implementation and prints the same line shape with "impl": "reference".
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (batch per GPU, height, width, input planes, channels, blocks)
+    "c3": dict(batch=1024, height=20, width=20, planes=32, channels=256, blocks=20,
+               label="config3: 20x20 board, 32 planes, stem 3x3 32->256, 20 residual blocks x 2 conv3x3 256->256, policy 1x1 + value GAP/dense, fp16"),
+    "c1": dict(batch=256, height=15, width=15, planes=32, channels=128, blocks=10,
+               label="config1: 15x15 board, 32 planes, stem 3x3 32->128, 10 residual blocks x 2 conv3x3 128->128, policy 1x1 + value GAP/dense, fp16"),
+}
+SEED = 1237
+
+
+def flops_per_position(cfg):
+    hw = cfg["height"] * cfg["width"]
+    c = cfg["channels"]
+    f = 2 * hw * 9 * cfg["planes"] * c + cfg["blocks"] * 2 * (2 * hw * 9 * c * c) + 2 * hw * c + 2 * c * 3
+    return f
+
+
+def synthetic_input(cfg, batch, seed):
+    from tests.util import pack_planes  # pure numpy helper
+    x = (np.random.default_rng(seed).random((batch, cfg["height"], cfg["width"], cfg["planes"])) < 0.3).astype(np.float32)
+    return x, pack_planes(x).view(np.int32)
+
+
+# ---------------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs (reading only)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------- CPU arm
+def cpu_reference_arm(cfg, steps, warmup, threads=None):
+    """minml's CPU backend (fp32, its own F(5x5,3x3) choice for inference, src/layers/Conv2D.cpp:463-467) on a bounded
+    sample: every host thread runs the whole trunk on its own shard of `per_thread` positions."""
+    from tests import checkers
+    from minml_b200 import layers
+    threads = threads or os.cpu_count() or 1
+    per_thread = 2
+    ref_lib = checkers.load_reference_cpu()
+    kind = "reference" if ref_lib is not None else "port"
+    weights = layers.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
+    x, _ = synthetic_input(cfg, threads * per_thread, SEED + 1)
+
+    if ref_lib is not None:
+        workers = [checkers.load_reference_cpu() if i else ref_lib for i in range(threads)]  # one backend context per thread
+
+        # transformed weights are computed once per layer and cached, as Conv2D does (src/layers/Conv2D.cpp:356-363)
+        names = ["stem_w"] + ["b%d_w%d" % (blk, j) for blk in range(cfg["blocks"]) for j in (1, 2)]
+        cache = {n: ref_lib.winograd_weight_transform(weights[n], 5) for n in names}
+
+        def conv(r, xs, wn, bn, ext):
+            return r.conv3x3_winograd(xs, weights[wn], weights[bn], ext, "relu", 5, cache[wn])
+
+        def run(i):
+            r = workers[i]
+            a = conv(r, x[i * per_thread:(i + 1) * per_thread], "stem_w", "stem_b", None)
+            for blk in range(cfg["blocks"]):
+                t = conv(r, a, "b%d_w1" % blk, "b%d_b1" % blk, None)
+                a = conv(r, t, "b%d_w2" % blk, "b%d_b2" % blk, a)
+            rows = a.reshape(-1, cfg["channels"])
+            r.gemm_ex(rows, weights["policy_w"].reshape(1, -1), weights["policy_b"], "linear")
+            r.gemm_ex(r.global_average_pooling(a), weights["value_w"], weights["value_b"], "linear")
+    else:
+        oracle = checkers.load_oracle()
+        from tests.util import oracle_trunk
+
+        def run(i):
+            oracle_trunk(oracle, weights, x[i * per_thread:(i + 1) * per_thread], cfg["blocks"])
+
+    def step():
+        ts = [threading.Thread(target=run, args=(i,)) for i in range(threads)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    positions = threads * per_thread * steps
+    return {"value": positions / dt, "unit": "positions/s", "cores": threads, "kind": kind,
+            "sample": "%d positions per step (%d per host thread, %d threads), %d steps, fp32, whole trunk" % (
+                threads * per_thread, per_thread, threads, steps),
+            "seconds": dt, "ms_per_step": dt / steps * 1e3}
+
+
+# ---------------------------------------------------------------------------------------------------- GPU arm
+def layer_roofline(B, L, ctx, cfg, peaks, torch):
+    """Times the three kernels of one channels -> channels 3x3 layer alone (CUDA events on the context's stream) and
+    returns the roofline record of the one that takes the largest share."""
+    b, h, w, c = cfg["batch"], cfg["height"], cfg["width"], cfg["channels"]
+    tiles = b * ((h + 3) // 4) * ((w + 3) // 4)
+    rng = np.random.default_rng(3)
+    wt = (rng.standard_normal((c, 3, 3, c)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    conv = L.Conv2D(ctx, wt, np.zeros(c, np.float32), "relu", torch.float16)
+    x = torch.randn((b, h, w, c), device="cuda", dtype=torch.float16)
+    res = torch.randn((b, h, w, c), device="cuda", dtype=torch.float16)
+    y = torch.empty_like(x)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    ctx.set_fusion(False)
+    conv.forward([x, res], y, ws)  # builds the transformed weights
+    v = ws.view((36, tiles, c), torch.float16)
+    m = ws.view((36, tiles, c), torch.float16, 36 * tiles * c * 2)
+    act_bytes = b * h * w * c * 2
+    mat_bytes = 36 * tiles * c * 2
+    stages = {
+        "winograd_input_transform": (lambda: B.winogradInputTransform(ctx, wt.shape, x, v, 4), act_bytes + mat_bytes, 0.0),
+        "gemm_tc (36 batched products)": (lambda: B.gemmBatched(ctx, "n", v, "t", conv.transformed, m), 2 * mat_bytes + 36 * c * c * 2,
+                                          2.0 * 36 * tiles * c * c),
+        "winograd_output_transform": (lambda: B.winogradOutputTransform(ctx, wt.shape, m, y, conv.bias, res, "relu", 4),
+                                      mat_bytes + 2 * act_bytes, 0.0),
+    }
+    out = {}
+    reps = 10
+    for name, (fn, nbytes, flops) in stages.items():
+        for _ in range(3):
+            fn()
+        ctx.synchronize()
+        e0 = B.lib.cuda_create_event(ctx.handle)
+        for _ in range(reps):
+            fn()
+        e1 = B.lib.cuda_create_event(ctx.handle)
+        ctx.synchronize()
+        sec = B.lib.cuda_get_time_between_events(e0, e1) / reps
+        B.lib.cuda_destroy_event(e0)
+        B.lib.cuda_destroy_event(e1)
+        out[name] = dict(seconds=sec, bytes=nbytes, flops=flops)
+    ctx.set_fusion(True)
+    total = sum(s["seconds"] for s in out.values())
+    name, top = max(out.items(), key=lambda kv: kv[1]["seconds"])
+    hbm = top["bytes"] / top["seconds"] / 1e9
+    rec = {"kernel": name, "bound": "hbm", "achieved": hbm, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm / peaks["hbm_gbs"],
+           "traffic": None, "peak_source": peaks["source"], "launch_ms": top["seconds"] * 1e3, "share_of_layer": top["seconds"] / total,
+           "algorithmic_bytes": top["bytes"],
+           "layer_ms": {k: s["seconds"] * 1e3 for k, s in out.items()},
+           "layer_gbs": {k: s["bytes"] / s["seconds"] / 1e9 for k, s in out.items()}}
+    if top["flops"] > 0:
+        tf = top["flops"] / top["seconds"] / 1e12
+        rec["tensor_tflops_executed"] = tf
+        rec["tensor_frac_of_measured_bf16_burst"] = tf / peaks["bf16_tflops"]
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        rec["traffic"] = json.load(open(traffic_file)).get(name)
+    return rec
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def gpu_arm(args, cfg):
+    import torch
+    import torch.distributed as dist
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ctx = B.Context(local)
+    batch = cfg["batch"]
+    weights = L.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
+    net = L.ResNetTrunk(ctx, weights, batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
+    _, packed = synthetic_input(cfg, batch, SEED + 1 + rank)
+    packed_host = torch.from_numpy(packed).pin_memory()
+    packed_dev = packed_host.cuda()
+    policy_host = torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory()
+    value_host = torch.empty((batch, 3), dtype=torch.float16).pin_memory()
+    h2d = packed_host.numel() * 4
+    d2h = policy_host.numel() * 2 + value_host.numel() * 2
+
+    def step_device():
+        net.predict(packed_dev)
+
+    def step_e2e():
+        B.lib.cuda_memcpy_from_host(ctx.handle, ctypes.c_void_p(net.packed.data_ptr()), 0, ctypes.c_void_p(packed_host.data_ptr()), h2d)
+        policy, value = net.predict(None)
+        B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(policy_host.data_ptr()), ctypes.c_void_p(policy.data_ptr()), 0, policy.numel() * 2)
+        B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(value_host.data_ptr()), ctypes.c_void_p(value.data_ptr()), 0, value.numel() * 2)
+        ctx.synchronize()  # the caller reads the result of every step
+
+    def timed(fn, steps):
+        barrier()
+        e0 = B.lib.cuda_create_event(ctx.handle)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        e1 = B.lib.cuda_create_event(ctx.handle)
+        ctx.synchronize()
+        wall = time.perf_counter() - t0
+        dev_s = B.lib.cuda_get_time_between_events(e0, e1)
+        B.lib.cuda_destroy_event(e0)
+        B.lib.cuda_destroy_event(e1)
+        barrier()
+        t = torch.tensor([dev_s, wall], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]), float(t[1])
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    ctx.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = B.launch_count()
+    dev_s, _ = timed(step_device, args.steps)
+    launches = B.launch_count() - launches0
+    net.packed = torch.empty_like(packed_dev)
+    for _ in range(2):
+        step_e2e()
+    e2e_dev_s, e2e_wall = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_s = max(e2e_dev_s, e2e_wall)  # the step ends when the host holds the result
+
+    # sanity: the resident and the host-fed run computed the same thing
+    ctx.synchronize()
+    result = None
+    if rank == 0:
+        peaks = load_peaks()
+        roof = layer_roofline(B, L, ctx, cfg, peaks, torch)
+        total_positions = batch * world * args.steps
+        value = total_positions / dev_s
+        fpp = flops_per_position(cfg)
+        result = {
+            "metric": "positions/sec for ResNet trunk", "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world,
+                       "l2": "activations of every layer (%.0f MB) exceed the 126 MB L2, no flush needed" % (
+                           batch * cfg["height"] * cfg["width"] * cfg["channels"] * 2 / 1e6)},
+            "algorithmic_tflops": value * fpp / 1e12, "frac_of_nominal_fp16_dense_peak": value * fpp / world / 2.25e15,
+            "e2e": {"value": total_positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s / args.steps * 1e3},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+        }
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return result
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = min(args.steps, 3)
+        base = cpu_reference_arm(cfg, steps, min(args.warmup, 1))
+        line = {"impl": "reference", "metric": "positions/sec for ResNet trunk", "value": base["value"], "unit": "positions/s", "n_gpus": args.gpus,
+                "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": cfg["label"], "note": "host CPU implementation; each step is a bounded sample of the workload"},
+                "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": base["value"], "unit": "positions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    result = gpu_arm(args, cfg)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            base = cpu_reference_arm(cfg, 1, 1)
+            result["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        else:
+            result["cpu_baseline"] = None
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,258 @@
+"""Python mirror of the reference's dispatcher functions (include/minml/core/math.hpp:28-225) for the inference path.
+
+Each function takes torch CUDA tensors, builds the POD descriptors and calls the matching `cuda_*` entry point of
+libminml_b200.so through ctypes -- the same calls, in the same argument order, that src/core/math.cpp makes.
+torch is used for device memory only.  After every call the context's sticky error is checked and raised.
+"""
+import ctypes
+
+import torch
+
+from . import _abi
+from ._abi import (ACTIVATION_LINEAR, ACTIVATION_RELU, ACTIVATION_SIGMOID, ACTIVATION_TANH,  # noqa: F401
+                   ACTIVATION_LEAKY_RELU, ACTIVATION_EXP, mlQuantizationData_t, mlShape_t, mlTensor_t)
+
+lib = _abi.load()
+
+_DTYPES = {
+    torch.float16: _abi.DTYPE_FLOAT16, torch.float32: _abi.DTYPE_FLOAT32, torch.float64: _abi.DTYPE_FLOAT64,
+    torch.uint8: _abi.DTYPE_UINT8, torch.int8: _abi.DTYPE_INT8, torch.int16: _abi.DTYPE_INT16, torch.int32: _abi.DTYPE_INT32,
+}
+ACTIVATIONS = {"linear": ACTIVATION_LINEAR, "sigmoid": ACTIVATION_SIGMOID, "tanh": ACTIVATION_TANH, "relu": ACTIVATION_RELU,
+               "leaky_relu": ACTIVATION_LEAKY_RELU, "exp": ACTIVATION_EXP}
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+def dtype_of(t):
+    return _DTYPES[t.dtype]
+
+
+def shape_of(t_or_dims):
+    dims = list(t_or_dims.shape) if isinstance(t_or_dims, torch.Tensor) else list(t_or_dims)
+    s = mlShape_t()
+    s.rank = len(dims)
+    for i, d in enumerate(dims):
+        s.dim[i] = int(d)
+    return s
+
+
+def desc(t):
+    """mlTensor_t for a dense torch tensor; None gives the empty descriptor (null data, rank 0)."""
+    d = mlTensor_t()
+    if t is None:
+        d.data = None
+        d.dtype = _abi.DTYPE_UNKNOWN
+        d.rank = 0
+        return d
+    assert t.is_contiguous(), "the backend ABI addresses dense row-major tensors only"
+    d.data = t.data_ptr()
+    d.dtype = dtype_of(t)
+    d.rank = t.dim()
+    for i, n in enumerate(t.shape):
+        d.dim[i] = int(n)
+    return d
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def act_code(act):
+    return ACTIVATIONS[act] if isinstance(act, str) else int(act)
+
+
+class Context:
+    """ml::Context on Device::cuda(index) (reference: src/core/Context.cpp:20-60)."""
+
+    def __init__(self, device_index=0):
+        n = lib.cuda_get_number_of_devices()
+        if n == 0:
+            raise BackendError("no CUDA device: libminml_b200 has no CPU fallback")
+        self.device_index = device_index
+        self.handle = lib.cuda_create_context(device_index)
+        if not self.handle:
+            raise BackendError("cuda_create_context failed: %s" % _last_error(None))
+
+    def synchronize(self):
+        lib.cuda_synchronize_with_context(self.handle)
+        self.check()
+
+    def check(self):
+        msg = _last_error(self.handle)
+        if msg:
+            lib.mb200_clear_last_error(self.handle)
+            raise BackendError(msg)
+
+    def set_fusion(self, enabled):
+        lib.mb200_set_fusion(self.handle, 1 if enabled else 0)
+
+    def wait_for_torch(self):
+        """Orders this context's stream after work torch has queued on its current stream."""
+        torch.cuda.current_stream().synchronize()
+
+    def close(self):
+        if self.handle:
+            lib.cuda_destroy_context(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _last_error(handle):
+    msg = lib.mb200_get_last_error(handle)
+    return msg.decode() if msg else None
+
+
+def launch_count():
+    return int(lib.mb200_get_launch_count())
+
+
+# ---------------------------------------------------------------------------------------------- Winograd
+def winogradWeightTransform(ctx, weight, matrices, invert=False, tile_size=None):
+    tile = tile_size if tile_size is not None else _tile_size(matrices, weight.shape[1])
+    lib.cuda_winograd_weight_transform(ctx.handle, tile, desc(weight), desc(matrices), bool(invert))
+    ctx.check()
+
+
+def winogradInputTransform(ctx, weight_shape, x, matrices, tile_size=None):
+    tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
+    lib.cuda_winograd_input_transform(ctx.handle, tile, desc(x), desc(matrices))
+    ctx.check()
+
+
+def winogradOutputTransform(ctx, weight_shape, matrices, output, bias=None, ext=None, act="linear", tile_size=None):
+    tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
+    lib.cuda_winograd_output_transform(ctx.handle, tile, desc(matrices), desc(bias), desc(ext), desc(output), act_code(act))
+    ctx.check()
+
+
+def _tile_size(matrices, kernel):
+    # reference: math.cpp:107-118 -- tile = sqrt(matrices.dim[0]) - (kernel - 1)
+    p = int(round(matrices.shape[0] ** 0.5))
+    return p - (kernel - 1)
+
+
+# ---------------------------------------------------------------------------------------------- GEMM
+def gemm(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0):
+    lib.cuda_gemm_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A), desc(B), beta, desc(C))
+    ctx.check()
+
+
+def gemmBatched(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0):
+    lib.cuda_gemm_batched_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A), desc(B), beta, desc(C))
+    ctx.check()
+
+
+def gemm_legacy(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0, batched=False):
+    fn = lib.cuda_gemm_batched if batched else lib.cuda_gemm
+    fn(ctx.handle, dtype_of(C), shape_of(C), ptr(C), shape_of(A), ptr(A), shape_of(B), ptr(B), opA.encode(), opB.encode(), alpha, beta)
+    ctx.check()
+
+
+def gemm_ex(ctx, D, alpha, opA, A, opB, B, beta, C, bias, act):
+    lib.cuda_gemm_ex(ctx.handle, dtype_of(D), shape_of(D), ptr(D), alpha, opA.encode(), shape_of(A), ptr(A), opB.encode(), shape_of(B), ptr(B),
+                     beta, shape_of(C if C is not None else D), ptr(C), ptr(bias), act_code(act))
+    ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- fused convolution
+def convolutionImplicitGemmForward(ctx, x, weights, output, bias=None, add=None, act="linear"):
+    lib.cuda_convolution_implicit_gemm_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(weights), ptr(x), ptr(weights), ptr(output),
+                                               ptr(bias), ptr(add), act_code(act))
+    ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- elementwise
+def addBiasAct(ctx, x, bias, y, act="linear", alpha=1.0, beta=0.0):
+    lib.cuda_add_bias_act(ctx.handle, alpha, desc(x), desc(bias), beta, desc(y), act_code(act))
+    ctx.check()
+
+
+def activationForward(ctx, x, y, act, alpha=1.0, beta=0.0):
+    lib.cuda_activation_forward(ctx.handle, alpha, desc(x), beta, desc(y), act_code(act))
+    ctx.check()
+
+
+def addTensors(ctx, y, alpha1=0.0, x1=None, alpha2=0.0, x2=None, alpha3=0.0, x3=None, beta=0.0):
+    lib.cuda_add_tensors(ctx.handle, alpha1, desc(x1), alpha2, desc(x2), alpha3, desc(x3), beta, desc(y))
+    ctx.check()
+
+
+def globalAveragePoolingForward(ctx, x, y, alpha=1.0, beta=0.0):
+    lib.cuda_global_average_pooling_forward(ctx.handle, alpha, desc(x), beta, desc(y))
+    ctx.check()
+
+
+def softmaxForward(ctx, x, y):
+    lib.cuda_softmax_forward(ctx.handle, dtype_of(x), shape_of(x), ptr(y), ptr(x))
+    ctx.check()
+
+
+def unpackInput(ctx, packed, dst):
+    lib.cuda_unpack_input(ctx.handle, shape_of(dst), dtype_of(dst), ptr(dst), ptr(packed))
+    ctx.check()
+
+
+def convertType(ctx, dst, src):
+    lib.cuda_convert_type(ctx.handle, ptr(dst), dtype_of(dst), ptr(src), dtype_of(src), src.numel())
+    ctx.check()
+
+
+def transpose_021(ctx, src, dst):
+    lib.cuda_transpose_021(ctx.handle, dtype_of(src), shape_of(src), ptr(src), ptr(dst))
+    ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- norms, attention
+def layernormForward(ctx, x, y, weights, bias, ext=None):
+    lib.cuda_layernorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x), ptr(y), ptr(weights), ptr(bias), ptr(ext))
+    ctx.check()
+
+
+def multiHeadAttentionGetWorkspaceSize(x_shape, weights_shape, num_heads, training=False):
+    return lib.cuda_multi_head_attention_get_workspace_size(shape_of(x_shape), shape_of(weights_shape), num_heads, training)
+
+
+def multiHeadAttentionForward(ctx, x, y, weights, num_heads, symmetric=False, workspace=None):
+    wshape = shape_of(weights) if weights is not None else shape_of([])
+    lib.cuda_multi_head_attention_forward(ctx.handle, shape_of(x), wshape, shape_of([]), dtype_of(x), ptr(x), ptr(y), ptr(weights), None,
+                                          ptr(workspace), None, num_heads, bool(symmetric))
+    ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- int8
+def qdata(scale, shift):
+    q = mlQuantizationData_t()
+    q.scale = float(scale)
+    q.shift = float(shift)
+    return q
+
+
+def im2row(ctx, x, output, kernel_size, invert=False, padding=None):
+    """`padding` is a host scalar of x's dtype (numpy scalar or 0-d torch CPU tensor) or None for zero."""
+    pad_ptr = None
+    keep = None
+    if padding is not None:
+        keep = torch.as_tensor(padding, dtype=x.dtype, device="cpu").reshape(1).contiguous()
+        pad_ptr = ctypes.c_void_p(keep.data_ptr())
+    lib.cuda_im2row(ctx.handle, dtype_of(x), shape_of(x), ptr(output), ptr(x), kernel_size, bool(invert), pad_ptr)
+    ctx.check()
+    del keep
+
+
+def quantized_scale_shift_act(ctx, output, output_qd, acc_i32, scales, bias, act="linear", ext=None, ext_qd=(1.0, 0.0)):
+    lib.cuda_quantized_scale_shift_act(ctx.handle, dtype_of(output), shape_of(output), ptr(output), qdata(*output_qd), ptr(acc_i32), ptr(scales),
+                                       ptr(bias), act_code(act), ptr(ext), qdata(*ext_qd))
+    ctx.check()
+
+
+def dequantize(ctx, src_i8, dst, scale, shift):
+    lib.cuda_dequantize(ctx.handle, dtype_of(dst), ptr(src_i8), ptr(dst), src_i8.numel(), float(scale), float(shift))
+    ctx.check()

@@ -1,0 +1,147 @@
+"""Convolutions on the GPU, driven the way minml's Conv2D layer drives its backend, against the oracle
+(reference tests: test/backend/test_conv2D.cpp:204-248,580-629, test/backend/test_quantization.cpp:56-240)."""
+import numpy as np
+import pytest
+import torch
+
+from tests.util import FP16_REL, INT8_REL, dev, host, max_rel_err, mean_abs_diff, oracle_trunk, pack_planes
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, b, h, w, cin, cout, k=3):
+    r = np.random.default_rng(seed)
+    x = r.uniform(-1, 1, (b, h, w, cin)).astype(np.float32)
+    wt = (r.standard_normal((cout, k, k, cin)) * np.sqrt(2.0 / (k * k * cin))).astype(np.float32)
+    bias = (r.standard_normal(cout) * 0.01).astype(np.float32)
+    ext = r.uniform(-1, 1, (b, h, w, cout)).astype(np.float32)
+    return x, wt, bias, ext
+
+
+def test_config0_fp32_three_call_path(ctx, oracle, refcpu):
+    """BASELINE config 0 at a reduced batch: fp32, 15x15, 128 -> 128, bias + ReLU, via the reference's own call triple."""
+    from minml_b200 import layers as L
+    x, wt, bias, _ = _case(1234, 8, 15, 15, 128, 128)
+    conv = L.Conv2D(ctx, wt, bias, "relu", torch.float32)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    y = torch.full((8, 15, 15, 128), float("nan"), device="cuda")
+    conv.forward([dev(x)], y, ws)
+    ctx.synchronize()
+    want = oracle.conv2d(x, wt, bias, None, "relu")
+    assert np.max(np.abs(host(y) - want)) <= 1e-4
+    assert np.max(np.abs(host(y) - refcpu.conv3x3_winograd(x, wt, bias, None, "relu"))) <= 1e-4
+
+
+@pytest.mark.parametrize("fusion", [False, True])
+@pytest.mark.parametrize("shape", [(4, 15, 15, 128, 128), (2, 20, 20, 256, 256), (3, 9, 11, 35, 21), (2, 15, 15, 32, 128), (1, 7, 5, 64, 192)])
+@pytest.mark.parametrize("act,use_ext", [("relu", False), ("relu", True), ("linear", True), ("sigmoid", False)])
+def test_fp16_conv3x3(ctx, oracle, fusion, shape, act, use_ext):
+    from minml_b200 import layers as L
+    b, h, w, cin, cout = shape
+    x, wt, bias, ext = [t.astype(np.float16).astype(np.float32) for t in _case(sum(shape), b, h, w, cin, cout)]
+    ctx.set_fusion(fusion)
+    conv = L.Conv2D(ctx, wt, bias, act, torch.float16)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    y = torch.full((b, h, w, cout), float("nan"), device="cuda", dtype=torch.float16)
+    inputs = [dev(x, torch.float16)] + ([dev(ext, torch.float16)] if use_ext else [])
+    conv.forward(inputs, y, ws)
+    conv.forward(inputs, y, ws)  # second call reuses the cached transformed weights
+    ctx.synchronize()
+    ctx.set_fusion(True)
+    want = oracle.conv2d(x, wt, bias, ext if use_ext else None, act)
+    assert max_rel_err(host(y), want) <= FP16_REL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("k,shape", [(3, (2, 15, 15, 128, 128)), (3, (1, 6, 7, 12, 20)), (1, (3, 15, 15, 128, 1)), (1, (2, 9, 9, 64, 96))])
+def test_single_call_fused_entry(ctx, oracle, dtype, k, shape):
+    """cuda_convolution_implicit_gemm_forward: y = act(conv(x, w) + bias + add) on raw weights."""
+    from minml_b200 import backend as B
+    b, h, w, cin, cout = shape
+    x, wt, bias, ext = _case(7, b, h, w, cin, cout, k)
+    if dtype == torch.float16:
+        x, wt, bias, ext = [t.astype(np.float16).astype(np.float32) for t in (x, wt, bias, ext)]
+    for act, use in (("relu", True), ("linear", False)):
+        y = torch.full((b, h, w, cout), float("nan"), device="cuda", dtype=dtype)
+        B.convolutionImplicitGemmForward(ctx, dev(x, dtype), dev(wt, dtype), y, dev(bias, dtype), dev(ext, dtype) if use else None, act)
+        ctx.synchronize()
+        want = oracle.conv2d(x, wt, bias, ext if use else None, act)
+        if dtype == torch.float16:
+            assert max_rel_err(host(y), want) <= FP16_REL
+        else:
+            assert np.max(np.abs(host(y) - want)) <= 2e-4
+
+
+@pytest.mark.parametrize("fusion", [False, True])
+@pytest.mark.parametrize("k,shape", [(3, (4, 20, 20, 128, 128)), (3, (2, 20, 20, 32, 128)), (3, (11, 12, 13, 36, 44)), (1, (11, 12, 13, 36, 44)),
+                                     (3, (2, 7, 5, 16, 24))])
+@pytest.mark.parametrize("zero_shift", [True, False])
+def test_int8_conv(ctx, oracle, fusion, k, shape, zero_shift):
+    """The integer branch of Conv2D::forward: int32 accumulators bit-exact, int8 outputs within one step, dequantised within 2e-2."""
+    from minml_b200 import layers as L
+    b, h, w, cin, cout = shape
+    r = np.random.default_rng(sum(shape) + k)
+    wf = (r.standard_normal((cout, k, k, cin)) * np.sqrt(2.0 / (k * k * cin))).astype(np.float32)
+    bias = (r.standard_normal(cout) * 0.01).astype(np.float32)
+    in_qd = (1.0 / 127.0, 0.0) if zero_shift else (0.011, 0.37)
+    out_qd = (0.02, 0.0) if zero_shift else (0.025, -0.4)
+    ext_qd = (0.013, 0.05)
+    xq = r.integers(-128, 128, (b, h, w, cin), dtype=np.int8)
+    extq = r.integers(-128, 128, (b, h, w, cout), dtype=np.int8)
+    q, cs, qb = oracle.quantize_weights(wf, bias, *in_qd)
+    ctx.set_fusion(fusion)
+    for act, use_ext, out_dtype in (("relu", True, torch.int8), ("linear", False, torch.int8), ("relu", False, torch.float32)):
+        conv = L.QuantizedConv2D(ctx, q, cs, qb, in_qd, out_qd, act, out_dtype)
+        ws = L.Workspace()
+        ws.reserve(conv.workspace_bytes(xq.shape))
+        y = torch.zeros((b, h, w, cout), device="cuda", dtype=out_dtype)
+        conv.forward([dev(xq)] + ([dev(extq)] if use_ext else []), y, ws, ext_qd)
+        ctx.synchronize()
+        want8, wantf, want_acc = oracle.conv2d_int8(xq, q, cs, qb, conv.input_zero, out_qd, act, extq if use_ext else None, ext_qd)
+        if not fusion:  # the eager path leaves the int32 accumulators in the workspace: they must match bit for bit
+            acc = ws.view((b * h * w, cout), torch.int32)
+            assert np.array_equal(host(acc).reshape(want_acc.shape), want_acc)
+        if out_dtype == torch.int8:
+            got = host(y).astype(np.int32)
+            assert np.max(np.abs(got - want8.astype(np.int32))) <= 1
+            deq_got = got * out_qd[0] + out_qd[1]
+            assert max_rel_err(deq_got, wantf) <= INT8_REL + 0.5 * out_qd[0] / max(np.max(np.abs(wantf)), 1e-9)
+        else:
+            assert max_rel_err(host(y), wantf) <= 1e-5
+    ctx.set_fusion(True)
+
+
+def test_int8_accumulators_fused_path_bit_exact(ctx, oracle):
+    """With a requantisation that is the identity on integers (scale 1, shift 0, fp32 out) the fused kernel's output IS the int32 accumulator."""
+    from minml_b200 import layers as L
+    b, h, w, cin, cout = 3, 20, 20, 64, 128
+    r = np.random.default_rng(99)
+    q = r.integers(-127, 128, (cout, 3, 3, cin), dtype=np.int8)
+    xq = r.integers(-128, 128, (b, h, w, cin), dtype=np.int8)
+    conv = L.QuantizedConv2D(ctx, q, np.ones(cout, np.float32), np.zeros(cout, np.float32), (1.0, 0.0), (1.0, 0.0), "linear", torch.float32)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(xq.shape))
+    y = torch.zeros((b, h, w, cout), device="cuda", dtype=torch.float32)
+    conv.forward([dev(xq)], y, ws)
+    ctx.synchronize()
+    _, _, want_acc = oracle.conv2d_int8(xq, q, np.ones(cout, np.float32), np.zeros(cout, np.float32), 0)
+    assert np.max(np.abs(want_acc)) < 2 ** 24  # exactly representable in fp32
+    assert np.array_equal(host(y).astype(np.int64), want_acc.astype(np.int64))
+
+
+@pytest.mark.parametrize("cfg", [(4, 15, 15, 32, 128, 2), (2, 20, 20, 32, 256, 2)])
+def test_trunk_matches_fp32_oracle(ctx, oracle, cfg):
+    """The benchmark topology end to end (packed planes in, policy and value out) against the fp32 oracle."""
+    from minml_b200 import layers as L
+    b, h, w, planes, channels, blocks = cfg
+    weights = L.make_trunk_weights(1235, planes, channels, blocks)
+    weights16 = {k: v.astype(np.float16).astype(np.float32) for k, v in weights.items()}
+    x = (np.random.default_rng(1).random((b, h, w, planes)) < 0.3).astype(np.float32)
+    net = L.ResNetTrunk(ctx, weights, b, h, w, planes, channels, blocks)
+    policy, value = net.predict(dev(pack_planes(x).view(np.int32)))
+    ctx.synchronize()
+    want_p, want_v = oracle_trunk(oracle, weights16, x, blocks)
+    assert max_rel_err(host(policy), want_p) <= FP16_REL
+    assert max_rel_err(host(value), want_v) <= FP16_REL

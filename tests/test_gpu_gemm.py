@@ -1,0 +1,147 @@
+"""Matrix products on the GPU against the oracle (reference tests: test/backend/test_gemms.cpp:178-374,
+test/backend/test_conv2D.cpp:204-248, test/backend/test_quantization.cpp:173-240)."""
+import numpy as np
+import pytest
+import torch
+
+from tests.util import FP16_REL, FP32_TOL, dev, host, init_for_test, max_rel_err, mean_abs_diff
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
+@pytest.mark.parametrize("ops", [("n", "n"), ("n", "t"), ("t", "n"), ("t", "t")])
+def test_gemm_all_transpositions(ctx, oracle, dtype, ops):
+    from minml_b200 import backend as B
+    m, n, k = 23, 29, 37
+    a = init_for_test((k, m) if ops[0] == "t" else (m, k))
+    b = init_for_test((n, k) if ops[1] == "t" else (k, n), 1.0)
+    c = init_for_test((m, n), 2.0)
+    if dtype == torch.float16:
+        a, b, c = [t.astype(np.float16).astype(np.float32) for t in (a, b, c)]
+    cd = dev(c, dtype)
+    B.gemm(ctx, ops[0], dev(a, dtype), ops[1], dev(b, dtype), cd, 1.1, 0.1)
+    ctx.synchronize()
+    want = oracle.gemm(ops[0], a, ops[1], b, c, 1.1, 0.1)
+    if dtype == torch.float16:
+        assert max_rel_err(host(cd), want) <= FP16_REL
+    else:
+        assert mean_abs_diff(host(cd), want) <= FP32_TOL
+    # the legacy entry point gives the same result
+    cd2 = dev(c, dtype)
+    B.gemm_legacy(ctx, ops[0], dev(a, dtype), ops[1], dev(b, dtype), cd2, 1.1, 0.1)
+    ctx.synchronize()
+    assert torch.equal(cd, cd2)
+
+
+# (M, N, K): aligned, ragged in every dimension, K not a multiple of the 64-element stage, N beyond one tile, tiny
+TC_SHAPES = [(256, 256, 256), (300, 72, 40), (129, 130, 72), (1000, 384, 136), (5, 3, 8), (128, 1, 128), (64, 3, 256), (4096, 128, 128)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_fp16_nt_tensor_core_path(ctx, oracle, shape, out_dtype):
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(m * 7 + n * 3 + k)
+    a = r.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = r.uniform(-1, 1, (n, k)).astype(np.float16)
+    c = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+    B.gemm(ctx, "n", dev(a), "t", dev(b), c)
+    ctx.synchronize()
+    want = oracle.gemm("n", a.astype(np.float32), "t", b.astype(np.float32))
+    assert max_rel_err(host(c), want) <= (2e-3 if out_dtype == torch.float16 else 1e-5)
+
+
+@pytest.mark.parametrize("broadcast_b", [False, True])
+def test_fp16_batched_nt(ctx, oracle, broadcast_b):
+    # the shape family of the Winograd products: [36, tiles, cin] x [36, cout, cin]^T
+    from minml_b200 import backend as B
+    batch, m, n, k = 36, 200, 96, 64
+    r = np.random.default_rng(11)
+    a = r.uniform(-1, 1, (batch, m, k)).astype(np.float16)
+    b = r.uniform(-1, 1, (n, k) if broadcast_b else (batch, n, k)).astype(np.float16)
+    c = torch.full((batch, m, n), float("nan"), device="cuda", dtype=torch.float16)
+    B.gemmBatched(ctx, "n", dev(a), "t", dev(b), c)
+    ctx.synchronize()
+    got = host(c)
+    for i in (0, 17, 35):
+        want = oracle.gemm("n", a[i].astype(np.float32), "t", (b if broadcast_b else b[i]).astype(np.float32))
+        assert max_rel_err(got[i], want) <= 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_batched_generic_and_beta(ctx, oracle, dtype):
+    from minml_b200 import backend as B
+    batch, m, n, k = 5, 23, 29, 37
+    a = init_for_test((batch, m, k))
+    b = init_for_test((batch, k, n), 1.0)
+    c = init_for_test((batch, m, n), 2.0)
+    if dtype == torch.float16:
+        a, b, c = [t.astype(np.float16).astype(np.float32) for t in (a, b, c)]
+    cd = dev(c, dtype)
+    B.gemmBatched(ctx, "n", dev(a, dtype), "n", dev(b, dtype), cd, 1.1, 0.1)
+    ctx.synchronize()
+    for i in range(batch):
+        want = oracle.gemm("n", a[i], "n", b[i], c[i], 1.1, 0.1)
+        if dtype == torch.float16:
+            assert max_rel_err(host(cd)[i], want) <= FP16_REL
+        else:
+            assert mean_abs_diff(host(cd)[i], want) <= FP32_TOL
+
+
+@pytest.mark.parametrize("shape", [(1024, 128, 1152), (300, 44, 36), (77, 200, 288), (256, 256, 128), (9, 5, 16)])
+def test_int8_nt_accumulators_are_exact(ctx, oracle, shape):
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(m + n + k)
+    a = r.integers(-128, 128, (m, k), dtype=np.int8)
+    b = r.integers(-128, 128, (n, k), dtype=np.int8)
+    c = torch.full((m, n), -1, device="cuda", dtype=torch.int32)
+    B.gemm(ctx, "n", dev(a), "t", dev(b), c)
+    ctx.synchronize()
+    assert np.array_equal(host(c), oracle.gemm_i8_nt(a, b))
+
+
+def test_int8_k_not_multiple_of_16_uses_generic_engine(ctx, oracle):
+    from minml_b200 import backend as B
+    r = np.random.default_rng(5)
+    a = r.integers(-128, 128, (33, 20), dtype=np.int8)
+    b = r.integers(-128, 128, (17, 20), dtype=np.int8)
+    c = torch.zeros(33, 17, device="cuda", dtype=torch.int32)
+    B.gemm(ctx, "n", dev(a), "t", dev(b), c)
+    ctx.synchronize()
+    assert np.array_equal(host(c), oracle.gemm_i8_nt(a, b))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(23, 29, 37), (450, 128, 64), (225, 3, 128), (400, 1, 256)])
+@pytest.mark.parametrize("act", ["linear", "relu", "sigmoid"])
+def test_gemm_ex_bias_residual_activation(ctx, oracle, dtype, shape, act):
+    # D = act(alpha * A B^T + beta * C + bias): 1x1 convolutions and dense layers (src/core/math.cpp:682-702)
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(m + n)
+    a = r.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = (r.standard_normal((n, k)) * 0.1).astype(np.float32)
+    c = r.uniform(-1, 1, (m, n)).astype(np.float32)
+    bias = r.standard_normal(n).astype(np.float32)
+    if dtype == torch.float16:
+        a, b, c, bias = [t.astype(np.float16).astype(np.float32) for t in (a, b, c, bias)]
+    for beta, use_bias in ((0.0, True), (1.0, True), (1.0, False), (0.0, False)):
+        d = torch.full((m, n), float("nan"), device="cuda", dtype=dtype)
+        B.gemm_ex(ctx, d, 1.0, "n", dev(a, dtype), "t", dev(b, dtype), beta, dev(c, dtype), dev(bias, dtype) if use_bias else None, act)
+        ctx.synchronize()
+        pre = oracle.gemm("n", a, "t", b, c, 1.0, beta)
+        want = oracle.add_bias_act(pre, bias if use_bias else None, act)
+        if dtype == torch.float16:
+            assert max_rel_err(host(d), want) <= FP16_REL
+        else:
+            assert mean_abs_diff(host(d), want) <= FP32_TOL
+
+
+def test_shape_mismatch_is_reported(ctx):
+    from minml_b200 import backend as B
+    with pytest.raises(B.BackendError):
+        B.gemm(ctx, "n", torch.zeros(4, 5, device="cuda"), "n", torch.zeros(6, 7, device="cuda"), torch.zeros(4, 7, device="cuda"))
+    ctx.synchronize()

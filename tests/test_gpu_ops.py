@@ -1,0 +1,206 @@
+"""Bandwidth-bound entry points on the GPU against the oracle: bias/activation, tensor sums, pooling, unpacking,
+conversion, transposition, softmax, layer norm, attention, and the eager int8 steps."""
+import numpy as np
+import pytest
+import torch
+
+from tests.util import FP16_REL, FP32_TOL, INT8_REL, dev, host, init_for_test, max_rel_err, mean_abs_diff
+
+pytestmark = pytest.mark.gpu
+
+
+def close(dtype, got, want, what=""):
+    if dtype == torch.float16:
+        assert max_rel_err(got, want) <= FP16_REL, what
+    else:
+        assert mean_abs_diff(got, want) <= FP32_TOL, what
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(23, 35), (4, 15, 15, 128), (1, 7), (3, 1000)])
+def test_add_bias_act_and_activation(ctx, oracle, dtype, shape):
+    from minml_b200 import backend as B
+    x = init_for_test(shape)
+    bias = init_for_test((shape[-1],), 1.0)
+    if dtype == torch.float16:
+        x, bias = x.astype(np.float16).astype(np.float32), bias.astype(np.float16).astype(np.float32)
+    for act in ("linear", "sigmoid", "tanh", "relu", "leaky_relu"):
+        y = torch.full(shape, float("nan"), device="cuda", dtype=dtype)
+        B.addBiasAct(ctx, dev(x, dtype), dev(bias, dtype), y, act)
+        ctx.synchronize()
+        close(dtype, host(y), oracle.add_bias_act(x, bias, act), act)
+        y2 = torch.full(shape, float("nan"), device="cuda", dtype=dtype)
+        B.activationForward(ctx, dev(x, dtype), y2, act)
+        ctx.synchronize()
+        close(dtype, host(y2), oracle.add_bias_act(x, None, act), act)
+    # alpha / beta:  y = act(x + b) * alpha + beta * y
+    y = dev(init_for_test(shape, 2.0), dtype)
+    y0 = host(y).copy()
+    B.addBiasAct(ctx, dev(x, dtype), dev(bias, dtype), y, "relu", alpha=0.5, beta=2.0)
+    ctx.synchronize()
+    close(dtype, host(y), oracle.add_bias_act(x, bias, "relu") * 0.5 + 2.0 * y0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [1, 37, 4096, 100003])
+def test_add_tensors(ctx, dtype, n):
+    from minml_b200 import backend as B
+    x1, x2, x3, y = [init_for_test((n,), s) for s in (0.0, 1.0, 2.0, 3.0)]
+    if dtype == torch.float16:
+        x1, x2, x3, y = [t.astype(np.float16).astype(np.float32) for t in (x1, x2, x3, y)]
+    yd = dev(y, dtype)
+    B.addTensors(ctx, yd, 1.0, dev(x1, dtype), 0.5, dev(x2, dtype), -2.0, dev(x3, dtype), 0.25)
+    ctx.synchronize()
+    close(dtype, host(yd), x1 + 0.5 * x2 - 2.0 * x3 + 0.25 * y)
+    yd = dev(y, dtype)
+    B.addTensors(ctx, yd, 1.0, dev(x1, dtype), 1.0, dev(x2, dtype))  # residual add: y = x1 + x2
+    ctx.synchronize()
+    close(dtype, host(yd), x1 + x2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(3, 5, 7, 36), (4, 15, 15, 128), (2, 20, 20, 256), (2, 3, 3, 5)])
+def test_global_average_pooling(ctx, oracle, dtype, shape):
+    from minml_b200 import backend as B
+    x = init_for_test(shape)
+    if dtype == torch.float16:
+        x = x.astype(np.float16).astype(np.float32)
+    y = torch.full((shape[0], shape[3]), float("nan"), device="cuda", dtype=dtype)
+    B.globalAveragePoolingForward(ctx, dev(x, dtype), y)
+    ctx.synchronize()
+    close(dtype, host(y), oracle.global_average_pooling(x))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int8])
+@pytest.mark.parametrize("channels", [32, 35, 64, 5])
+def test_unpack_input_is_exact(ctx, oracle, dtype, channels):
+    from minml_b200 import backend as B
+    rows = 7 * 9
+    words = (channels + 31) // 32
+    packed = np.random.default_rng(channels).integers(0, 2 ** 32, size=rows * words, dtype=np.uint64).astype(np.uint32)
+    dst = torch.full((7, 9, channels), 3, device="cuda", dtype=dtype)
+    B.unpackInput(ctx, dev(packed.view(np.int32)), dst)
+    ctx.synchronize()
+    assert np.array_equal(host(dst).astype(np.float32), oracle.unpack_input(packed, (7, 9, channels)))
+
+
+def test_convert_and_transpose(ctx):
+    from minml_b200 import backend as B
+    x = init_for_test((1237,), 0.0, 50.0)
+    for src_t, dst_t in ((torch.float32, torch.float16), (torch.float16, torch.float32), (torch.float32, torch.int8), (torch.int8, torch.float32),
+                         (torch.int32, torch.float16)):
+        src = dev(x).to(src_t)
+        dst = torch.zeros(1237, device="cuda", dtype=dst_t)
+        B.convertType(ctx, dst, src)
+        ctx.synchronize()
+        if dst_t == torch.int8:  # the backend converts by truncation through fp32, like static_cast in the reference
+            assert torch.equal(dst, src.float().trunc().to(torch.int8))
+        else:
+            assert torch.equal(dst, src.float().to(dst_t))
+    for dtype in (torch.float32, torch.float16, torch.int8):
+        t = (dev(init_for_test((3, 37, 45))) * 100).to(dtype).contiguous()
+        out = torch.zeros(3, 45, 37, device="cuda", dtype=dtype)
+        B.transpose_021(ctx, t, out)
+        ctx.synchronize()
+        assert torch.equal(out, t.transpose(1, 2).contiguous())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_softmax(ctx, oracle, dtype):
+    from minml_b200 import backend as B
+    for shape in ((50, 3), (7, 225), (3, 1000)):
+        x = init_for_test(shape, 0.0, 3.0)
+        if dtype == torch.float16:
+            x = x.astype(np.float16).astype(np.float32)
+        y = torch.zeros(shape, device="cuda", dtype=dtype)
+        B.softmaxForward(ctx, dev(x, dtype), y)
+        ctx.synchronize()
+        close(dtype, host(y), oracle.softmax(x))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(3, 5, 7, 36), (2, 15, 15, 256), (11, 33)])
+def test_layernorm(ctx, oracle, dtype, shape):
+    from minml_b200 import backend as B
+    r = np.random.default_rng(1)
+    x = r.standard_normal(shape).astype(np.float32)
+    ext = r.standard_normal(shape).astype(np.float32)
+    gamma = r.standard_normal(shape[-1]).astype(np.float32)
+    beta = r.standard_normal(shape[-1]).astype(np.float32)
+    if dtype == torch.float16:
+        x, ext, gamma, beta = [t.astype(np.float16).astype(np.float32) for t in (x, ext, gamma, beta)]
+    for e in (None, ext):
+        y = torch.zeros(shape, device="cuda", dtype=dtype)
+        B.layernormForward(ctx, dev(x, dtype), y, dev(gamma, dtype), dev(beta, dtype), None if e is None else dev(e, dtype))
+        ctx.synchronize()
+        close(dtype, host(y), oracle.layernorm(x, gamma, beta, e))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("cfg", [(2, 5, 6, 2, 8, False), (2, 15, 15, 8, 32, False), (1, 4, 4, 3, 16, True), (1, 9, 7, 4, 20, False)])
+def test_multi_head_attention(ctx, oracle, dtype, cfg):
+    # reference: test/backend/test_attention.cpp:273-300,441-503
+    from minml_b200 import backend as B
+    b, h, w, heads, d, symmetric = cfg
+    r = np.random.default_rng(h * w)
+    parts = 2 if symmetric else 3
+    x = r.standard_normal((b, h, w, parts * heads * d)).astype(np.float32)
+    n = 2 * max(h, w) - 1
+    table = (r.standard_normal((heads, n, (n + 3) // 4 * 4)) * 0.5).astype(np.float32)
+    if dtype == torch.float16:
+        x, table = x.astype(np.float16).astype(np.float32), table.astype(np.float16).astype(np.float32)
+    for t in (None, table):
+        y = torch.zeros((b, h, w, heads * d), device="cuda", dtype=dtype)
+        B.multiHeadAttentionForward(ctx, dev(x, dtype), y, None if t is None else dev(t, dtype), heads, symmetric)
+        ctx.synchronize()
+        close(dtype, host(y), oracle.mha_forward(x, heads, t, symmetric))
+    assert B.multiHeadAttentionGetWorkspaceSize((b, h, w, parts * heads * d), table.shape, heads) == b * heads * (h * w) ** 2
+
+
+# ---------------------------------------------------------------------------------------------------- eager int8 steps
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 6, 7, 12, 3), (3, 20, 20, 32, 3), (2, 5, 5, 7, 3), (2, 4, 4, 16, 1), (1, 9, 9, 8, 5)])
+def test_im2row_is_exact(ctx, oracle, dtype, shape):
+    # reference: test/backend/test_gemm_conv.cpp:68-178 (exact equality)
+    from minml_b200 import backend as B
+    b, h, w, c, k = shape
+    x = (init_for_test((b, h, w, c)) * 100).astype({torch.int8: np.int8, torch.float16: np.float16, torch.float32: np.float32}[dtype])
+    for invert in (False, True):
+        for pad in (None, 3):
+            out = torch.zeros((b * h * w, k * k * c), device="cuda", dtype=dtype)
+            B.im2row(ctx, dev(x), out, k, invert, pad)
+            ctx.synchronize()
+            want = oracle.im2row(x, k, invert, pad)
+            assert np.array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("shape", [(11 * 12 * 13, 44), (300, 128), (7, 5)])
+def test_scale_shift_act(ctx, oracle, shape):
+    # reference: test/backend/test_quantization.cpp:173-240 (int8 and fp32 outputs, with and without ext)
+    from minml_b200 import backend as B
+    r = np.random.default_rng(shape[1])
+    acc = r.integers(-30000, 30000, shape, dtype=np.int32)
+    scales = r.uniform(1e-4, 1e-3, shape[1]).astype(np.float32)
+    bias = r.standard_normal(shape[1]).astype(np.float32)
+    ext = r.integers(-128, 128, shape, dtype=np.int8)
+    out_qd, ext_qd = (0.06, 0.2), (0.03, -0.1)
+    for act in ("linear", "relu", "sigmoid", "tanh"):
+        for e in (None, ext):
+            want8, wantf = oracle.scale_shift_act(acc, scales, bias, out_qd, act, e, ext_qd)
+            y8 = torch.zeros(shape, device="cuda", dtype=torch.int8)
+            B.quantized_scale_shift_act(ctx, y8, out_qd, dev(acc), dev(scales), dev(bias), act, None if e is None else dev(e), ext_qd)
+            yf = torch.zeros(shape, device="cuda", dtype=torch.float32)
+            B.quantized_scale_shift_act(ctx, yf, out_qd, dev(acc), dev(scales), dev(bias), act, None if e is None else dev(e), ext_qd)
+            ctx.synchronize()
+            assert max_rel_err(host(yf), wantf) <= 1e-5
+            assert np.max(np.abs(host(y8).astype(np.int32) - want8.astype(np.int32))) <= 1  # fused multiply-add may move a tie
+            assert np.mean(host(y8) != want8) <= 1e-3
+
+
+def test_dequantize(ctx):
+    from minml_b200 import backend as B
+    q = dev(np.arange(-128, 128, dtype=np.int8))
+    out = torch.zeros(256, device="cuda")
+    B.dequantize(ctx, q, out, 0.05, -0.3)
+    ctx.synchronize()
+    assert torch.allclose(out, q.float() * 0.05 - 0.3, atol=1e-6)

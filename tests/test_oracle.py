@@ -1,0 +1,182 @@
+"""Pins the oracle: (1) against the known-answer vectors the reference's own tests hold for the Winograd transforms,
+(2) against minml's CPU backend compiled from the reference sources, op by op, on seeded inputs.  CPU only."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def init_for_test(shape, shift=0.0, scale=1.0):
+    """sin(i / 10 + shift) * scale -- the deterministic fill of the reference's tests (src/utils/testing_util.cpp:31-55)."""
+    n = int(np.prod(shape))
+    return (np.sin(np.arange(n, dtype=np.float32) / 10.0 + shift) * scale).astype(np.float32).reshape(shape)
+
+
+def mean_abs_diff(a, b):
+    """The reference's test metric (src/utils/testing_util.cpp:73-107)."""
+    return float(np.mean(np.abs(a.astype(np.float64) - b.astype(np.float64))))
+
+
+# ------------------------------------------------------------------------------------------ known-answer vectors
+def _tile(matrices, channel):
+    p = int(round(matrices.shape[0] ** 0.5))
+    return matrices[:, 0, channel].reshape(p, p)
+
+
+def test_known_answers_input(oracle):
+    ka = json.load(open(os.path.join(GOLDEN, "winograd_known_answers.json")))["input_transform"]
+    ones = np.ones((1, 4, 4, 2), np.float32)
+    ramp = np.repeat(np.arange(1, 17, dtype=np.float32).reshape(1, 4, 4, 1), 2, axis=3)
+    for x, case in zip((ones, ramp), ka):
+        v = oracle.winograd_input_transform(x)
+        for ch in range(2):
+            assert mean_abs_diff(_tile(v, ch), np.array(case["tile_6x6"], np.float32)) <= 1e-4
+
+
+def test_known_answers_output(oracle):
+    ka = json.load(open(os.path.join(GOLDEN, "winograd_known_answers.json")))["output_transform"]
+    ones = np.ones((36, 1, 2), np.float32)
+    ramp = np.repeat(np.arange(1, 37, dtype=np.float32).reshape(36, 1, 1), 2, axis=2)
+    for m, case in zip((ones, ramp), ka):
+        y = oracle.winograd_output_transform(m, (1, 4, 4, 2))
+        for ch in range(2):
+            assert mean_abs_diff(y[0, :, :, ch], np.array(case["tile_4x4"], np.float32)) <= 1e-4
+
+
+def test_known_answers_weight(oracle):
+    ka = json.load(open(os.path.join(GOLDEN, "winograd_known_answers.json")))["weight_transform"]
+    nines = np.full((1, 3, 3, 2), 9.0, np.float32)
+    ramp = np.repeat(np.arange(1, 10, dtype=np.float32).reshape(1, 3, 3, 1), 2, axis=3)
+    for w, case in zip((nines, ramp), ka):
+        u = oracle.winograd_weight_transform(w)
+        for ch in range(2):
+            assert mean_abs_diff(u[:, 0, ch].reshape(6, 6), np.array(case["tile_6x6"], np.float32)) <= 1e-4
+
+
+# ------------------------------------------------------------------------------------------ oracle vs reference CPU backend
+@pytest.mark.parametrize("tile", [4])
+def test_winograd_transforms_match_reference(oracle, refcpu, tile):
+    # the odd shapes of the reference's own tests: test/backend/test_winograd.cpp:396-470 (3 x 9 x 11 x 35, 35 -> 21 filters)
+    x = init_for_test((3, 9, 11, 35))
+    w = init_for_test((21, 3, 3, 35), 1.0)
+    assert mean_abs_diff(oracle.winograd_input_transform(x, tile), refcpu.winograd_input_transform(x, w.shape, tile)) <= 1e-5
+    assert mean_abs_diff(oracle.winograd_weight_transform(w, tile), refcpu.winograd_weight_transform(w, tile)) <= 1e-5
+    tiles = 3 * 3 * 3
+    m = init_for_test((36, tiles, 21), 2.0)
+    bias = init_for_test((21,), 3.0)
+    ext = init_for_test((3, 9, 11, 21), 4.0)
+    for act in ("linear", "relu", "sigmoid", "tanh"):
+        a = oracle.winograd_output_transform(m, (3, 9, 11, 21), bias, ext, act, tile)
+        b = refcpu.winograd_output_transform(m, w.shape, (3, 9, 11, 21), bias, ext, act, tile)
+        assert mean_abs_diff(a, b) <= 1e-5, act
+
+
+def test_winograd_conv_equals_direct_conv(oracle, refcpu):
+    # reference: TestConv2D winograd_conv2D_3x3_forward, test/backend/test_conv2D.cpp:580-629 (bias + sigmoid)
+    r = rng(1)
+    x = r.uniform(-1, 1, (2, 13, 17, 35)).astype(np.float32)
+    w = (r.standard_normal((21, 3, 3, 35)) * 0.1).astype(np.float32)
+    bias = (r.standard_normal(21) * 0.1).astype(np.float32)
+    ext = r.uniform(-1, 1, (2, 13, 17, 21)).astype(np.float32)
+    direct = oracle.conv2d(x, w, bias, ext, "sigmoid")
+    ref = refcpu.conv3x3_winograd(x, w, bias, ext, "sigmoid")
+    assert np.max(np.abs(direct - ref)) <= 1e-4
+    u = oracle.winograd_weight_transform(w)
+    v = oracle.winograd_input_transform(x)
+    m = np.stack([oracle.gemm("n", v[p], "t", u[p]) for p in range(36)])
+    mine = oracle.winograd_output_transform(m, direct.shape, bias, ext, "sigmoid")
+    assert np.max(np.abs(direct - mine)) <= 1e-4
+
+
+@pytest.mark.parametrize("ops", [("n", "n"), ("n", "t"), ("t", "n"), ("t", "t")])
+def test_gemm_matches_reference(oracle, refcpu, ops):
+    # reference: test/backend/test_gemms.cpp:178-374, M=23 N=29 K=37, alpha=1.1 beta=0.1
+    m, n, k = 23, 29, 37
+    a = init_for_test((k, m) if ops[0] == "t" else (m, k))
+    b = init_for_test((n, k) if ops[1] == "t" else (k, n), 1.0)
+    c = init_for_test((m, n), 2.0)
+    got = oracle.gemm(ops[0], a, ops[1], b, c, 1.1, 0.1)
+    ref = refcpu.gemm(ops[0], a, ops[1], b, c, 1.1, 0.1)
+    assert mean_abs_diff(got, ref) <= 1e-4
+
+
+def test_gemm_ex_matches_reference(oracle, refcpu):
+    a = init_for_test((23, 37))
+    b = init_for_test((29, 37), 1.0)
+    bias = init_for_test((29,), 2.0)
+    ref = refcpu.gemm_ex(a, b, bias, "relu")
+    got = oracle.add_bias_act(oracle.gemm("n", a, "t", b), bias, "relu")
+    assert mean_abs_diff(got, ref) <= 1e-4
+
+
+def test_misc_ops_match_reference(oracle, refcpu):
+    r = rng(2)
+    x = r.standard_normal((3, 5, 7, 36)).astype(np.float32)
+    assert mean_abs_diff(oracle.global_average_pooling(x), refcpu.global_average_pooling(x)) <= 1e-5
+    gamma = r.standard_normal(36).astype(np.float32)
+    beta = r.standard_normal(36).astype(np.float32)
+    ext = r.standard_normal(x.shape).astype(np.float32)
+    assert mean_abs_diff(oracle.layernorm(x, gamma, beta), refcpu.layernorm(x, gamma, beta)) <= 1e-5
+    assert mean_abs_diff(oracle.layernorm(x, gamma, beta, ext), refcpu.layernorm(x, gamma, beta, ext)) <= 1e-5
+    bias = r.standard_normal(36).astype(np.float32)
+    for act in ("linear", "relu", "sigmoid", "tanh"):
+        assert mean_abs_diff(oracle.add_bias_act(x, bias, act), refcpu.add_bias_act(x, bias, act)) <= 1e-5
+    packed = r.integers(0, 2 ** 32, size=(4 * 6 * 2,), dtype=np.uint64).astype(np.uint32)
+    assert np.array_equal(oracle.unpack_input(packed, (4, 6, 35)), refcpu.unpack_input(packed, (4, 6, 35)))
+    assert np.array_equal(oracle.im2row(x, 3), refcpu.im2row(x, 3))
+
+
+def test_attention_matches_reference(oracle, refcpu):
+    r = rng(3)
+    heads, d, h, w = 2, 8, 5, 6
+    x = r.standard_normal((2, h, w, 3 * heads * d)).astype(np.float32)
+    n = 2 * max(h, w) - 1
+    table = (r.standard_normal((heads, n, (n + 3) // 4 * 4)) * 0.5).astype(np.float32)
+    assert mean_abs_diff(oracle.mha_forward(x, heads, None), refcpu.mha_forward(x, heads, None)) <= 1e-5
+    assert mean_abs_diff(oracle.mha_forward(x, heads, table), refcpu.mha_forward(x, heads, table)) <= 1e-5
+
+
+# ------------------------------------------------------------------------------------------ int8 restatement
+def test_int8_conv_self_consistency(oracle):
+    """int32 accumulators equal an int64 numpy convolution; padding uses the quantised zero; requantisation follows the formulas."""
+    r = rng(4)
+    x = r.integers(-128, 128, (2, 6, 7, 12), dtype=np.int8)
+    wq = r.integers(-127, 128, (9, 3, 3, 12), dtype=np.int8)
+    scales = r.uniform(0.001, 0.01, 9).astype(np.float32)
+    bias = r.standard_normal(9).astype(np.float32)
+    zero = -3
+    y8, yf, acc = oracle.conv2d_int8(x, wq, scales, bias, zero, (0.05, 0.1), "relu")
+    xp = np.full((2, 8, 9, 12), zero, np.int64)
+    xp[:, 1:-1, 1:-1, :] = x
+    ref = np.zeros((2, 6, 7, 9), np.int64)
+    for i in range(3):
+        for j in range(3):
+            ref += np.einsum("bhwc,oc->bhwo", xp[:, i:i + 6, j:j + 7, :], wq[:, i, j, :].astype(np.int64))
+    assert np.array_equal(acc, ref.astype(np.int32))
+    f = np.maximum(acc.astype(np.float32) * scales + bias, 0.0)
+    assert np.allclose(yf, f, atol=1e-6)
+    # im2row (padded with the quantised zero) followed by the int8 GEMM gives the same accumulators
+    rows = oracle.im2row(x, 3, pad=np.int8(zero))
+    assert np.array_equal(oracle.gemm_i8_nt(rows, wq.reshape(9, -1)).reshape(acc.shape), acc)
+    y8b, yfb = oracle.scale_shift_act(acc, scales, bias, (0.05, 0.1), "relu")
+    assert np.array_equal(yfb, yf)
+    assert np.max(np.abs(y8b.astype(np.int32) - y8.astype(np.int32))) <= 1  # (x - z) / s  versus  x * (1/s) - z/s
+
+
+def test_quantize_weights(oracle):
+    r = rng(5)
+    w = (r.standard_normal((8, 3, 3, 4)) * 0.2).astype(np.float32)
+    bias = r.standard_normal(8).astype(np.float32)
+    q, cs, qb = oracle.quantize_weights(w, bias, 0.02, 0.3)
+    for co in range(8):
+        s = 127.0 / np.abs(w[co]).max()
+        assert np.array_equal(q[co], np.clip(np.round(w[co] * np.float32(s)), -128, 127).astype(np.int8))
+        assert abs(cs[co] - 0.02 / s) <= 1e-7
+        assert abs(qb[co] - (0.3 / s * q[co].astype(np.int32).sum() + bias[co])) <= 1e-4
