@@ -31,6 +31,17 @@ namespace mb200
 			int tile_size = 0;
 	};
 
+	struct PendingInt8
+	{
+			// state of the deferred int8 sequence im2row -> int8 GEMM -> scale_shift_act (see conv_igemm.cu)
+			int stage = 0; // 0 nothing pending, 1 im2row recorded, 2 GEMM recorded
+			mlTensor_t x {};
+			void *rows = nullptr; // im2row destination
+			mlTensor_t w {}; // [cout, 9 * cin] int8
+			mlTensor_t acc {}; // [b*h*w, cout] int32
+			int pad = 0;
+	};
+
 	struct Context
 	{
 			int device = 0;
@@ -42,6 +53,7 @@ namespace mb200
 			bool has_error = false;
 			std::string error;
 			PendingWinograd pending;
+			PendingInt8 pending_i8;
 			int sm_count = 148;
 			bool kernels_with_waits = false; // a kernel that polls mbarriers ran since the last synchronize
 			int *dev_status = nullptr; // device word set to non-zero by a kernel whose bounded wait ran out

@@ -21,6 +21,8 @@ namespace mb200
 	 * Each returns true when it consumed the call. */
 	bool im2row_defer(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &input_shape, void *output, const void *input, int kernel_size,
 			bool invert, const void *padding);
+	bool int8_gemm_defer(mlContext_t ctx, char opA, char opB, const mlTensor_t &A, const mlTensor_t &B, const mlTensor_t &C);
+	void flush_pending_int8(mlContext_t ctx);
 	bool requant_complete_fused(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &shape, void *output, mlQuantizationData_t output_qd,
 			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd);
 } /* namespace mb200 */

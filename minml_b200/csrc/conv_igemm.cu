@@ -1,47 +1,651 @@
 /*
- * conv_igemm.cu -- fused 3x3 convolution kernels (placeholder until the tcgen05 implicit-GEMM kernel lands).
+ * conv_igemm.cu -- fused 3x3 convolution as an implicit GEMM on the tcgen05 tensor cores:
+ *
+ *      y = epilogue( conv3x3(x, w) ),  stride 1, "same" padding, NHWC, w [cout, 3, 3, cin]
+ *      fp16:  epilogue = act(acc + bias + ext)                       fp32 accumulation, fp16 out
+ *      int8:  epilogue = requantise(act(acc * scale[c] + shift[c] + dequant(ext)))   exact int32 accumulation
+ *
+ * It is the single-kernel replacement for the two three-call sequences minml's Conv2D::forward issues
+ * (Winograd: src/layers/Conv2D.cpp:365-377; int8: src/layers/Conv2D.cpp:214-239) and the body of
+ * cuda_convolution_implicit_gemm_forward (empty in the reference without cuDNN, src/backend/cuda/cudnn_math.cpp:691-694).
+ * Nothing but x, w, bias, ext and y crosses HBM: there is no transformed-input, im2row or accumulator tensor.
+ *
+ * GEMM view: M = b*h*w output positions, N = cout, K = 9*cin ordered (kh, kw, cin) -- the weight tensor as stored is
+ * the K-major B operand [N, K].  The A operand is never materialised: for every 128-byte slice of K, producer warps
+ * gather the 16-byte channel chunks of 256 positions straight from x into the 128B-swizzled shared-memory tile that
+ * tcgen05.mma reads (cp.async with zero fill outside the image; a non-zero int8 padding value is stored directly).
+ *
+ * One CTA per SM, persistent over 256 x BN output tiles:
+ *   warp 0        TMA loads of the weight tile (BN rows x 128 bytes of K)
+ *   warp 1        tcgen05.mma issue: per K slice, two M=128 instructions chains share one weight tile
+ *   warps 2-9     epilogue: tcgen05.ld, bias / residual / activation / requantisation, 16-byte stores
+ *   warps 10-13   A-operand gather
+ * Every wait is bounded (tc.cuh); on a timeout the kernel sets its status word and drains.
  */
 #include "common.cuh"
 #include "conv.cuh"
+#include "tc.cuh"
+
+#include <cstring>
 
 namespace mb200
 {
+	namespace
+	{
+		using namespace tc;
+
+		constexpr int BM = 256; // two M = 128 halves
+		constexpr int NUM_THREADS = 14 * 32;
+		constexpr int PRODUCER_WARP0 = 10;
+		constexpr int NUM_PRODUCERS = 128;
+		constexpr int A_STAGE_BYTES = BM * 128;
+
+		template<int BN>
+		struct Cfg
+		{
+				static constexpr int b_stage_bytes = BN * 128;
+				static constexpr int stage_bytes = A_STAGE_BYTES + b_stage_bytes;
+				static constexpr int stages = (BN == 256) ? 3 : 4;
+				static constexpr int smem_bytes = stages * stage_bytes + 1024;
+				static constexpr int acc_buffers = 512 / (2 * BN); // 1 for BN = 256, 2 for BN = 128
+		};
+
+		struct ConvParams
+		{
+				const void *x;
+				void *y;
+				const void *bias; // fp16 [cout] (fp16 kind)
+				const void *ext; // fp16 or int8 [b, h, w, cout]
+				int batch, height, width, cin, cout;
+				int M, K;
+				int act;
+				int out_dtype;
+				const float *scales; // int8 kind
+				const float *shifts;
+				float ext_scale, ext_shift, out_scale, out_shift;
+				int pad_byte;
+				int *status;
+		};
+
+		struct ConvBarriers
+		{
+				uint64_t full[4];
+				uint64_t empty[4];
+				uint64_t tmem_full[2];
+				uint64_t tmem_empty[2];
+				uint32_t tmem_base;
+				int abort_flag;
+		};
+
+		__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes)
+		{
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(src_bytes) : "memory");
+		}
+		__device__ __forceinline__ void cp_async_commit()
+		{
+			asm volatile("cp.async.commit_group;" ::: "memory");
+		}
+		template<int N>
+		__device__ __forceinline__ void cp_async_wait()
+		{
+			asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory");
+		}
+		__device__ __forceinline__ void st_shared_16(uint32_t dst, uint32_t v)
+		{
+			asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "r"(v) : "memory");
+		}
+
+		template<int KIND, int BN>
+		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w, const ConvParams p)
+		{
+			using C = Cfg<BN>;
+			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
+			constexpr int CHUNK_ELEMS = 16 / ES;
+			extern __shared__ uint8_t smem_raw[];
+			__shared__ ConvBarriers bars;
+
+			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+			const int warp = threadIdx.x / 32;
+			const int lane = threadIdx.x % 32;
+
+			const int m_tiles = (p.M + BM - 1) / BM;
+			const int n_tiles = (p.cout + BN - 1) / BN;
+			const int total_tiles = m_tiles * n_tiles;
+			const int k_blocks = (p.K * ES + 127) / 128;
+
+			if (threadIdx.x == 0)
+			{
+				for (int s = 0; s < C::stages; s++)
+				{
+					mbar_init(smem_u32(&bars.full[s]), NUM_PRODUCERS + 1);
+					mbar_init(smem_u32(&bars.empty[s]), 1);
+				}
+				for (int a = 0; a < 2; a++)
+				{
+					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
+					mbar_init(smem_u32(&bars.tmem_empty[a]), 8);
+				}
+				bars.abort_flag = 0;
+				fence_mbar_init();
+			}
+			if (warp == 1)
+			{
+				tmem_alloc(smem_u32(&bars.tmem_base), 512);
+				tmem_relinquish();
+			}
+			tcgen05_fence_before();
+			__syncthreads();
+			tcgen05_fence_after();
+			const uint32_t tmem_base = bars.tmem_base;
+			volatile int *abort_flag = &bars.abort_flag;
+
+			if (warp == 0)
+			{ /* ------------------------------------------------ weight tiles by TMA */
+				if (elect_one())
+				{
+					prefetch_tensormap(&map_w);
+					uint32_t it = 0;
+					bool ok = true;
+					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+					{
+						const int nt = tile % n_tiles;
+						for (int kb = 0; kb < k_blocks; kb++, it++)
+						{
+							const int s = it % C::stages;
+							if (!mbar_wait(smem_u32(&bars.empty[s]), ((it / C::stages) & 1u) ^ 1u, abort_flag))
+							{
+								ok = false;
+								break;
+							}
+							const uint32_t full = smem_u32(&bars.full[s]);
+							mbar_arrive_expect_tx(full, C::b_stage_bytes);
+							tma_load_3d(smem_base + s * C::stage_bytes + A_STAGE_BYTES, &map_w, full, kb * (128 / ES), nt * BN, 0);
+						}
+					}
+				}
+				__syncwarp();
+			}
+			else if (warp == 1)
+			{ /* ------------------------------------------- MMA issue */
+				if (elect_one())
+				{
+					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN);
+					uint32_t it = 0, local_tile = 0;
+					bool ok = true;
+					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local_tile++)
+					{
+						const uint32_t buf = local_tile % C::acc_buffers;
+						const uint32_t use = local_tile / C::acc_buffers;
+						if (!mbar_wait(smem_u32(&bars.tmem_empty[buf]), (use & 1u) ^ 1u, abort_flag))
+							break;
+						tcgen05_fence_after();
+						const uint32_t tmem_d = tmem_base + buf * 2 * BN;
+						for (int kb = 0; kb < k_blocks; kb++, it++)
+						{
+							const int s = it % C::stages;
+							if (!mbar_wait(smem_u32(&bars.full[s]), (it / C::stages) & 1u, abort_flag))
+							{
+								ok = false;
+								break;
+							}
+							tcgen05_fence_after();
+							const uint32_t addr_a = smem_base + s * C::stage_bytes;
+							const uint64_t desc_a0 = make_desc_k_sw128(addr_a);
+							const uint64_t desc_a1 = make_desc_k_sw128(addr_a + 128 * 128);
+							const uint64_t desc_b = make_desc_k_sw128(addr_a + A_STAGE_BYTES);
+#pragma unroll
+							for (int k = 0; k < 4; k++)
+							{
+								const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+								mma_ss<KIND>(tmem_d, desc_a0 + 2 * k, desc_b + 2 * k, idesc, accumulate);
+								mma_ss<KIND>(tmem_d + BN, desc_a1 + 2 * k, desc_b + 2 * k, idesc, accumulate);
+							}
+							mma_commit(smem_u32(&bars.empty[s]));
+						}
+						if (ok)
+							mma_commit(smem_u32(&bars.tmem_full[buf]));
+					}
+				}
+				__syncwarp();
+			}
+			else if (warp < PRODUCER_WARP0)
+			{ /* ------------------------------------------------------------ epilogue */
+				const int q = warp % 4;
+				const int mh = (warp - 2) / 4;
+				uint32_t local_tile = 0;
+				for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
+				{
+					const int nt = tile % n_tiles;
+					const int mt = tile / n_tiles;
+					const uint32_t buf = local_tile % C::acc_buffers;
+					const uint32_t use = local_tile / C::acc_buffers;
+					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), use & 1u, abort_flag))
+						break;
+					tcgen05_fence_after();
+					const int row = mt * BM + mh * 128 + q * 32 + lane;
+					const bool row_ok = row < p.M;
+					const long long off = static_cast<long long>(row) * p.cout;
+					const int n_valid_tile = min(BN, p.cout - nt * BN);
+					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 2 * BN + mh * BN;
+					for (int c = 0; c < BN / 32; c++)
+					{
+						if (c * 32 >= n_valid_tile)
+							break;
+						uint32_t r[32];
+						tmem_ld_32x32(taddr + c * 32, r);
+						tmem_wait_ld();
+						if (!row_ok)
+							continue;
+						const int n0 = nt * BN + c * 32;
+						const int n_valid = min(32, p.cout - n0);
+						float v[32];
+						if (KIND == 0)
+						{
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = __uint_as_float(r[j]);
+							if (p.bias != nullptr)
+							{
+								const __half *bp = reinterpret_cast<const __half*>(p.bias) + n0;
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										v[j] += __half2float(bp[j]);
+							}
+							if (p.ext != nullptr)
+							{
+								const __half *ep = reinterpret_cast<const __half*>(p.ext) + off + n0;
+								if (n_valid == 32 && (reinterpret_cast<uintptr_t>(ep) % 16) == 0)
+								{
+#pragma unroll
+									for (int j = 0; j < 32; j += 8)
+									{
+										const uint4 raw = *reinterpret_cast<const uint4*>(ep + j);
+										const uint32_t w4[4] = { raw.x, raw.y, raw.z, raw.w };
+#pragma unroll
+										for (int t = 0; t < 4; t++)
+										{
+											const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[t]));
+											v[j + 2 * t] += f.x;
+											v[j + 2 * t + 1] += f.y;
+										}
+									}
+								}
+								else
+								{
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											v[j] += __half2float(ep[j]);
+								}
+							}
+							if (p.act != ACTIVATION_LINEAR)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									v[j] = apply_activation(v[j], p.act);
+							}
+						}
+						else if (p.out_dtype != DTYPE_INT32)
+						{
+							const int8_t *ep = (p.ext != nullptr) ? reinterpret_cast<const int8_t*>(p.ext) + off + n0 : nullptr;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+								{
+									float x = static_cast<float>(static_cast<int>(r[j])) * p.scales[n0 + j] + p.shifts[n0 + j];
+									if (ep != nullptr)
+										x += static_cast<float>(ep[j]) * p.ext_scale + p.ext_shift;
+									v[j] = (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU) ? apply_activation(x,
+											p.act) : x;
+								}
+						}
+
+						if (p.out_dtype == DTYPE_FLOAT16)
+						{
+							__half *dp = reinterpret_cast<__half*>(p.y) + off + n0;
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j += 8)
+								{
+									uint4 pk;
+									const __half2 h0 = __floats2half2_rn(v[j + 0], v[j + 1]);
+									const __half2 h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+									const __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]);
+									const __half2 h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+									pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+									pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+									pk.z = *reinterpret_cast<const uint32_t*>(&h2);
+									pk.w = *reinterpret_cast<const uint32_t*>(&h3);
+									*reinterpret_cast<uint4*>(dp + j) = pk;
+								}
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = __float2half_rn(v[j]);
+							}
+						}
+						else if (p.out_dtype == DTYPE_FLOAT32)
+						{
+							float *dp = reinterpret_cast<float*>(p.y) + off + n0;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+									dp[j] = v[j];
+						}
+						else if (p.out_dtype == DTYPE_INT8)
+						{
+							int8_t *dp = reinterpret_cast<int8_t*>(p.y) + off + n0;
+							uint32_t packed[8];
+#pragma unroll
+							for (int j = 0; j < 32; j += 4)
+							{
+								uint32_t w4 = 0;
+#pragma unroll
+								for (int t = 0; t < 4; t++)
+								{
+									const int qv = static_cast<int>(fmaxf(-128.0f, fminf(127.0f, roundf((v[j + t] - p.out_shift) / p.out_scale))));
+									w4 |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * t);
+								}
+								packed[j / 4] = w4;
+							}
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+								*reinterpret_cast<uint4*>(dp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+								*reinterpret_cast<uint4*>(dp + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = static_cast<int8_t>((packed[j / 4] >> (8 * (j % 4))) & 0xFFu);
+							}
+						}
+						else
+						{ // raw int32 accumulators
+							int *dp = reinterpret_cast<int*>(p.y) + off + n0;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+									dp[j] = static_cast<int>(r[j]);
+						}
+					}
+					tcgen05_fence_before();
+					__syncwarp();
+					if (lane == 0)
+						mbar_arrive(smem_u32(&bars.tmem_empty[buf]));
+				}
+			}
+			else
+			{ /* ------------------------------------------------------------ A-operand gather */
+				const int pt = threadIdx.x - PRODUCER_WARP0 * 32; // 0..127
+				const int j = pt % 8; // 16-byte chunk of the 128-byte K slice
+				const int g = pt / 8; // rows g, g + 16, g + 32, ...
+				const uint32_t row_byte = static_cast<uint32_t>(g) * 128 + static_cast<uint32_t>((j ^ (g & 7)) * 16);
+				const uint8_t *xb = reinterpret_cast<const uint8_t*>(p.x);
+				const uint32_t pad_word = static_cast<uint32_t>(p.pad_byte & 0xFF) * 0x01010101u;
+				const bool store_pad = (KIND == 1) && (p.pad_byte != 0);
+				const int hw = p.height * p.width;
+				constexpr int LAG = 2;
+				uint32_t it = 0;
+				bool ok = true;
+				for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+				{
+					const int mt = tile / n_tiles;
+					int pos_hw[16]; // (h << 16) | w, or -1 for a row beyond M
+					int pos_off[16]; // element offset of the position's channel 0
+#pragma unroll
+					for (int i = 0; i < 16; i++)
+					{
+						const int m = mt * BM + g + 16 * i;
+						if (m < p.M)
+						{
+							const int rem = m % hw;
+							const int h = rem / p.width;
+							pos_hw[i] = (h << 16) | (rem - h * p.width);
+							pos_off[i] = m * p.cin;
+						}
+						else
+						{
+							pos_hw[i] = -1;
+							pos_off[i] = 0;
+						}
+					}
+					for (int kb = 0; kb < k_blocks; kb++, it++)
+					{
+						const int s = it % C::stages;
+						if (!mbar_wait(smem_u32(&bars.empty[s]), ((it / C::stages) & 1u) ^ 1u, abort_flag))
+						{
+							ok = false;
+							break;
+						}
+						const uint32_t dst0 = smem_base + s * C::stage_bytes + row_byte;
+						const int k0 = kb * (128 / ES) + j * CHUNK_ELEMS;
+						const bool k_ok = k0 < p.K;
+						const int tap = k_ok ? k0 / p.cin : 0;
+						const int c0 = k0 - tap * p.cin;
+						const int dh = tap / 3 - 1, dw = tap % 3 - 1;
+						const int delta = (dh * p.width + dw) * p.cin + c0;
+#pragma unroll
+						for (int i = 0; i < 16; i++)
+						{
+							const int h = (pos_hw[i] >> 16) + dh, w = (pos_hw[i] & 0xFFFF) + dw;
+							const bool inside = k_ok && pos_hw[i] >= 0 && h >= 0 && h < p.height && w >= 0 && w < p.width;
+							const uint32_t dst = dst0 + i * 16 * 128;
+							if (inside)
+								cp_async_16(dst, xb + static_cast<long long>(pos_off[i] + delta) * ES, 16);
+							else if (store_pad && k_ok && pos_hw[i] >= 0)
+								st_shared_16(dst, pad_word);
+							else
+								cp_async_16(dst, xb, 0); // zero fill
+						}
+						cp_async_commit();
+						if (it >= LAG)
+						{
+							cp_async_wait<LAG>();
+							fence_proxy_async_smem();
+							mbar_arrive(smem_u32(&bars.full[(it - LAG) % C::stages]));
+						}
+					}
+				}
+				// drain: the last LAG slices that were issued but not yet published
+				cp_async_wait<0>();
+				fence_proxy_async_smem();
+				if (ok)
+				{
+					const uint32_t first = it >= LAG ? it - LAG : 0;
+					for (uint32_t t = first; t < it; t++)
+						mbar_arrive(smem_u32(&bars.full[t % C::stages]));
+				}
+			}
+
+			/* ---------------------------------------------------------------- teardown */
+			tcgen05_fence_before();
+			__syncthreads();
+			if (bars.abort_flag != 0)
+			{
+				if (threadIdx.x == 0 && p.status != nullptr)
+					atomicExch(p.status, 2);
+				__nanosleep(1000000);
+			}
+			if (warp == 1)
+			{
+				tcgen05_fence_after();
+				tmem_dealloc(tmem_base, 512);
+			}
+		}
+
+		template<int KIND, int BN>
+		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const ConvParams &p)
+		{
+			using C = Cfg<BN>;
+			static bool configured = false;
+			if (!configured)
+			{
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+						"conv_igemm: shared memory opt-in"))
+					return false;
+				configured = true;
+			}
+			const int tiles = ((p.M + BM - 1) / BM) * ((p.cout + BN - 1) / BN);
+			const int grid = std::min(tiles, get(ctx)->sm_count);
+			kernel_conv3x3_igemm<KIND, BN> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, p);
+			MB200_COUNT_LAUNCH();
+			get(ctx)->kernels_with_waits = true;
+			return check_cuda(ctx, cudaGetLastError(), "conv_igemm launch");
+		}
+
+		bool shape_ok(int kind, const mlTensor_t &x, int cout, const void *w)
+		{
+			const int chunk = (kind == 0) ? 8 : 16;
+			if (x.rank != 4 || x.dim[3] % chunk != 0)
+				return false;
+			if (!aligned_to(x.data, 16) || !aligned_to(w, 16))
+				return false;
+			const long long m = static_cast<long long>(x.dim[0]) * x.dim[1] * x.dim[2];
+			if (m <= 0 || m * std::max(x.dim[3], cout) >= (1LL << 31))
+				return false;
+			if (x.dim[1] >= 32768 || x.dim[2] >= 32768)
+				return false;
+			return true;
+		}
+
+		bool run(mlContext_t ctx, int kind, const mlTensor_t &x, const void *w, int cout, ConvParams p)
+		{
+			const int es = (kind == 0) ? 2 : 1;
+			p.x = x.data;
+			p.batch = x.dim[0];
+			p.height = x.dim[1];
+			p.width = x.dim[2];
+			p.cin = x.dim[3];
+			p.cout = cout;
+			p.M = x.dim[0] * x.dim[1] * x.dim[2];
+			p.K = 9 * x.dim[3];
+			p.status = get(ctx)->dev_status;
+			const int bn = (cout > 128) ? 256 : 128;
+			CUtensorMap map_w;
+			const uint64_t dims[3] = { static_cast<uint64_t>(p.K), static_cast<uint64_t>(cout), 1 };
+			const uint64_t strides[2] = { static_cast<uint64_t>(p.K) * es, static_cast<uint64_t>(p.K) * es * cout };
+			const uint32_t box[3] = { static_cast<uint32_t>(128 / es), static_cast<uint32_t>(bn), 1 };
+			if (!encode_tensor_map(ctx, &map_w, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box,
+					CU_TENSOR_MAP_SWIZZLE_128B))
+				return false;
+			if (kind == 0)
+				return bn == 256 ? launch<0, 256>(ctx, map_w, p) : launch<0, 128>(ctx, map_w, p);
+			return bn == 256 ? launch<1, 256>(ctx, map_w, p) : launch<1, 128>(ctx, map_w, p);
+		}
+	}
+
 	bool conv_fused_input_supported(const mlTensor_t &x)
 	{
-		(void) x;
-		return false;
+		return x.dtype == DTYPE_FLOAT16 && shape_ok(0, x, 1, x.data);
 	}
 	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act)
 	{
-		(void) x;
-		(void) w;
-		(void) y;
 		(void) act;
-		return false;
+		if (x.dtype != DTYPE_FLOAT16 || w.dtype != DTYPE_FLOAT16 || y.dtype != DTYPE_FLOAT16)
+			return false;
+		if (w.rank != 4 || w.dim[1] != 3 || w.dim[2] != 3 || w.dim[3] != x.dim[3])
+			return false;
+		return shape_ok(0, x, w.dim[0], w.data) && aligned_to(y.data, 2);
 	}
 	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
 			mlActivationType_t act)
 	{
-		(void) x;
-		(void) w;
-		(void) bias;
-		(void) ext;
-		(void) y;
-		(void) act;
-		record_error(ctx, "fused convolution kernel not available");
-		return false;
+		ConvParams p;
+		std::memset(&p, 0, sizeof(p));
+		p.y = y.data;
+		p.bias = bias;
+		p.ext = ext;
+		p.act = act;
+		p.out_dtype = DTYPE_FLOAT16;
+		return run(ctx, 0, x, w.data, w.dim[0], p);
 	}
+
+	/* ------------------------------------------------------------------------------------------------------------
+	 * Deferred int8 sequence: im2row (recorded) -> int8 GEMM (recorded) -> scale_shift_act (launches the fused kernel).
+	 * ---------------------------------------------------------------------------------------------------------- */
 	bool im2row_defer(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &input_shape, void *output, const void *input, int kernel_size,
 			bool invert, const void *padding)
 	{
-		(void) ctx; (void) dtype; (void) input_shape; (void) output; (void) input; (void) kernel_size; (void) invert; (void) padding;
-		return false;
+		Context *c = get(ctx);
+		if (c == nullptr || !c->fusion || dtype != DTYPE_INT8 || kernel_size != 3 || invert)
+			return false;
+		const mlTensor_t x = make_tensor(input, DTYPE_INT8, input_shape);
+		if (!shape_ok(1, x, 1, input))
+			return false;
+		flush_pending(ctx);
+		c->pending_i8.stage = 1;
+		c->pending_i8.x = x;
+		c->pending_i8.rows = output;
+		c->pending_i8.pad = (padding == nullptr) ? 0 : *reinterpret_cast<const int8_t*>(padding);
+		return true;
+	}
+	bool int8_gemm_defer(mlContext_t ctx, char opA, char opB, const mlTensor_t &A, const mlTensor_t &B, const mlTensor_t &C)
+	{
+		Context *c = get(ctx);
+		if (c == nullptr || c->pending_i8.stage != 1)
+			return false;
+		if (is_transpose(opA) || !is_transpose(opB) || A.data != c->pending_i8.rows || A.dtype != DTYPE_INT8 || B.dtype != DTYPE_INT8
+				|| C.dtype != DTYPE_INT32 || A.rank != 2 || B.rank != 2 || C.rank != 2)
+			return false;
+		const mlTensor_t &x = c->pending_i8.x;
+		if (B.dim[1] != 9 * x.dim[3] || A.dim[1] != B.dim[1] || C.dim[1] != B.dim[0] || !aligned_to(B.data, 16))
+			return false;
+		c->pending_i8.stage = 2;
+		c->pending_i8.w = B;
+		c->pending_i8.acc = C;
+		return true;
 	}
 	bool requant_complete_fused(mlContext_t ctx, mlDataType_t dtype, const mlShape_t &shape, void *output, mlQuantizationData_t output_qd,
 			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd)
 	{
-		(void) ctx; (void) dtype; (void) shape; (void) output; (void) output_qd; (void) input; (void) scales; (void) bias; (void) act; (void) ext;
-		(void) ext_qd;
-		return false;
+		Context *c = get(ctx);
+		if (c == nullptr || c->pending_i8.stage != 2 || input != c->pending_i8.acc.data)
+			return false;
+		if (dtype != DTYPE_INT8 && dtype != DTYPE_FLOAT16 && dtype != DTYPE_FLOAT32)
+			return false;
+		const mlTensor_t x = c->pending_i8.x;
+		const int cout = c->pending_i8.w.dim[0];
+		if (volume(shape) != static_cast<long long>(x.dim[0]) * x.dim[1] * x.dim[2] * cout || last_dim(shape) != cout)
+			return false;
+		ConvParams p;
+		std::memset(&p, 0, sizeof(p));
+		p.y = output;
+		p.ext = ext;
+		p.act = act;
+		p.out_dtype = dtype;
+		p.scales = reinterpret_cast<const float*>(scales);
+		p.shifts = reinterpret_cast<const float*>(bias);
+		p.ext_scale = ext_qd.scale;
+		p.ext_shift = ext_qd.shift;
+		p.out_scale = output_qd.scale;
+		p.out_shift = output_qd.shift;
+		p.pad_byte = c->pending_i8.pad;
+		c->pending_i8.stage = 0;
+		return run(ctx, 1, x, c->pending_i8.w.data, cout, p);
+	}
+	void flush_pending_int8(mlContext_t ctx)
+	{
+		Context *c = get(ctx);
+		if (c == nullptr || c->pending_i8.stage == 0)
+			return;
+		const PendingInt8 pend = c->pending_i8;
+		c->pending_i8.stage = 0;
+		const bool fusion = c->fusion;
+		c->fusion = false;
+		const int8_t pad = static_cast<int8_t>(pend.pad);
+		cuda_im2row(ctx, DTYPE_INT8, shape_of(pend.x), pend.rows, pend.x.data, 3, false, &pad);
+		if (pend.stage == 2)
+		{
+			mlTensor_t a = make_tensor(pend.rows, DTYPE_INT8, make_shape( { pend.acc.dim[0], pend.w.dim[1] }));
+			cuda_gemm_v2(ctx, 'n', 't', 1.0f, a, pend.w, 0.0f, pend.acc);
+		}
+		c->fusion = fusion;
 	}
 } /* namespace mb200 */

@@ -117,7 +117,11 @@ namespace mb200
 	void flush_pending(mlContext_t ctx)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending.stage == 0)
+		if (c == nullptr)
+			return;
+		if (c->pending_i8.stage != 0)
+			flush_pending_int8(ctx);
+		if (c->pending.stage == 0)
 			return;
 		const PendingWinograd p = c->pending;
 		c->pending.stage = 0; // the eager entry points below call flush_pending again

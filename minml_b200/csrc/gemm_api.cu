@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include "winograd.cuh"
+#include "conv.cuh"
 
 using namespace mb200;
 
@@ -167,6 +168,8 @@ extern "C"
 {
 	void cuda_gemm_v2(mlContext_t context, char opA, char opB, float alpha, const mlTensor_t A, const mlTensor_t B, float beta, mlTensor_t C)
 	{
+		if (context != nullptr && mb200::int8_gemm_defer(context, opA, opB, A, B, C))
+			return;
 		run_gemm(context, "cuda_gemm_v2", opA, opB, alpha, operand_of(A), operand_of(B), beta, operand_of(C), nullptr, nullptr, ACTIVATION_LINEAR,
 				1);
 	}
