@@ -362,6 +362,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="three kernels per 3x3 layer (fusion off) instead of the fused convolution")
+    ap.add_argument("--layer", action="store_true", help="time only one channels -> channels 3x3 layer (the roofline record); used for ncu captures")
+    ap.add_argument("--layer-batch", type=int, default=0, help="batch size for --layer (default: the config's)")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", "0"))
@@ -381,6 +383,15 @@ def main():
         print(json.dumps(line))
         return
 
+    if args.layer:
+        import torch
+        from minml_b200 import backend as B
+        from minml_b200 import layers as L
+        cfg = dict(cfg, batch=args.layer_batch or cfg["batch"])
+        ctx = B.Context(0)
+        print(json.dumps(layer_roofline(B, L, ctx, cfg, load_peaks(), torch, fused=not args.eager)))
+        ctx.close()
+        return
     result = gpu_arm(args, cfg)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

@@ -12,13 +12,16 @@
  *
  * GEMM view: M = b*h*w output positions, N = cout, K = 9*cin ordered (kh, kw, cin) -- the weight tensor as stored is
  * the K-major B operand [N, K].  The A operand is never materialised: for every 128-byte slice of K, producer warps
- * gather the 16-byte channel chunks of 256 positions straight from x into the 128B-swizzled shared-memory tile that
+ * gather the 16-byte channel chunks of 128 positions straight from x into the 128B-swizzled shared-memory tile that
  * tcgen05.mma reads (cp.async with zero fill outside the image; a non-zero int8 padding value is stored directly).
  *
- * One CTA per SM, persistent over 256 x BN output tiles:
+ * One CTA per SM, persistent over 128 x BN output tiles, two accumulator buffers in tensor memory so that the
+ * epilogue of tile i overlaps the main loop of tile i + 1:
  *   warp 0        TMA loads of the weight tile (BN rows x 128 bytes of K)
- *   warp 1        tcgen05.mma issue: per K slice, two M=128 instructions chains share one weight tile
- *   warps 2-9     epilogue: tcgen05.ld, bias / residual / activation / requantisation, 16-byte stores
+ *   warp 1        tcgen05.mma issue (one elected lane); owns the tensor-memory allocation
+ *   warps 2-9     epilogue: tcgen05.ld, bias / residual / activation / requantisation; residual reads and output
+ *                 writes of the fp16 path are staged through shared memory so that every global access of a warp
+ *                 covers whole 64-byte row segments
  *   warps 10-13   A-operand gather
  * Every wait is bounded (tc.cuh); on a timeout the kernel sets its status word and drains.
  */
@@ -34,20 +37,24 @@ namespace mb200
 	{
 		using namespace tc;
 
-		constexpr int BM = 256; // two M = 128 halves
+		constexpr int BM = 128;
 		constexpr int NUM_THREADS = 14 * 32;
 		constexpr int PRODUCER_WARP0 = 10;
 		constexpr int NUM_PRODUCERS = 128;
 		constexpr int A_STAGE_BYTES = BM * 128;
+		constexpr int EPI_PITCH = 80; // bytes per staged row: 64 of payload + 16 of padding against bank conflicts
+		constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
+		constexpr int MAX_STAGES = 6;
 
 		template<int BN>
 		struct Cfg
 		{
 				static constexpr int b_stage_bytes = BN * 128;
 				static constexpr int stage_bytes = A_STAGE_BYTES + b_stage_bytes;
-				static constexpr int stages = (BN == 256) ? 3 : 4;
-				static constexpr int smem_bytes = stages * stage_bytes + 1024;
-				static constexpr int acc_buffers = 512 / (2 * BN); // 1 for BN = 256, 2 for BN = 128
+				static constexpr int stages = (BN == 256) ? 4 : 6;
+				static constexpr int lag = stages - 2; // gather slices in flight per producer thread
+				static constexpr int smem_bytes = stages * stage_bytes + 8 * EPI_WARP_BYTES + 1024;
+				static constexpr int tmem_columns = 2 * BN;
 		};
 
 		struct ConvParams
@@ -69,8 +76,8 @@ namespace mb200
 
 		struct ConvBarriers
 		{
-				uint64_t full[4];
-				uint64_t empty[4];
+				uint64_t full[MAX_STAGES];
+				uint64_t empty[MAX_STAGES];
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
@@ -94,6 +101,44 @@ namespace mb200
 		{
 			asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "r"(v) : "memory");
 		}
+		__device__ __forceinline__ void st_shared_v4(uint32_t dst, const uint4 &v)
+		{
+			asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+		}
+		__device__ __forceinline__ uint4 ld_shared_v4(uint32_t src)
+		{
+			uint4 v;
+			asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(src) : "memory");
+			return v;
+		}
+		__device__ __forceinline__ bool aligned_to_16(const void *ptr)
+		{
+			return (reinterpret_cast<uintptr_t>(ptr) % 16) == 0;
+		}
+		__device__ __forceinline__ void add_half8(float *v, const uint4 &raw)
+		{
+			const uint32_t w4[4] = { raw.x, raw.y, raw.z, raw.w };
+#pragma unroll
+			for (int t = 0; t < 4; t++)
+			{
+				const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[t]));
+				v[2 * t] += f.x;
+				v[2 * t + 1] += f.y;
+			}
+		}
+		__device__ __forceinline__ uint4 pack_half8(const float *v)
+		{
+			uint4 pk;
+			const __half2 h0 = __floats2half2_rn(v[0], v[1]);
+			const __half2 h1 = __floats2half2_rn(v[2], v[3]);
+			const __half2 h2 = __floats2half2_rn(v[4], v[5]);
+			const __half2 h3 = __floats2half2_rn(v[6], v[7]);
+			pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+			pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+			pk.z = *reinterpret_cast<const uint32_t*>(&h2);
+			pk.w = *reinterpret_cast<const uint32_t*>(&h3);
+			return pk;
+		}
 
 		template<int KIND, int BN>
 		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w, const ConvParams p)
@@ -105,6 +150,7 @@ namespace mb200
 			__shared__ ConvBarriers bars;
 
 			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+			const uint32_t epi_base = smem_base + C::stages * C::stage_bytes;
 			const int warp = threadIdx.x / 32;
 			const int lane = threadIdx.x % 32;
 
@@ -130,7 +176,7 @@ namespace mb200
 			}
 			if (warp == 1)
 			{
-				tmem_alloc(smem_u32(&bars.tmem_base), 512);
+				tmem_alloc(smem_u32(&bars.tmem_base), C::tmem_columns);
 				tmem_relinquish();
 			}
 			tcgen05_fence_before();
@@ -174,12 +220,11 @@ namespace mb200
 					bool ok = true;
 					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local_tile++)
 					{
-						const uint32_t buf = local_tile % C::acc_buffers;
-						const uint32_t use = local_tile / C::acc_buffers;
-						if (!mbar_wait(smem_u32(&bars.tmem_empty[buf]), (use & 1u) ^ 1u, abort_flag))
+						const uint32_t buf = local_tile & 1u;
+						if (!mbar_wait(smem_u32(&bars.tmem_empty[buf]), ((local_tile >> 1) & 1u) ^ 1u, abort_flag))
 							break;
 						tcgen05_fence_after();
-						const uint32_t tmem_d = tmem_base + buf * 2 * BN;
+						const uint32_t tmem_d = tmem_base + buf * BN;
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
 							const int s = it % C::stages;
@@ -190,16 +235,11 @@ namespace mb200
 							}
 							tcgen05_fence_after();
 							const uint32_t addr_a = smem_base + s * C::stage_bytes;
-							const uint64_t desc_a0 = make_desc_k_sw128(addr_a);
-							const uint64_t desc_a1 = make_desc_k_sw128(addr_a + 128 * 128);
+							const uint64_t desc_a = make_desc_k_sw128(addr_a);
 							const uint64_t desc_b = make_desc_k_sw128(addr_a + A_STAGE_BYTES);
 #pragma unroll
 							for (int k = 0; k < 4; k++)
-							{
-								const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-								mma_ss<KIND>(tmem_d, desc_a0 + 2 * k, desc_b + 2 * k, idesc, accumulate);
-								mma_ss<KIND>(tmem_d + BN, desc_a1 + 2 * k, desc_b + 2 * k, idesc, accumulate);
-							}
+								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
 							mma_commit(smem_u32(&bars.empty[s]));
 						}
 						if (ok)
@@ -210,34 +250,111 @@ namespace mb200
 			}
 			else if (warp < PRODUCER_WARP0)
 			{ /* ------------------------------------------------------------ epilogue */
-				const int q = warp % 4;
-				const int mh = (warp - 2) / 4;
+				const int q = warp % 4; // tensor-memory lane quarter
+				const int col_half = (warp - 2) / 4; // which half of the BN columns this warp handles
+				const uint32_t sbuf = epi_base + (warp - 2) * EPI_WARP_BYTES;
+				const int rr = lane / 4, seg = lane % 4; // cooperative access: 8 rows x 4 segments of 16 bytes per instruction
+				const bool rows_vectorisable = (p.cout % 8 == 0) && aligned_to_16(p.y) && (p.ext == nullptr || aligned_to_16(p.ext));
 				uint32_t local_tile = 0;
 				for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
 				{
 					const int nt = tile % n_tiles;
 					const int mt = tile / n_tiles;
-					const uint32_t buf = local_tile % C::acc_buffers;
-					const uint32_t use = local_tile / C::acc_buffers;
-					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), use & 1u, abort_flag))
+					const uint32_t buf = local_tile & 1u;
+					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), (local_tile >> 1) & 1u, abort_flag))
 						break;
 					tcgen05_fence_after();
-					const int row = mt * BM + mh * 128 + q * 32 + lane;
+					const int row0 = mt * BM + q * 32; // first row of this warp
+					const int row = row0 + lane;
 					const bool row_ok = row < p.M;
 					const long long off = static_cast<long long>(row) * p.cout;
+					const int col_begin = col_half * (BN / 2);
 					const int n_valid_tile = min(BN, p.cout - nt * BN);
-					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 2 * BN + mh * BN;
-					for (int c = 0; c < BN / 32; c++)
+					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+					for (int c = col_begin / 32; c < (col_begin + BN / 2) / 32; c++)
 					{
 						if (c * 32 >= n_valid_tile)
-							break;
+							break; // warp-uniform
+						const int n0 = nt * BN + c * 32;
+						const int n_valid = min(32, p.cout - n0);
+						const bool fast = (KIND == 0) && rows_vectorisable && n_valid == 32;
+
+						uint4 res[4];
+						if (fast && p.ext != nullptr)
+						{ // issue the residual reads before waiting on tensor memory
+							const __half *ep = reinterpret_cast<const __half*>(p.ext);
+#pragma unroll
+							for (int i = 0; i < 4; i++)
+							{
+								const int r = row0 + rr + 8 * i;
+								res[i] = (r < p.M) ? *reinterpret_cast<const uint4*>(ep + static_cast<long long>(r) * p.cout + n0 + seg * 8) : make_uint4(0,
+										0, 0, 0);
+							}
+						}
 						uint32_t r[32];
 						tmem_ld_32x32(taddr + c * 32, r);
 						tmem_wait_ld();
+
+						if (fast)
+						{
+							float v[32];
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = __uint_as_float(r[j]);
+							if (p.bias != nullptr)
+							{
+								const uint4 *bp = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.bias) + n0);
+								if (aligned_to_16(p.bias))
+								{
+#pragma unroll
+									for (int k = 0; k < 4; k++)
+										add_half8(v + 8 * k, bp[k]);
+								}
+								else
+								{
+									const __half *bs = reinterpret_cast<const __half*>(p.bias) + n0;
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										v[j] += __half2float(bs[j]);
+								}
+							}
+							if (p.ext != nullptr)
+							{ // through shared memory: cooperative layout -> one row per lane
+#pragma unroll
+								for (int i = 0; i < 4; i++)
+									st_shared_v4(sbuf + (rr + 8 * i) * EPI_PITCH + seg * 16, res[i]);
+								__syncwarp();
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									add_half8(v + 8 * k, ld_shared_v4(sbuf + lane * EPI_PITCH + k * 16));
+								__syncwarp();
+							}
+							if (p.act != ACTIVATION_LINEAR)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									v[j] = apply_activation(v[j], p.act);
+							}
+#pragma unroll
+							for (int k = 0; k < 4; k++)
+								st_shared_v4(sbuf + lane * EPI_PITCH + k * 16, pack_half8(v + 8 * k));
+							__syncwarp();
+							__half *yp = reinterpret_cast<__half*>(p.y);
+#pragma unroll
+							for (int i = 0; i < 4; i++)
+							{
+								const int rg = row0 + rr + 8 * i;
+								const uint4 val = ld_shared_v4(sbuf + (rr + 8 * i) * EPI_PITCH + seg * 16);
+								if (rg < p.M)
+									*reinterpret_cast<uint4*>(yp + static_cast<long long>(rg) * p.cout + n0 + seg * 8) = val;
+							}
+							__syncwarp();
+							continue;
+						}
+
+						/* general path: one row per lane, any alignment, column tails, and the int8 kinds */
 						if (!row_ok)
 							continue;
-						const int n0 = nt * BN + c * 32;
-						const int n_valid = min(32, p.cout - n0);
 						float v[32];
 						if (KIND == 0)
 						{
@@ -255,89 +372,58 @@ namespace mb200
 							if (p.ext != nullptr)
 							{
 								const __half *ep = reinterpret_cast<const __half*>(p.ext) + off + n0;
-								if (n_valid == 32 && (reinterpret_cast<uintptr_t>(ep) % 16) == 0)
-								{
-#pragma unroll
-									for (int j = 0; j < 32; j += 8)
-									{
-										const uint4 raw = *reinterpret_cast<const uint4*>(ep + j);
-										const uint32_t w4[4] = { raw.x, raw.y, raw.z, raw.w };
-#pragma unroll
-										for (int t = 0; t < 4; t++)
-										{
-											const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[t]));
-											v[j + 2 * t] += f.x;
-											v[j + 2 * t + 1] += f.y;
-										}
-									}
-								}
-								else
-								{
-#pragma unroll
-									for (int j = 0; j < 32; j++)
-										if (j < n_valid)
-											v[j] += __half2float(ep[j]);
-								}
-							}
-							if (p.act != ACTIVATION_LINEAR)
-							{
-#pragma unroll
-								for (int j = 0; j < 32; j++)
-									v[j] = apply_activation(v[j], p.act);
-							}
-						}
-						else if (p.out_dtype != DTYPE_INT32)
-						{
-							const int8_t *ep = (p.ext != nullptr) ? reinterpret_cast<const int8_t*>(p.ext) + off + n0 : nullptr;
-#pragma unroll
-							for (int j = 0; j < 32; j++)
-								if (j < n_valid)
-								{
-									float x = static_cast<float>(static_cast<int>(r[j])) * p.scales[n0 + j] + p.shifts[n0 + j];
-									if (ep != nullptr)
-										x += static_cast<float>(ep[j]) * p.ext_scale + p.ext_shift;
-									v[j] = (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU) ? apply_activation(x,
-											p.act) : x;
-								}
-						}
-
-						if (p.out_dtype == DTYPE_FLOAT16)
-						{
-							__half *dp = reinterpret_cast<__half*>(p.y) + off + n0;
-							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
-							{
-#pragma unroll
-								for (int j = 0; j < 32; j += 8)
-								{
-									uint4 pk;
-									const __half2 h0 = __floats2half2_rn(v[j + 0], v[j + 1]);
-									const __half2 h1 = __floats2half2_rn(v[j + 2], v[j + 3]);
-									const __half2 h2 = __floats2half2_rn(v[j + 4], v[j + 5]);
-									const __half2 h3 = __floats2half2_rn(v[j + 6], v[j + 7]);
-									pk.x = *reinterpret_cast<const uint32_t*>(&h0);
-									pk.y = *reinterpret_cast<const uint32_t*>(&h1);
-									pk.z = *reinterpret_cast<const uint32_t*>(&h2);
-									pk.w = *reinterpret_cast<const uint32_t*>(&h3);
-									*reinterpret_cast<uint4*>(dp + j) = pk;
-								}
-							}
-							else
-							{
 #pragma unroll
 								for (int j = 0; j < 32; j++)
 									if (j < n_valid)
-										dp[j] = __float2half_rn(v[j]);
+										v[j] += __half2float(ep[j]);
 							}
-						}
-						else if (p.out_dtype == DTYPE_FLOAT32)
-						{
-							float *dp = reinterpret_cast<float*>(p.y) + off + n0;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = apply_activation(v[j], p.act);
+							__half *dp = reinterpret_cast<__half*>(p.y) + off + n0;
 #pragma unroll
 							for (int j = 0; j < 32; j++)
 								if (j < n_valid)
-									dp[j] = v[j];
+									dp[j] = __float2half_rn(v[j]);
+							continue;
 						}
-						else if (p.out_dtype == DTYPE_INT8)
+						if (p.out_dtype == DTYPE_INT32)
+						{ // raw accumulators
+							int *dp = reinterpret_cast<int*>(p.y) + off + n0;
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								if (j < n_valid)
+									dp[j] = static_cast<int>(r[j]);
+							continue;
+						}
+						const int8_t *ep = (p.ext != nullptr) ? reinterpret_cast<const int8_t*>(p.ext) + off + n0 : nullptr;
+						const bool act_on = (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU);
+						uint32_t ext_words[8];
+						const bool ext_vec = ep != nullptr && n_valid == 32 && (reinterpret_cast<uintptr_t>(ep) % 16) == 0;
+						if (ext_vec)
+						{
+							const uint4 e0 = *reinterpret_cast<const uint4*>(ep), e1 = *reinterpret_cast<const uint4*>(ep + 16);
+							ext_words[0] = e0.x; ext_words[1] = e0.y; ext_words[2] = e0.z; ext_words[3] = e0.w;
+							ext_words[4] = e1.x; ext_words[5] = e1.y; ext_words[6] = e1.z; ext_words[7] = e1.w;
+						}
+#pragma unroll
+						for (int j = 0; j < 32; j++)
+						{
+							float x = 0.0f;
+							if (j < n_valid)
+							{
+								x = static_cast<float>(static_cast<int>(r[j])) * p.scales[n0 + j] + p.shifts[n0 + j];
+								if (ep != nullptr)
+								{
+									const int e = ext_vec ? static_cast<int>(static_cast<int8_t>((ext_words[j / 4] >> (8 * (j % 4))) & 0xFFu)) : static_cast<int>(ep[j]);
+									x += static_cast<float>(e) * p.ext_scale + p.ext_shift;
+								}
+								if (act_on)
+									x = apply_activation(x, p.act);
+							}
+							v[j] = x;
+						}
+						if (p.out_dtype == DTYPE_INT8)
 						{
 							int8_t *dp = reinterpret_cast<int8_t*>(p.y) + off + n0;
 							uint32_t packed[8];
@@ -366,13 +452,30 @@ namespace mb200
 										dp[j] = static_cast<int8_t>((packed[j / 4] >> (8 * (j % 4))) & 0xFFu);
 							}
 						}
-						else
-						{ // raw int32 accumulators
-							int *dp = reinterpret_cast<int*>(p.y) + off + n0;
+						else if (p.out_dtype == DTYPE_FLOAT16)
+						{
+							__half *dp = reinterpret_cast<__half*>(p.y) + off + n0;
 #pragma unroll
 							for (int j = 0; j < 32; j++)
 								if (j < n_valid)
-									dp[j] = static_cast<int>(r[j]);
+									dp[j] = __float2half_rn(v[j]);
+						}
+						else
+						{
+							float *dp = reinterpret_cast<float*>(p.y) + off + n0;
+							if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dp) % 16) == 0)
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j += 4)
+									*reinterpret_cast<float4*>(dp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = v[j];
+							}
 						}
 					}
 					tcgen05_fence_before();
@@ -391,16 +494,17 @@ namespace mb200
 				const uint32_t pad_word = static_cast<uint32_t>(p.pad_byte & 0xFF) * 0x01010101u;
 				const bool store_pad = (KIND == 1) && (p.pad_byte != 0);
 				const int hw = p.height * p.width;
-				constexpr int LAG = 2;
+				constexpr int LAG = C::lag;
+				constexpr int ROWS = BM / 16; // rows per producer thread
 				uint32_t it = 0;
 				bool ok = true;
 				for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
 				{
 					const int mt = tile / n_tiles;
-					int pos_hw[16]; // (h << 16) | w, or -1 for a row beyond M
-					int pos_off[16]; // element offset of the position's channel 0
+					int pos_hw[ROWS]; // (h << 16) | w, or -1 for a row beyond M
+					int pos_off[ROWS]; // element offset of the position's channel 0
 #pragma unroll
-					for (int i = 0; i < 16; i++)
+					for (int i = 0; i < ROWS; i++)
 					{
 						const int m = mt * BM + g + 16 * i;
 						if (m < p.M)
@@ -432,7 +536,7 @@ namespace mb200
 						const int dh = tap / 3 - 1, dw = tap % 3 - 1;
 						const int delta = (dh * p.width + dw) * p.cin + c0;
 #pragma unroll
-						for (int i = 0; i < 16; i++)
+						for (int i = 0; i < ROWS; i++)
 						{
 							const int h = (pos_hw[i] >> 16) + dh, w = (pos_hw[i] & 0xFFFF) + dw;
 							const bool inside = k_ok && pos_hw[i] >= 0 && h >= 0 && h < p.height && w >= 0 && w < p.width;
@@ -476,7 +580,7 @@ namespace mb200
 			if (warp == 1)
 			{
 				tcgen05_fence_after();
-				tmem_dealloc(tmem_base, 512);
+				tmem_dealloc(tmem_base, C::tmem_columns);
 			}
 		}
 
