@@ -17,18 +17,26 @@
  *
  * One CTA per SM, persistent over 128 x BN output tiles, two accumulator buffers in tensor memory so that the
  * epilogue of tile i overlaps the main loop of tile i + 1:
- *   warp 0        TMA loads of the weight tile (BN rows x 128 bytes of K)
+ *   warp 0        TMA loads of the weight tile (BN rows x 128 bytes of K) and, in the TMA_A variant, of the A slice
  *   warp 1        tcgen05.mma issue (one elected lane); owns the tensor-memory allocation
  *   warps 2-9     epilogue: tcgen05.ld, bias / residual / activation / requantisation; residual reads and output
  *                 writes of the fp16 path are staged through shared memory so that every global access of a warp
  *                 covers whole 64-byte row segments
- *   warps 10-13   A-operand gather
+ *   warps 10, 11, 14, 15   A-operand gather (cp.async variant only)
+ *
+ * Two variants of the A operand path:
+ *   TMA_A = true   im2col-mode TMA: one request per K slice delivers 128 output positions x 128 bytes of channels of one
+ *                  filter tap, zero-filled outside the image.  Needs cin * element size to be a multiple of 128 bytes and
+ *                  a zero padding value.  This is the fast path (256 -> 256 fp16: 1.23 PFLOP/s against 0.92 for the gather).
+ *   TMA_A = false  cp.async gather of 16-byte channel chunks: any cin that is a multiple of 8 (fp16) / 16 (int8), any
+ *                  int8 padding value.
  * Every wait is bounded (tc.cuh); on a timeout the kernel sets its status word and drains.
  */
 #include "common.cuh"
 #include "conv.cuh"
 #include "tc.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace mb200
@@ -38,7 +46,7 @@ namespace mb200
 		using namespace tc;
 
 		constexpr int BM = 128;
-		constexpr int NUM_THREADS = 14 * 32;
+		constexpr int NUM_THREADS = 16 * 32;
 		constexpr int PRODUCER_WARP0 = 10;
 		constexpr int NUM_PRODUCERS = 128;
 		constexpr int A_STAGE_BYTES = BM * 128;
@@ -46,14 +54,17 @@ namespace mb200
 		constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
 		constexpr int MAX_STAGES = 6;
 
-		template<int BN>
+		/* TMA_A: the A operand is fetched by im2col-mode TMA (one request per K slice) instead of the cp.async gather.
+		 * Possible when every 128-byte K slice lies inside one filter tap and the padding value is zero. */
+		template<int BN, bool TMA_A>
 		struct Cfg
 		{
 				static constexpr int b_stage_bytes = BN * 128;
-				static constexpr int stage_bytes = A_STAGE_BYTES + b_stage_bytes;
-				static constexpr int stages = (BN == 256) ? 4 : 6;
-				static constexpr int lag = stages - 2; // gather slices in flight per producer thread
-				static constexpr int smem_bytes = stages * stage_bytes + 8 * EPI_WARP_BYTES + 1024;
+				// The two operand rings are sized separately: the gathered A slices (cp.async, many small requests) need more
+				// slices in flight to cover their latency than the weight slices that one TMA request fetches.
+				static constexpr int a_stages = TMA_A ? ((BN == 256) ? 4 : 6) : 6;
+				static constexpr int b_stages = TMA_A ? a_stages : ((BN == 256) ? 3 : 6);
+				static constexpr int smem_bytes = a_stages * A_STAGE_BYTES + b_stages * b_stage_bytes + 8 * EPI_WARP_BYTES + 1024;
 				static constexpr int tmem_columns = 2 * BN;
 		};
 
@@ -76,8 +87,10 @@ namespace mb200
 
 		struct ConvBarriers
 		{
-				uint64_t full[MAX_STAGES];
-				uint64_t empty[MAX_STAGES];
+				uint64_t full_a[MAX_STAGES];
+				uint64_t empty_a[MAX_STAGES];
+				uint64_t full_b[MAX_STAGES];
+				uint64_t empty_b[MAX_STAGES];
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
@@ -96,6 +109,15 @@ namespace mb200
 		__device__ __forceinline__ void cp_async_wait()
 		{
 			asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory");
+		}
+		__device__ __forceinline__ void cp_async_wait_all()
+		{
+			asm volatile("cp.async.wait_all;" ::: "memory");
+		}
+		/* One arrival on the mbarrier, delivered when all cp.async issued so far by this thread have completed. */
+		__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar)
+		{
+			asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(bar) : "memory");
 		}
 		__device__ __forceinline__ void st_shared_16(uint32_t dst, uint32_t v)
 		{
@@ -140,17 +162,49 @@ namespace mb200
 			return pk;
 		}
 
-		template<int KIND, int BN>
-		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w, const ConvParams p)
+		/* Everything but ReLU goes through one out-of-line call per element: the epilogue code stays small enough for the
+		 * instruction cache that the gather, the MMA issue and the epilogue share. */
+		__device__ __noinline__ float activation_out_of_line(float x, int act)
 		{
-			using C = Cfg<BN>;
+			return apply_activation(x, act);
+		}
+		__device__ __forceinline__ void activate32(float (&v)[32], int act)
+		{
+			if (act == ACTIVATION_RELU)
+			{
+#pragma unroll
+				for (int j = 0; j < 32; j++)
+					v[j] = fmaxf(v[j], 0.0f);
+			}
+			else if (act != ACTIVATION_LINEAR)
+			{
+#pragma unroll
+				for (int j = 0; j < 32; j++)
+					v[j] = activation_out_of_line(v[j], act);
+			}
+		}
+
+		__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n,
+				uint16_t off_w, uint16_t off_h)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+		}
+
+		template<int KIND, int BN, bool TMA_A>
+		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w,
+				const __grid_constant__ CUtensorMap map_x, const ConvParams p)
+		{
+			using C = Cfg<BN, TMA_A>;
 			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
 			constexpr int CHUNK_ELEMS = 16 / ES;
 			extern __shared__ uint8_t smem_raw[];
 			__shared__ ConvBarriers bars;
 
 			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-			const uint32_t epi_base = smem_base + C::stages * C::stage_bytes;
+			const uint32_t b_base = smem_base + C::a_stages * A_STAGE_BYTES;
+			const uint32_t epi_base = b_base + C::b_stages * C::b_stage_bytes;
 			const int warp = threadIdx.x / 32;
 			const int lane = threadIdx.x % 32;
 
@@ -161,10 +215,15 @@ namespace mb200
 
 			if (threadIdx.x == 0)
 			{
-				for (int s = 0; s < C::stages; s++)
+				for (int s = 0; s < C::a_stages; s++)
 				{
-					mbar_init(smem_u32(&bars.full[s]), NUM_PRODUCERS + 1);
-					mbar_init(smem_u32(&bars.empty[s]), 1);
+					mbar_init(smem_u32(&bars.full_a[s]), NUM_PRODUCERS);
+					mbar_init(smem_u32(&bars.empty_a[s]), 1);
+				}
+				for (int s = 0; s < C::b_stages; s++)
+				{
+					mbar_init(smem_u32(&bars.full_b[s]), 1);
+					mbar_init(smem_u32(&bars.empty_b[s]), 1);
 				}
 				for (int a = 0; a < 2; a++)
 				{
@@ -190,22 +249,36 @@ namespace mb200
 				if (elect_one())
 				{
 					prefetch_tensormap(&map_w);
+					if (TMA_A)
+						prefetch_tensormap(&map_x);
 					uint32_t it = 0;
 					bool ok = true;
 					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
 					{
 						const int nt = tile % n_tiles;
+						// first output position of the tile -> (image, row, column); im2col TMA walks on from there
+						const int m0 = (tile / n_tiles) * BM;
+						const int img0 = m0 / (p.height * p.width);
+						const int h0 = (m0 - img0 * p.height * p.width) / p.width;
+						const int w0 = m0 - img0 * p.height * p.width - h0 * p.width;
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
-							const int s = it % C::stages;
-							if (!mbar_wait(smem_u32(&bars.empty[s]), ((it / C::stages) & 1u) ^ 1u, abort_flag))
+							const int s = it % C::b_stages;
+							if (!mbar_wait(smem_u32(&bars.empty_b[s]), ((it / C::b_stages) & 1u) ^ 1u, abort_flag))
 							{
 								ok = false;
 								break;
 							}
-							const uint32_t full = smem_u32(&bars.full[s]);
-							mbar_arrive_expect_tx(full, C::b_stage_bytes);
-							tma_load_3d(smem_base + s * C::stage_bytes + A_STAGE_BYTES, &map_w, full, kb * (128 / ES), nt * BN, 0);
+							const uint32_t full = smem_u32(&bars.full_b[s]);
+							mbar_arrive_expect_tx(full, C::b_stage_bytes + (TMA_A ? A_STAGE_BYTES : 0));
+							if (TMA_A)
+							{
+								const int k0 = kb * (128 / ES);
+								const int tap = k0 / p.cin;
+								tma_load_im2col_4d(smem_base + s * A_STAGE_BYTES, &map_x, full, k0 - tap * p.cin, w0 - 1, h0 - 1, img0,
+										static_cast<uint16_t>(tap % 3), static_cast<uint16_t>(tap / 3));
+							}
+							tma_load_3d(b_base + s * C::b_stage_bytes, &map_w, full, kb * (128 / ES), nt * BN, 0);
 						}
 					}
 				}
@@ -227,20 +300,24 @@ namespace mb200
 						const uint32_t tmem_d = tmem_base + buf * BN;
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
-							const int s = it % C::stages;
-							if (!mbar_wait(smem_u32(&bars.full[s]), (it / C::stages) & 1u, abort_flag))
+							const int sa = it % C::a_stages, sb = it % C::b_stages;
+							if (!mbar_wait(smem_u32(&bars.full_b[sb]), (it / C::b_stages) & 1u, abort_flag)
+									|| (!TMA_A && !mbar_wait(smem_u32(&bars.full_a[sa]), (it / C::a_stages) & 1u, abort_flag)))
 							{
 								ok = false;
 								break;
 							}
 							tcgen05_fence_after();
-							const uint32_t addr_a = smem_base + s * C::stage_bytes;
-							const uint64_t desc_a = make_desc_k_sw128(addr_a);
-							const uint64_t desc_b = make_desc_k_sw128(addr_a + A_STAGE_BYTES);
+							if (!TMA_A)
+								fence_proxy_async_smem(); // the A slice was written through the generic proxy by other threads
+							const uint64_t desc_a = make_desc_k_sw128(smem_base + sa * A_STAGE_BYTES);
+							const uint64_t desc_b = make_desc_k_sw128(b_base + sb * C::b_stage_bytes);
 #pragma unroll
 							for (int k = 0; k < 4; k++)
 								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-							mma_commit(smem_u32(&bars.empty[s]));
+							if (!TMA_A)
+								mma_commit(smem_u32(&bars.empty_a[sa]));
+							mma_commit(smem_u32(&bars.empty_b[sb]));
 						}
 						if (ok)
 							mma_commit(smem_u32(&bars.tmem_full[buf]));
@@ -329,12 +406,7 @@ namespace mb200
 									add_half8(v + 8 * k, ld_shared_v4(sbuf + lane * EPI_PITCH + k * 16));
 								__syncwarp();
 							}
-							if (p.act != ACTIVATION_LINEAR)
-							{
-#pragma unroll
-								for (int j = 0; j < 32; j++)
-									v[j] = apply_activation(v[j], p.act);
-							}
+							activate32(v, p.act);
 #pragma unroll
 							for (int k = 0; k < 4; k++)
 								st_shared_v4(sbuf + lane * EPI_PITCH + k * 16, pack_half8(v + 8 * k));
@@ -377,9 +449,7 @@ namespace mb200
 									if (j < n_valid)
 										v[j] += __half2float(ep[j]);
 							}
-#pragma unroll
-							for (int j = 0; j < 32; j++)
-								v[j] = apply_activation(v[j], p.act);
+							activate32(v, p.act);
 							__half *dp = reinterpret_cast<__half*>(p.y) + off + n0;
 #pragma unroll
 							for (int j = 0; j < 32; j++)
@@ -418,11 +488,11 @@ namespace mb200
 									const int e = ext_vec ? static_cast<int>(static_cast<int8_t>((ext_words[j / 4] >> (8 * (j % 4))) & 0xFFu)) : static_cast<int>(ep[j]);
 									x += static_cast<float>(e) * p.ext_scale + p.ext_shift;
 								}
-								if (act_on)
-									x = apply_activation(x, p.act);
 							}
 							v[j] = x;
 						}
+						if (act_on)
+							activate32(v, p.act);
 						if (p.out_dtype == DTYPE_INT8)
 						{
 							int8_t *dp = reinterpret_cast<int8_t*>(p.y) + off + n0;
@@ -484,9 +554,11 @@ namespace mb200
 						mbar_arrive(smem_u32(&bars.tmem_empty[buf]));
 				}
 			}
-			else
+			else if (!TMA_A && (warp == 10 || warp == 11 || warp == 14 || warp == 15))
 			{ /* ------------------------------------------------------------ A-operand gather */
-				const int pt = threadIdx.x - PRODUCER_WARP0 * 32; // 0..127
+				// The gather warps sit on the two scheduler partitions (warp % 4 = 2, 3) that do not host the MMA-issuing
+				// warp, so their address arithmetic never delays a tcgen05.mma issue slot; warps 12 and 13 stay idle.
+				const int pt = ((warp < 12) ? (warp - 10) : (warp - 12)) * 32 + lane; // 0..127
 				const int j = pt % 8; // 16-byte chunk of the 128-byte K slice
 				const int g = pt / 8; // rows g, g + 16, g + 32, ...
 				const uint32_t row_byte = static_cast<uint32_t>(g) * 128 + static_cast<uint32_t>((j ^ (g & 7)) * 16);
@@ -494,41 +566,41 @@ namespace mb200
 				const uint32_t pad_word = static_cast<uint32_t>(p.pad_byte & 0xFF) * 0x01010101u;
 				const bool store_pad = (KIND == 1) && (p.pad_byte != 0);
 				const int hw = p.height * p.width;
-				constexpr int LAG = C::lag;
 				constexpr int ROWS = BM / 16; // rows per producer thread
 				uint32_t it = 0;
 				bool ok = true;
 				for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
 				{
 					const int mt = tile / n_tiles;
-					int pos_hw[ROWS]; // (h << 16) | w, or -1 for a row beyond M
+					uint32_t tap_mask[ROWS]; // bit t set: tap t of this row lies inside the image (0 for a row beyond M)
 					int pos_off[ROWS]; // element offset of the position's channel 0
 #pragma unroll
 					for (int i = 0; i < ROWS; i++)
 					{
 						const int m = mt * BM + g + 16 * i;
+						tap_mask[i] = 0;
+						pos_off[i] = 0;
 						if (m < p.M)
 						{
 							const int rem = m % hw;
 							const int h = rem / p.width;
-							pos_hw[i] = (h << 16) | (rem - h * p.width);
+							const int w = rem - h * p.width;
+							const uint32_t rows_ok = (h > 0 ? 1u : 0u) | 2u | (h + 1 < p.height ? 4u : 0u);
+							const uint32_t cols_ok = (w > 0 ? 1u : 0u) | 2u | (w + 1 < p.width ? 4u : 0u);
+							tap_mask[i] = ((rows_ok & 1u) ? cols_ok : 0u) | ((rows_ok & 2u) ? (cols_ok << 3) : 0u) | ((rows_ok & 4u) ? (cols_ok << 6) : 0u)
+									| (1u << 9); // bit 9: the row exists
 							pos_off[i] = m * p.cin;
-						}
-						else
-						{
-							pos_hw[i] = -1;
-							pos_off[i] = 0;
 						}
 					}
 					for (int kb = 0; kb < k_blocks; kb++, it++)
 					{
-						const int s = it % C::stages;
-						if (!mbar_wait(smem_u32(&bars.empty[s]), ((it / C::stages) & 1u) ^ 1u, abort_flag))
+						const int s = it % C::a_stages;
+						if (!mbar_wait(smem_u32(&bars.empty_a[s]), ((it / C::a_stages) & 1u) ^ 1u, abort_flag))
 						{
 							ok = false;
 							break;
 						}
-						const uint32_t dst0 = smem_base + s * C::stage_bytes + row_byte;
+						const uint32_t dst0 = smem_base + s * A_STAGE_BYTES + row_byte;
 						const int k0 = kb * (128 / ES) + j * CHUNK_ELEMS;
 						const bool k_ok = k0 < p.K;
 						const int tap = k_ok ? k0 / p.cin : 0;
@@ -538,34 +610,21 @@ namespace mb200
 #pragma unroll
 						for (int i = 0; i < ROWS; i++)
 						{
-							const int h = (pos_hw[i] >> 16) + dh, w = (pos_hw[i] & 0xFFFF) + dw;
-							const bool inside = k_ok && pos_hw[i] >= 0 && h >= 0 && h < p.height && w >= 0 && w < p.width;
+							const bool inside = k_ok && ((tap_mask[i] >> tap) & 1u);
 							const uint32_t dst = dst0 + i * 16 * 128;
-							if (inside)
-								cp_async_16(dst, xb + static_cast<long long>(pos_off[i] + delta) * ES, 16);
-							else if (store_pad && k_ok && pos_hw[i] >= 0)
+							if (store_pad && !inside && k_ok && (tap_mask[i] >> 9))
 								st_shared_16(dst, pad_word);
-							else
-								cp_async_16(dst, xb, 0); // zero fill
+							else // src-size 0 writes 16 zero bytes: padding outside the image, rows beyond M, K tail
+								cp_async_16(dst, inside ? xb + static_cast<long long>(pos_off[i] + delta) * ES : xb, inside ? 16u : 0u);
 						}
-						cp_async_commit();
-						if (it >= LAG)
-						{
-							cp_async_wait<LAG>();
-							fence_proxy_async_smem();
-							mbar_arrive(smem_u32(&bars.full[(it - LAG) % C::stages]));
-						}
+						if (store_pad)
+							fence_proxy_async_smem(); // the padding values were plain stores
+						// the barrier receives this thread's arrival when its copies above have landed; the thread itself
+						// moves on and fills the next free stage
+						cp_async_arrive_noinc(smem_u32(&bars.full_a[s]));
 					}
 				}
-				// drain: the last LAG slices that were issued but not yet published
-				cp_async_wait<0>();
-				fence_proxy_async_smem();
-				if (ok)
-				{
-					const uint32_t first = it >= LAG ? it - LAG : 0;
-					for (uint32_t t = first; t < it; t++)
-						mbar_arrive(smem_u32(&bars.full[t % C::stages]));
-				}
+				cp_async_wait_all(); // nothing of this thread may still be in flight when the CTA retires
 			}
 
 			/* ---------------------------------------------------------------- teardown */
@@ -584,21 +643,21 @@ namespace mb200
 			}
 		}
 
-		template<int KIND, int BN>
-		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const ConvParams &p)
+		template<int KIND, int BN, bool TMA_A>
+		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
-			using C = Cfg<BN>;
+			using C = Cfg<BN, TMA_A>;
 			static bool configured = false;
 			if (!configured)
 			{
-				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
 						"conv_igemm: shared memory opt-in"))
 					return false;
 				configured = true;
 			}
 			const int tiles = ((p.M + BM - 1) / BM) * ((p.cout + BN - 1) / BN);
 			const int grid = std::min(tiles, get(ctx)->sm_count);
-			kernel_conv3x3_igemm<KIND, BN> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, p);
+			kernel_conv3x3_igemm<KIND, BN, TMA_A> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
 			MB200_COUNT_LAUNCH();
 			get(ctx)->kernels_with_waits = true;
 			return check_cuda(ctx, cudaGetLastError(), "conv_igemm launch");
@@ -616,6 +675,55 @@ namespace mb200
 				return false;
 			if (x.dim[1] >= 32768 || x.dim[2] >= 32768)
 				return false;
+			return true;
+		}
+
+		/* im2col-mode tensor map over x [n, h, w, c]: one request delivers 128 consecutive output positions x 128 bytes of
+		 * channels for one filter tap, walking w, then h, then n, with zeros outside the image.  For a 3x3 filter with padding 1
+		 * the base pixel of output (p, q) is (q - 1, p - 1): lower corner -1, upper corner -1, tap offsets 0..2. */
+		bool encode_im2col_map(mlContext_t ctx, CUtensorMap *map, int kind, const mlTensor_t &x)
+		{
+			typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+					const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+					CUtensorMapFloatOOBfill);
+			static encode_fn fn = []() -> encode_fn
+			{
+				void *ptr = nullptr;
+				cudaDriverEntryPointQueryResult result;
+				if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &ptr, cudaEnableDefault, &result) != cudaSuccess || ptr == nullptr)
+				{
+					cudaGetLastError();
+					return nullptr;
+				}
+				return reinterpret_cast<encode_fn>(ptr);
+			}();
+			if (fn == nullptr)
+			{
+				record_error(ctx, "cuTensorMapEncodeIm2col is not available from the driver");
+				return false;
+			}
+			const int es = (kind == 0) ? 2 : 1;
+			const cuuint64_t dims[4] = { static_cast<cuuint64_t>(x.dim[3]), static_cast<cuuint64_t>(x.dim[2]), static_cast<cuuint64_t>(x.dim[1]),
+					static_cast<cuuint64_t>(x.dim[0]) };
+			const cuuint64_t strides[3] = { static_cast<cuuint64_t>(x.dim[3]) * es, static_cast<cuuint64_t>(x.dim[3]) * es * x.dim[2],
+					static_cast<cuuint64_t>(x.dim[3]) * es * x.dim[2] * x.dim[1] };
+			const int lower[2] = { -1, -1 };
+			const int upper[2] = { -1, -1 };
+			const cuuint32_t traversal[4] = { 1, 1, 1, 1 };
+			const CUresult status = fn(map, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x.data, dims, strides,
+					lower, upper, static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(BM), traversal, CU_TENSOR_MAP_INTERLEAVE_NONE,
+					CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+			if (status != CUDA_SUCCESS)
+			{
+				record_error(ctx, "cuTensorMapEncodeIm2col failed with code %d", static_cast<int>(status));
+				return false;
+			}
+			// Drivers up to CUDA 13.1 encode im2col maps of tensors smaller than 128 KiB with a flag (bit 21 of the second
+			// descriptor word) that must be cleared -- the same adjustment CUTLASS applies after this call.
+			int driver_version = 0;
+			if (cudaDriverGetVersion(&driver_version) == cudaSuccess && driver_version <= 13010
+					&& volume(x) * es < 131072)
+				reinterpret_cast<uint64_t*>(map)[1] &= ~(1ull << 21);
 			return true;
 		}
 
@@ -639,9 +747,22 @@ namespace mb200
 			if (!encode_tensor_map(ctx, &map_w, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box,
 					CU_TENSOR_MAP_SWIZZLE_128B))
 				return false;
+			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
+			const char *force_gather = std::getenv("MINML_B200_CONV_GATHER");
+			const bool tma_a = (p.cin * es) % 128 == 0 && p.pad_byte == 0 && !(force_gather != nullptr && force_gather[0] == '1');
+			CUtensorMap map_x;
+			std::memset(&map_x, 0, sizeof(map_x));
+			if (tma_a && !encode_im2col_map(ctx, &map_x, kind, x))
+				return false;
 			if (kind == 0)
-				return bn == 256 ? launch<0, 256>(ctx, map_w, p) : launch<0, 128>(ctx, map_w, p);
-			return bn == 256 ? launch<1, 256>(ctx, map_w, p) : launch<1, 128>(ctx, map_w, p);
+			{
+				if (tma_a)
+					return bn == 256 ? launch<0, 256, true>(ctx, map_w, map_x, p) : launch<0, 128, true>(ctx, map_w, map_x, p);
+				return bn == 256 ? launch<0, 256, false>(ctx, map_w, map_x, p) : launch<0, 128, false>(ctx, map_w, map_x, p);
+			}
+			if (tma_a)
+				return bn == 256 ? launch<1, 256, true>(ctx, map_w, map_x, p) : launch<1, 128, true>(ctx, map_w, map_x, p);
+			return bn == 256 ? launch<1, 256, false>(ctx, map_w, map_x, p) : launch<1, 128, false>(ctx, map_w, map_x, p);
 		}
 	}
 

@@ -61,7 +61,8 @@ def test_transforms_against_oracle(ctx, oracle, dtype, tile, k, shape):
             assert max_rel_err(got, want) <= FP16_REL, what
 
     v = torch.full((p * p, tiles, cin), float("nan"), device="cuda", dtype=dtype)
-    B.winogradInputTransform(ctx, wt.shape, dev(x, dtype), v, tile_size=tile)
+    xd = dev(x, dtype)  # stays alive until the synchronize below: the backend may defer the transform (see fusion.cu)
+    B.winogradInputTransform(ctx, wt.shape, xd, v, tile_size=tile)
     u = torch.full((p * p, cout, cin), float("nan"), device="cuda", dtype=dtype)
     B.winogradWeightTransform(ctx, dev(wt, dtype), u, tile_size=tile)
     ctx.synchronize()
