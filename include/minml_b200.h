@@ -243,6 +243,20 @@ void mb200_set_fusion(mlContext_t context, int enabled);
 /* Library build identification: "minml_b200 <version> sm_100a". */
 const char *mb200_version(void);
 
+/* No counterpart in the reference.
+ * y = act(conv3x3(x, w) + bias + add) by F(4x4,3x3) Winograd, for callers that must never allocate device memory: a
+ * program that gave the whole GPU to its own arena at start-up, or one that cannot take the device-wide synchronisation
+ * of cudaMalloc / cudaFree in its serving loop.  Same arguments and result as cuda_convolution_implicit_gemm_forward
+ * (fp16 or fp32, 3x3 weights [cout, 3, 3, cin]); the transformed weights, transformed input and products live in a fixed
+ * MB200_NOALLOC_SCRATCH_BYTES array inside the library image (held by every GPU that loads the library until the process
+ * exits) instead of the context workspace.  A problem needing more than that (36 * elem * (cout*cin + tiles*cin + tiles*cout),
+ * tiles = b * ceil(h/4) * ceil(w/4)) is refused with an error on the context.  The call performs no cudaMalloc / cudaFree.
+ * All calls on a device share the array: calls on one context are ordered by its stream, calls that overlap on the GPU
+ * (different contexts) race.  The first call on each device resolves the array's device address; issue it before any
+ * stream capture begins. */
+#define MB200_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
+void mb200_convolution_forward_noalloc(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, mlShape_t weights_shape, const void *input, const void *weights, void *output, const void *bias, const void *add, mlActivationType_t act);
+
 #ifdef __cplusplus
 }
 #endif
