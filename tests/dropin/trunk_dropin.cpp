@@ -23,6 +23,10 @@
 #include <minml/utils/json.hpp>
 #include <minml/utils/serialization.hpp>
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -32,6 +36,21 @@
 #include <vector>
 
 using namespace ml;
+
+static void on_crash(int sig)
+{ // a crash in host code prints where it happened (function names only) instead of dying silently
+	void *frames[64];
+	const int n = backtrace(frames, 64);
+	const char msg[] = "trunk_dropin: fatal signal, backtrace follows\n";
+	(void) !write(2, msg, sizeof(msg) - 1);
+	backtrace_symbols_fd(frames, n, 2);
+	_exit(128 + sig);
+}
+static void stage(const char *what)
+{
+	if (std::getenv("DROPIN_VERBOSE") != nullptr)
+		std::fprintf(stderr, "[trunk_dropin] %s\n", what);
+}
 
 static void build(Graph &g, int batch, int h, int w, int planes, int channels, int blocks)
 {
@@ -54,20 +73,20 @@ static void build(Graph &g, int batch, int h, int w, int planes, int channels, i
 static std::vector<float> to_host_fp32(Graph &g, int index)
 {
 	Tensor out = g.getOutput(index); // a view sharing the data
-	Tensor host(out.shape(), DataType::FLOAT32, Device::cpu());
 	Tensor tmp(out.shape(), out.dtype(), Device::cpu());
 	tmp.copyFrom(g.context(), out);
 	g.context().synchronize();
 	Context cpu_ctx;
-	host.copyFrom(cpu_ctx, tmp);
-	host.convertTo(cpu_ctx, DataType::FLOAT32);
-	std::vector<float> result(host.volume());
-	std::memcpy(result.data(), host.data(), sizeof(float) * result.size());
+	tmp.convertTo(cpu_ctx, DataType::FLOAT32);
+	std::vector<float> result(tmp.volume());
+	std::memcpy(result.data(), tmp.data(), sizeof(float) * result.size());
 	return result;
 }
 
 int main(int argc, char *argv[])
 {
+	signal(SIGSEGV, on_crash);
+	signal(SIGABRT, on_crash);
 	if (argc < 8)
 	{
 		std::fprintf(stderr, "usage: %s batch height width planes channels blocks fp16|fp32 [repeats]\n", argv[0]);
@@ -77,28 +96,33 @@ int main(int argc, char *argv[])
 	const int channels = std::atoi(argv[5]), blocks = std::atoi(argv[6]);
 	const bool fp16 = std::strcmp(argv[7], "fp16") == 0;
 	const int repeats = argc > 8 ? std::atoi(argv[8]) : 0;
-	if (Device::numberOfCudaDevices() == 0)
-	{
-		std::printf("{\"error\": \"no CUDA device visible to the backend\"}\n");
-		return 3;
-	}
-
+	stage("build cpu graph");
 	Graph cpu_graph;
 	build(cpu_graph, batch, h, w, planes, channels, blocks);
-	cpu_graph.makeTrainable(false);
-	FoldAdd().optimize(cpu_graph);
+	cpu_graph.makeTrainable(false); // Graph::save of a trainable graph wants an optimizer
 
-	// the same parameters for the second graph, through minml's own serialisation
+	// the same parameters for the second graph, through minml's own serialisation (before the Add layers are folded away)
+	stage("save / load");
 	SerializedObject binary;
 	const Json description = cpu_graph.save(binary);
 	Graph gpu_graph;
 	gpu_graph.load(description, binary);
 	gpu_graph.makeTrainable(false);
+	FoldAdd().optimize(cpu_graph);
+	FoldAdd().optimize(gpu_graph);
+	if (Device::numberOfCudaDevices() == 0)
+	{
+		std::printf("{\"error\": \"no CUDA device visible to the backend\"}\n");
+		return 3;
+	}
+	stage("moveTo cuda");
 	gpu_graph.moveTo(Device::cuda(0));
+	stage("moved");
 	if (fp16)
 		gpu_graph.convertTo(DataType::FLOAT16);
 
 	// Bernoulli(0.3) input planes
+	stage("inputs");
 	std::mt19937 rng(1234);
 	std::vector<float> input(static_cast<size_t>(batch) * h * w * planes);
 	for (float &v : input)
@@ -115,10 +139,13 @@ int main(int argc, char *argv[])
 		gpu_graph.getInput().copyFrom(gpu_graph.context(), staged);
 	}
 
+	stage("predict cpu");
 	cpu_graph.predict(batch);
 	cpu_graph.context().synchronize();
+	stage("predict cuda");
 	gpu_graph.predict(batch);
 	gpu_graph.context().synchronize();
+	stage("predicted");
 
 	double seconds = 0.0;
 	if (repeats > 0)
