@@ -34,3 +34,48 @@ def test_reference_graph_fp16(cfg, fusion):
 def test_reference_graph_fp32():
     r = run(2, 15, 15, 32, 64, 2, "fp32")
     assert r["policy_rel_err"] <= 1e-4 and r["value_rel_err"] <= 1e-4
+
+
+# ------------------------------------------------------------------------------------------- the reference's own test suite
+TESTS_BINARY = os.path.join(os.path.dirname(BINARY), "minml_tests")
+
+# tests of the reference whose device half exercises the inference path of this backend: all of them must pass
+IN_SCOPE = """
+TestConv2D.explicit_gemm_conv2D_1x1_forward_fp32 TestConv2D.explicit_gemm_conv2D_5x5_forward_fp32 TestConv2D.winograd_conv2D_3x3_forward
+TestConv2D.winograd_conv2D_5x5_forward TestConv2D.im2row3x3 TestConv2D.im2row3x3_invert TestConv2D.im2row5x5 TestConv2D.im2row5x5_invert
+TestGemm.float32_NN TestGemm.float32_NT TestGemm.float32_TN TestGemm.float32_TT TestGemm.float16_NN TestGemm.float16_NT TestGemm.float16_TN
+TestGemm.float16_TT TestGemmEx.float32_NT TestGemmEx.float16_NT TestGlobalAveragePooling.forward_fp32 TestGlobalAveragePooling.forward_fp16
+TestSoftmax.ForwardOnCUDA_fp32 TestSoftmax.ForwardOnCUDA_fp16 TestLayerNorm.forward TestQuantization.conv2D_1x1_forward
+TestTensorOp.setall_cuda TestTensorOp.addBiasAct_fp32 TestTensorOp.addBiasAct_fp16 TestTensorOp.addTensors
+TestWinograd3x3_4x4.cudaInputTransform TestWinograd3x3_4x4.cudaOutputTransform TestWinograd3x3_4x4.cudaWeightTransform
+TestWinograd5x5_2x2.cudaInputTransform TestWinograd5x5_2x2.cudaOutputTransform TestWinograd5x5_2x2.cudaWeightTransform
+TestWinograd3x3_4x4.cudaInputTransform_fp16 TestWinograd3x3_4x4.cudaOutputTransform_fp16 TestWinograd3x3_4x4.cudaWeightTransform_fp16
+TestWinograd5x5_2x2.cudaInputTransform_fp16 TestWinograd5x5_2x2.cudaOutputTransform_fp16 TestWinograd5x5_2x2.cudaWeightTransform_fp16
+""".split()
+
+# tests that call entry points this backend exports as stubs (training, pooling / scaling variants, batch and RMS norm,
+# depthwise convolution, window and transpose operations, gradient / update transforms), plus one test that fails on the
+# reference's own CPU backend as well (TestMultiHeadAttention.forward passes the bias table in the wrong argument)
+OUT_OF_SCOPE_PREFIXES = (
+    "TestMultiHeadAttention.forward", "TestConv2D.explicit_gemm_conv2D_1x1_backward", "TestConv2D.explicit_gemm_conv2D_5x5_backward",
+    "TestConv2D.winograd_conv2D_3x3_backward", "TestConv2D.winograd_conv2D_3x3_update", "TestConv2D.winograd_conv2D_5x5_backward",
+    "TestConv2D.winograd_conv2D_5x5_update", "TestSpaceToDepth.", "TestDepthToSpace.", "TestGlobalAveragePooling.backward", "TestChannelScaling.",
+    "TestChannelAveragePooling.", "TestSpatialScaling.", "TestBatchNorm.", "TestLayerNorm.backward", "TestRMSNorm.",
+    "TestQuantization.depthwise_conv2D_forward", "TestTensorOp.sumOverFirstDim", "TestTensorOp.window_", "TestTensorOp.transpose",
+    "TestWinograd3x3_4x4.cudaGradientTransform", "TestWinograd3x3_4x4.cudaUpdateTransform", "TestWinograd5x5_2x2.cudaGradientTransform",
+    "TestWinograd5x5_2x2.cudaUpdateTransform",
+)
+
+
+def test_reference_test_suite_against_this_backend():
+    """test/backend/*.cpp of the reference, compiled unchanged (against a stand-in gtest header), with this library as the CUDA backend."""
+    if not os.path.exists(TESTS_BINARY):
+        pytest.skip("oracle/_ref/minml_tests not built (needs the reference checkout: make -C oracle reftests)")
+    out = subprocess.run([TESTS_BINARY], capture_output=True, text=True, timeout=900)
+    lines = out.stdout.strip().splitlines()
+    summary = json.loads(lines[-1])
+    passed = {l.split("]", 1)[1].strip() for l in lines if l.startswith("[ OK")}
+    missing = [t for t in IN_SCOPE if t not in passed]
+    assert missing == [], "in-scope reference tests that did not pass: %s" % missing
+    unexpected = [t for t in summary["failed_tests"] if not t.startswith(OUT_OF_SCOPE_PREFIXES)]
+    assert unexpected == [], "reference tests failed outside the stubbed set: %s" % unexpected
