@@ -1,0 +1,170 @@
+"""Per-kernel timing of every hot entry point of the backend at the sizes of the benchmark configurations.
+
+    python -m minml_b200.kernel_bench [--config c3|c1|c2|c4] [--reps N] [--only substring]
+
+Each entry point is timed alone with CUDA events on the context's stream (3 warm-up calls, N timed calls).  For every kernel
+the line gives the time, the algorithmic bytes (each input read once, each output written once) and FLOPs of one call, and
+the achieved GB/s and TFLOP/s as fractions of the measured peaks (MEASURED_PEAKS.json at the repository root, else the
+fallback figures 6650 GB/s and 1590 TFLOP/s).  Working sets are the real activation sizes of the configuration, which for
+c3 exceed the L2 cache; smaller configurations are noted as L2-resident in the output.
+"""
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import backend as B
+from . import layers as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SIZES = {
+    "c3": dict(batch=1024, h=20, w=20, c=256, planes=32),
+    "c1": dict(batch=256, h=15, w=15, c=128, planes=32),
+    "c2": dict(batch=512, h=20, w=20, c=128, planes=32),
+    "c4": dict(batch=256, h=15, w=15, c=256, planes=32),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(ctx, fn, reps):
+    for _ in range(3):
+        fn()
+    ctx.synchronize()
+    e0 = B.lib.cuda_create_event(ctx.handle)
+    for _ in range(reps):
+        fn()
+    e1 = B.lib.cuda_create_event(ctx.handle)
+    ctx.synchronize()
+    sec = B.lib.cuda_get_time_between_events(e0, e1) / reps
+    B.lib.cuda_destroy_event(e0)
+    B.lib.cuda_destroy_event(e1)
+    return sec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="c3", choices=sorted(SIZES))
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    s = SIZES[args.config]
+    b, h, w, c, planes = s["batch"], s["h"], s["w"], s["c"], s["planes"]
+    hbm, tflops, source = peaks()
+    ctx = B.Context(0)
+    rng = np.random.default_rng(0)
+    f16 = torch.float16
+    act_bytes = b * h * w * c * 2
+    tiles = b * ((h + 3) // 4) * ((w + 3) // 4)
+
+    def rand(*shape, dtype=f16):
+        return (torch.randn(shape, device="cuda") * 0.5).to(dtype)
+
+    x, res, y = rand(b, h, w, c), rand(b, h, w, c), torch.empty((b, h, w, c), device="cuda", dtype=f16)
+    wt = (rng.standard_normal((c, 3, 3, c)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    conv = L.Conv2D(ctx, wt, np.zeros(c, np.float32), "relu", f16)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    v = ws.view((36, tiles, c), f16)
+    m = ws.view((36, tiles, c), f16, 36 * tiles * c * 2)
+    mat_bytes = 36 * tiles * c * 2
+    bias = rand(c)
+    rows = b * h * w
+    results = []
+
+    def add(name, fn, nbytes, flops=0.0, note=""):
+        if args.only and args.only not in name:
+            return
+        sec = timed(ctx, fn, args.reps)
+        rec = {"kernel": name, "config": args.config, "ms": sec * 1e3, "algorithmic_MB": nbytes / 1e6, "GB/s": nbytes / sec / 1e9,
+               "hbm_frac": nbytes / sec / 1e9 / hbm, "peaks": source}
+        if flops:
+            rec["TFLOP/s"] = flops / sec / 1e12
+            rec["tensor_frac"] = flops / sec / 1e12 / tflops
+        if note:
+            rec["note"] = note
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    # ---- the fused 3x3 layer (one kernel for the recognised call triple) and its three-kernel equivalent
+    ctx.set_fusion(True)
+    add("conv3x3 fused (fp16, bias+residual+relu)", lambda: conv.forward([x, res], y, ws), 3 * act_bytes + 9 * c * c * 2,
+        2.0 * rows * 9 * c * c)
+    ctx.set_fusion(False)
+    conv.forward([x, res], y, ws)
+    add("winograd_input_transform", lambda: B.winogradInputTransform(ctx, wt.shape, x, v, 4), act_bytes + mat_bytes)
+    add("gemm_batched 36 x [tiles,c] x [c,c]^T", lambda: B.gemmBatched(ctx, "n", v, "t", conv.transformed, m), 2 * mat_bytes + 36 * c * c * 2,
+        2.0 * 36 * tiles * c * c)
+    add("winograd_output_transform (+bias+residual+relu)", lambda: B.winogradOutputTransform(ctx, wt.shape, m, y, conv.bias, res, "relu", 4),
+        mat_bytes + 2 * act_bytes)
+    add("winograd_weight_transform", lambda: B.winogradWeightTransform(ctx, conv.weights, conv.transformed, False, 4), (9 + 36) * c * c * 2)
+    ctx.set_fusion(True)
+
+    # ---- heads: 1x1 policy convolution (N = 1), global average pooling, dense value head (N = 3)
+    wp = rand(1, c)
+    pol = torch.empty((rows, 1), device="cuda", dtype=f16)
+    add("gemm_ex 1x1 policy head [rows,c] x [1,c]^T", lambda: B.gemm_ex(ctx, pol, 1.0, "n", x.view(rows, c), "t", wp, 0.0, None, rand(1), "linear"),
+        act_bytes + rows * 2, 2.0 * rows * c)
+    pooled = torch.empty((b, c), device="cuda", dtype=f16)
+    add("global_average_pooling", lambda: B.globalAveragePoolingForward(ctx, x, pooled), act_bytes + b * c * 2)
+    wv = rand(3, c)
+    val = torch.empty((b, 3), device="cuda", dtype=f16)
+    add("gemm_ex dense value head [b,c] x [3,c]^T", lambda: B.gemm_ex(ctx, val, 1.0, "n", pooled, "t", wv, 0.0, None, rand(3), "linear"),
+        b * c * 2 + b * 6, 2.0 * b * c * 3, note="launch-latency bound at this size")
+
+    # ---- elementwise / layout
+    packed = torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
+    x0 = torch.empty((b, h, w, planes), device="cuda", dtype=f16)
+    add("unpack_input (32 planes)", lambda: B.unpackInput(ctx, packed, x0), rows * 4 + rows * planes * 2)
+    add("add_bias_act (relu)", lambda: B.addBiasAct(ctx, x, bias, y, "relu"), 2 * act_bytes)
+    add("activation_forward (relu)", lambda: B.activationForward(ctx, x, y, "relu"), 2 * act_bytes)
+    add("add_tensors (y = x1 + x2)", lambda: B.addTensors(ctx, y, 1.0, x, 1.0, res), 3 * act_bytes)
+    xf = torch.empty((b, h, w, c), device="cuda", dtype=torch.float32)
+    add("convert_type fp16 -> fp32", lambda: B.convertType(ctx, xf, x), act_bytes * 3)
+    gamma, beta = rand(c), rand(c)
+    add("layernorm_forward", lambda: B.layernormForward(ctx, x, y, gamma, beta), 2 * act_bytes)
+    add("softmax_forward (rows of c)", lambda: B.softmaxForward(ctx, x.view(rows, c), y.view(rows, c)), 2 * act_bytes)
+
+    # ---- int8: fused convolution and the eager steps
+    xq = torch.randint(-128, 128, (b, h, w, c), device="cuda", dtype=torch.int8)
+    extq = torch.randint(-128, 128, (b, h, w, c), device="cuda", dtype=torch.int8)
+    yq = torch.empty((b, h, w, c), device="cuda", dtype=torch.int8)
+    qw = rng.integers(-127, 128, (c, 3, 3, c), dtype=np.int8)
+    qconv = L.QuantizedConv2D(ctx, qw, np.full(c, 1e-4, np.float32), np.zeros(c, np.float32), (0.02, 0.0), (0.05, 0.0), "relu", torch.int8)
+    qws = L.Workspace()
+    qws.reserve(qconv.workspace_bytes(xq.shape))
+    add("conv3x3 fused (int8, requantise+residual+relu)", lambda: qconv.forward([xq, extq], yq, qws, (0.03, 0.0)), 3 * rows * c + 9 * c * c,
+        2.0 * rows * 9 * c * c, note="tensor_frac is against the bf16 peak; the int8 peak is twice that")
+    ctx.set_fusion(False)
+    acc = qws.view((rows, c), torch.int32)
+    rows_i8 = qws.view((rows, 9 * c), torch.int8, rows * c * 4)
+    add("im2row int8 3x3", lambda: B.im2row(ctx, xq, rows_i8, 3, False, np.int8(0)), rows * c + rows * 9 * c)
+    add("gemm int8 [rows,9c] x [c,9c]^T -> int32", lambda: B.gemm(ctx, "n", rows_i8, "t", qconv.weights.view(c, 9 * c), acc),
+        rows * 9 * c + rows * c * 4 + 9 * c * c, 2.0 * rows * 9 * c * c)
+    add("quantized_scale_shift_act -> int8", lambda: B.quantized_scale_shift_act(ctx, yq, (0.05, 0.0), acc, qconv.channel_scales, qconv.bias, "relu",
+                                                                                 extq, (0.03, 0.0)), rows * c * 4 + 2 * rows * c)
+    ctx.set_fusion(True)
+
+    # ---- attention (config 4 geometry: 8 heads of c / 8)
+    heads = 8
+    qkv = rand(b, h, w, 3 * c)
+    n = 2 * max(h, w) - 1
+    table = rand(heads, n, (n + 3) // 4 * 4)
+    att = torch.empty((b, h, w, c), device="cuda", dtype=f16)
+    t = h * w
+    add("multi_head_attention_forward (8 heads, rel-pos bias)", lambda: B.multiHeadAttentionForward(ctx, qkv, att, table, heads), 4 * act_bytes,
+        4.0 * b * heads * t * t * (c // heads))
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()
