@@ -81,6 +81,7 @@ namespace mb200
 				const float *scales; // int8 kind
 				const float *shifts;
 				float ext_scale, ext_shift, out_scale, out_shift;
+				float inv_out_scale, inv_out_shift; // 1 / out_scale and -out_shift / out_scale, rounded like AffineTransform::get_inverse
 				int pad_byte;
 				int *status;
 		};
@@ -424,7 +425,57 @@ namespace mb200
 							continue;
 						}
 
-						/* general path: one row per lane, any alignment, column tails, and the int8 kinds */
+						if (KIND == 1 && p.out_dtype == DTYPE_INT8 && n_valid == 32 && (p.cout % 16) == 0 && aligned_to_16(p.y) && aligned_to_16(p.scales)
+								&& aligned_to_16(p.shifts) && (p.ext == nullptr || aligned_to_16(p.ext)))
+						{ /* int8 -> int8 fast path.  The arithmetic is the scalar loop of the reference's CPU backend, operation for
+						   * operation and without fused multiply-adds: x = acc * scale[c] + shift[c] (+ ext * s_e + z_e); activation;
+						   * q = clamp(round(x * (1 / s_o) + (-z_o / s_o)))  (src/layers/Conv2D.cpp:283-304, src/layers/quantization.cpp:43-47) */
+							if (!row_ok)
+								continue;
+							const float4 *sp = reinterpret_cast<const float4*>(p.scales + n0);
+							const float4 *hp = reinterpret_cast<const float4*>(p.shifts + n0);
+							uint32_t ext_words[8];
+							if (p.ext != nullptr)
+							{
+								const uint4 *ep = reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(p.ext) + off + n0);
+								const uint4 e0 = ep[0], e1 = ep[1];
+								ext_words[0] = e0.x; ext_words[1] = e0.y; ext_words[2] = e0.z; ext_words[3] = e0.w;
+								ext_words[4] = e1.x; ext_words[5] = e1.y; ext_words[6] = e1.z; ext_words[7] = e1.w;
+							}
+							const bool relu = p.act == ACTIVATION_RELU;
+							const bool other_act = p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH;
+							uint32_t packed[8];
+#pragma unroll
+							for (int g4 = 0; g4 < 8; g4++)
+							{
+								const float4 sc = sp[g4], sh = hp[g4];
+								const float scs[4] = { sc.x, sc.y, sc.z, sc.w }, shs[4] = { sh.x, sh.y, sh.z, sh.w };
+								uint32_t w4 = 0;
+#pragma unroll
+								for (int t = 0; t < 4; t++)
+								{
+									float x = __fadd_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[4 * g4 + t])), scs[t]), shs[t]);
+									if (p.ext != nullptr)
+									{
+										const int e = static_cast<int>(static_cast<int8_t>((ext_words[g4] >> (8 * t)) & 0xFFu));
+										x = __fadd_rn(x, __fadd_rn(__fmul_rn(static_cast<float>(e), p.ext_scale), p.ext_shift));
+									}
+									if (relu)
+										x = fmaxf(x, 0.0f);
+									else if (other_act)
+										x = activation_out_of_line(x, p.act);
+									const float qf = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(x, p.inv_out_scale), p.inv_out_shift))));
+									w4 |= (static_cast<uint32_t>(static_cast<int>(qf)) & 0xFFu) << (8 * t);
+								}
+								packed[g4] = w4;
+							}
+							int8_t *dp = reinterpret_cast<int8_t*>(p.y) + off + n0;
+							*reinterpret_cast<uint4*>(dp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+							*reinterpret_cast<uint4*>(dp + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+							continue;
+						}
+
+						/* general path: one row per lane, any alignment, column tails, and the other int8 output kinds */
 						if (!row_ok)
 							continue;
 						float v[32];
@@ -851,6 +902,8 @@ namespace mb200
 		p.ext_shift = ext_qd.shift;
 		p.out_scale = output_qd.scale;
 		p.out_shift = output_qd.shift;
+		p.inv_out_scale = 1.0f / output_qd.scale;
+		p.inv_out_shift = -output_qd.shift / output_qd.scale;
 		p.pad_byte = c->pending_i8.pad;
 		c->pending_i8.stage = 0;
 		return run(ctx, 1, x, c->pending_i8.w.data, cout, p);

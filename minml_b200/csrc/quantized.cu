@@ -30,22 +30,69 @@ namespace mb200
 			*p = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, roundf((x - shift) / scale))));
 		}
 
-		template<typename T>
+		/* One thread requantises VEC consecutive channels of one row (VEC = 4: 16-byte accumulator and scale loads). */
+		template<typename T, int VEC>
 		__global__ void __launch_bounds__(256) kernel_scale_shift_act(T *__restrict__ output, const int *__restrict__ input,
 				const float *__restrict__ scales, const float *__restrict__ bias, const int8_t *__restrict__ ext, long long rows, int channels,
 				int act, float out_scale, float out_shift, float ext_scale, float ext_shift)
 		{
-			const long long total = rows * channels;
+			const long long total = rows * channels / VEC;
 			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			const bool act_on = (act == ACTIVATION_SIGMOID || act == ACTIVATION_TANH || act == ACTIVATION_RELU);
 			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
 			{
-				const int c = static_cast<int>(i % channels);
-				float x = static_cast<float>(input[i]) * scales[c] + bias[c];
-				if (ext != nullptr)
-					x += static_cast<float>(ext[i]) * ext_scale + ext_shift;
-				if (act == ACTIVATION_SIGMOID || act == ACTIVATION_TANH || act == ACTIVATION_RELU)
-					x = apply_activation(x, act);
-				store_value<T>(output + i, x, 0.0f, out_scale, out_shift);
+				const long long e = i * VEC;
+				const int c = static_cast<int>(e % channels);
+				int acc[VEC];
+				float sc[VEC], sh[VEC];
+				int ex[VEC];
+				if (VEC == 4)
+				{
+					const int4 a = *reinterpret_cast<const int4*>(input + e);
+					acc[0] = a.x; acc[1 % VEC] = a.y; acc[2 % VEC] = a.z; acc[3 % VEC] = a.w;
+					const float4 s4 = *reinterpret_cast<const float4*>(scales + c), b4 = *reinterpret_cast<const float4*>(bias + c);
+					sc[0] = s4.x; sc[1 % VEC] = s4.y; sc[2 % VEC] = s4.z; sc[3 % VEC] = s4.w;
+					sh[0] = b4.x; sh[1 % VEC] = b4.y; sh[2 % VEC] = b4.z; sh[3 % VEC] = b4.w;
+					if (ext != nullptr)
+					{
+						const uint32_t w4 = *reinterpret_cast<const uint32_t*>(ext + e);
+#pragma unroll
+						for (int k = 0; k < VEC; k++)
+							ex[k] = static_cast<int>(static_cast<int8_t>((w4 >> (8 * k)) & 0xFFu));
+					}
+				}
+				else
+				{
+					acc[0] = input[e];
+					sc[0] = scales[c];
+					sh[0] = bias[c];
+					if (ext != nullptr)
+						ex[0] = ext[e];
+				}
+				float x[VEC];
+#pragma unroll
+				for (int k = 0; k < VEC; k++)
+				{
+					x[k] = static_cast<float>(acc[k]) * sc[k] + sh[k];
+					if (ext != nullptr)
+						x[k] += static_cast<float>(ex[k]) * ext_scale + ext_shift;
+					if (act_on)
+						x[k] = apply_activation(x[k], act);
+				}
+				if (VEC == 4 && sizeof(T) == 1)
+				{
+					uint32_t w4 = 0;
+#pragma unroll
+					for (int k = 0; k < VEC; k++)
+						w4 |= (static_cast<uint32_t>(static_cast<int>(fmaxf(-128.0f, fminf(127.0f, roundf((x[k] - out_shift) / out_scale))))) & 0xFFu) << (8 * k);
+					*reinterpret_cast<uint32_t*>(output + e) = w4;
+				}
+				else
+				{
+#pragma unroll
+					for (int k = 0; k < VEC; k++)
+						store_value<T>(output + e + k, x[k], 0.0f, out_scale, out_shift);
+				}
 			}
 		}
 
@@ -127,29 +174,35 @@ extern "C"
 		if (rows == 0 || channels == 0)
 			return;
 		cudaStream_t stream = use_stream(context);
-		const int grid = static_cast<int>(std::min<long long>((rows * channels + 255) / 256, static_cast<long long>(get(context)->sm_count) * 16));
+		const bool vec4 = channels % 4 == 0 && aligned_to(input, 16) && aligned_to(scales, 16) && aligned_to(bias, 16) && aligned_to(output, 16)
+				&& (ext == nullptr || aligned_to(ext, 4));
+		const int grid = static_cast<int>(std::min<long long>((rows * channels / (vec4 ? 4 : 1) + 255) / 256,
+				static_cast<long long>(get(context)->sm_count) * 16));
+#define LAUNCH_SSA(T) do { if (vec4) kernel_scale_shift_act<T, 4> <<<grid, 256, 0, stream>>>(ARGS(T)); \
+		else kernel_scale_shift_act<T, 1> <<<grid, 256, 0, stream>>>(ARGS(T)); } while (0)
 #define ARGS(T) reinterpret_cast<T*>(output), reinterpret_cast<const int*>(input), reinterpret_cast<const float*>(scales), \
 		reinterpret_cast<const float*>(bias), reinterpret_cast<const int8_t*>(ext), rows, channels, static_cast<int>(act), \
 		output_qd.scale, output_qd.shift, ext_qd.scale, ext_qd.shift
 		switch (dtype)
 		{
 			case DTYPE_FLOAT16:
-				kernel_scale_shift_act<__half> <<<grid, 256, 0, stream>>>(ARGS(__half));
+				LAUNCH_SSA(__half);
 				break;
 			case DTYPE_FLOAT32:
-				kernel_scale_shift_act<float> <<<grid, 256, 0, stream>>>(ARGS(float));
+				LAUNCH_SSA(float);
 				break;
 			case DTYPE_FLOAT64:
-				kernel_scale_shift_act<double> <<<grid, 256, 0, stream>>>(ARGS(double));
+				LAUNCH_SSA(double);
 				break;
 			case DTYPE_INT8:
-				kernel_scale_shift_act<int8_t> <<<grid, 256, 0, stream>>>(ARGS(int8_t));
+				LAUNCH_SSA(int8_t);
 				break;
 			default:
 				record_error(context, "cuda_quantized_scale_shift_act: output dtype %d not supported", static_cast<int>(dtype));
 				return;
 		}
 #undef ARGS
+#undef LAUNCH_SSA
 		MB200_COUNT_LAUNCH();
 		check_cuda(context, cudaGetLastError(), "cuda_quantized_scale_shift_act");
 	}

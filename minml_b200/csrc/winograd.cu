@@ -197,11 +197,26 @@ namespace mb200
 				}
 		}
 
+		/* Raw (unconverted) packet of VEC elements, so that a whole patch can be fetched before any arithmetic starts:
+		 * all loads of a thread are independent and in flight together, which is what a bandwidth-bound kernel needs. */
+		template<typename D, int VEC> struct Raw;
+		template<> struct Raw<float, 1> { using type = float; };
+		template<> struct Raw<float, 4> { using type = float4; };
+		template<> struct Raw<__half, 1> { using type = unsigned short; };
+		template<> struct Raw<__half, 2> { using type = unsigned int; };
+		template<> struct Raw<__half, 4> { using type = uint2; };
+		template<typename D, int VEC>
+		__device__ __forceinline__ void unpack_raw(const typename Raw<D, VEC>::type &raw, float (&v)[VEC])
+		{
+			Pack<D, VEC>::load(reinterpret_cast<const D*>(&raw), v);
+		}
+
 		template<int K, int T, typename D, int VEC>
 		__global__ void __launch_bounds__(128) kernel_input_transform(D *__restrict__ matrices, const D *__restrict__ input, int batch, int height,
 				int width, int channels, int tiles_h, int tiles_w)
 		{
 			using M = WM<K, T>;
+			using R = typename Raw<D, VEC>::type;
 			constexpr int P = M::P;
 			constexpr int PAD = K / 2;
 			const int cvecs = channels / VEC;
@@ -215,15 +230,10 @@ namespace mb200
 			const int th = static_cast<int>((tile / tiles_w) % tiles_h);
 			const int b = static_cast<int>(tile / (static_cast<long long>(tiles_w) * tiles_h));
 
-			// tmp = B^T d, computed one input row at a time so only P x P x VEC values are live
-			float tmp[P][P][VEC];
-#pragma unroll
-			for (int i = 0; i < P; i++)
-#pragma unroll
-				for (int j = 0; j < P; j++)
-#pragma unroll
-					for (int v = 0; v < VEC; v++)
-						tmp[i][j][v] = 0.0f;
+			// 1. fetch the whole zero-padded patch: P*P independent loads (a position outside the image reads element 0 and is masked)
+			R raw[P][P];
+			const R *src = reinterpret_cast<const R*>(input + c0);
+			const long long pitch = channels / VEC; // packets per position
 #pragma unroll
 			for (int r = 0; r < P; r++)
 			{
@@ -232,25 +242,36 @@ namespace mb200
 				for (int c = 0; c < P; c++)
 				{
 					const int w = T * tw - PAD + c;
-					float d[VEC];
-					if (h >= 0 && h < height && w >= 0 && w < width)
-						Pack<D, VEC>::load(input + ((static_cast<long long>(b) * height + h) * width + w) * channels + c0, d);
-					else
-					{
-#pragma unroll
-						for (int v = 0; v < VEC; v++)
-							d[v] = 0.0f;
-					}
-#pragma unroll
-					for (int i = 0; i < P; i++)
-						if (M::bt(i, r) != 0.0f)
-						{
-#pragma unroll
-							for (int v = 0; v < VEC; v++)
-								tmp[i][c][v] += M::bt(i, r) * d[v];
-						}
+					const bool inside = h >= 0 && h < height && w >= 0 && w < width;
+					const long long off = inside ? ((static_cast<long long>(b) * height + h) * width + w) * pitch : 0;
+					raw[r][c] = src[off];
+					if (!inside)
+						raw[r][c] = R();
 				}
 			}
+			// 2. tmp = B^T d
+			float tmp[P][P][VEC];
+#pragma unroll
+			for (int c = 0; c < P; c++)
+			{
+				float d[P][VEC];
+#pragma unroll
+				for (int r = 0; r < P; r++)
+					unpack_raw<D, VEC>(raw[r][c], d[r]);
+#pragma unroll
+				for (int i = 0; i < P; i++)
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+					{
+						float s = 0.0f;
+#pragma unroll
+						for (int r = 0; r < P; r++)
+							if (M::bt(i, r) != 0.0f)
+								s += M::bt(i, r) * d[r][v];
+						tmp[i][c][v] = s;
+					}
+			}
+			// 3. V = tmp B, one store per matrix
 #pragma unroll
 			for (int i = 0; i < P; i++)
 #pragma unroll
@@ -277,6 +298,7 @@ namespace mb200
 				int tiles_w)
 		{
 			using M = WM<K, T>;
+			using R = typename Raw<D, VEC>::type;
 			constexpr int P = M::P;
 			const int cvecs = channels / VEC;
 			const long long total_tiles = static_cast<long long>(batch) * tiles_h * tiles_w;
@@ -289,31 +311,29 @@ namespace mb200
 			const int th = static_cast<int>((tile / tiles_w) % tiles_h);
 			const int b = static_cast<int>(tile / (static_cast<long long>(tiles_w) * tiles_h));
 
-			// tmp = A^T M  (T x P), accumulated one matrix row at a time
-			float tmp[T][P][VEC];
-#pragma unroll
-			for (int i = 0; i < T; i++)
-#pragma unroll
-				for (int j = 0; j < P; j++)
-#pragma unroll
-					for (int v = 0; v < VEC; v++)
-						tmp[i][j][v] = 0.0f;
+			// 1. all P*P matrix elements and the T*T residual values of this tile are fetched before any arithmetic
+			R raw[P][P];
+			const R *src = reinterpret_cast<const R*>(matrices + c0);
+			const long long pitch = channels / VEC;
 #pragma unroll
 			for (int r = 0; r < P; r++)
 #pragma unroll
 				for (int c = 0; c < P; c++)
-				{
-					float m[VEC];
-					Pack<D, VEC>::load(matrices + (static_cast<long long>(r * P + c) * total_tiles + tile) * channels + c0, m);
+					raw[r][c] = src[(static_cast<long long>(r * P + c) * total_tiles + tile) * pitch];
+			R raw_ext[T][T];
+			if (ext != nullptr)
+			{
+				const R *esrc = reinterpret_cast<const R*>(ext + c0);
 #pragma unroll
-					for (int i = 0; i < T; i++)
-						if (M::at(i, r) != 0.0f)
-						{
+				for (int i = 0; i < T; i++)
 #pragma unroll
-							for (int v = 0; v < VEC; v++)
-								tmp[i][c][v] += M::at(i, r) * m[v];
-						}
-				}
+					for (int j = 0; j < T; j++)
+					{
+						const int h = T * th + i, w = T * tw + j;
+						const bool inside = h < height && w < width;
+						raw_ext[i][j] = esrc[inside ? ((static_cast<long long>(b) * height + h) * width + w) * pitch : 0];
+					}
+			}
 			float bias_value[VEC];
 			if (bias != nullptr)
 				Pack<D, VEC>::load(bias + c0, bias_value);
@@ -323,18 +343,37 @@ namespace mb200
 				for (int v = 0; v < VEC; v++)
 					bias_value[v] = 0.0f;
 			}
+			// 2. tmp = A^T M
+			float tmp[T][P][VEC];
+#pragma unroll
+			for (int c = 0; c < P; c++)
+			{
+				float mcol[P][VEC];
+#pragma unroll
+				for (int r = 0; r < P; r++)
+					unpack_raw<D, VEC>(raw[r][c], mcol[r]);
+#pragma unroll
+				for (int i = 0; i < T; i++)
+#pragma unroll
+					for (int v = 0; v < VEC; v++)
+					{
+						float s = 0.0f;
+#pragma unroll
+						for (int r = 0; r < P; r++)
+							if (M::at(i, r) != 0.0f)
+								s += M::at(i, r) * mcol[r][v];
+						tmp[i][c][v] = s;
+					}
+			}
+			// 3. y = tmp A + ext + bias, activation, clipped store
 #pragma unroll
 			for (int i = 0; i < T; i++)
 			{
 				const int h = T * th + i;
-				if (h >= height)
-					continue;
 #pragma unroll
 				for (int j = 0; j < T; j++)
 				{
 					const int w = T * tw + j;
-					if (w >= width)
-						continue;
 					float out[VEC];
 #pragma unroll
 					for (int v = 0; v < VEC; v++)
@@ -346,11 +385,10 @@ namespace mb200
 								s += tmp[i][c][v] * M::at(j, c);
 						out[v] = s;
 					}
-					const long long off = ((static_cast<long long>(b) * height + h) * width + w) * channels + c0;
 					if (ext != nullptr)
 					{
 						float e[VEC];
-						Pack<D, VEC>::load(ext + off, e);
+						unpack_raw<D, VEC>(raw_ext[i][j], e);
 #pragma unroll
 						for (int v = 0; v < VEC; v++)
 							out[v] += e[v];
@@ -358,7 +396,8 @@ namespace mb200
 #pragma unroll
 					for (int v = 0; v < VEC; v++)
 						out[v] = apply_activation(out[v] + bias_value[v], act);
-					Pack<D, VEC>::store(output + off, out);
+					if (h < height && w < width)
+						Pack<D, VEC>::store(output + ((static_cast<long long>(b) * height + h) * width + w) * channels + c0, out);
 				}
 			}
 		}
