@@ -1,0 +1,271 @@
+/*
+ * attention_mma.cu -- fp16 multi-head attention forward on the warp-level tensor-core path (mma.sync m16n8k16, fp32
+ * accumulation), flash-attention style: the [b, heads, T, T] score tensor that the reference materialises in its workspace
+ * (src/backend/cuda/kernels/attention.cu:494-568: batched GEMM, softmax kernel, batched GEMM) never exists.
+ *
+ *   input  [b, h, w, parts * heads * d]   packed [q | k | v] (parts = 3) or [q = k | v] (parts = 2)
+ *   S = Q K^T / sqrt(d);  S[i, j] += table[head, r + clamp(hj - hi, -r, r), r + clamp(wj - wi, -r, r)];  P = softmax(S);  O = P V
+ *
+ * One CTA per (head, batch item) stages K and V of that head in shared memory once; each of its 4 warps owns 16 queries at
+ * a time and walks the keys in blocks of 64 with a running maximum and sum, keeping S, P and O in registers.
+ * Tokens here are at most a few hundred (a 20x20 board has 400) with head dimensions of 16-128, shapes for which a
+ * tcgen05 tile (M = 128, accumulators in tensor memory, both operands from shared memory) would spend most of its cycles on
+ * layout changes between the two products; the warp-level instruction keeps P in the accumulator registers it came from.
+ */
+#include "common.cuh"
+
+namespace mb200
+{
+	namespace
+	{
+		constexpr int WARPS = 4;
+		constexpr int KEY_BLOCK = 64;
+
+		__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+		{
+			asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+					: "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+		}
+		__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t &r0, uint32_t &r1, uint32_t smem_addr)
+		{
+			asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr));
+		}
+		__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+		{
+			const __half2 h = __floats2half2_rn(lo, hi);
+			return *reinterpret_cast<const uint32_t*>(&h);
+		}
+
+		/* D = head dimension (multiple of 16). */
+		template<int D>
+		__global__ void __launch_bounds__(WARPS * 32) kernel_mha_mma(__half *__restrict__ output, const __half *__restrict__ input,
+				const __half *__restrict__ table, int height, int width, int heads, int parts, int table_n, int table_pad)
+		{
+			constexpr int LD = D + 8; // row pitch in halves: 16-byte aligned rows, conflict-free fragment loads
+			constexpr int KC = D / 16; // k-chunks of the first product
+			constexpr int NT = D / 8; // n-tiles of the second product
+			extern __shared__ __align__(16) unsigned char smem_raw[];
+			const int tokens = height * width;
+			const int padded = (tokens + KEY_BLOCK - 1) / KEY_BLOCK * KEY_BLOCK;
+			__half *sk = reinterpret_cast<__half*>(smem_raw);
+			__half *sv = sk + padded * LD;
+			float *st = reinterpret_cast<float*>(sv + padded * LD);
+			int *spos = reinterpret_cast<int*>(st + table_n * table_pad); // (h << 16) | w of every token
+
+			const int head = blockIdx.x, b = blockIdx.y;
+			const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+			const int g = lane / 4, tig = lane % 4;
+			const int stride = parts * heads * D; // channels per token
+			const __half *base = input + static_cast<long long>(b) * tokens * stride;
+			const int k_off = (parts == 3 ? 1 : 0) * heads * D + head * D;
+			const int v_off = (parts - 1) * heads * D + head * D;
+
+			// stage K and V (16 bytes per access), zero rows beyond the last token
+			constexpr int CHUNKS = D / 8;
+			for (int i = threadIdx.x; i < padded * CHUNKS; i += blockDim.x)
+			{
+				const int t = i / CHUNKS, ch = i % CHUNKS;
+				uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+				if (t < tokens)
+				{
+					kv = *reinterpret_cast<const uint4*>(base + static_cast<long long>(t) * stride + k_off + ch * 8);
+					vv = *reinterpret_cast<const uint4*>(base + static_cast<long long>(t) * stride + v_off + ch * 8);
+				}
+				*reinterpret_cast<uint4*>(sk + t * LD + ch * 8) = kv;
+				*reinterpret_cast<uint4*>(sv + t * LD + ch * 8) = vv;
+			}
+			for (int i = threadIdx.x; i < table_n * table_pad; i += blockDim.x)
+				st[i] = __half2float(table[static_cast<long long>(head) * table_n * table_pad + i]);
+			for (int i = threadIdx.x; i < padded; i += blockDim.x)
+				spos[i] = ((i / width) << 16) | (i % width);
+			__syncthreads();
+
+			const float scale = rsqrtf(static_cast<float>(D));
+			const int range = (table_n - 1) / 2;
+			const uint32_t sv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(sv));
+
+			for (int q0 = warp * 16; q0 < tokens; q0 += WARPS * 16)
+			{
+				// Q fragments of rows q0 + g and q0 + g + 8
+				uint32_t qa[KC][4];
+				const int r0 = q0 + g, r1 = q0 + g + 8;
+#pragma unroll
+				for (int kc = 0; kc < KC; kc++)
+				{
+					const int col = head * D + kc * 16 + tig * 2;
+					qa[kc][0] = (r0 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r0) * stride + col) : 0u;
+					qa[kc][1] = (r1 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r1) * stride + col) : 0u;
+					qa[kc][2] = (r0 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r0) * stride + col + 8) : 0u;
+					qa[kc][3] = (r1 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r1) * stride + col + 8) : 0u;
+				}
+				const int p0 = spos[min(r0, padded - 1)], p1 = spos[min(r1, padded - 1)];
+				const int qh0 = p0 >> 16, qw0 = p0 & 0xFFFF, qh1 = p1 >> 16, qw1 = p1 & 0xFFFF;
+
+				float o[NT][4];
+#pragma unroll
+				for (int n = 0; n < NT; n++)
+#pragma unroll
+					for (int k = 0; k < 4; k++)
+						o[n][k] = 0.0f;
+				float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
+
+				for (int kb = 0; kb < padded; kb += KEY_BLOCK)
+				{
+					float s[KEY_BLOCK / 8][4];
+#pragma unroll
+					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
+					{
+#pragma unroll
+						for (int k = 0; k < 4; k++)
+							s[nt][k] = 0.0f;
+						const __half *krow = sk + (kb + nt * 8 + g) * LD + tig * 2;
+#pragma unroll
+						for (int kc = 0; kc < KC; kc++)
+						{
+							const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kc * 16);
+							const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kc * 16 + 8);
+							mma_16816(s[nt], qa[kc], b0, b1);
+						}
+					}
+					// scale, relative-position bias, mask keys beyond the last token; block maxima
+					float bm0 = -1.0e30f, bm1 = -1.0e30f;
+#pragma unroll
+					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
+#pragma unroll
+						for (int e = 0; e < 2; e++)
+						{
+							const int j = kb + nt * 8 + tig * 2 + e;
+							float v0 = s[nt][e] * scale, v1 = s[nt][2 + e] * scale;
+							if (table != nullptr)
+							{
+								const int pj = spos[j];
+								const int jh = pj >> 16, jw = pj & 0xFFFF;
+								v0 += st[(min(max(jh - qh0, -range), range) + range) * table_pad + min(max(jw - qw0, -range), range) + range];
+								v1 += st[(min(max(jh - qh1, -range), range) + range) * table_pad + min(max(jw - qw1, -range), range) + range];
+							}
+							if (j >= tokens)
+							{
+								v0 = -1.0e30f;
+								v1 = -1.0e30f;
+							}
+							s[nt][e] = v0;
+							s[nt][2 + e] = v1;
+							bm0 = fmaxf(bm0, v0);
+							bm1 = fmaxf(bm1, v1);
+						}
+					bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
+					bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
+					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
+					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
+					const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);
+					const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1);
+					m0 = n0;
+					m1 = n1;
+					float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
+#pragma unroll
+						for (int e = 0; e < 2; e++)
+						{
+							const float e0 = __expf(s[nt][e] - n0), e1 = __expf(s[nt][2 + e] - n1);
+							s[nt][e] = e0;
+							s[nt][2 + e] = e1;
+							sum0 += e0;
+							sum1 += e1;
+						}
+					l0 = l0 * c0 + sum0;
+					l1 = l1 * c1 + sum1;
+#pragma unroll
+					for (int n = 0; n < NT; n++)
+					{
+						o[n][0] *= c0;
+						o[n][1] *= c0;
+						o[n][2] *= c1;
+						o[n][3] *= c1;
+					}
+					// O += P V: the accumulator layout of two neighbouring score tiles is the A-fragment layout of one k16 step
+#pragma unroll
+					for (int kc = 0; kc < KEY_BLOCK / 16; kc++)
+					{
+						uint32_t pa[4];
+						pa[0] = pack_half2(s[2 * kc][0], s[2 * kc][1]);
+						pa[1] = pack_half2(s[2 * kc][2], s[2 * kc][3]);
+						pa[2] = pack_half2(s[2 * kc + 1][0], s[2 * kc + 1][1]);
+						pa[3] = pack_half2(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+#pragma unroll
+						for (int n = 0; n < NT; n++)
+						{
+							uint32_t b0, b1;
+							// lanes 0-15 name the 16 key rows of this step; the transposing load returns V^T fragments
+							ldmatrix_x2_trans(b0, b1, sv_addr + static_cast<uint32_t>(((kb + kc * 16 + (lane & 15)) * LD + n * 8) * 2));
+							mma_16816(o[n], pa, b0, b1);
+						}
+					}
+				}
+				// the row sums live in the four lanes of a quad
+				l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+				l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+				l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+				l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+				const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+				__half *out = output + static_cast<long long>(b) * tokens * heads * D + head * D;
+#pragma unroll
+				for (int n = 0; n < NT; n++)
+				{
+					if (r0 < tokens)
+						*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r0) * heads * D + n * 8 + tig * 2) = pack_half2(o[n][0] * inv0,
+								o[n][1] * inv0);
+					if (r1 < tokens)
+						*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r1) * heads * D + n * 8 + tig * 2) = pack_half2(o[n][2] * inv1,
+								o[n][3] * inv1);
+				}
+			}
+		}
+
+		template<int D>
+		bool launch(mlContext_t ctx, __half *output, const __half *input, const __half *table, int batch, int height, int width, int heads, int parts,
+				int table_n, int table_pad)
+		{
+			const int tokens = height * width;
+			const int padded = (tokens + KEY_BLOCK - 1) / KEY_BLOCK * KEY_BLOCK;
+			const size_t smem = static_cast<size_t>(2) * padded * (D + 8) * sizeof(__half) + static_cast<size_t>(table_n) * table_pad * sizeof(float)
+					+ static_cast<size_t>(padded) * sizeof(int);
+			if (smem > 200 * 1024)
+				return false;
+			if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_mha_mma<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+					"attention: shared memory opt-in"))
+				return false;
+			kernel_mha_mma<D> <<<dim3(heads, batch), WARPS * 32, smem, use_stream(ctx)>>>(output, input, table, height, width, heads, parts, table_n,
+					table_pad);
+			MB200_COUNT_LAUNCH();
+			check_cuda(ctx, cudaGetLastError(), "cuda_multi_head_attention_forward");
+			return true;
+		}
+	}
+
+	/* Returns false when the shape is outside what this kernel handles (the caller then uses the generic kernel). */
+	bool mha_forward_mma(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
+			int head_dim, int parts, int table_n, int table_pad)
+	{
+		if (height >= 32768 || width >= 32768 || batch > 65535)
+			return false;
+		if (!aligned_to(input, 16) || !aligned_to(output, 4) || (parts * heads * head_dim) % 8 != 0)
+			return false;
+		__half *o = reinterpret_cast<__half*>(output);
+		const __half *x = reinterpret_cast<const __half*>(input);
+		const __half *t = reinterpret_cast<const __half*>(table);
+		switch (head_dim)
+		{
+			case 16:
+				return launch<16>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+			case 32:
+				return launch<32>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+			case 64:
+				return launch<64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+			case 128:
+				return launch<128>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+			default:
+				return false;
+		}
+	}
+} /* namespace mb200 */

@@ -18,6 +18,9 @@
 
 namespace mb200
 {
+	bool mha_forward_mma(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
+			int head_dim, int parts, int table_n, int table_pad); // attention_mma.cu
+
 	namespace
 	{
 		template<typename T>
@@ -222,6 +225,10 @@ extern "C"
 			table_n = weights_shape.dim[1];
 			table_pad = weights_shape.dim[2];
 		}
+		// fp16 with a head dimension of 16, 32, 64 or 128: the tensor-core kernel; anything else: the generic kernel below
+		if (dtype == DTYPE_FLOAT16 && mha_forward_mma(context, output, input, table, batch, height, width, num_heads, head_dim, parts, table_n,
+				table_pad))
+			return;
 		const size_t smem = sizeof(float)
 				* (static_cast<size_t>(tokens) * (head_dim + 1) + static_cast<size_t>(tokens) * head_dim + static_cast<size_t>(table_n) * table_pad
 						+ static_cast<size_t>(MHA_WARPS) * head_dim + static_cast<size_t>(MHA_WARPS) * tokens);

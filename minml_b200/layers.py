@@ -247,3 +247,61 @@ class ResNetTrunk:
         self.gap.forward([cur], self.pooled)
         self.value.forward([self.pooled], self.value_out)
         return self.policy_out, self.value_out
+
+
+# ------------------------------------------------------------------------------------------------------ hybrid block
+def make_hybrid_weights(seed, embed, heads, ffn, board):
+    """N(0, 0.02) weights for the conv + attention block: a 3x3 residual block, pre-LN attention with a relative-position
+    table [heads, 2R-1, round_up(2R-1, 4)] (R = board size), and a ReLU feed-forward network embed -> ffn -> embed."""
+    rng = np.random.default_rng(seed)
+
+    def n(*shape):
+        return (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    size = 2 * board - 1
+    return {
+        "c1_w": n(embed, 3, 3, embed), "c1_b": n(embed), "c2_w": n(embed, 3, 3, embed), "c2_b": n(embed),
+        "ln1_g": np.ones(embed, np.float32), "ln1_b": np.zeros(embed, np.float32),
+        "qkv_w": n(3 * embed, 1, 1, embed), "qkv_b": n(3 * embed), "table": n(heads, size, (size + 3) // 4 * 4),
+        "proj_w": n(embed, 1, 1, embed), "proj_b": n(embed),
+        "ln2_g": np.ones(embed, np.float32), "ln2_b": np.zeros(embed, np.float32),
+        "ffn1_w": n(ffn, 1, 1, embed), "ffn1_b": n(ffn), "ffn2_w": n(embed, 1, 1, ffn), "ffn2_b": n(embed),
+    }
+
+
+class HybridBlock:
+    """x -> 3x3 residual block -> x + proj(MHA(qkv(LN(x)))) -> x + FFN(LN(x)), every layer through the calls minml's
+    Conv2D (k = 3 and k = 1), LayerNormalization and MultiHeadAttention layers make; skips ride in the convolutions' `ext`."""
+
+    def __init__(self, ctx, weights, batch, height, width, embed, heads, ffn, dtype=torch.float16):
+        self.ctx = ctx
+        self.conv1 = Conv2D(ctx, weights["c1_w"], weights["c1_b"], "relu", dtype)
+        self.conv2 = Conv2D(ctx, weights["c2_w"], weights["c2_b"], "relu", dtype)
+        self.ln1 = LayerNormalization(ctx, weights["ln1_g"], weights["ln1_b"], dtype)
+        self.qkv = Conv2D(ctx, weights["qkv_w"], weights["qkv_b"], "linear", dtype)
+        self.mha = MultiHeadAttention(ctx, heads, weights["table"], dtype)
+        self.proj = Conv2D(ctx, weights["proj_w"], weights["proj_b"], "linear", dtype)
+        self.ln2 = LayerNormalization(ctx, weights["ln2_g"], weights["ln2_b"], dtype)
+        self.ffn1 = Conv2D(ctx, weights["ffn1_w"], weights["ffn1_b"], "relu", dtype)
+        self.ffn2 = Conv2D(ctx, weights["ffn2_w"], weights["ffn2_b"], "linear", dtype)
+
+        def buf(c):
+            return torch.empty((batch, height, width, c), dtype=dtype, device="cuda")
+        self.t1, self.a, self.n1, self.att, self.a2, self.n2, self.out = (buf(embed) for _ in range(7))
+        self.qkv_out, self.f1 = buf(3 * embed), buf(ffn)
+        self.workspace = Workspace()
+        self.workspace.reserve(self.conv1.workspace_bytes((batch, height, width, embed)))
+        self.flops_per_item = (2 * 2 * height * width * 9 * embed * embed + 2 * height * width * embed * (3 * embed + embed + 2 * ffn)
+                               + 4 * (height * width) ** 2 * embed)
+
+    def predict(self, x):
+        ws = self.workspace
+        self.conv1.forward([x], self.t1, ws)
+        self.conv2.forward([self.t1, x], self.a, ws)
+        self.ln1.forward([self.a], self.n1)
+        self.qkv.forward([self.n1], self.qkv_out, ws)
+        self.mha.forward([self.qkv_out], self.att)
+        self.proj.forward([self.att, self.a], self.a2, ws)
+        self.ln2.forward([self.a2], self.n2)
+        self.ffn1.forward([self.n2], self.f1, ws)
+        self.ffn2.forward([self.f1, self.a2], self.out, ws)
+        return self.out

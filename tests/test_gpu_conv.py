@@ -155,3 +155,43 @@ def test_trunk_matches_fp32_oracle(ctx, oracle, cfg):
     want_p, want_v = oracle_trunk(oracle, weights16, x, blocks)
     assert max_rel_err(host(policy), want_p) <= FP16_REL
     assert max_rel_err(host(value), want_v) <= FP16_REL
+
+
+@pytest.mark.parametrize("cfg", [(2, 15, 15, 256, 8, 1024), (1, 9, 7, 64, 4, 128)])
+def test_hybrid_block_matches_fp32_oracle(ctx, oracle, cfg):
+    """BASELINE config 4 topology (3x3 residual block, pre-LN attention with relative-position bias, ReLU feed-forward) at a small batch."""
+    from minml_b200 import layers as L
+    from tests.util import oracle_hybrid
+    b, h, w, embed, heads, ffn = cfg
+    weights = L.make_hybrid_weights(4321, embed, heads, ffn, max(h, w))
+    weights16 = {k: v.astype(np.float16).astype(np.float32) for k, v in weights.items()}
+    x = np.random.default_rng(3).standard_normal((b, h, w, embed)).astype(np.float16).astype(np.float32)
+    block = L.HybridBlock(ctx, weights, b, h, w, embed, heads, ffn)
+    xd = dev(x, torch.float16)
+    out = block.predict(xd)
+    ctx.synchronize()
+    want = oracle_hybrid(oracle, weights16, x, heads)
+    assert max_rel_err(host(out), want) <= FP16_REL
+
+
+@pytest.mark.parametrize("cfg", [(4, 15, 15, 32, 128, 2), (2, 20, 20, 32, 256, 3)])
+def test_quantized_trunk(ctx, oracle, cfg):
+    """BASELINE config 2 topology (int8 activations and weights between the 3x3 layers, fp16 heads): the heads' outputs against the
+    oracle's integer chain with the same calibrated scales, and, loosely, against the fp32 trunk (the quantisation error itself)."""
+    from minml_b200 import layers as L
+    from minml_b200 import networks as N
+    from tests.util import oracle_quantized_trunk
+    b, h, w, planes, channels, blocks = cfg
+    weights = {k: v.astype(np.float16).astype(np.float32) for k, v in L.make_trunk_weights(1235, planes, channels, blocks).items()}
+    x = (np.random.default_rng(1).random((b, h, w, planes)) < 0.3).astype(np.float32)
+    net = N.QuantizedTrunk(ctx, weights, b, h, w, planes, channels, blocks, calibration_batches=1)
+    policy, value = net.predict(dev(pack_planes(x).view(np.int32)))
+    ctx.synchronize()
+    want_p, want_v = oracle_quantized_trunk(oracle, weights, x, blocks, net.scales)
+    # one int8 step of disagreement per layer (the oracle and the device round ties alike, but the fused kernel's fp32 sum can differ
+    # in the last bit) moves the heads by far less than the fp16 tolerance
+    assert max_rel_err(host(policy), want_p) <= FP16_REL
+    assert max_rel_err(host(value), want_v) <= FP16_REL
+    ref_p, ref_v = oracle_trunk(oracle, weights, x, blocks)
+    assert max_rel_err(host(policy), ref_p) <= 0.1
+    assert max_rel_err(host(value), ref_v) <= 0.1

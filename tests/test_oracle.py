@@ -180,3 +180,17 @@ def test_quantize_weights(oracle):
         assert np.array_equal(q[co], np.clip(np.round(w[co] * np.float32(s)), -128, 127).astype(np.int8))
         assert abs(cs[co] - 0.02 / s) <= 1e-7
         assert abs(qb[co] - (0.3 / s * q[co].astype(np.int32).sum() + bias[co])) <= 1e-4
+
+
+def test_host_weight_quantisation_matches_oracle(oracle):
+    """minml_b200.networks.quantize_weights (numpy) against the oracle's restatement of src/layers/quantization.cpp:59-97."""
+    from minml_b200.networks import quantize_weights
+    r = np.random.default_rng(5)
+    w = r.standard_normal((24, 3, 3, 16)).astype(np.float32)
+    bias = r.standard_normal(24).astype(np.float32)
+    for in_scale, in_shift in ((1.0, 0.0), (0.0131, 0.0), (0.02, 0.4)):
+        q, cs, qb = quantize_weights(w, bias, in_scale, in_shift)
+        q2, cs2, qb2 = oracle.quantize_weights(w, bias, in_scale, in_shift)
+        assert np.array_equal(q, q2)
+        assert np.allclose(cs, cs2, rtol=1e-6, atol=0)
+        assert np.allclose(qb, qb2, rtol=1e-5, atol=1e-6)

@@ -45,6 +45,25 @@ def oracle_trunk(oracle, weights, x, blocks):
     return policy, value
 
 
+def oracle_quantized_trunk(oracle, weights, x01, blocks, scales):
+    """The int8 trunk (minml_b200.networks.QuantizedTrunk) layer by layer on the oracle's integer convolution.
+    `scales[t]` is the per-tensor activation scale of tensor t (stem output, then two per block); shifts are 0."""
+    def qconv(xq, wn, bn, s_in, s_out, ext=None, s_ext=1.0):
+        q, cs, qb = oracle.quantize_weights(weights[wn], weights[bn], s_in, 0.0)
+        return oracle.conv2d_int8(xq, q, cs, qb, 0, (s_out, 0.0), "relu", ext, (s_ext, 0.0))
+    a, _, _ = qconv(x01.astype(np.int8), "stem_w", "stem_b", 1.0, scales[0])
+    real = None
+    for i in range(blocks):
+        s_in, s_mid, s_out = scales[2 * i], scales[1 + 2 * i], scales[2 + 2 * i]
+        t, _, _ = qconv(a, "b%d_w1" % i, "b%d_b1" % i, s_in, s_mid)
+        a, real, _ = qconv(t, "b%d_w2" % i, "b%d_b2" % i, s_mid, s_out, a, s_in)
+    real = real.astype(np.float16).astype(np.float32)  # the last block hands fp16 to the heads
+    policy = oracle.conv2d(real, weights["policy_w"], weights["policy_b"], None, "linear")
+    pooled = oracle.global_average_pooling(real)
+    value = oracle.add_bias_act(oracle.gemm("n", pooled, "t", weights["value_w"]), weights["value_b"], "linear")
+    return policy, value
+
+
 def pack_planes(x01):
     """[..., c] array of {0, 1} -> uint32 words [..., ceil(c / 32)], channel j in bit j % 32 of word j // 32."""
     c = x01.shape[-1]
@@ -53,3 +72,20 @@ def pack_planes(x01):
     for j in range(c):
         out[..., j // 32] |= (x01[..., j].astype(np.uint32) & 1) << np.uint32(j % 32)
     return out
+
+
+def oracle_hybrid(oracle, w, x, heads):
+    """fp32 forward of the conv + attention block (same topology as minml_b200.layers.HybridBlock)."""
+    def conv1x1(t, wn, bn, ext=None, act="linear"):
+        b, h, ww, c = t.shape
+        out = oracle.gemm("n", t.reshape(-1, c), "t", w[wn].reshape(w[wn].shape[0], -1))
+        if ext is not None:
+            out = out + ext.reshape(out.shape)
+        return oracle.add_bias_act(out, w[bn], act).reshape(b, h, ww, -1)
+    t1 = oracle.conv2d(x, w["c1_w"], w["c1_b"], None, "relu")
+    a = oracle.conv2d(t1, w["c2_w"], w["c2_b"], x, "relu")
+    n1 = oracle.layernorm(a, w["ln1_g"], w["ln1_b"])
+    att = oracle.mha_forward(conv1x1(n1, "qkv_w", "qkv_b"), heads, w["table"])
+    a2 = conv1x1(att, "proj_w", "proj_b", a)
+    n2 = oracle.layernorm(a2, w["ln2_g"], w["ln2_b"])
+    return conv1x1(conv1x1(n2, "ffn1_w", "ffn1_b", None, "relu"), "ffn2_w", "ffn2_b", a2)
