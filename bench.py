@@ -37,13 +37,22 @@ CONFIGS = {
                label="config3: 20x20 board, 32 planes, stem 3x3 32->256, 20 residual blocks x 2 conv3x3 256->256, policy 1x1 + value GAP/dense, fp16"),
     "c1": dict(batch=256, height=15, width=15, planes=32, channels=128, blocks=10,
                label="config1: 15x15 board, 32 planes, stem 3x3 32->128, 10 residual blocks x 2 conv3x3 128->128, policy 1x1 + value GAP/dense, fp16"),
+    "c2": dict(kind="int8_trunk", batch=512, height=20, width=20, planes=32, channels=128, blocks=10,
+               label="config2: int8 trunk, 20x20 board, 32 planes, 128 channels, 10 residual blocks, per-channel int8 weights, per-tensor int8 "
+                     "activations calibrated on 64 seeded batches, int32 accumulate, fp32 requantisation, fp16 heads"),
+    "c4": dict(kind="hybrid", batch=256, height=15, width=15, planes=256, channels=256, blocks=1, heads=8, ffn=1024,
+               label="config4: 15x15 board as 225 tokens, embed 256: 3x3 residual block, pre-LN attention (8 heads of 32, relative-position bias), "
+                     "FFN 256->1024->256 ReLU, fp16"),
 }
 SEED = 1237
+METRIC = {"trunk": "positions/sec for ResNet trunk", "int8_trunk": "positions/sec for ResNet trunk", "hybrid": "positions/sec for conv+attention block"}
 
 
 def flops_per_position(cfg):
     hw = cfg["height"] * cfg["width"]
     c = cfg["channels"]
+    if cfg.get("kind") == "hybrid":
+        return 2 * 2 * hw * 9 * c * c + 2 * hw * c * (3 * c + c + 2 * cfg["ffn"]) + 4 * hw * hw * c
     f = 2 * hw * 9 * cfg["planes"] * c + cfg["blocks"] * 2 * (2 * hw * 9 * c * c) + 2 * hw * c + 2 * c * 3
     return f
 
@@ -107,12 +116,23 @@ def cpu_reference_arm(cfg, steps, warmup, threads=None):
     from minml_b200 import layers
     threads = threads or os.cpu_count() or 1
     per_thread = 2
-    ref_lib = checkers.load_reference_cpu()
+    hybrid = cfg.get("kind") == "hybrid"
+    ref_lib = None if hybrid else checkers.load_reference_cpu()
     kind = "reference" if ref_lib is not None else "port"
-    weights = layers.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
-    x, _ = synthetic_input(cfg, threads * per_thread, SEED + 1)
+    if hybrid:  # the conv + attention block runs on the oracle (fp32, scalar C), one shard per host thread
+        weights = layers.make_hybrid_weights(SEED, cfg["channels"], cfg["heads"], cfg["ffn"], max(cfg["height"], cfg["width"]))
+        x = np.random.default_rng(SEED + 1).standard_normal((threads * per_thread, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float32)
+    else:
+        weights = layers.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
+        x, _ = synthetic_input(cfg, threads * per_thread, SEED + 1)
 
-    if ref_lib is not None:
+    if hybrid:
+        oracle = checkers.load_oracle()
+        from tests.util import oracle_hybrid
+
+        def run(i):
+            oracle_hybrid(oracle, weights, x[i * per_thread:(i + 1) * per_thread], cfg["heads"])
+    elif ref_lib is not None:
         workers = [checkers.load_reference_cpu() if i else ref_lib for i in range(threads)]  # one backend context per thread
 
         # transformed weights are computed once per layer and cached, as Conv2D does (src/layers/Conv2D.cpp:356-363)
@@ -153,8 +173,9 @@ def cpu_reference_arm(cfg, steps, warmup, threads=None):
     dt = time.perf_counter() - t0
     positions = threads * per_thread * steps
     return {"value": positions / dt, "unit": "positions/s", "cores": threads, "kind": kind,
-            "sample": "%d positions per step (%d per host thread, %d threads), %d steps, fp32, whole trunk" % (
-                threads * per_thread, per_thread, threads, steps),
+            "sample": "%d positions per step (%d per host thread, %d threads), %d steps, fp32, whole %s" % (
+                threads * per_thread, per_thread, threads, steps, "block" if hybrid else "trunk (fp32 arithmetic also for the int8 configuration)"
+                if cfg.get("kind") == "int8_trunk" else "trunk"),
             "seconds": dt, "ms_per_step": dt / steps * 1e3}
 
 
@@ -240,6 +261,45 @@ def layer_roofline(B, L, ctx, cfg, peaks, torch, fused=True):
     return rec
 
 
+def int8_layer_roofline(B, L, ctx, cfg, peaks, torch):
+    """One channels -> channels int8 3x3 layer (im2row -> int8 GEMM -> requantise, recognised and run as one tcgen05 kernel).
+    There is no measured int8 peak: the record uses twice the measured bf16 figure, the ratio of the nominal dense peaks."""
+    b, h, w, c = cfg["batch"], cfg["height"], cfg["width"], cfg["channels"]
+    rows = b * h * w
+    rng = np.random.default_rng(3)
+    qw = rng.integers(-127, 128, (c, 3, 3, c), dtype=np.int8)
+    conv = L.QuantizedConv2D(ctx, qw, np.full(c, 1e-4, np.float32), np.zeros(c, np.float32), (0.02, 0.0), (0.05, 0.0), "relu", torch.int8)
+    x = torch.randint(-128, 128, (b, h, w, c), device="cuda", dtype=torch.int8)
+    res = torch.randint(-128, 128, (b, h, w, c), device="cuda", dtype=torch.int8)
+    y = torch.empty_like(x)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    reps = 10
+    for _ in range(3):
+        conv.forward([x, res], y, ws, (0.03, 0.0))
+    ctx.synchronize()
+    e0 = B.lib.cuda_create_event(ctx.handle)
+    for _ in range(reps):
+        conv.forward([x, res], y, ws, (0.03, 0.0))
+    e1 = B.lib.cuda_create_event(ctx.handle)
+    ctx.synchronize()
+    sec = B.lib.cuda_get_time_between_events(e0, e1) / reps
+    B.lib.cuda_destroy_event(e0)
+    B.lib.cuda_destroy_event(e1)
+    ops = 2.0 * rows * 9 * c * c
+    tops = ops / sec / 1e12
+    nbytes = 3 * rows * c + 9 * c * c
+    peak = 2.0 * peaks["bf16_tflops"]
+    rec = {"kernel": "kernel_conv3x3_igemm (int8, %d -> %d, fused requantise + residual + ReLU)" % (c, c), "bound": "tensor", "achieved": tops,
+           "peak": peak, "unit": "TFLOP/s", "frac": tops / peak, "traffic": None,
+           "peak_source": "2 x the bf16 figure of " + peaks["source"] + " (int8 dense peak is nominally twice bf16; no int8 figure is measured)",
+           "launch_ms": sec * 1e3, "algorithmic_flops": ops, "algorithmic_bytes": nbytes, "hbm_gbs_at_algorithmic_bytes": nbytes / sec / 1e9}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        rec["traffic"] = json.load(open(traffic_file)).get("kernel_conv3x3_igemm_int8_c%d_b%d" % (c, b))
+    return rec
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -272,25 +332,49 @@ def gpu_arm(args, cfg):
     ctx = B.Context(local)
     ctx.set_fusion(not args.eager)
     batch = cfg["batch"]
-    weights = L.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
-    net = L.ResNetTrunk(ctx, weights, batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
-    _, packed = synthetic_input(cfg, batch, SEED + 1 + rank)
-    packed_host = torch.from_numpy(packed).pin_memory()
-    packed_dev = packed_host.cuda()
-    policy_host = torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory()
-    value_host = torch.empty((batch, 3), dtype=torch.float16).pin_memory()
-    h2d = packed_host.numel() * 4
-    d2h = policy_host.numel() * 2 + value_host.numel() * 2
+    kind = cfg.get("kind", "trunk")
+    if kind == "hybrid":
+        weights = L.make_hybrid_weights(SEED, cfg["channels"], cfg["heads"], cfg["ffn"], max(cfg["height"], cfg["width"]))
+        net = L.HybridBlock(ctx, weights, batch, cfg["height"], cfg["width"], cfg["channels"], cfg["heads"], cfg["ffn"])
+        tokens = np.random.default_rng(SEED + 1 + rank).standard_normal((batch, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float16)
+        in_host = torch.from_numpy(tokens).pin_memory()
+        in_stage = torch.empty_like(in_host, device="cuda")
+        out_hosts = [torch.empty(tokens.shape, dtype=torch.float16).pin_memory()]
+
+        def predict(x):
+            return (net.predict(x),)
+    else:
+        weights = L.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
+        shape = (batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
+        if kind == "int8_trunk":
+            from minml_b200 import networks as N
+            net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64)
+        else:
+            net = L.ResNetTrunk(ctx, weights, *shape)
+        _, packed = synthetic_input(cfg, batch, SEED + 1 + rank)
+        in_host = torch.from_numpy(packed).pin_memory()
+        in_stage = torch.empty_like(in_host, device="cuda")
+        out_hosts = [torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory(),
+                     torch.empty((batch, 3), dtype=torch.float16).pin_memory()]
+        predict = net.predict
+    in_dev = in_host.cuda()
+    h2d = in_host.numel() * in_host.element_size()
+    d2h = sum(t.numel() * t.element_size() for t in out_hosts)
 
     def step_device():
-        net.predict(packed_dev)
+        return predict(in_dev)
 
     def step_e2e():
-        B.lib.cuda_memcpy_from_host(ctx.handle, ctypes.c_void_p(net.packed.data_ptr()), 0, ctypes.c_void_p(packed_host.data_ptr()), h2d)
-        policy, value = net.predict(None)
-        B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(policy_host.data_ptr()), ctypes.c_void_p(policy.data_ptr()), 0, policy.numel() * 2)
-        B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(value_host.data_ptr()), ctypes.c_void_p(value.data_ptr()), 0, value.numel() * 2)
+        B.lib.cuda_memcpy_from_host(ctx.handle, ctypes.c_void_p(in_stage.data_ptr()), 0, ctypes.c_void_p(in_host.data_ptr()), h2d)
+        outs = predict(in_stage)
+        for dst, src in zip(out_hosts, outs):
+            B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(src.data_ptr()), 0, src.numel() * src.element_size())
         ctx.synchronize()  # the caller reads the result of every step
+        return outs
+
+    def host_copy(t):
+        ctx.synchronize()
+        return t.detach().cpu().clone()
 
     def timed(fn, steps):
         barrier()
@@ -319,30 +403,34 @@ def gpu_arm(args, cfg):
     launches0 = B.launch_count()
     dev_s, _ = timed(step_device, args.steps)
     launches = B.launch_count() - launches0
-    net.packed = torch.empty_like(packed_dev)
+    resident = [host_copy(t) for t in step_device()]
     for _ in range(2):
         step_e2e()
     e2e_dev_s, e2e_wall = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None
     e2e_s = max(e2e_dev_s, e2e_wall)  # the step ends when the host holds the result
 
-    # sanity: the resident and the host-fed run computed the same thing
+    # sanity: the host-fed run computed what the resident run computed, and nothing overflowed
     ctx.synchronize()
+    outputs_ok = all(bool(torch.isfinite(h.float()).all()) and torch.equal(h, r) for h, r in zip(out_hosts, resident))
     result = None
     if rank == 0:
         peaks = load_peaks()
-        roof = layer_roofline(B, L, ctx, cfg, peaks, torch, fused=not args.eager)
+        if kind == "int8_trunk":
+            roof = int8_layer_roofline(B, L, ctx, cfg, peaks, torch)
+        else:
+            roof = layer_roofline(B, L, ctx, cfg, peaks, torch, fused=not args.eager)
         total_positions = batch * world * args.steps
         value = total_positions / dev_s
         fpp = flops_per_position(cfg)
         result = {
-            "metric": "positions/sec for ResNet trunk", "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC.get(kind, METRIC["trunk"]), "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "i8" if kind == "int8_trunk" else "f16", "data": "synthetic", "outputs_finite_and_equal": outputs_ok,
             "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world, "conv3x3": "three-kernel Winograd" if args.eager else "fused implicit GEMM",
                        "l2": "activations of every layer (%.0f MB) exceed the 126 MB L2, no flush needed" % (
                            batch * cfg["height"] * cfg["width"] * cfg["channels"] * 2 / 1e6)},
-            "algorithmic_tflops": value * fpp / 1e12, "frac_of_nominal_fp16_dense_peak": value * fpp / world / 2.25e15,
+            "algorithmic_tflops": value * fpp / 1e12, "frac_of_nominal_dense_peak": value * fpp / world / (4.5e15 if kind == "int8_trunk" else 2.25e15),
             "e2e": {"value": total_positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_s / args.steps * 1e3},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
@@ -374,7 +462,7 @@ def main():
             return
         steps = min(args.steps, 3)
         base = cpu_reference_arm(cfg, steps, min(args.warmup, 1))
-        line = {"impl": "reference", "metric": "positions/sec for ResNet trunk", "value": base["value"], "unit": "positions/s", "n_gpus": args.gpus,
+        line = {"impl": "reference", "metric": METRIC.get(cfg.get("kind", "trunk"), METRIC["trunk"]), "value": base["value"], "unit": "positions/s", "n_gpus": args.gpus,
                 "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": cfg["label"], "note": "host CPU implementation; each step is a bounded sample of the workload"},
