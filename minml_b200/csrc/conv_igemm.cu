@@ -52,17 +52,20 @@ namespace mb200
 		constexpr int A_STAGE_BYTES = BM * 128;
 		constexpr int EPI_PITCH = 80; // bytes per staged row: 64 of payload + 16 of padding against bank conflicts
 		constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
-		constexpr int MAX_STAGES = 6;
+		constexpr int MAX_STAGES = 8;
 
 		/* TMA_A: the A operand is fetched by im2col-mode TMA (one request per K slice) instead of the cp.async gather.
 		 * Possible when every 128-byte K slice lies inside one filter tap and the padding value is zero. */
-		template<int BN, bool TMA_A>
+		/* CTAS: 1 = every CTA computes 128 x BN tiles on its own; 2 = the two CTAs of a cluster compute a 256 x BN tile with
+		 * tcgen05 cta_group::2: each holds its own 128 rows of A and HALF of the weight slice, so the weight bytes a CTA pulls
+		 * from L2 per tile are halved (the operand fetch from L2, not the tensor pipe, is what limits the single-CTA kernel). */
+		template<int BN, bool TMA_A, int CTAS = 1>
 		struct Cfg
 		{
-				static constexpr int b_stage_bytes = BN * 128;
+				static constexpr int b_stage_bytes = BN / CTAS * 128;
 				// The two operand rings are sized separately: the gathered A slices (cp.async, many small requests) need more
 				// slices in flight to cover their latency than the weight slices that one TMA request fetches.
-				static constexpr int a_stages = TMA_A ? ((BN == 256) ? 4 : 6) : 6;
+				static constexpr int a_stages = (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
 				static constexpr int b_stages = TMA_A ? a_stages : ((BN == 256) ? 3 : 6);
 				static constexpr int smem_bytes = a_stages * A_STAGE_BYTES + b_stages * b_stage_bytes + 8 * EPI_WARP_BYTES + 1024;
 				static constexpr int tmem_columns = 2 * BN;
@@ -193,11 +196,12 @@ namespace mb200
 					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
 		}
 
-		template<int KIND, int BN, bool TMA_A>
+		template<int KIND, int BN, bool TMA_A, int CTAS>
 		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w,
 				const __grid_constant__ CUtensorMap map_x, const ConvParams p)
 		{
-			using C = Cfg<BN, TMA_A>;
+			static_assert(CTAS == 1 || TMA_A, "the paired kernel fetches both operands by TMA");
+			using C = Cfg<BN, TMA_A, CTAS>;
 			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
 			constexpr int CHUNK_ELEMS = 16 / ES;
 			extern __shared__ uint8_t smem_raw[];
@@ -211,8 +215,13 @@ namespace mb200
 
 			const int m_tiles = (p.M + BM - 1) / BM;
 			const int n_tiles = (p.cout + BN - 1) / BN;
-			const int total_tiles = m_tiles * n_tiles;
 			const int k_blocks = (p.K * ES + 127) / 128;
+			// A work unit is CTAS vertically adjacent 128-row tiles of one column block; CTA `cta_rank` of the cluster owns tile
+			// unit_m * CTAS + cta_rank (which may lie wholly beyond M for the last unit: it then computes on rows it never stores).
+			const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+			const bool leader = cta_rank == 0;
+			const int first_unit = blockIdx.x / CTAS, unit_step = gridDim.x / CTAS;
+			const int total_units = ((m_tiles + CTAS - 1) / CTAS) * n_tiles;
 
 			if (threadIdx.x == 0)
 			{
@@ -229,7 +238,7 @@ namespace mb200
 				for (int a = 0; a < 2; a++)
 				{
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
-					mbar_init(smem_u32(&bars.tmem_empty[a]), 8);
+					mbar_init(smem_u32(&bars.tmem_empty[a]), 8 * CTAS);
 				}
 				bars.abort_flag = 0;
 				fence_mbar_init();
@@ -240,7 +249,10 @@ namespace mb200
 				tmem_relinquish();
 			}
 			tcgen05_fence_before();
-			__syncthreads();
+			if (CTAS == 2)
+				cluster_sync(); // the peer's barriers exist before anything signals them
+			else
+				__syncthreads();
 			tcgen05_fence_after();
 			const uint32_t tmem_base = bars.tmem_base;
 			volatile int *abort_flag = &bars.abort_flag;
@@ -254,11 +266,13 @@ namespace mb200
 						prefetch_tensormap(&map_x);
 					uint32_t it = 0;
 					bool ok = true;
-					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+					for (int unit = first_unit; unit < total_units && ok; unit += unit_step)
 					{
-						const int nt = tile % n_tiles;
+						const int nt = unit % n_tiles;
 						// first output position of the tile -> (image, row, column); im2col TMA walks on from there
-						const int m0 = (tile / n_tiles) * BM;
+						int m0 = ((unit / n_tiles) * CTAS + static_cast<int>(cta_rank)) * BM;
+						if (CTAS == 2 && m0 >= p.M)
+							m0 = 0; // a tile wholly beyond M: fetch rows that exist, the epilogue stores none of them
 						const int img0 = m0 / (p.height * p.width);
 						const int h0 = (m0 - img0 * p.height * p.width) / p.width;
 						const int w0 = m0 - img0 * p.height * p.width - h0 * p.width;
@@ -271,6 +285,18 @@ namespace mb200
 								break;
 							}
 							const uint32_t full = smem_u32(&bars.full_b[s]);
+							if (CTAS == 2)
+							{ // both CTAs' slices are counted on the leader's barrier, which expects the bytes of both
+								if (leader)
+									mbar_arrive_expect_tx(full, 2 * (C::b_stage_bytes + A_STAGE_BYTES));
+								const uint32_t full_leader = map_to_cta(full, 0);
+								const int k0 = kb * (128 / ES);
+								const int tap = k0 / p.cin;
+								tma_load_im2col_4d_pair(smem_base + s * A_STAGE_BYTES, &map_x, full_leader, k0 - tap * p.cin, w0 - 1, h0 - 1, img0,
+										static_cast<uint16_t>(tap % 3), static_cast<uint16_t>(tap / 3));
+								tma_load_3d_pair(b_base + s * C::b_stage_bytes, &map_w, full_leader, k0, nt * BN + static_cast<int>(cta_rank) * (BN / 2), 0);
+								continue;
+							}
 							mbar_arrive_expect_tx(full, C::b_stage_bytes + (TMA_A ? A_STAGE_BYTES : 0));
 							if (TMA_A)
 							{
@@ -287,15 +313,17 @@ namespace mb200
 			}
 			else if (warp == 1)
 			{ /* ------------------------------------------- MMA issue */
-				if (elect_one())
-				{
-					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN);
+				if (leader && elect_one())
+				{ // in a pair only the even CTA issues; its instructions drive the tensor cores of both SMs
+					const uint32_t idesc = (CTAS == 2) ? ((KIND == 0) ? make_idesc_f16_pair(BN) : make_idesc_i8_pair(BN))
+							: ((KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN));
 					uint32_t it = 0, local_tile = 0;
 					bool ok = true;
-					for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local_tile++)
+					for (int unit = first_unit; unit < total_units && ok; unit += unit_step, local_tile++)
 					{
 						const uint32_t buf = local_tile & 1u;
-						if (!mbar_wait(smem_u32(&bars.tmem_empty[buf]), ((local_tile >> 1) & 1u) ^ 1u, abort_flag))
+						const uint32_t empty_bar = smem_u32(&bars.tmem_empty[buf]), empty_parity = ((local_tile >> 1) & 1u) ^ 1u;
+						if (!((CTAS == 2) ? mbar_wait_cluster(empty_bar, empty_parity, abort_flag) : mbar_wait(empty_bar, empty_parity, abort_flag)))
 							break;
 						tcgen05_fence_after();
 						const uint32_t tmem_d = tmem_base + buf * BN;
@@ -313,15 +341,30 @@ namespace mb200
 								fence_proxy_async_smem(); // the A slice was written through the generic proxy by other threads
 							const uint64_t desc_a = make_desc_k_sw128(smem_base + sa * A_STAGE_BYTES);
 							const uint64_t desc_b = make_desc_k_sw128(b_base + sb * C::b_stage_bytes);
+							if (CTAS == 2)
+							{
 #pragma unroll
-							for (int k = 0; k < 4; k++)
-								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-							if (!TMA_A)
-								mma_commit(smem_u32(&bars.empty_a[sa]));
-							mma_commit(smem_u32(&bars.empty_b[sb]));
+								for (int k = 0; k < 4; k++)
+									mma_ss_pair<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+								mma_commit_pair(smem_u32(&bars.empty_b[sb])); // frees the stage in both CTAs
+							}
+							else
+							{
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+								if (!TMA_A)
+									mma_commit(smem_u32(&bars.empty_a[sa]));
+								mma_commit(smem_u32(&bars.empty_b[sb]));
+							}
 						}
 						if (ok)
-							mma_commit(smem_u32(&bars.tmem_full[buf]));
+						{
+							if (CTAS == 2)
+								mma_commit_pair(smem_u32(&bars.tmem_full[buf]));
+							else
+								mma_commit(smem_u32(&bars.tmem_full[buf]));
+						}
 					}
 				}
 				__syncwarp();
@@ -334,10 +377,10 @@ namespace mb200
 				const int rr = lane / 4, seg = lane % 4; // cooperative access: 8 rows x 4 segments of 16 bytes per instruction
 				const bool rows_vectorisable = (p.cout % 8 == 0) && aligned_to_16(p.y) && (p.ext == nullptr || aligned_to_16(p.ext));
 				uint32_t local_tile = 0;
-				for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
+				for (int unit = first_unit; unit < total_units; unit += unit_step, local_tile++)
 				{
-					const int nt = tile % n_tiles;
-					const int mt = tile / n_tiles;
+					const int nt = unit % n_tiles;
+					const int mt = (unit / n_tiles) * CTAS + static_cast<int>(cta_rank);
 					const uint32_t buf = local_tile & 1u;
 					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), (local_tile >> 1) & 1u, abort_flag))
 						break;
@@ -602,7 +645,12 @@ namespace mb200
 					tcgen05_fence_before();
 					__syncwarp();
 					if (lane == 0)
-						mbar_arrive(smem_u32(&bars.tmem_empty[buf]));
+					{
+						if (CTAS == 2) // the issuing CTA waits for the epilogue warps of both
+							mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[buf]), 0));
+						else
+							mbar_arrive(smem_u32(&bars.tmem_empty[buf]));
+					}
 				}
 			}
 			else if (!TMA_A && (warp == 10 || warp == 11 || warp == 14 || warp == 15))
@@ -620,9 +668,9 @@ namespace mb200
 				constexpr int ROWS = BM / 16; // rows per producer thread
 				uint32_t it = 0;
 				bool ok = true;
-				for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+				for (int unit = first_unit; unit < total_units && ok; unit += unit_step)
 				{
-					const int mt = tile / n_tiles;
+					const int mt = unit / n_tiles;
 					uint32_t tap_mask[ROWS]; // bit t set: tap t of this row lies inside the image (0 for a row beyond M)
 					int pos_off[ROWS]; // element offset of the position's channel 0
 #pragma unroll
@@ -680,7 +728,10 @@ namespace mb200
 
 			/* ---------------------------------------------------------------- teardown */
 			tcgen05_fence_before();
-			__syncthreads();
+			if (CTAS == 2)
+				cluster_sync(); // neither CTA retires while the other may still signal its barriers or read its operands
+			else
+				__syncthreads();
 			if (bars.abort_flag != 0)
 			{
 				if (threadIdx.x == 0 && p.status != nullptr)
@@ -701,17 +752,68 @@ namespace mb200
 			static bool configured = false;
 			if (!configured)
 			{
-				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
 						"conv_igemm: shared memory opt-in"))
 					return false;
 				configured = true;
 			}
 			const int tiles = ((p.M + BM - 1) / BM) * ((p.cout + BN - 1) / BN);
 			const int grid = std::min(tiles, get(ctx)->sm_count);
-			kernel_conv3x3_igemm<KIND, BN, TMA_A> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
+			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
 			MB200_COUNT_LAUNCH();
 			get(ctx)->kernels_with_waits = true;
 			return check_cuda(ctx, cudaGetLastError(), "conv_igemm launch");
+		}
+
+		/* Paired kernel: clusters of two CTAs, as many clusters as the device can hold at once (queried once per device). */
+		template<int KIND, int BN>
+		bool launch_pair(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
+		{
+			using C = Cfg<BN, true, 2>;
+			static int max_clusters[64] = { 0 }; // per device; 0 = not queried yet, -1 = clusters of this size cannot be placed
+			const int device = get(ctx)->device;
+			cudaLaunchConfig_t config;
+			std::memset(&config, 0, sizeof(config));
+			cudaLaunchAttribute attribute;
+			attribute.id = cudaLaunchAttributeClusterDimension;
+			attribute.val.clusterDim.x = 2;
+			attribute.val.clusterDim.y = 1;
+			attribute.val.clusterDim.z = 1;
+			config.blockDim = dim3(NUM_THREADS, 1, 1);
+			config.dynamicSmemBytes = C::smem_bytes;
+			config.stream = use_stream(ctx);
+			config.attrs = &attribute;
+			config.numAttrs = 1;
+			if (device < 0 || device >= 64)
+				return false;
+			if (max_clusters[device] == 0)
+			{
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+						"conv_igemm pair: shared memory opt-in"))
+					return false;
+				config.gridDim = dim3(2 * (get(ctx)->sm_count / 2), 1, 1);
+				int n = 0;
+				if (cudaOccupancyMaxActiveClusters(&n, kernel_conv3x3_igemm<KIND, BN, true, 2>, &config) != cudaSuccess || n <= 0)
+				{
+					cudaGetLastError();
+					n = -1;
+				}
+				max_clusters[device] = n;
+			}
+			if (max_clusters[device] < 0)
+				return false;
+			const int units = (((p.M + BM - 1) / BM + 1) / 2) * ((p.cout + BN - 1) / BN);
+			config.gridDim = dim3(2 * std::min(units, max_clusters[device]), 1, 1);
+			const cudaError_t status = cudaLaunchKernelEx(&config, kernel_conv3x3_igemm<KIND, BN, true, 2>, map_w, map_x, p);
+			MB200_COUNT_LAUNCH();
+			get(ctx)->kernels_with_waits = true;
+			return check_cuda(ctx, status, "conv_igemm pair launch") && check_cuda(ctx, cudaGetLastError(), "conv_igemm pair launch");
+		}
+
+		bool env_flag(const char *name)
+		{
+			const char *v = std::getenv(name);
+			return v != nullptr && v[0] == '1';
 		}
 
 		bool shape_ok(int kind, const mlTensor_t &x, int cout, const void *w)
@@ -791,20 +893,28 @@ namespace mb200
 			p.K = 9 * x.dim[3];
 			p.status = get(ctx)->dev_status;
 			const int bn = (cout > 128) ? 256 : 128;
+			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
+			static const bool force_gather = env_flag("MINML_B200_CONV_GATHER"); // measurement switches: each forces the slower variant
+			static const bool force_single = env_flag("MINML_B200_CONV_SINGLE_CTA");
+			const bool tma_a = (p.cin * es) % 128 == 0 && p.pad_byte == 0 && !force_gather;
+			const bool pair = tma_a && !force_single && p.M > BM && get(ctx)->sm_count >= 2;
 			CUtensorMap map_w;
 			const uint64_t dims[3] = { static_cast<uint64_t>(p.K), static_cast<uint64_t>(cout), 1 };
 			const uint64_t strides[2] = { static_cast<uint64_t>(p.K) * es, static_cast<uint64_t>(p.K) * es * cout };
-			const uint32_t box[3] = { static_cast<uint32_t>(128 / es), static_cast<uint32_t>(bn), 1 };
+			const uint32_t box[3] = { static_cast<uint32_t>(128 / es), static_cast<uint32_t>(pair ? bn / 2 : bn), 1 };
 			if (!encode_tensor_map(ctx, &map_w, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box,
 					CU_TENSOR_MAP_SWIZZLE_128B))
 				return false;
-			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
-			const char *force_gather = std::getenv("MINML_B200_CONV_GATHER");
-			const bool tma_a = (p.cin * es) % 128 == 0 && p.pad_byte == 0 && !(force_gather != nullptr && force_gather[0] == '1');
 			CUtensorMap map_x;
 			std::memset(&map_x, 0, sizeof(map_x));
 			if (tma_a && !encode_im2col_map(ctx, &map_x, kind, x))
 				return false;
+			if (pair)
+			{
+				if (kind == 0)
+					return bn == 256 ? launch_pair<0, 256>(ctx, map_w, map_x, p) : launch_pair<0, 128>(ctx, map_w, map_x, p);
+				return bn == 256 ? launch_pair<1, 256>(ctx, map_w, map_x, p) : launch_pair<1, 128>(ctx, map_w, map_x, p);
+			}
 			if (kind == 0)
 			{
 				if (tma_a)

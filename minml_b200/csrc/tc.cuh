@@ -199,6 +199,109 @@ namespace mb200
 		{
 			asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 		}
+
+		/* ---------------------------------------------------------------- CTA pairs (cluster of 2, tcgen05 cta_group::2)
+		 * One tcgen05.mma issued by the even CTA of the pair multiplies a 256-row A tile (128 rows in each CTA's shared
+		 * memory) by a B tile whose N rows are split in halves between the two CTAs; each CTA's tensor memory receives
+		 * the 128 accumulator rows of its own A half.  Both CTAs use the same shared-memory layout, so one descriptor
+		 * names the operand in both. */
+		__device__ __forceinline__ uint32_t cluster_ctarank()
+		{
+			uint32_t r;
+			asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+			return r;
+		}
+		/* shared::cluster address of the same shared-memory location in the CTA of rank `cta` */
+		__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
+		{
+			uint32_t r;
+			asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+			return r;
+		}
+		/* All threads of all CTAs of the cluster; release / acquire at cluster scope. */
+		__device__ __forceinline__ void cluster_sync()
+		{
+			asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+			asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+		}
+		/* `bar` is a shared::cluster address (own or peer CTA). */
+		__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar)
+		{
+			asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar) : "memory");
+		}
+		__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+		{
+			uint32_t done;
+			asm volatile(
+					"{\n\t"
+					".reg .pred P;\n\t"
+					"mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+					"selp.u32 %0, 1, 0, P;\n\t"
+					"}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+			return done != 0;
+		}
+		/* Bounded wait on an own barrier whose arrivals come from the peer CTA as well. */
+		__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+		{
+			for (uint32_t it = 0; it < SPIN_LIMIT; ++it)
+			{
+				if (mbar_try_wait_cluster(bar, parity))
+					return true;
+				if ((it & 255u) == 255u && *abort_flag != 0)
+					return false;
+			}
+			*abort_flag = 1;
+			return false;
+		}
+		/* TMA loads into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair
+		 * (`bar` is a shared::cluster address).  The source is always this GPU's own memory; no multicast. */
+		__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+		}
+		__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n,
+				uint16_t off_w, uint16_t off_h)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+		}
+		template<int KIND>
+		__device__ __forceinline__ void mma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+		{
+			if (KIND == 0)
+				asm volatile(
+						"{\n\t"
+						".reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+			else
+				asm volatile(
+						"{\n\t"
+						".reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+		}
+		/* One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once every tcgen05.mma issued so
+		 * far by this thread has completed.  (A barrier arrival, not a data load.) */
+		__device__ __forceinline__ void mma_commit_pair(uint32_t bar)
+		{
+			asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+					:: "r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+		}
+		/* Instruction descriptors with M = 256 (128 rows per CTA). */
+		__host__ __device__ constexpr uint32_t make_idesc_f16_pair(int n)
+		{
+			return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+		}
+		__host__ __device__ constexpr uint32_t make_idesc_i8_pair(int n)
+		{
+			return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+		}
 	} /* namespace tc */
 
 	/* Host side: cuTensorMapEncodeTiled fetched through the runtime so the library has no link-time dependency
