@@ -897,7 +897,10 @@ namespace mb200
 			static const bool force_gather = env_flag("MINML_B200_CONV_GATHER"); // measurement switches: each forces the slower variant
 			static const bool force_single = env_flag("MINML_B200_CONV_SINGLE_CTA");
 			const bool tma_a = (p.cin * es) % 128 == 0 && p.pad_byte == 0 && !force_gather;
-			const bool pair = tma_a && !force_single && p.M > BM && get(ctx)->sm_count >= 2;
+			// Pairs pay off where the operand fetch is the limit (256-column tiles: 0.383 -> 0.353 ms on the 256 -> 256 layer); with
+			// 128-column tiles the epilogue is, and coupling two CTAs' accumulator hand-offs costs more than it saves (measured).
+			static const bool force_pair = env_flag("MINML_B200_CONV_PAIR");
+			const bool pair = tma_a && !force_single && (bn == 256 || force_pair) && p.M > BM && get(ctx)->sm_count >= 2;
 			CUtensorMap map_w;
 			const uint64_t dims[3] = { static_cast<uint64_t>(p.K), static_cast<uint64_t>(cout), 1 };
 			const uint64_t strides[2] = { static_cast<uint64_t>(p.K) * es, static_cast<uint64_t>(p.K) * es * cout };
