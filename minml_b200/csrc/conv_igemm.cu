@@ -46,8 +46,17 @@ namespace mb200
 		using namespace tc;
 
 		constexpr int BM = 128;
-		constexpr int NUM_THREADS = 16 * 32;
-		constexpr int PRODUCER_WARP0 = 10;
+		/* Warp roles.  Warp 0: TMA, warp 1: MMA issue, then the epilogue warps, then (gather variant) the A-operand producers on
+		 * warps 10, 11, 14, 15.  The int8 epilogue costs about 22 instructions per output element against 4 for fp16 and its
+		 * tiles take half as many tensor cycles, so the int8 TMA variant runs 16 epilogue warps (four per tensor-memory lane
+		 * quarter) instead of 8. */
+		template<int KIND, bool TMA_A>
+		struct Roles
+		{
+				static constexpr int epi_warps = (KIND == 1 && TMA_A) ? 16 : 8;
+				static constexpr int threads = (TMA_A ? (2 + epi_warps) : 16) * 32;
+				static constexpr int staging_bytes = (KIND == 0) ? 8 * 32 * 80 : 0; // only the fp16 epilogue stages rows in shared memory
+		};
 		constexpr int NUM_PRODUCERS = 128;
 		constexpr int A_STAGE_BYTES = BM * 128;
 		constexpr int EPI_PITCH = 80; // bytes per staged row: 64 of payload + 16 of padding against bank conflicts
@@ -59,7 +68,7 @@ namespace mb200
 		/* CTAS: 1 = every CTA computes 128 x BN tiles on its own; 2 = the two CTAs of a cluster compute a 256 x BN tile with
 		 * tcgen05 cta_group::2: each holds its own 128 rows of A and HALF of the weight slice, so the weight bytes a CTA pulls
 		 * from L2 per tile are halved (the operand fetch from L2, not the tensor pipe, is what limits the single-CTA kernel). */
-		template<int BN, bool TMA_A, int CTAS = 1>
+		template<int KIND, int BN, bool TMA_A, int CTAS = 1>
 		struct Cfg
 		{
 				static constexpr int b_stage_bytes = BN / CTAS * 128;
@@ -67,7 +76,7 @@ namespace mb200
 				// slices in flight to cover their latency than the weight slices that one TMA request fetches.
 				static constexpr int a_stages = (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
 				static constexpr int b_stages = TMA_A ? a_stages : ((BN == 256) ? 3 : 6);
-				static constexpr int smem_bytes = a_stages * A_STAGE_BYTES + b_stages * b_stage_bytes + 8 * EPI_WARP_BYTES + 1024;
+				static constexpr int smem_bytes = a_stages * A_STAGE_BYTES + b_stages * b_stage_bytes + Roles<KIND, TMA_A>::staging_bytes + 1024;
 				static constexpr int tmem_columns = 2 * BN;
 		};
 
@@ -188,6 +197,15 @@ namespace mb200
 			}
 		}
 
+		/* Four int32 -> four int8 with saturation, byte t of the result = value t. */
+		__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
+		{
+			uint32_t hi, out;
+			asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+			asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+			return out;
+		}
+
 		__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n,
 				uint16_t off_w, uint16_t off_h)
 		{
@@ -197,11 +215,13 @@ namespace mb200
 		}
 
 		template<int KIND, int BN, bool TMA_A, int CTAS>
-		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w,
+		__global__ void __launch_bounds__((Roles<KIND, TMA_A>::threads), 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w,
 				const __grid_constant__ CUtensorMap map_x, const ConvParams p)
 		{
 			static_assert(CTAS == 1 || TMA_A, "the paired kernel fetches both operands by TMA");
-			using C = Cfg<BN, TMA_A, CTAS>;
+			using C = Cfg<KIND, BN, TMA_A, CTAS>;
+			constexpr int EPI_WARPS = Roles<KIND, TMA_A>::epi_warps;
+			constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
 			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
 			constexpr int CHUNK_ELEMS = 16 / ES;
 			extern __shared__ uint8_t smem_raw[];
@@ -238,7 +258,7 @@ namespace mb200
 				for (int a = 0; a < 2; a++)
 				{
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
-					mbar_init(smem_u32(&bars.tmem_empty[a]), 8 * CTAS);
+					mbar_init(smem_u32(&bars.tmem_empty[a]), EPI_WARPS * CTAS);
 				}
 				bars.abort_flag = 0;
 				fence_mbar_init();
@@ -369,13 +389,15 @@ namespace mb200
 				}
 				__syncwarp();
 			}
-			else if (warp < PRODUCER_WARP0)
+			else if (warp < 2 + EPI_WARPS)
 			{ /* ------------------------------------------------------------ epilogue */
 				const int q = warp % 4; // tensor-memory lane quarter
-				const int col_half = (warp - 2) / 4; // which half of the BN columns this warp handles
+				const int col_part = (warp - 2) / 4; // which share of the BN columns this warp handles
 				const uint32_t sbuf = epi_base + (warp - 2) * EPI_WARP_BYTES;
 				const int rr = lane / 4, seg = lane % 4; // cooperative access: 8 rows x 4 segments of 16 bytes per instruction
 				const bool rows_vectorisable = (p.cout % 8 == 0) && aligned_to_16(p.y) && (p.ext == nullptr || aligned_to_16(p.ext));
+				const bool i8_rows_vectorisable = p.out_dtype == DTYPE_INT8 && (p.cout % 16) == 0 && aligned_to_16(p.y) && aligned_to_16(p.scales)
+						&& aligned_to_16(p.shifts) && (p.ext == nullptr || aligned_to_16(p.ext));
 				uint32_t local_tile = 0;
 				for (int unit = first_unit; unit < total_units; unit += unit_step, local_tile++)
 				{
@@ -389,10 +411,10 @@ namespace mb200
 					const int row = row0 + lane;
 					const bool row_ok = row < p.M;
 					const long long off = static_cast<long long>(row) * p.cout;
-					const int col_begin = col_half * (BN / 2);
+					const int col_begin = col_part * COLS_PER_WARP;
 					const int n_valid_tile = min(BN, p.cout - nt * BN);
 					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-					for (int c = col_begin / 32; c < (col_begin + BN / 2) / 32; c++)
+					for (int c = col_begin / 32; c < (col_begin + COLS_PER_WARP) / 32; c++)
 					{
 						if (c * 32 >= n_valid_tile)
 							break; // warp-uniform
@@ -411,6 +433,15 @@ namespace mb200
 								res[i] = (r < p.M) ? *reinterpret_cast<const uint4*>(ep + static_cast<long long>(r) * p.cout + n0 + seg * 8) : make_uint4(0,
 										0, 0, 0);
 							}
+						}
+						const bool fast_i8 = (KIND == 1) && i8_rows_vectorisable && n_valid == 32;
+						uint32_t ext_words[8];
+						if (fast_i8 && p.ext != nullptr && row_ok)
+						{ // likewise: the int8 residual row segment of this lane
+							const uint4 *ep = reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(p.ext) + off + n0);
+							const uint4 e0 = ep[0], e1 = ep[1];
+							ext_words[0] = e0.x; ext_words[1] = e0.y; ext_words[2] = e0.z; ext_words[3] = e0.w;
+							ext_words[4] = e1.x; ext_words[5] = e1.y; ext_words[6] = e1.z; ext_words[7] = e1.w;
 						}
 						uint32_t r[32];
 						tmem_ld_32x32(taddr + c * 32, r);
@@ -468,8 +499,7 @@ namespace mb200
 							continue;
 						}
 
-						if (KIND == 1 && p.out_dtype == DTYPE_INT8 && n_valid == 32 && (p.cout % 16) == 0 && aligned_to_16(p.y) && aligned_to_16(p.scales)
-								&& aligned_to_16(p.shifts) && (p.ext == nullptr || aligned_to_16(p.ext)))
+						if (fast_i8)
 						{ /* int8 -> int8 fast path.  The arithmetic is the scalar loop of the reference's CPU backend, operation for
 						   * operation and without fused multiply-adds: x = acc * scale[c] + shift[c] (+ ext * s_e + z_e); activation;
 						   * q = clamp(round(x * (1 / s_o) + (-z_o / s_o)))  (src/layers/Conv2D.cpp:283-304, src/layers/quantization.cpp:43-47) */
@@ -477,14 +507,6 @@ namespace mb200
 								continue;
 							const float4 *sp = reinterpret_cast<const float4*>(p.scales + n0);
 							const float4 *hp = reinterpret_cast<const float4*>(p.shifts + n0);
-							uint32_t ext_words[8];
-							if (p.ext != nullptr)
-							{
-								const uint4 *ep = reinterpret_cast<const uint4*>(reinterpret_cast<const int8_t*>(p.ext) + off + n0);
-								const uint4 e0 = ep[0], e1 = ep[1];
-								ext_words[0] = e0.x; ext_words[1] = e0.y; ext_words[2] = e0.z; ext_words[3] = e0.w;
-								ext_words[4] = e1.x; ext_words[5] = e1.y; ext_words[6] = e1.z; ext_words[7] = e1.w;
-							}
 							const bool relu = p.act == ACTIVATION_RELU;
 							const bool other_act = p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH;
 							uint32_t packed[8];
@@ -493,7 +515,7 @@ namespace mb200
 							{
 								const float4 sc = sp[g4], sh = hp[g4];
 								const float scs[4] = { sc.x, sc.y, sc.z, sc.w }, shs[4] = { sh.x, sh.y, sh.z, sh.w };
-								uint32_t w4 = 0;
+								int q4[4];
 #pragma unroll
 								for (int t = 0; t < 4; t++)
 								{
@@ -507,10 +529,11 @@ namespace mb200
 										x = fmaxf(x, 0.0f);
 									else if (other_act)
 										x = activation_out_of_line(x, p.act);
-									const float qf = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(x, p.inv_out_scale), p.inv_out_shift))));
-									w4 |= (static_cast<uint32_t>(static_cast<int>(qf)) & 0xFFu) << (8 * t);
+									// round half away from zero, then saturate: the float -> int conversion saturates at the int32 range and
+									// the packing instruction at the int8 range, which together are the reference's clamp(round(.), -128, 127)
+									q4[t] = __float2int_rz(roundf(__fadd_rn(__fmul_rn(x, p.inv_out_scale), p.inv_out_shift)));
 								}
-								packed[g4] = w4;
+								packed[g4] = pack_sat_s8x4(q4[0], q4[1], q4[2], q4[3]);
 							}
 							int8_t *dp = reinterpret_cast<int8_t*>(p.y) + off + n0;
 							*reinterpret_cast<uint4*>(dp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -562,7 +585,6 @@ namespace mb200
 						}
 						const int8_t *ep = (p.ext != nullptr) ? reinterpret_cast<const int8_t*>(p.ext) + off + n0 : nullptr;
 						const bool act_on = (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU);
-						uint32_t ext_words[8];
 						const bool ext_vec = ep != nullptr && n_valid == 32 && (reinterpret_cast<uintptr_t>(ep) % 16) == 0;
 						if (ext_vec)
 						{
@@ -748,7 +770,7 @@ namespace mb200
 		template<int KIND, int BN, bool TMA_A>
 		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
-			using C = Cfg<BN, TMA_A>;
+			using C = Cfg<KIND, BN, TMA_A>;
 			static bool configured = false;
 			if (!configured)
 			{
@@ -759,7 +781,7 @@ namespace mb200
 			}
 			const int tiles = ((p.M + BM - 1) / BM) * ((p.cout + BN - 1) / BN);
 			const int grid = std::min(tiles, get(ctx)->sm_count);
-			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1> <<<grid, NUM_THREADS, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
+			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1> <<<grid, Roles<KIND, TMA_A>::threads, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
 			MB200_COUNT_LAUNCH();
 			get(ctx)->kernels_with_waits = true;
 			return check_cuda(ctx, cudaGetLastError(), "conv_igemm launch");
@@ -769,7 +791,7 @@ namespace mb200
 		template<int KIND, int BN>
 		bool launch_pair(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
-			using C = Cfg<BN, true, 2>;
+			using C = Cfg<KIND, BN, true, 2>;
 			static int max_clusters[64] = { 0 }; // per device; 0 = not queried yet, -1 = clusters of this size cannot be placed
 			const int device = get(ctx)->device;
 			cudaLaunchConfig_t config;
@@ -779,7 +801,7 @@ namespace mb200
 			attribute.val.clusterDim.x = 2;
 			attribute.val.clusterDim.y = 1;
 			attribute.val.clusterDim.z = 1;
-			config.blockDim = dim3(NUM_THREADS, 1, 1);
+			config.blockDim = dim3(Roles<KIND, true>::threads, 1, 1);
 			config.dynamicSmemBytes = C::smem_bytes;
 			config.stream = use_stream(ctx);
 			config.attrs = &attribute;

@@ -110,16 +110,30 @@ def main():
     ctx.set_fusion(True)
 
     # ---- heads: 1x1 policy convolution (N = 1), global average pooling, dense value head (N = 3)
-    wp = rand(1, c)
+    wp, bp, bv = rand(1, c), rand(1), rand(3)
     pol = torch.empty((rows, 1), device="cuda", dtype=f16)
-    add("gemm_ex 1x1 policy head [rows,c] x [1,c]^T", lambda: B.gemm_ex(ctx, pol, 1.0, "n", x.view(rows, c), "t", wp, 0.0, None, rand(1), "linear"),
+    add("gemm_ex 1x1 policy head [rows,c] x [1,c]^T", lambda: B.gemm_ex(ctx, pol, 1.0, "n", x.view(rows, c), "t", wp, 0.0, None, bp, "linear"),
         act_bytes + rows * 2, 2.0 * rows * c)
     pooled = torch.empty((b, c), device="cuda", dtype=f16)
     add("global_average_pooling", lambda: B.globalAveragePoolingForward(ctx, x, pooled), act_bytes + b * c * 2)
     wv = rand(3, c)
     val = torch.empty((b, 3), device="cuda", dtype=f16)
-    add("gemm_ex dense value head [b,c] x [3,c]^T", lambda: B.gemm_ex(ctx, val, 1.0, "n", pooled, "t", wv, 0.0, None, rand(3), "linear"),
+    add("gemm_ex dense value head [b,c] x [3,c]^T", lambda: B.gemm_ex(ctx, val, 1.0, "n", pooled, "t", wv, 0.0, None, bv, "linear"),
         b * c * 2 + b * 6, 2.0 * b * c * 3, note="launch-latency bound at this size")
+
+    # ---- 1x1 convolutions / dense layers of the attention block: gemm_ex with fused bias (+ residual, + ReLU)
+    for n_out, k_in, label in ((3 * c, c, "qkv projection"), (c, c, "output projection + residual"), (4 * c, c, "FFN up + relu"),
+                               (c, 4 * c, "FFN down + residual")):
+        a_in = rand(rows, k_in)
+        w_in, b_in = rand(n_out, k_in), rand(n_out)
+        out = torch.empty((rows, n_out), device="cuda", dtype=f16)
+        ext = rand(rows, n_out) if "residual" in label else None
+        act = "relu" if "relu" in label else "linear"
+        add("gemm_ex [rows,%d] x [%d,%d]^T %s" % (k_in, n_out, k_in, label),
+            lambda a_in=a_in, w_in=w_in, b_in=b_in, out=out, ext=ext, act=act: B.gemm_ex(ctx, out, 1.0, "n", a_in, "t", w_in, 1.0 if ext is not None else 0.0,
+                                                                                          ext, b_in, act),
+            rows * (k_in + n_out * (2 if ext is not None else 1)) * 2 + n_out * k_in * 2, 2.0 * rows * n_out * k_in)
+        del a_in, w_in, out, ext
 
     # ---- elementwise / layout
     packed = torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
