@@ -35,6 +35,7 @@
 #include "common.cuh"
 #include "conv.cuh"
 #include "tc.cuh"
+#include "epilogue.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -44,6 +45,7 @@ namespace mb200
 	namespace
 	{
 		using namespace tc;
+		using namespace epi;
 
 		constexpr int BM = 128;
 		/* Warp roles.  Warp 0: TMA, warp 1: MMA issue, then the epilogue warps, then (gather variant) the A-operand producers on
@@ -59,8 +61,8 @@ namespace mb200
 		};
 		constexpr int NUM_PRODUCERS = 128;
 		constexpr int A_STAGE_BYTES = BM * 128;
-		constexpr int EPI_PITCH = 80; // bytes per staged row: 64 of payload + 16 of padding against bank conflicts
-		constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
+		constexpr int EPI_PITCH = epi::PITCH;
+		constexpr int EPI_WARP_BYTES = epi::WARP_BYTES;
 		constexpr int MAX_STAGES = 8;
 
 		/* TMA_A: the A operand is fetched by im2col-mode TMA (one request per K slice) instead of the cp.async gather.
@@ -136,76 +138,6 @@ namespace mb200
 		{
 			asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" :: "r"(dst), "r"(v) : "memory");
 		}
-		__device__ __forceinline__ void st_shared_v4(uint32_t dst, const uint4 &v)
-		{
-			asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-		}
-		__device__ __forceinline__ uint4 ld_shared_v4(uint32_t src)
-		{
-			uint4 v;
-			asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(src) : "memory");
-			return v;
-		}
-		__device__ __forceinline__ bool aligned_to_16(const void *ptr)
-		{
-			return (reinterpret_cast<uintptr_t>(ptr) % 16) == 0;
-		}
-		__device__ __forceinline__ void add_half8(float *v, const uint4 &raw)
-		{
-			const uint32_t w4[4] = { raw.x, raw.y, raw.z, raw.w };
-#pragma unroll
-			for (int t = 0; t < 4; t++)
-			{
-				const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[t]));
-				v[2 * t] += f.x;
-				v[2 * t + 1] += f.y;
-			}
-		}
-		__device__ __forceinline__ uint4 pack_half8(const float *v)
-		{
-			uint4 pk;
-			const __half2 h0 = __floats2half2_rn(v[0], v[1]);
-			const __half2 h1 = __floats2half2_rn(v[2], v[3]);
-			const __half2 h2 = __floats2half2_rn(v[4], v[5]);
-			const __half2 h3 = __floats2half2_rn(v[6], v[7]);
-			pk.x = *reinterpret_cast<const uint32_t*>(&h0);
-			pk.y = *reinterpret_cast<const uint32_t*>(&h1);
-			pk.z = *reinterpret_cast<const uint32_t*>(&h2);
-			pk.w = *reinterpret_cast<const uint32_t*>(&h3);
-			return pk;
-		}
-
-		/* Everything but ReLU goes through one out-of-line call per element: the epilogue code stays small enough for the
-		 * instruction cache that the gather, the MMA issue and the epilogue share. */
-		__device__ __noinline__ float activation_out_of_line(float x, int act)
-		{
-			return apply_activation(x, act);
-		}
-		__device__ __forceinline__ void activate32(float (&v)[32], int act)
-		{
-			if (act == ACTIVATION_RELU)
-			{
-#pragma unroll
-				for (int j = 0; j < 32; j++)
-					v[j] = fmaxf(v[j], 0.0f);
-			}
-			else if (act != ACTIVATION_LINEAR)
-			{
-#pragma unroll
-				for (int j = 0; j < 32; j++)
-					v[j] = activation_out_of_line(v[j], act);
-			}
-		}
-
-		/* Four int32 -> four int8 with saturation, byte t of the result = value t. */
-		__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
-		{
-			uint32_t hi, out;
-			asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
-			asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
-			return out;
-		}
-
 		__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n,
 				uint16_t off_w, uint16_t off_h)
 		{

@@ -9,14 +9,16 @@
  * Design (one CTA per SM, persistent over output tiles of 128 x BN):
  *   warp 0      TMA producer: A and B tiles (128 bytes of K per row, 128B swizzle) into a ring of shared-memory stages
  *   warp 1      issues tcgen05.mma (one elected lane); owns the tensor-memory allocation
- *   warps 2-5   epilogue: tcgen05.ld of the fp32 / s32 accumulators, alpha/beta/bias/activation or requantisation,
- *               vectorised stores.  Two accumulator buffers in tensor memory let the epilogue of tile i overlap the
- *               main loop of tile i+1.
+ *   warps 2-9   epilogue (two warps per tensor-memory lane quarter, each half of the tile's columns): tcgen05.ld of the
+ *               fp32 / s32 accumulators, alpha/beta/bias/activation or requantisation.  fp16 results (and the fp16 C operand)
+ *               are staged through shared memory so that one global access covers 8 rows x 64 contiguous bytes.  Two
+ *               accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of tile i+1.
  * Both operands are K-major (row-major A[M,K] and B[N,K]); K tails and M/N tails are zero-filled by TMA.
  */
 #include "common.cuh"
 #include "tc.cuh"
 #include "gemm.cuh"
+#include "epilogue.cuh"
 
 #include <cuda.h>
 
@@ -72,17 +74,19 @@ namespace mb200
 	namespace
 	{
 		using namespace tc;
+		using namespace epi;
 
 		constexpr int BM = 128;
 		constexpr int BK_BYTES = 128; // one swizzle row: 64 fp16 or 128 int8
-		constexpr int NUM_THREADS = 192;
+		constexpr int EPI_WARPS = 8;
+		constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 
 		template<int BN>
 		struct Tiling
 		{
 				static constexpr int stage_bytes = BM * BK_BYTES + BN * BK_BYTES;
 				static constexpr int stages = (BN == 256) ? 4 : 6;
-				static constexpr int smem_bytes = stages * stage_bytes + 1024;
+				static constexpr int smem_bytes = stages * stage_bytes + EPI_WARPS * epi::WARP_BYTES + 1024;
 				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
 		};
 
@@ -129,7 +133,7 @@ namespace mb200
 				for (int a = 0; a < 2; a++)
 				{
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
-					mbar_init(smem_u32(&bars.tmem_empty[a]), 4);
+					mbar_init(smem_u32(&bars.tmem_empty[a]), EPI_WARPS);
 				}
 				bars.abort_flag = 0;
 				fence_mbar_init();
@@ -222,6 +226,13 @@ namespace mb200
 			else
 			{ /* ------------------------------------------------------------ epilogue */
 				const int q = warp % 4; // tensor-memory lane quarter this warp may read
+				const int col_part = (warp - 2) / 4; // which half of the tile's columns
+				const uint32_t sbuf = smem_base + T::stages * T::stage_bytes + (warp - 2) * epi::WARP_BYTES;
+				const int rr = lane / 4, seg = lane % 4; // cooperative access: 8 rows x 4 segments of 16 bytes per instruction
+				const bool use_c = p.beta != 0.0f && p.C != nullptr;
+				// fp16 rows can be moved in 16-byte pieces when every row (of every batch item) starts on a 16-byte boundary
+				const bool rows_vectorisable = (KIND == 0) && p.out_dtype == DTYPE_FLOAT16 && aligned_to_16(p.D) && (p.ldd % 8) == 0
+						&& (p.stride_d % 8) == 0 && (!use_c || (aligned_to_16(p.C) && (p.ldc % 8) == 0 && (p.stride_c % 8) == 0));
 				uint32_t local_tile = 0;
 				for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
 				{
@@ -234,24 +245,87 @@ namespace mb200
 						break;
 					tcgen05_fence_after();
 
-					const int row = mt * BM + q * 32 + lane;
+					const int row0 = mt * BM + q * 32;
+					const int row = row0 + lane;
 					const bool row_ok = row < p.M;
 					const long long d_off = static_cast<long long>(b) * p.stride_d + static_cast<long long>(row) * p.ldd;
 					const long long c_off = static_cast<long long>(b) * p.stride_c + static_cast<long long>(row) * p.ldc;
 					const int n_valid_tile = min(BN, p.N - nt * BN);
 
-					for (int c = 0; c < BN / 32; c++)
+					for (int c = col_part * (BN / 64); c < (col_part + 1) * (BN / 64); c++)
 					{
 						if (c * 32 >= n_valid_tile)
 							break; // warp-uniform
+						const int n0 = nt * BN + c * 32;
+						const int n_valid = min(32, p.N - n0);
+						const bool fast = rows_vectorisable && n_valid == 32;
+						uint4 res[4];
+						if (fast && use_c)
+						{ // issue the reads of C before waiting on tensor memory
+							const __half *cp = reinterpret_cast<const __half*>(p.C) + static_cast<long long>(b) * p.stride_c;
+#pragma unroll
+							for (int i = 0; i < 4; i++)
+							{
+								const int rg = row0 + rr + 8 * i;
+								res[i] = (rg < p.M) ? *reinterpret_cast<const uint4*>(cp + static_cast<long long>(rg) * p.ldc + n0 + seg * 8) : make_uint4(0, 0,
+										0, 0);
+							}
+						}
 						uint32_t r[32];
 						tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
 						tmem_wait_ld();
+						float v[32];
+						if (fast)
+						{
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = __uint_as_float(r[j]) * p.alpha;
+							if (use_c)
+							{ // through shared memory: cooperative layout -> one row per lane
+#pragma unroll
+								for (int i = 0; i < 4; i++)
+									st_shared_v4(sbuf + (rr + 8 * i) * epi::PITCH + seg * 16, res[i]);
+								__syncwarp();
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									add_half8(v + 8 * k, ld_shared_v4(sbuf + lane * epi::PITCH + k * 16), p.beta);
+								__syncwarp();
+							}
+							if (p.bias != nullptr)
+							{
+								const __half *bs = reinterpret_cast<const __half*>(p.bias) + n0;
+								if (aligned_to_16(bs))
+								{
+#pragma unroll
+									for (int k = 0; k < 4; k++)
+										add_half8(v + 8 * k, reinterpret_cast<const uint4*>(bs)[k]);
+								}
+								else
+								{
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										v[j] += __half2float(bs[j]);
+								}
+							}
+							activate32(v, p.act);
+#pragma unroll
+							for (int k = 0; k < 4; k++)
+								st_shared_v4(sbuf + lane * epi::PITCH + k * 16, pack_half8(v + 8 * k));
+							__syncwarp();
+							__half *dp = reinterpret_cast<__half*>(p.D) + static_cast<long long>(b) * p.stride_d;
+#pragma unroll
+							for (int i = 0; i < 4; i++)
+							{
+								const int rg = row0 + rr + 8 * i;
+								const uint4 val = ld_shared_v4(sbuf + (rr + 8 * i) * epi::PITCH + seg * 16);
+								if (rg < p.M)
+									*reinterpret_cast<uint4*>(dp + static_cast<long long>(rg) * p.ldd + n0 + seg * 8) = val;
+							}
+							__syncwarp();
+							continue;
+						}
 						if (!row_ok)
 							continue;
-						const int n0 = nt * BN + c * 32;
-						const int n_valid = min(32, p.N - n0);
-						float v[32];
 						if (KIND == 0)
 						{
 #pragma unroll
@@ -295,12 +369,7 @@ namespace mb200
 											v[j] += bp[j];
 								}
 							}
-							if (p.act != ACTIVATION_LINEAR)
-							{
-#pragma unroll
-								for (int j = 0; j < 32; j++)
-									v[j] = apply_activation(v[j], p.act);
-							}
+							activate32(v, p.act);
 						}
 						else if (p.out_dtype != DTYPE_INT32)
 						{ // fused requantisation: x = acc * scale[n] + shift[n] (+ dequantised ext), activation
@@ -312,8 +381,10 @@ namespace mb200
 									float x = requant_prepare(static_cast<int>(r[j]), p.scales[n0 + j], p.shifts[n0 + j]);
 									if (ep != nullptr)
 										x += static_cast<float>(ep[j]) * p.ext_scale + p.ext_shift;
-									v[j] = (p.act == ACTIVATION_LEAKY_RELU || p.act == ACTIVATION_EXP) ? x : apply_activation(x, p.act);
+									v[j] = x;
 								}
+							if (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU)
+								activate32(v, p.act);
 						}
 
 						if (p.out_dtype == DTYPE_FLOAT16)
