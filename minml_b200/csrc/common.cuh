@@ -20,6 +20,10 @@
 
 namespace mb200
 {
+	/* Upper bound on device indices for per-device caches (kernel attributes are set per device, and one process may hold
+	 * contexts on several devices, as minml's multi-GPU host code does). */
+	constexpr int MAX_DEVICES = 64;
+
 	struct PendingWinograd
 	{
 			// state of the deferred three-call Winograd sequence (see fusion.cu)

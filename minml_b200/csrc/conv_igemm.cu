@@ -703,7 +703,11 @@ namespace mb200
 		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
 			using C = Cfg<KIND, BN, TMA_A>;
-			static bool configured = false;
+			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
+			const int device = get(ctx)->device;
+			if (device < 0 || device >= MAX_DEVICES)
+				return false;
+			bool &configured = configured_on[device];
 			if (!configured)
 			{
 				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
@@ -724,7 +728,7 @@ namespace mb200
 		bool launch_pair(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
 			using C = Cfg<KIND, BN, true, 2>;
-			static int max_clusters[64] = { 0 }; // per device; 0 = not queried yet, -1 = clusters of this size cannot be placed
+			static int max_clusters[MAX_DEVICES] = { 0 }; // per device; 0 = not queried yet, -1 = clusters of this size cannot be placed
 			const int device = get(ctx)->device;
 			cudaLaunchConfig_t config;
 			std::memset(&config, 0, sizeof(config));
@@ -738,7 +742,7 @@ namespace mb200
 			config.stream = use_stream(ctx);
 			config.attrs = &attribute;
 			config.numAttrs = 1;
-			if (device < 0 || device >= 64)
+			if (device < 0 || device >= MAX_DEVICES)
 				return false;
 			if (max_clusters[device] == 0)
 			{

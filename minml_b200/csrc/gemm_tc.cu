@@ -485,7 +485,11 @@ namespace mb200
 		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const GemmTcParams &p, int sm_count)
 		{
 			using T = Tiling<BN>;
-			static bool configured = false;
+			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
+			const int device = get(ctx)->device;
+			if (device < 0 || device >= MAX_DEVICES)
+				return false;
+			bool &configured = configured_on[device];
 			if (!configured)
 			{
 				if (!check_cuda(ctx,
