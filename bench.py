@@ -311,23 +311,17 @@ def load_peaks():
 
 def gpu_arm(args, cfg):
     import torch
-    import torch.distributed as dist
     from minml_b200 import backend as B
     from minml_b200 import layers as L
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    from minml_b200.replicas import Replicas
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the backend has no CPU fallback")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    replicas = Replicas("nccl")
+    world, rank = replicas.world, replicas.rank
+    barrier = replicas.barrier
 
     ctx = B.Context(local)
     ctx.set_fusion(not args.eager)
@@ -336,7 +330,7 @@ def gpu_arm(args, cfg):
     if kind == "hybrid":
         weights = L.make_hybrid_weights(SEED, cfg["channels"], cfg["heads"], cfg["ffn"], max(cfg["height"], cfg["width"]))
         net = L.HybridBlock(ctx, weights, batch, cfg["height"], cfg["width"], cfg["channels"], cfg["heads"], cfg["ffn"])
-        tokens = np.random.default_rng(SEED + 1 + rank).standard_normal((batch, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float16)
+        tokens = np.random.default_rng(replicas.input_seed(SEED)).standard_normal((batch, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float16)
         in_host = torch.from_numpy(tokens).pin_memory()
         in_stage = torch.empty_like(in_host, device="cuda")
         out_hosts = [torch.empty(tokens.shape, dtype=torch.float16).pin_memory()]
@@ -351,7 +345,7 @@ def gpu_arm(args, cfg):
             net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64)
         else:
             net = L.ResNetTrunk(ctx, weights, *shape)
-        _, packed = synthetic_input(cfg, batch, SEED + 1 + rank)
+        _, packed = synthetic_input(cfg, batch, replicas.input_seed(SEED))
         in_host = torch.from_numpy(packed).pin_memory()
         in_stage = torch.empty_like(in_host, device="cuda")
         out_hosts = [torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory(),
@@ -389,10 +383,8 @@ def gpu_arm(args, cfg):
         B.lib.cuda_destroy_event(e0)
         B.lib.cuda_destroy_event(e1)
         barrier()
-        t = torch.tensor([dev_s, wall], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0]), float(t[1])
+        dev_max, wall_max = replicas.max_over_ranks([dev_s, wall])
+        return dev_max, wall_max
 
     for _ in range(max(args.warmup, 3)):
         step_device()
@@ -420,7 +412,7 @@ def gpu_arm(args, cfg):
             roof = int8_layer_roofline(B, L, ctx, cfg, peaks, torch)
         else:
             roof = layer_roofline(B, L, ctx, cfg, peaks, torch, fused=not args.eager)
-        total_positions = batch * world * args.steps
+        total_positions = replicas.global_units(batch) * args.steps
         value = total_positions / dev_s
         fpp = flops_per_position(cfg)
         result = {
@@ -436,8 +428,7 @@ def gpu_arm(args, cfg):
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
         }
     ctx.close()
-    if world > 1:
-        dist.destroy_process_group()
+    replicas.close()
     return result
 
 
