@@ -9,6 +9,8 @@
  *
  * Status tags:
  *   [hot]    implemented with hand-written sm_100a kernels (the convolution / matrix-multiply inference path)
+ *   [next]   implemented: the layers adjacent to that path in minml's current architectures (batch-norm inference and
+ *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling)
  *   [infra]  thin native wrapper over the CUDA runtime
  *   [stub]   exported so that minml links; records the sticky error "not implemented" on the context and
  *            launches nothing (training, MoE, pooling variants, ...)
@@ -103,7 +105,7 @@ void cuda_convolution_implicit_gemm_forward(mlContext_t context, mlDataType_t dt
 
 /* ---- Depthwise convolution
  *      replaces src/backend/cuda/kernels/depthwise_conv.cu ---- */
-void cuda_depthwise_conv_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, float beta, mlTensor_t y); /* [stub] [111] */
+void cuda_depthwise_conv_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, float beta, mlTensor_t y); /* [next] [111] */
 void cuda_depthwise_conv_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t w, float beta, mlTensor_t dx); /* [stub] [113] */
 void cuda_depthwise_conv_update(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t dy, float beta, mlTensor_t dw); /* [stub] [115] */
 
@@ -113,7 +115,7 @@ void cuda_average_pooling_forward(mlContext_t context, float alpha, const mlTens
 void cuda_average_pooling_backward(mlContext_t context, float alpha, const mlTensor_t dy, float beta, mlTensor_t dx, int size); /* [stub] [122] */
 void cuda_global_average_pooling_forward(mlContext_t context, float alpha, const mlTensor_t x, float beta, mlTensor_t y); /* [hot] [127] */
 void cuda_global_average_pooling_backward(mlContext_t context, float alpha, const mlTensor_t dy, float beta, mlTensor_t dx); /* [stub] [128] */
-void cuda_channel_scaling_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t scales, float beta, mlTensor_t y); /* [stub] [129] */
+void cuda_channel_scaling_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t scales, float beta, mlTensor_t y); /* [next] [129] */
 void cuda_channel_scaling_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t x, const mlTensor_t scales, float beta_dx, mlTensor_t dx, float beta_scales, mlTensor_t dscales); /* [stub] [131] */
 void cuda_channel_average_pooling_forward(mlContext_t context, float alpha, const mlTensor_t x, float beta, mlTensor_t y); /* [stub] [137] */
 void cuda_channel_average_pooling_backward(mlContext_t context, float alpha, const mlTensor_t dy, float beta, mlTensor_t dx); /* [stub] [138] */
@@ -140,11 +142,11 @@ void cuda_add_bias_act(mlContext_t context, float alpha, const mlTensor_t x, con
 
 /* ---- Batch normalisation
  *      replaces src/backend/cuda/kernels/batchnorm.cu ---- */
-void cuda_batchnorm_inference(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, const mlTensor_t avg_var, float beta, mlTensor_t y, mlActivationType_t act); /* [stub] [177] */
+void cuda_batchnorm_inference(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, const mlTensor_t avg_var, float beta, mlTensor_t y, mlActivationType_t act); /* [next] [177] */
 void cuda_batchnorm_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, float beta, mlTensor_t y, mlTensor_t running_stats, mlActivationType_t act); /* [stub] [179] */
 void cuda_batchnorm_backward(mlContext_t context, float alpha, const mlTensor_t x, mlTensor_t dy, const mlTensor_t w, const mlTensor_t b, const mlTensor_t running_stats, float beta_dx, mlTensor_t dx, float beta_dw, mlTensor_t dw, mlTensor_t db, mlActivationType_t act); /* [stub] [181] */
 void cuda_batchnorm_update(mlContext_t context, const mlTensor_t running_stat, mlTensor_t avg_var); /* [stub] [184] */
-void cuda_fold_batchnorm(mlContext_t context, mlTensor_t layer_weights, mlTensor_t layer_bias, const mlTensor_t bn_weights, const mlTensor_t bn_bias, const mlTensor_t bn_avg_var); /* [stub] [185] */
+void cuda_fold_batchnorm(mlContext_t context, mlTensor_t layer_weights, mlTensor_t layer_bias, const mlTensor_t bn_weights, const mlTensor_t bn_bias, const mlTensor_t bn_avg_var); /* [next] [185] */
 
 /* ---- Layer / RMS normalisation
  *      replaces src/backend/cuda/kernels/layernorm.cu:480-527, src/backend/cuda/kernels/rmsnorm.cu ---- */
@@ -221,7 +223,7 @@ void cuda_combined_loss(mlContext_t context, float *result, const mlTensor_t *ou
 /* ---- Quantisation
  *      replaces src/backend/cuda/kernels/quantized.cu:515-645 ---- */
 void cuda_dequantize(mlContext_t context, mlDataType_t dtype, const void *input, void *output, int elements, float scale, float shift); /* [hot] [316] */
-void cuda_quantized_depthwise_conv_forward(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, mlShape_t weights_shape, const void *input, const void *weights, const void *scales, const void *bias, void *output, mlQuantizationData_t output_qd, int padding_value); /* [stub] [318] */
+void cuda_quantized_depthwise_conv_forward(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, mlShape_t weights_shape, const void *input, const void *weights, const void *scales, const void *bias, void *output, mlQuantizationData_t output_qd, int padding_value); /* [next] [318] */
 void cuda_quantized_scale_shift_act(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *output, mlQuantizationData_t output_qd, const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd); /* [hot] [321] */
 void cuda_im2row(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, void *output, const void *input, int kernel_size, bool invert, const void *padding); /* [hot] [324] */
 void cuda_transpose(mlContext_t context, mlDataType_t dtype, mlShape_t output_shape, mlShape_t input_shape, void *output, const void *input, const int *ordering); /* [stub] [326] */

@@ -256,3 +256,31 @@ def quantized_scale_shift_act(ctx, output, output_qd, acc_i32, scales, bias, act
 def dequantize(ctx, src_i8, dst, scale, shift):
     lib.cuda_dequantize(ctx.handle, dtype_of(dst), ptr(src_i8), ptr(dst), src_i8.numel(), float(scale), float(shift))
     ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- layers next to the convolution path
+def batchnormInference(ctx, x, y, weights, bias, avg_var, act="linear", alpha=1.0, beta=0.0):
+    """ml::batchnormInference (src/core/math.cpp): avg_var is fp32 [2, channels] = (mean, variance); weights / bias may be None."""
+    lib.cuda_batchnorm_inference(ctx.handle, alpha, desc(x), desc(weights), desc(bias), desc(avg_var), beta, desc(y), act_code(act))
+    ctx.check()
+
+
+def foldBatchnorm(ctx, layer_weights, layer_bias, bn_weights, bn_bias, bn_avg_var):
+    lib.cuda_fold_batchnorm(ctx.handle, desc(layer_weights), desc(layer_bias), desc(bn_weights), desc(bn_bias), desc(bn_avg_var))
+    ctx.check()
+
+
+def depthwiseConvForward(ctx, x, w, y, bias=None, alpha=1.0, beta=0.0):
+    lib.cuda_depthwise_conv_forward(ctx.handle, alpha, desc(x), desc(w), desc(bias), beta, desc(y))
+    ctx.check()
+
+
+def quantized_depthwise_conv_forward(ctx, x, w, scales, bias, y, output_qd, padding_value=0):
+    lib.cuda_quantized_depthwise_conv_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(w), ptr(x), ptr(w), ptr(scales), ptr(bias), ptr(y),
+                                              qdata(*output_qd), int(padding_value))
+    ctx.check()
+
+
+def channelScalingForward(ctx, x, scales, y, alpha=1.0, beta=0.0):
+    lib.cuda_channel_scaling_forward(ctx.handle, alpha, desc(x), desc(scales), beta, desc(y))
+    ctx.check()

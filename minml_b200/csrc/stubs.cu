@@ -30,10 +30,6 @@ extern "C"
 	{
 		NOT_IMPLEMENTED(context, "cuda_winograd_update_transform");
 	}
-	void cuda_depthwise_conv_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, float beta, mlTensor_t y) /* [111] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_depthwise_conv_forward");
-	}
 	void cuda_depthwise_conv_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t w, float beta, mlTensor_t dx) /* [113] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_depthwise_conv_backward");
@@ -53,10 +49,6 @@ extern "C"
 	void cuda_global_average_pooling_backward(mlContext_t context, float alpha, const mlTensor_t dy, float beta, mlTensor_t dx) /* [128] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_global_average_pooling_backward");
-	}
-	void cuda_channel_scaling_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t scales, float beta, mlTensor_t y) /* [129] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_channel_scaling_forward");
 	}
 	void cuda_channel_scaling_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t x, const mlTensor_t scales, float beta_dx, mlTensor_t dx, float beta_scales, mlTensor_t dscales) /* [131] */
 	{
@@ -90,10 +82,6 @@ extern "C"
 	{
 		NOT_IMPLEMENTED(context, "cudnn_depthwise_conv_update");
 	}
-	void cuda_batchnorm_inference(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, const mlTensor_t avg_var, float beta, mlTensor_t y, mlActivationType_t act) /* [177] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_batchnorm_inference");
-	}
 	void cuda_batchnorm_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t w, const mlTensor_t b, float beta, mlTensor_t y, mlTensor_t running_stats, mlActivationType_t act) /* [179] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_batchnorm_forward");
@@ -105,10 +93,6 @@ extern "C"
 	void cuda_batchnorm_update(mlContext_t context, const mlTensor_t running_stat, mlTensor_t avg_var) /* [184] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_batchnorm_update");
-	}
-	void cuda_fold_batchnorm(mlContext_t context, mlTensor_t layer_weights, mlTensor_t layer_bias, const mlTensor_t bn_weights, const mlTensor_t bn_bias, const mlTensor_t bn_avg_var) /* [185] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_fold_batchnorm");
 	}
 	void cuda_layernorm_backward(mlContext_t context, mlShape_t shape, const void *input, void *gradient_prev, void *gradient_next, const void *weights, void *weights_update, void *bias_update) /* [193] */
 	{
@@ -264,10 +248,6 @@ extern "C"
 	void cuda_combined_loss(mlContext_t context, float *result, const mlTensor_t *outputs, const mlTensor_t *targets, const mlTensor_t *masks, const float *weights) /* [310] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_combined_loss");
-	}
-	void cuda_quantized_depthwise_conv_forward(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, mlShape_t weights_shape, const void *input, const void *weights, const void *scales, const void *bias, void *output, mlQuantizationData_t output_qd, int padding_value) /* [318] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_quantized_depthwise_conv_forward");
 	}
 	void cuda_transpose(mlContext_t context, mlDataType_t dtype, mlShape_t output_shape, mlShape_t input_shape, void *output, const void *input, const int *ordering) /* [326] */
 	{

@@ -506,3 +506,114 @@ void oracle_add_bias_act(const float *x, const float *bias, float *y, int act, s
 		for (int c = 0; c < channels; c++)
 			y[r * channels + c] = activate(x[r * channels + c] + (bias != NULL ? bias[c] : 0.0f), act);
 }
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Layers adjacent to the convolution path (batch norm at inference time, depthwise convolution, channel scaling).
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* y = alpha * act(x * scale[c] + shift[c]) + beta * y with scale = gamma / sqrt(var + 1e-6), shift = beta_bn - mean * scale;
+ * avg_var = [mean[channels], var[channels]]  (src/backend/cuda/kernels/batchnorm.cu:58-100; CPU: src/backend/cpu/normalization.cpp) */
+void oracle_batchnorm_inference(const float *x, float *y, const float *gamma, const float *beta_bn, const float *avg_var, float alpha,
+		float beta, int act, size_t rows, int channels)
+{
+	for (size_t r = 0; r < rows; r++)
+		for (int c = 0; c < channels; c++)
+		{
+			const float scale = (gamma ? gamma[c] : 1.0f) / sqrtf(avg_var[channels + c] + 1.0e-6f);
+			const float shift = -avg_var[c] * scale + (beta_bn ? beta_bn[c] : 0.0f);
+			float v = activate(x[r * channels + c] * scale + shift, act) * alpha;
+			if (beta != 0.0f)
+				v += beta * y[r * channels + c];
+			y[r * channels + c] = v;
+		}
+}
+/* Folds the same scale / shift into a layer: weights [outer, inner]; per_row != 0: one channel per row ([cout, ...] weights),
+ * else one channel per column (depthwise [k*k, c])  (batchnorm.cu:400-438, src/backend/cpu/normalization.cpp cpu_fold_batchnorm) */
+void oracle_fold_batchnorm(float *weights, float *bias, const float *gamma, const float *beta_bn, const float *avg_var, int outer, int inner,
+		int per_row)
+{
+	const int channels = per_row ? outer : inner;
+	for (int c = 0; c < channels; c++)
+	{
+		const float scale = (gamma ? gamma[c] : 1.0f) / sqrtf(avg_var[channels + c] + 1.0e-6f);
+		const float shift = -avg_var[c] * scale + (beta_bn ? beta_bn[c] : 0.0f);
+		if (per_row)
+			for (int i = 0; i < inner; i++)
+				weights[(size_t) c * inner + i] *= scale;
+		else
+			for (int i = 0; i < outer; i++)
+				weights[(size_t) i * inner + c] *= scale;
+		if (bias)
+			bias[c] = bias[c] * scale + shift;
+	}
+}
+/* y = alpha * dwconv(x, w) + bias + beta * y; x [b,h,w,c], w [k,k,c], stride 1, zero "same" padding (depthwise_conv.cu:110-182) */
+void oracle_depthwise_conv(const float *x, const float *w, const float *bias, float *y, float alpha, float beta, int batch, int height,
+		int width, int channels, int k)
+{
+	const int pad = (k - 1) / 2;
+	for (int b = 0; b < batch; b++)
+		for (int h = 0; h < height; h++)
+			for (int q = 0; q < width; q++)
+				for (int c = 0; c < channels; c++)
+				{
+					double acc = 0.0;
+					for (int i = 0; i < k; i++)
+						for (int j = 0; j < k; j++)
+						{
+							const int hh = h + i - pad, ww = q + j - pad;
+							if (hh >= 0 && hh < height && ww >= 0 && ww < width)
+								acc += (double) x[(((size_t) b * height + hh) * width + ww) * channels + c] * (double) w[((size_t) i * k + j) * channels + c];
+						}
+					const size_t off = (((size_t) b * height + h) * width + q) * channels + c;
+					float v = (float) acc * alpha + (bias ? bias[c] : 0.0f);
+					if (beta != 0.0f)
+						v += beta * y[off];
+					y[off] = v;
+				}
+}
+/* The integer branch of DepthwiseConv2D::forward on the CPU (src/layers/DepthwiseConv2D.cpp:104-140): the accumulator starts at 0,
+ * positions outside the image contribute weight * input_zero, then acc * scale[c] + bias[c], requantised with the inverse transform. */
+void oracle_depthwise_conv_int8(const int8_t *x, const int8_t *w, const float *scales, const float *bias, int8_t *y_i8, float *y_f32,
+		float out_scale, float out_shift, int input_zero, int batch, int height, int width, int channels, int k)
+{
+	const int pad = (k - 1) / 2;
+	const float inv_scale = 1.0f / out_scale, inv_shift = -out_shift / out_scale;
+	for (int b = 0; b < batch; b++)
+		for (int h = 0; h < height; h++)
+			for (int q = 0; q < width; q++)
+				for (int c = 0; c < channels; c++)
+				{
+					int32_t acc = 0;
+					for (int i = 0; i < k; i++)
+						for (int j = 0; j < k; j++)
+						{
+							const int hh = h + i - pad, ww = q + j - pad;
+							const int wv = w[((size_t) i * k + j) * channels + c];
+							if (hh >= 0 && hh < height && ww >= 0 && ww < width)
+								acc += wv * (int) x[(((size_t) b * height + hh) * width + ww) * channels + c];
+							else
+								acc += wv * input_zero;
+						}
+					const size_t off = (((size_t) b * height + h) * width + q) * channels + c;
+					const float tmp = (float) acc * (scales ? scales[c] : 1.0f) + (bias ? bias[c] : 0.0f);
+					if (y_f32)
+						y_f32[off] = tmp;
+					if (y_i8)
+						y_i8[off] = (int8_t) quantize_i8(tmp * inv_scale + inv_shift);
+				}
+}
+/* y = alpha * x * s[b, c] + beta * y; x [b, hw, c], s [b, c]  (src/backend/cuda/kernels/global_pooling.cu:99-123) */
+void oracle_channel_scaling(const float *x, const float *scales, float *y, float alpha, float beta, int batch, int hw, int channels)
+{
+	for (int b = 0; b < batch; b++)
+		for (int i = 0; i < hw; i++)
+			for (int c = 0; c < channels; c++)
+			{
+				const size_t off = ((size_t) b * hw + i) * channels + c;
+				float v = x[off] * scales[(size_t) b * channels + c] * alpha;
+				if (beta != 0.0f)
+					v += beta * y[off];
+				y[off] = v;
+			}
+}

@@ -143,6 +143,45 @@ class Oracle:
                                None if pad_arr is None else pad_arr.ctypes.data_as(ctypes.c_void_p))
         return out
 
+    def batchnorm_inference(self, x, gamma, beta_bn, avg_var, act="linear", alpha=1.0, beta=0.0, y=None):
+        x = _f32(x)
+        c = x.shape[-1]
+        out = np.zeros_like(x) if y is None else _f32(y).copy()
+        self.lib.oracle_batchnorm_inference(_fp(x), _fp(out), _fp(_f32(gamma)), _fp(_f32(beta_bn)), _fp(_f32(avg_var)), ctypes.c_float(alpha),
+                                            ctypes.c_float(beta), ACT[act], ctypes.c_size_t(x.size // c), c)
+        return out
+
+    def fold_batchnorm(self, weights, bias, gamma, beta_bn, avg_var):
+        """Returns (folded weights, folded bias); [k, k, c] weights are depthwise (one channel per column)."""
+        w, b = _f32(weights).copy(), _f32(bias).copy()
+        per_row = w.ndim != 3
+        outer = w.shape[0] if per_row else w.shape[0] * w.shape[1]
+        self.lib.oracle_fold_batchnorm(_fp(w), _fp(b), _fp(_f32(gamma)), _fp(_f32(beta_bn)), _fp(_f32(avg_var)), outer, w.size // outer, int(per_row))
+        return w, b
+
+    def depthwise_conv(self, x, w, bias=None, alpha=1.0, beta=0.0, y=None):
+        x, w = _f32(x), _f32(w)
+        b, h, wd, c = x.shape
+        out = np.zeros_like(x) if y is None else _f32(y).copy()
+        self.lib.oracle_depthwise_conv(_fp(x), _fp(w), _fp(_f32(bias)), _fp(out), ctypes.c_float(alpha), ctypes.c_float(beta), b, h, wd, c, w.shape[0])
+        return out
+
+    def depthwise_conv_int8(self, x, w, scales, bias, out_qd=(1.0, 0.0), input_zero=0):
+        """Returns (y_int8, y_fp32)."""
+        x, w = np.ascontiguousarray(x, np.int8), np.ascontiguousarray(w, np.int8)
+        b, h, wd, c = x.shape
+        y8, yf = np.empty(x.shape, np.int8), np.empty(x.shape, np.float32)
+        self.lib.oracle_depthwise_conv_int8(_i8(x), _i8(w), _fp(_f32(scales)), _fp(_f32(bias)), _i8(y8), _fp(yf), ctypes.c_float(out_qd[0]),
+                                            ctypes.c_float(out_qd[1]), int(input_zero), b, h, wd, c, w.shape[0])
+        return y8, yf
+
+    def channel_scaling(self, x, scales, alpha=1.0, beta=0.0, y=None):
+        x = _f32(x)
+        b, c = x.shape[0], x.shape[-1]
+        out = np.zeros_like(x) if y is None else _f32(y).copy()
+        self.lib.oracle_channel_scaling(_fp(x), _fp(_f32(scales)), _fp(out), ctypes.c_float(alpha), ctypes.c_float(beta), b, x.size // (b * c), c)
+        return out
+
     def global_average_pooling(self, x, alpha=1.0, beta=0.0, y=None):
         x = _f32(x)
         b, h, w, c = x.shape
@@ -245,6 +284,10 @@ class ReferenceCpu:
             "cpu_multi_head_attention_forward": [V, T, T, T, T, T, I],
             "cpu_unpack_input": [V, S, I, V, V],
             "cpu_activation_forward": [V, I, S, V, V, I],
+            "cpu_batchnorm_inference": [V, I, S, V, V, V, I],
+            "cpu_fold_batchnorm": [V, T, T, T, T, T],
+            "cpu_depthwise_conv_forward": [V, F, T, T, T, F, T],
+            "cpu_channel_scaling_forward": [V, F, T, T, F, T],
         }
         for name, argtypes in sigs.items():
             fn = getattr(lib, name)
@@ -307,6 +350,33 @@ class ReferenceCpu:
         m = self.gemm("n", v, "t", u, batched=True)
         out_shape = x.shape[:3] + (w.shape[0],)
         return self.winograd_output_transform(m, w.shape, out_shape, bias, ext, act, tile)
+
+    def batchnorm_inference(self, x, gamma, beta_bn, avg_var, act="linear"):
+        """cpu_batchnorm_inference takes one [4, c] fp32 tensor: mean, variance, gamma, beta (src/backend/cpu/normalization.cpp:134-139)."""
+        x = _f32(x)
+        c = x.shape[-1]
+        packed = np.ascontiguousarray(np.concatenate([_f32(avg_var).reshape(2, c), _f32(gamma).reshape(1, c), _f32(beta_bn).reshape(1, c)]), np.float32)
+        y = np.zeros_like(x)
+        self.lib.cpu_batchnorm_inference(self.ctx, DTYPE_FLOAT32, _shape(x.shape), _vp(x), _vp(y), _vp(packed), ACT[act])
+        return y
+
+    def fold_batchnorm(self, weights, bias, gamma, beta_bn, avg_var):
+        w, b = _f32(weights).copy(), _f32(bias).copy()
+        g, bb, av = _f32(gamma), _f32(beta_bn), _f32(avg_var)
+        self.lib.cpu_fold_batchnorm(self.ctx, _tensor(w), _tensor(b), _tensor(g), _tensor(bb), _tensor(av))
+        return w, b
+
+    def depthwise_conv(self, x, w, bias):
+        x, w, bias = _f32(x), _f32(w), _f32(bias)
+        y = np.zeros_like(x)
+        self.lib.cpu_depthwise_conv_forward(self.ctx, 1.0, _tensor(x), _tensor(w), _tensor(bias), 0.0, _tensor(y))
+        return y
+
+    def channel_scaling(self, x, scales):
+        x, scales = _f32(x), _f32(scales)
+        y = np.zeros_like(x)
+        self.lib.cpu_channel_scaling_forward(self.ctx, 1.0, _tensor(x), _tensor(scales), 0.0, _tensor(y))
+        return y
 
     def global_average_pooling(self, x):
         x = _f32(x)

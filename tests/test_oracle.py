@@ -194,3 +194,58 @@ def test_host_weight_quantisation_matches_oracle(oracle):
         assert np.array_equal(q, q2)
         assert np.allclose(cs, cs2, rtol=1e-6, atol=0)
         assert np.allclose(qb, qb2, rtol=1e-5, atol=1e-6)
+
+
+def test_batchnorm_depthwise_and_channel_scaling_against_reference_cpu(oracle, refcpu):
+    """The oracle's restatements of the layers next to the convolution path, op by op against minml's CPU backend."""
+    r = np.random.default_rng(17)
+    c = 128
+    x = r.standard_normal((3, 9, 11, c)).astype(np.float32)
+    gamma, beta_bn = r.uniform(0.5, 1.5, c).astype(np.float32), r.standard_normal(c).astype(np.float32)
+    avg_var = np.stack([r.standard_normal(c), r.uniform(0.2, 2.0, c)]).astype(np.float32)
+    for act in ("linear", "relu", "sigmoid", "tanh"):
+        assert np.max(np.abs(oracle.batchnorm_inference(x, gamma, beta_bn, avg_var, act) - refcpu.batchnorm_inference(x, gamma, beta_bn, avg_var, act))) <= 1e-5
+    # folding: [cout, k, k, cin] per output channel, [k, k, c] (depthwise) per channel
+    for shape in ((c, 3, 3, 20), (7, 7, c)):
+        w = r.standard_normal(shape).astype(np.float32)
+        b = r.standard_normal(c).astype(np.float32)
+        w1, b1 = oracle.fold_batchnorm(w, b, gamma, beta_bn, avg_var)
+        w2, b2 = refcpu.fold_batchnorm(w, b, gamma, beta_bn, avg_var)
+        assert np.max(np.abs(w1 - w2)) <= 1e-6 and np.max(np.abs(b1 - b2)) <= 1e-5
+    # folding then convolving equals convolving then normalising
+    w = (r.standard_normal((c, 1, 1, 16)) * 0.3).astype(np.float32)
+    b = (r.standard_normal(c) * 0.1).astype(np.float32)
+    x16 = r.standard_normal((2, 5, 5, 16)).astype(np.float32)
+    wf, bf = oracle.fold_batchnorm(w, b, gamma, beta_bn, avg_var)
+    direct = oracle.batchnorm_inference(oracle.conv2d(x16, w, b, None, "linear"), gamma, beta_bn, avg_var, "relu")
+    assert np.max(np.abs(oracle.conv2d(x16, wf, bf, None, "relu") - direct)) <= 1e-4
+    for k in (3, 5, 7):
+        wd = (r.standard_normal((k, k, c)) * 0.2).astype(np.float32)
+        bias = r.standard_normal(c).astype(np.float32)
+        assert np.max(np.abs(oracle.depthwise_conv(x, wd, bias) - refcpu.depthwise_conv(x, wd, bias))) <= 1e-4
+    s = r.uniform(0, 1, (3, c)).astype(np.float32)
+    assert np.max(np.abs(oracle.channel_scaling(x, s) - refcpu.channel_scaling(x, s))) <= 1e-6
+
+
+def test_int8_depthwise_restatement_matches_a_plain_numpy_loop(oracle):
+    """The integer branch of DepthwiseConv2D::forward (src/layers/DepthwiseConv2D.cpp:104-140) written out once more in numpy."""
+    r = np.random.default_rng(18)
+    b, h, w, c, k = 2, 6, 7, 24, 7
+    x = r.integers(-128, 128, (b, h, w, c), dtype=np.int8)
+    wt = r.integers(-127, 128, (k, k, c), dtype=np.int8)
+    scales = r.uniform(1e-4, 3e-4, c).astype(np.float32)
+    bias = r.standard_normal(c).astype(np.float32) * 0.1
+    zero, pad = -3, (k - 1) // 2
+    xp = np.full((b, h + 2 * pad, w + 2 * pad, c), zero, np.int32)
+    xp[:, pad:pad + h, pad:pad + w] = x
+    acc = np.zeros((b, h, w, c), np.int32)
+    for i in range(k):
+        for j in range(k):
+            acc += xp[:, i:i + h, j:j + w] * wt[i, j].astype(np.int32)
+    want_f = acc.astype(np.float32) * scales + bias
+    out_qd = (0.01, 0.05)
+    t = want_f * np.float32(1.0 / np.float32(out_qd[0])) + np.float32(-np.float32(out_qd[1]) / np.float32(out_qd[0]))
+    want_8 = np.clip(np.sign(t) * np.floor(np.abs(t) + np.float32(0.5)), -128, 127).astype(np.int8)
+    y8, yf = oracle.depthwise_conv_int8(x, wt, scales, bias, out_qd, zero)
+    assert np.array_equal(yf, want_f)
+    assert np.array_equal(y8, want_8)
