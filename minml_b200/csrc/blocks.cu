@@ -14,9 +14,16 @@
  *                                  which its own CPU path does not do.)
  *   cuda_channel_scaling_forward   y = alpha * x * s[b, c] + beta * y, x [b,h,w,c], s [b,c]   (global_pooling.cu:99-123,360-407)
  *
- * All of them are HBM-bound: every thread owns a 16-byte group of channels (8 halves / 4 floats / 16 int8), so a warp reads and
- * writes whole 128-byte lines along the channel axis; accumulation is fp32 (the reference accumulates fp16 depthwise convolutions
- * in half2).
+ * Batch norm and channel scaling are HBM-bound: a thread owns a fixed 16-byte group of channels (its scale and shift are computed
+ * once) and strides over rows, so a warp reads and writes whole 128-byte lines.
+ *
+ * The depthwise convolutions are bound by the fp32 multiply-adds (k x k per output element, no reuse across channels, nothing for
+ * the tensor cores): a thread owns one output row of a small group of channels and walks along it.  Input column ww feeds the k
+ * output columns ww - pad .. ww + pad, whose partial sums sit in k register accumulators that shift by one per step; the k x k
+ * filter taps of the thread's channels stay in registers as fp32 for the whole row.  Every input element is therefore loaded k
+ * times (once per filter row), not k x k times, and the inner loop is k multiply-adds per loaded value.  Accumulation is fp32 (the
+ * reference accumulates fp16 depthwise convolutions in half2); the int8 variant runs on the same fp32 path, which is exact there:
+ * every partial sum is an integer below 49 * 128 * 128 < 2^24.
  */
 #include "common.cuh"
 
@@ -28,36 +35,6 @@ using namespace mb200;
 
 namespace
 {
-	template<typename T, int VEC>
-	struct Pack;
-	template<>
-	struct Pack<__half, 8>
-	{
-			uint4 raw;
-			__device__ void load(const __half *p) { raw = *reinterpret_cast<const uint4*>(p); }
-			__device__ void store(__half *p) const { *reinterpret_cast<uint4*>(p) = raw; }
-			__device__ float get(int i) const { return __half2float(reinterpret_cast<const __half*>(&raw)[i]); }
-			__device__ void set(int i, float v) { reinterpret_cast<__half*>(&raw)[i] = __float2half_rn(v); }
-	};
-	template<>
-	struct Pack<float, 4>
-	{
-			float4 raw;
-			__device__ void load(const float *p) { raw = *reinterpret_cast<const float4*>(p); }
-			__device__ void store(float *p) const { *reinterpret_cast<float4*>(p) = raw; }
-			__device__ float get(int i) const { return reinterpret_cast<const float*>(&raw)[i]; }
-			__device__ void set(int i, float v) { reinterpret_cast<float*>(&raw)[i] = v; }
-	};
-	template<typename T>
-	struct Pack<T, 1>
-	{
-			T raw;
-			__device__ void load(const T *p) { raw = *p; }
-			__device__ void store(T *p) const { *p = raw; }
-			__device__ float get(int) const { return static_cast<float>(raw); }
-			__device__ void set(int, float v) { raw = static_cast<T>(v); }
-	};
-
 	inline int grid_for(long long work_items, int block, int sm_count)
 	{
 		const long long blocks = (work_items + block - 1) / block;
@@ -65,38 +42,88 @@ namespace
 	}
 	__device__ __forceinline__ float to_float(float v) { return v; }
 	__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+	__device__ __forceinline__ float to_float(int8_t v) { return static_cast<float>(static_cast<int>(v)); }
+	template<typename T> __device__ __forceinline__ T from_float(float v);
+	template<> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+	template<> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+	template<> __device__ __forceinline__ int8_t from_float<int8_t>(float v) { return static_cast<int8_t>(static_cast<int>(v)); }
+
+	/* VEC consecutive elements moved with one load / store (the address must be aligned to VEC * sizeof(T)). */
+	template<typename T, int VEC>
+	struct alignas(sizeof(T) * VEC) Group
+	{
+			T v[VEC];
+	};
+	template<typename T, int VEC>
+	__device__ __forceinline__ void load_group(const T *p, float (&out)[VEC])
+	{
+		const Group<T, VEC> g = *reinterpret_cast<const Group<T, VEC>*>(p);
+#pragma unroll
+		for (int k = 0; k < VEC; k++)
+			out[k] = to_float(g.v[k]);
+	}
+	template<typename T, int VEC>
+	__device__ __forceinline__ void store_group(T *p, const float (&in)[VEC])
+	{
+		Group<T, VEC> g;
+#pragma unroll
+		for (int k = 0; k < VEC; k++)
+			g.v[k] = from_float<T>(in[k]);
+		*reinterpret_cast<Group<T, VEC>*>(p) = g;
+	}
 
 	/* ------------------------------------------------------------------------------------------------ batch norm */
+	/* block = (channel groups, rows): thread (tx, ty) owns channel group blockIdx.y * blockDim.x + tx and the rows ty, ty + step, ... */
 	template<typename T, int VEC>
-	__global__ void kernel_batchnorm_inference(T *y, const T *x, const T *gamma, const T *beta_bn, const float *avg_var, long long rows,
-			int channels, float alpha, float beta, int act)
+	__global__ void __launch_bounds__(256) kernel_batchnorm_inference(T *y, const T *x, const T *gamma, const T *beta_bn, const float *avg_var,
+			long long rows, int channels, float alpha, float beta, int act)
 	{
-		const int groups = channels / VEC;
-		const long long total = rows * groups;
-		for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x)
+		const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+		if (c0 >= channels)
+			return;
+		float scale[VEC], shift[VEC];
+#pragma unroll
+		for (int k = 0; k < VEC; k++)
 		{
-			const int c0 = static_cast<int>(i % groups) * VEC;
-			const long long off = (i / groups) * channels + c0;
-			Pack<T, VEC> in, out;
-			in.load(x + off);
+			const float g = (gamma != nullptr) ? to_float(gamma[c0 + k]) : 1.0f;
+			const float b = (beta_bn != nullptr) ? to_float(beta_bn[c0 + k]) : 0.0f;
+			scale[k] = g / sqrtf(avg_var[channels + c0 + k] + 1.0e-6f);
+			shift[k] = -avg_var[c0 + k] * scale[k] + b;
+		}
+		for (long long r = blockIdx.x * static_cast<long long>(blockDim.y) + threadIdx.y; r < rows; r += static_cast<long long>(gridDim.x) * blockDim.y)
+		{
+			const long long off = r * channels + c0;
+			float in[VEC], out[VEC];
+			load_group<T, VEC>(x + off, in);
 			if (beta != 0.0f)
-				out.load(y + off);
+				load_group<T, VEC>(y + off, out);
 #pragma unroll
 			for (int k = 0; k < VEC; k++)
 			{
-				const int c = c0 + k;
-				const float g = (gamma != nullptr) ? to_float(gamma[c]) : 1.0f;
-				const float b = (beta_bn != nullptr) ? to_float(beta_bn[c]) : 0.0f;
-				const float scale = g / sqrtf(avg_var[channels + c] + 1.0e-6f);
-				const float shift = -avg_var[c] * scale + b;
-				float v = apply_activation(in.get(k) * scale + shift, act) * alpha;
-				if (beta != 0.0f)
-					v += beta * out.get(k);
-				out.set(k, v);
+				float v = in[k] * scale[k] + shift[k];
+				if (act == ACTIVATION_RELU)
+					v = fmaxf(v, 0.0f);
+				else if (act != ACTIVATION_LINEAR)
+					v = apply_activation(v, act);
+				v *= alpha;
+				out[k] = (beta != 0.0f) ? v + beta * out[k] : v;
 			}
-			out.store(y + off);
+			store_group<T, VEC>(y + off, out);
 		}
 	}
+	template<typename T, int VEC>
+	void launch_batchnorm(cudaStream_t stream, int sm_count, T *y, const T *x, const T *w, const T *b, const float *av, long long rows, int channels,
+			float alpha, float beta, int act)
+	{
+		const int groups = channels / VEC;
+		const int tx = std::min(groups, 256);
+		const int ty = std::max(1, 256 / tx);
+		const dim3 block(tx, ty);
+		const int row_blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((rows + ty - 1) / ty, static_cast<long long>(sm_count) * 8)));
+		const dim3 grid(row_blocks, ceil_div(groups, tx));
+		kernel_batchnorm_inference<T, VEC> <<<grid, block, 0, stream>>>(y, x, w, b, av, rows, channels, alpha, beta, act);
+	}
+
 	/* weights viewed as [outer, inner]; channel = row (per_row) or column.  One thread per element; the bias is updated by the
 	 * threads of the first column / row. */
 	template<typename T>
@@ -111,19 +138,20 @@ namespace
 			const int c = per_row ? r : col;
 			const float g = (gamma != nullptr) ? to_float(gamma[c]) : 1.0f;
 			const float scale = g / sqrtf(avg_var[channels + c] + 1.0e-6f);
-			weights[i] = static_cast<T>(to_float(weights[i]) * scale);
+			weights[i] = from_float<T>(to_float(weights[i]) * scale);
 			if ((per_row ? col : r) == 0 && bias != nullptr)
 			{
 				const float b = (beta_bn != nullptr) ? to_float(beta_bn[c]) : 0.0f;
 				const float shift = -avg_var[c] * scale + b;
-				bias[c] = static_cast<T>(to_float(bias[c]) * scale + shift);
+				bias[c] = from_float<T>(to_float(bias[c]) * scale + shift);
 			}
 		}
 	}
 
 	/* ------------------------------------------------------------------------------------------------ channel scaling */
 	template<typename T, int VEC>
-	__global__ void kernel_channel_scaling(T *y, const T *x, const T *scales, int hw, int channels, float alpha, float beta)
+	__global__ void __launch_bounds__(256) kernel_channel_scaling(T *y, const T *x, const T *scales, int hw, int channels, float alpha,
+			float beta)
 	{
 		const int groups = channels / VEC;
 		const int b = blockIdx.y;
@@ -132,171 +160,235 @@ namespace
 		{
 			const int c0 = static_cast<int>(i % groups) * VEC;
 			const long long off = (static_cast<long long>(b) * hw + i / groups) * channels + c0;
-			Pack<T, VEC> in, out, s;
-			in.load(x + off);
-			s.load(scales + static_cast<long long>(b) * channels + c0);
+			float in[VEC], s[VEC], out[VEC];
+			load_group<T, VEC>(x + off, in);
+			load_group<T, VEC>(scales + static_cast<long long>(b) * channels + c0, s);
 			if (beta != 0.0f)
-				out.load(y + off);
+				load_group<T, VEC>(y + off, out);
 #pragma unroll
 			for (int k = 0; k < VEC; k++)
 			{
-				float v = in.get(k) * s.get(k) * alpha;
-				if (beta != 0.0f)
-					v += beta * out.get(k);
-				out.set(k, v);
+				const float v = in[k] * s[k] * alpha;
+				out[k] = (beta != 0.0f) ? v + beta * out[k] : v;
 			}
-			out.store(y + off);
+			store_group<T, VEC>(y + off, out);
 		}
 	}
 
 	/* ------------------------------------------------------------------------------------------------ depthwise convolution */
-	/* grid (ceil(h / ROWS), batch), block (channel groups, ROWS): a thread owns one output row of one group of VEC channels and
-	 * walks along it.  Input column ww contributes to the K output columns ww - PAD .. ww + PAD, whose partial sums sit in K
-	 * register accumulators that shift by one per step: every input element is loaded once per filter row (K times in all, not
-	 * K x K), the filter taps come from L1 (K x K x channels elements, read by every thread of the CTA). */
-	template<typename T, int VEC, int K>
-	__global__ void kernel_depthwise_conv(T *y, const T *x, const T *w, const T *bias, int height, int width, int channels, float alpha,
-			float beta)
+	struct DepthwiseParams
+	{
+			int height, width, channels;
+			float alpha, beta; // floating point: y = alpha * conv + bias + beta * y
+			const float *scales; // int8: x = acc * scales[c] + bias_f32[c]
+			const float *bias_f32;
+			float inv_scale, inv_shift; // int8 requantisation: q = clamp(round(x * inv_scale + inv_shift))
+			float pad_value; // value of positions outside the image (the quantised zero; 0 for floating point)
+	};
+	constexpr int DEPTHWISE_SMEM_LIMIT = 96 * 1024;
+	/* grid (row tiles x column tiles, batch, ceil(groups / blockDim.x)), block (32 channel groups, rows).  QUANT: int8 in / out.
+	 * The CTA first copies its input patch -- (rows + K - 1) x (tile_w + K - 1) positions of its channels, positions outside the
+	 * image holding the padding value -- into shared memory; the arithmetic then needs no bounds checks and no global latency.
+	 * A thread owns one output row of one group of VEC channels and walks along it: input column c feeds the K output columns
+	 * c - K + 1 .. c through the K filter columns, so K partial sums live in a ring of register accumulators (the ring index is a
+	 * compile-time constant because the column loop is unrolled K times). */
+	template<typename T, int VEC, int K, bool QUANT>
+	__global__ void __launch_bounds__(256, 2) kernel_depthwise_conv(T *y, const T *x, const T *w, const T *bias, const DepthwiseParams p,
+			int tile_w, int tiles_w)
 	{
 		constexpr int PAD = (K - 1) / 2;
-		const int groups = channels / VEC;
-		const int h = blockIdx.x * blockDim.y + threadIdx.y;
-		const int b = blockIdx.y;
-		if (h >= height)
-			return;
-		for (int g = threadIdx.x; g < groups; g += blockDim.x)
+		extern __shared__ __align__(16) unsigned char smem_raw[];
+		Group<T, VEC> *tile = reinterpret_cast<Group<T, VEC>*>(smem_raw);
+		const int tx = threadIdx.x, ty = threadIdx.y, ntx = blockDim.x, nty = blockDim.y;
+		const int h0 = (blockIdx.x / tiles_w) * nty, w0 = (blockIdx.x % tiles_w) * tile_w;
+		const int c0 = (blockIdx.z * ntx + tx) * VEC;
+		const bool lane_ok = c0 < p.channels;
+		const int in_rows = nty + K - 1, in_cols = tile_w + K - 1;
+		const long long image = static_cast<long long>(blockIdx.y) * p.height * p.width * p.channels + c0;
+		const T *xb = x + image;
+		T *yb = y + image;
+
+		Group<T, VEC> pad_group;
+#pragma unroll
+		for (int k = 0; k < VEC; k++)
+			pad_group.v[k] = from_float<T>(p.pad_value);
+		for (int pix = ty; pix < in_rows * in_cols; pix += nty)
 		{
-			const int c0 = g * VEC;
-			float bv[VEC];
+			const int r = pix / in_cols, cc = pix - r * in_cols;
+			const int hh = h0 + r - PAD, ww = w0 + cc - PAD;
+			Group<T, VEC> g = pad_group;
+			if (lane_ok && hh >= 0 && hh < p.height && ww >= 0 && ww < p.width)
+				g = *reinterpret_cast<const Group<T, VEC>*>(xb + (static_cast<long long>(hh) * p.width + ww) * p.channels);
+			tile[pix * ntx + tx] = g;
+		}
+		__syncthreads();
+		const int h = h0 + ty;
+		if (!lane_ok || h >= p.height)
+			return;
+
+		float filt[K * K][VEC];
+#pragma unroll
+		for (int t = 0; t < K * K; t++)
+			load_group<T, VEC>(w + static_cast<long long>(t) * p.channels + c0, filt[t]);
+		float post_scale[VEC], post_shift[VEC];
+#pragma unroll
+		for (int k = 0; k < VEC; k++)
+		{
+			if (QUANT)
+			{
+				post_scale[k] = (p.scales != nullptr) ? p.scales[c0 + k] : 1.0f;
+				post_shift[k] = (p.bias_f32 != nullptr) ? p.bias_f32[c0 + k] : 0.0f;
+			}
+			else
+			{
+				post_scale[k] = p.alpha;
+				post_shift[k] = (bias != nullptr) ? to_float(bias[c0 + k]) : 0.0f;
+			}
+		}
+		float acc[K][VEC]; // ring: output column o of the tile lives in acc[o mod K]
+#pragma unroll
+		for (int s = 0; s < K; s++)
 #pragma unroll
 			for (int k = 0; k < VEC; k++)
-				bv[k] = (bias != nullptr) ? to_float(bias[c0 + k]) : 0.0f;
-			const T *xb = x + static_cast<long long>(b) * height * width * channels + c0;
-			T *yb = y + static_cast<long long>(b) * height * width * channels + c0;
-			const T *wb = w + c0;
-			float acc[K][VEC]; // acc[s]: output column ww - PAD + s
+				acc[s][k] = 0.0f;
+
+		const int out_cols = min(tile_w, p.width - w0);
+		const int ncols = out_cols + K - 1; // input columns of the patch this row needs
+		const Group<T, VEC> *row0 = tile + static_cast<long long>(ty) * in_cols * ntx + tx;
+		for (int col0 = 0; col0 < ncols; col0 += K)
+		{
 #pragma unroll
-			for (int s = 0; s < K; s++)
-#pragma unroll
-				for (int k = 0; k < VEC; k++)
-					acc[s][k] = 0.0f;
-			for (int ww = 0; ww < width + PAD; ww++)
+			for (int u = 0; u < K; u++)
 			{
-				if (ww < width)
+				const int col = col0 + u;
+				if (col < ncols)
 				{
 #pragma unroll
 					for (int i = 0; i < K; i++)
 					{
-						const int hh = h + i - PAD;
-						if (hh < 0 || hh >= height)
-							continue;
-						Pack<T, VEC> in;
-						in.load(xb + (static_cast<long long>(hh) * width + ww) * channels);
+						const Group<T, VEC> g = row0[(i * in_cols + col) * ntx];
 #pragma unroll
-						for (int s = 0; s < K; s++)
-						{ // output ww - PAD + s sees this input through filter column K - 1 - s
-							Pack<T, VEC> f;
-							f.load(wb + static_cast<long long>(i * K + (K - 1 - s)) * channels);
+						for (int j = 0; j < K; j++) // filter column j: output column col - j, ring slot (u - j) mod K
 #pragma unroll
 							for (int k = 0; k < VEC; k++)
-								acc[s][k] += in.get(k) * f.get(k);
+								acc[(u - j + K) % K][k] = fmaf(to_float(g.v[k]), filt[i * K + j][k], acc[(u - j + K) % K][k]);
+					}
+					if (col >= K - 1)
+					{ // output column col - (K - 1) is complete; its slot is (u + 1) mod K
+						float (&done)[VEC] = acc[(u + 1) % K];
+						const long long off = (static_cast<long long>(h) * p.width + (w0 + col - (K - 1))) * p.channels;
+						float out[VEC];
+						if (QUANT)
+						{
+#pragma unroll
+							for (int k = 0; k < VEC; k++)
+							{ // the host's CPU loop, operation for operation, without fused multiply-adds
+								const float t = __fadd_rn(__fmul_rn(done[k], post_scale[k]), post_shift[k]);
+								out[k] = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(t, p.inv_scale), p.inv_shift))));
+							}
 						}
+						else
+						{
+							if (p.beta != 0.0f)
+								load_group<T, VEC>(yb + off, out);
+#pragma unroll
+							for (int k = 0; k < VEC; k++)
+							{
+								const float v = done[k] * post_scale[k] + post_shift[k];
+								out[k] = (p.beta != 0.0f) ? v + p.beta * out[k] : v;
+							}
+						}
+						store_group<T, VEC>(yb + off, out);
 					}
-				}
-				const int col = ww - PAD; // complete: no later input column reaches it
-				if (col >= 0)
-				{
-					const long long off = (static_cast<long long>(h) * width + col) * channels;
-					Pack<T, VEC> out;
-					if (beta != 0.0f)
-						out.load(yb + off);
 #pragma unroll
 					for (int k = 0; k < VEC; k++)
-					{
-						float v = acc[0][k] * alpha + bv[k];
-						if (beta != 0.0f)
-							v += beta * out.get(k);
-						out.set(k, v);
-					}
-					out.store(yb + off);
+						acc[(u + 1) % K][k] = 0.0f; // the slot that the next column opens (or the one just emitted)
 				}
-#pragma unroll
-				for (int s = 0; s + 1 < K; s++)
-#pragma unroll
-					for (int k = 0; k < VEC; k++)
-						acc[s][k] = acc[s + 1][k];
-#pragma unroll
-				for (int k = 0; k < VEC; k++)
-					acc[K - 1][k] = 0.0f;
-			}
-		}
-	}
-	/* int8: one thread per (row, channel); channels are consecutive across the threads of a warp (coalesced byte accesses). */
-	template<int K>
-	__global__ void kernel_depthwise_conv_int8(int8_t *y, const int8_t *x, const int8_t *w, const float *scales, const float *bias, int height,
-			int width, int channels, float inv_scale, float inv_shift, int padding_value)
-	{
-		constexpr int PAD = (K - 1) / 2;
-		const int h = blockIdx.x * blockDim.y + threadIdx.y;
-		const int b = blockIdx.y;
-		if (h >= height)
-			return;
-		for (int c = threadIdx.x; c < channels; c += blockDim.x)
-		{
-			int filt[K * K];
-#pragma unroll
-			for (int t = 0; t < K * K; t++)
-				filt[t] = w[static_cast<long long>(t) * channels + c];
-			const float scale = (scales != nullptr) ? scales[c] : 1.0f;
-			const float shift = (bias != nullptr) ? bias[c] : 0.0f;
-			const int8_t *xb = x + static_cast<long long>(b) * height * width * channels + c;
-			int8_t *yb = y + static_cast<long long>(b) * height * width * channels + c;
-			for (int col = 0; col < width; col++)
-			{
-				int acc = 0;
-#pragma unroll
-				for (int i = 0; i < K; i++)
-				{
-					const int hh = h + i - PAD;
-#pragma unroll
-					for (int j = 0; j < K; j++)
-					{
-						const int ww = col + j - PAD;
-						const bool inside = hh >= 0 && hh < height && ww >= 0 && ww < width;
-						const int v = inside ? static_cast<int>(xb[(static_cast<long long>(hh) * width + ww) * channels]) : padding_value;
-						acc += filt[i * K + j] * v;
-					}
-				}
-				const float t = __fadd_rn(__fmul_rn(static_cast<float>(acc), scale), shift);
-				const float q = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(t, inv_scale), inv_shift))));
-				yb[(static_cast<long long>(h) * width + col) * channels] = static_cast<int8_t>(q);
 			}
 		}
 	}
 
-	template<typename T, int VEC>
-	void launch_depthwise(cudaStream_t stream, int k, const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &b, mlTensor_t &y, float alpha,
-			float beta)
+	/* Shared-memory opt-in above 48 KB and the large carve-out, once per device and kernel instantiation. */
+	template<typename T, int VEC, int K, bool QUANT>
+	bool depthwise_opt_in(int device)
 	{
-		const int batch = x.dim[0], height = x.dim[1], width = x.dim[2], channels = x.dim[3];
-		const int groups = channels / VEC;
-		const int tx = std::min(groups, 64);
-		const int rows = std::max(1, 256 / tx);
-		const dim3 block(tx, rows);
-		const dim3 grid(ceil_div(height, rows), batch);
-		T *yp = reinterpret_cast<T*>(y.data);
-		const T *xp = reinterpret_cast<const T*>(x.data), *wp = reinterpret_cast<const T*>(w.data), *bp = reinterpret_cast<const T*>(b.data);
-		switch (k)
+		static bool done[MAX_DEVICES] = { false };
+		if (device < 0 || device >= MAX_DEVICES)
+			return false;
+		if (!done[device])
 		{
-			case 3:
-				kernel_depthwise_conv<T, VEC, 3> <<<grid, block, 0, stream>>>(yp, xp, wp, bp, height, width, channels, alpha, beta);
-				break;
-			case 5:
-				kernel_depthwise_conv<T, VEC, 5> <<<grid, block, 0, stream>>>(yp, xp, wp, bp, height, width, channels, alpha, beta);
-				break;
-			default:
-				kernel_depthwise_conv<T, VEC, 7> <<<grid, block, 0, stream>>>(yp, xp, wp, bp, height, width, channels, alpha, beta);
-				break;
+			if (cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEPTHWISE_SMEM_LIMIT)
+					!= cudaSuccess || cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, QUANT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+							cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+			{
+				cudaGetLastError();
+				return false;
+			}
+			done[device] = true;
+		}
+		return true;
+	}
+	template<typename T, int VEC, int K, bool QUANT>
+	bool launch_depthwise_kv(cudaStream_t stream, int device, int batch, T *y, const T *x, const T *w, const T *bias, const DepthwiseParams &p)
+	{
+		const int groups = p.channels / VEC;
+		const int tx = std::min(groups, 32);
+		// the largest patch (rows x columns) that fits the shared-memory budget
+		int ty = std::max(1, std::min(p.height, 256 / tx)), tile_w = std::min(p.width, 32);
+		auto patch_bytes = [&](int rows, int cols)
+		{
+			return static_cast<size_t>(rows + K - 1) * (cols + K - 1) * tx * VEC * sizeof(T);
+		};
+		while (patch_bytes(ty, tile_w) > static_cast<size_t>(DEPTHWISE_SMEM_LIMIT) && (ty > 1 || tile_w > 1))
+		{
+			if (tile_w >= ty && tile_w > 1)
+				tile_w = (tile_w + 1) / 2;
+			else
+				ty = (ty + 1) / 2;
+		}
+		const size_t smem = patch_bytes(ty, tile_w);
+		if (!depthwise_opt_in<T, VEC, K, QUANT>(device)) // also asks for the large shared-memory carve-out: several patches per SM
+			return false;
+		const int tiles_w = ceil_div(p.width, tile_w);
+		const dim3 block(tx, ty);
+		const dim3 grid(ceil_div(p.height, ty) * tiles_w, batch, ceil_div(groups, tx));
+		kernel_depthwise_conv<T, VEC, K, QUANT> <<<grid, block, smem, stream>>>(y, x, w, bias, p, tile_w, tiles_w);
+		return true;
+	}
+	/* The widest channel group that keeps the k x k fp32 filter taps in registers: 8 / 4 / 2 channels for k = 3 / 5 / 7. */
+	template<typename T, bool QUANT>
+	bool launch_depthwise(cudaStream_t stream, int device, int k, int batch, T *y, const T *x, const T *w, const T *bias, const DepthwiseParams &p)
+	{
+		auto ok = [&](int vec)
+		{
+			const size_t bytes = sizeof(T) * vec;
+			return p.channels % vec == 0 && aligned_to(x, bytes) && aligned_to(y, bytes) && aligned_to(w, bytes);
+		};
+		constexpr int WIDEST = (sizeof(T) == 4) ? 4 : 8;
+		if (k == 3)
+		{
+			if (ok(WIDEST))
+				return launch_depthwise_kv<T, WIDEST, 3, QUANT>(stream, device, batch, y, x, w, bias, p);
+			else if (ok(2))
+				return launch_depthwise_kv<T, 2, 3, QUANT>(stream, device, batch, y, x, w, bias, p);
+			else
+				return launch_depthwise_kv<T, 1, 3, QUANT>(stream, device, batch, y, x, w, bias, p);
+		}
+		else if (k == 5)
+		{
+			if (ok(4))
+				return launch_depthwise_kv<T, 4, 5, QUANT>(stream, device, batch, y, x, w, bias, p);
+			else if (ok(2))
+				return launch_depthwise_kv<T, 2, 5, QUANT>(stream, device, batch, y, x, w, bias, p);
+			else
+				return launch_depthwise_kv<T, 1, 5, QUANT>(stream, device, batch, y, x, w, bias, p);
+		}
+		else
+		{
+			if (ok(2))
+				return launch_depthwise_kv<T, 2, 7, QUANT>(stream, device, batch, y, x, w, bias, p);
+			else
+				return launch_depthwise_kv<T, 1, 7, QUANT>(stream, device, batch, y, x, w, bias, p);
 		}
 	}
 }
@@ -329,11 +421,9 @@ extern "C"
 				const __half *xp = reinterpret_cast<const __half*>(x.data), *wp = reinterpret_cast<const __half*>(w.data),
 						*bp = reinterpret_cast<const __half*>(b.data);
 				if (channels % 8 == 0 && aligned_to(xp, 16) && aligned_to(yp, 16))
-					kernel_batchnorm_inference<__half, 8> <<<grid_for(rows * (channels / 8), 256, sms), 256, 0, stream>>>(yp, xp, wp, bp, av, rows,
-							channels, alpha, beta, act);
+					launch_batchnorm<__half, 8>(stream, sms, yp, xp, wp, bp, av, rows, channels, alpha, beta, act);
 				else
-					kernel_batchnorm_inference<__half, 1> <<<grid_for(rows * channels, 256, sms), 256, 0, stream>>>(yp, xp, wp, bp, av, rows, channels,
-							alpha, beta, act);
+					launch_batchnorm<__half, 1>(stream, sms, yp, xp, wp, bp, av, rows, channels, alpha, beta, act);
 				break;
 			}
 			case DTYPE_FLOAT32:
@@ -342,11 +432,9 @@ extern "C"
 				const float *xp = reinterpret_cast<const float*>(x.data), *wp = reinterpret_cast<const float*>(w.data),
 						*bp = reinterpret_cast<const float*>(b.data);
 				if (channels % 4 == 0 && aligned_to(xp, 16) && aligned_to(yp, 16))
-					kernel_batchnorm_inference<float, 4> <<<grid_for(rows * (channels / 4), 256, sms), 256, 0, stream>>>(yp, xp, wp, bp, av, rows,
-							channels, alpha, beta, act);
+					launch_batchnorm<float, 4>(stream, sms, yp, xp, wp, bp, av, rows, channels, alpha, beta, act);
 				else
-					kernel_batchnorm_inference<float, 1> <<<grid_for(rows * channels, 256, sms), 256, 0, stream>>>(yp, xp, wp, bp, av, rows, channels,
-							alpha, beta, act);
+					launch_batchnorm<float, 1>(stream, sms, yp, xp, wp, bp, av, rows, channels, alpha, beta, act);
 				break;
 			}
 			default:
@@ -410,6 +498,10 @@ extern "C"
 		MB200_REQUIRE(context, batch <= 65535, "cuda_channel_scaling_forward: batch %d exceeds one launch", batch);
 		cudaStream_t stream = use_stream(context);
 		const int sms = get(context)->sm_count;
+		auto blocks_per_image = [&](int vec)
+		{
+			return std::max(1, grid_for(static_cast<long long>(hw) * (channels / vec), 256, sms) / batch + 1);
+		};
 		switch (x.dtype)
 		{
 			case DTYPE_FLOAT16:
@@ -417,11 +509,9 @@ extern "C"
 				__half *yp = reinterpret_cast<__half*>(y.data);
 				const __half *xp = reinterpret_cast<const __half*>(x.data), *sp = reinterpret_cast<const __half*>(scales.data);
 				if (channels % 8 == 0 && aligned_to(xp, 16) && aligned_to(yp, 16) && aligned_to(sp, 16))
-					kernel_channel_scaling<__half, 8> <<<dim3(std::max(1, grid_for(static_cast<long long>(hw) * (channels / 8), 256, sms) / batch + 1), batch), 256, 0,
-							stream>>>(yp, xp, sp, hw, channels, alpha, beta);
+					kernel_channel_scaling<__half, 8> <<<dim3(blocks_per_image(8), batch), 256, 0, stream>>>(yp, xp, sp, hw, channels, alpha, beta);
 				else
-					kernel_channel_scaling<__half, 1> <<<dim3(std::max(1, grid_for(static_cast<long long>(hw) * channels, 256, sms) / batch + 1), batch), 256, 0,
-							stream>>>(yp, xp, sp, hw, channels, alpha, beta);
+					kernel_channel_scaling<__half, 1> <<<dim3(blocks_per_image(1), batch), 256, 0, stream>>>(yp, xp, sp, hw, channels, alpha, beta);
 				break;
 			}
 			case DTYPE_FLOAT32:
@@ -429,11 +519,9 @@ extern "C"
 				float *yp = reinterpret_cast<float*>(y.data);
 				const float *xp = reinterpret_cast<const float*>(x.data), *sp = reinterpret_cast<const float*>(scales.data);
 				if (channels % 4 == 0 && aligned_to(xp, 16) && aligned_to(yp, 16) && aligned_to(sp, 16))
-					kernel_channel_scaling<float, 4> <<<dim3(std::max(1, grid_for(static_cast<long long>(hw) * (channels / 4), 256, sms) / batch + 1), batch), 256, 0,
-							stream>>>(yp, xp, sp, hw, channels, alpha, beta);
+					kernel_channel_scaling<float, 4> <<<dim3(blocks_per_image(4), batch), 256, 0, stream>>>(yp, xp, sp, hw, channels, alpha, beta);
 				else
-					kernel_channel_scaling<float, 1> <<<dim3(std::max(1, grid_for(static_cast<long long>(hw) * channels, 256, sms) / batch + 1), batch), 256, 0,
-							stream>>>(yp, xp, sp, hw, channels, alpha, beta);
+					kernel_channel_scaling<float, 1> <<<dim3(blocks_per_image(1), batch), 256, 0, stream>>>(yp, xp, sp, hw, channels, alpha, beta);
 				break;
 			}
 			default:
@@ -458,26 +546,28 @@ extern "C"
 			return;
 		MB200_REQUIRE(context, x.dim[0] <= 65535, "cuda_depthwise_conv_forward: batch %d exceeds one launch", x.dim[0]);
 		cudaStream_t stream = use_stream(context);
-		const int channels = x.dim[3];
-		const bool aligned = aligned_to(x.data, 16) && aligned_to(y.data, 16) && aligned_to(w.data, 16);
+		DepthwiseParams p = { };
+		p.height = x.dim[1];
+		p.width = x.dim[2];
+		p.channels = x.dim[3];
+		p.alpha = alpha;
+		p.beta = beta;
+		bool launched = false;
 		switch (x.dtype)
 		{
 			case DTYPE_FLOAT16:
-				if (channels % 8 == 0 && aligned)
-					launch_depthwise<__half, 8>(stream, w.dim[0], x, w, b, y, alpha, beta);
-				else
-					launch_depthwise<__half, 1>(stream, w.dim[0], x, w, b, y, alpha, beta);
+				launched = launch_depthwise<__half, false>(stream, get(context)->device, w.dim[0], x.dim[0], reinterpret_cast<__half*>(y.data),
+						reinterpret_cast<const __half*>(x.data), reinterpret_cast<const __half*>(w.data), reinterpret_cast<const __half*>(b.data), p);
 				break;
 			case DTYPE_FLOAT32:
-				if (channels % 4 == 0 && aligned)
-					launch_depthwise<float, 4>(stream, w.dim[0], x, w, b, y, alpha, beta);
-				else
-					launch_depthwise<float, 1>(stream, w.dim[0], x, w, b, y, alpha, beta);
+				launched = launch_depthwise<float, false>(stream, get(context)->device, w.dim[0], x.dim[0], reinterpret_cast<float*>(y.data),
+						reinterpret_cast<const float*>(x.data), reinterpret_cast<const float*>(w.data), reinterpret_cast<const float*>(b.data), p);
 				break;
 			default:
 				record_error(context, "cuda_depthwise_conv_forward: dtype %d not supported", static_cast<int>(x.dtype));
 				return;
 		}
+		MB200_REQUIRE(context, launched, "cuda_depthwise_conv_forward: shared-memory opt-in failed");
 		MB200_COUNT_LAUNCH();
 		check_cuda(context, cudaGetLastError(), "cuda_depthwise_conv_forward");
 	}
@@ -493,31 +583,24 @@ extern "C"
 		MB200_REQUIRE(context, weights_shape.dim[1] == k && (k == 3 || k == 5 || k == 7) && weights_shape.dim[2] == input_shape.dim[3],
 				"cuda_quantized_depthwise_conv_forward: filter shape not supported");
 		MB200_REQUIRE(context, output_qd.scale != 0.0f, "cuda_quantized_depthwise_conv_forward: output scale is zero");
+		MB200_REQUIRE(context, padding_value >= -128 && padding_value <= 127, "cuda_quantized_depthwise_conv_forward: padding value %d is not an int8", padding_value);
 		flush_pending(context);
-		const int batch = input_shape.dim[0], height = input_shape.dim[1], width = input_shape.dim[2], channels = input_shape.dim[3];
 		if (volume(input_shape) == 0)
 			return;
-		MB200_REQUIRE(context, batch <= 65535, "cuda_quantized_depthwise_conv_forward: batch %d exceeds one launch", batch);
+		MB200_REQUIRE(context, input_shape.dim[0] <= 65535, "cuda_quantized_depthwise_conv_forward: batch %d exceeds one launch", input_shape.dim[0]);
 		cudaStream_t stream = use_stream(context);
-		const int tx = std::min(channels, 128);
-		const int rows = std::max(1, 256 / tx);
-		const dim3 block(tx, rows), grid(ceil_div(height, rows), batch);
-		const float inv_scale = 1.0f / output_qd.scale, inv_shift = -output_qd.shift / output_qd.scale; // AffineTransform::get_inverse
-		int8_t *yp = reinterpret_cast<int8_t*>(output);
-		const int8_t *xp = reinterpret_cast<const int8_t*>(input), *wp = reinterpret_cast<const int8_t*>(weights);
-		const float *sp = reinterpret_cast<const float*>(scales), *bp = reinterpret_cast<const float*>(bias);
-		switch (k)
-		{
-			case 3:
-				kernel_depthwise_conv_int8<3> <<<grid, block, 0, stream>>>(yp, xp, wp, sp, bp, height, width, channels, inv_scale, inv_shift, padding_value);
-				break;
-			case 5:
-				kernel_depthwise_conv_int8<5> <<<grid, block, 0, stream>>>(yp, xp, wp, sp, bp, height, width, channels, inv_scale, inv_shift, padding_value);
-				break;
-			default:
-				kernel_depthwise_conv_int8<7> <<<grid, block, 0, stream>>>(yp, xp, wp, sp, bp, height, width, channels, inv_scale, inv_shift, padding_value);
-				break;
-		}
+		DepthwiseParams p = { };
+		p.height = input_shape.dim[1];
+		p.width = input_shape.dim[2];
+		p.channels = input_shape.dim[3];
+		p.scales = reinterpret_cast<const float*>(scales);
+		p.bias_f32 = reinterpret_cast<const float*>(bias);
+		p.inv_scale = 1.0f / output_qd.scale; // AffineTransform::get_inverse (include/minml/layers/quantization.hpp:52-63)
+		p.inv_shift = -output_qd.shift / output_qd.scale;
+		p.pad_value = static_cast<float>(padding_value);
+		const bool launched = launch_depthwise<int8_t, true>(stream, get(context)->device, k, input_shape.dim[0], reinterpret_cast<int8_t*>(output),
+				reinterpret_cast<const int8_t*>(input), reinterpret_cast<const int8_t*>(weights), static_cast<const int8_t*>(nullptr), p);
+		MB200_REQUIRE(context, launched, "cuda_quantized_depthwise_conv_forward: shared-memory opt-in failed");
 		MB200_COUNT_LAUNCH();
 		check_cuda(context, cudaGetLastError(), "cuda_quantized_depthwise_conv_forward");
 	}

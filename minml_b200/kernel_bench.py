@@ -177,6 +177,18 @@ def main():
     t = h * w
     add("multi_head_attention_forward (8 heads, rel-pos bias)", lambda: B.multiHeadAttentionForward(ctx, qkv, att, table, heads), 4 * act_bytes,
         4.0 * b * heads * t * t * (c // heads))
+
+    # ---- layers next to the convolution path: batch norm at inference, depthwise 7x7 (fp16 and int8), channel scaling
+    avg_var = torch.cat([torch.randn(1, c, device="cuda"), torch.rand(1, c, device="cuda") + 0.5]).contiguous()
+    add("batchnorm_inference (+relu)", lambda: B.batchnormInference(ctx, x, y, gamma, beta, avg_var, "relu"), 2 * act_bytes)
+    wdw = rand(7, 7, c)
+    add("depthwise_conv_forward 7x7 fp16", lambda: B.depthwiseConvForward(ctx, x, wdw, y, bias), 2 * act_bytes + 49 * c * 2)
+    wdq = torch.randint(-127, 128, (7, 7, c), device="cuda", dtype=torch.int8)
+    dscale, dbias = torch.full((c,), 1e-4, device="cuda"), torch.zeros(c, device="cuda")
+    add("quantized_depthwise_conv_forward 7x7 int8", lambda: B.quantized_depthwise_conv_forward(ctx, xq, wdq, dscale, dbias, yq, (0.05, 0.0), 0),
+        2 * rows * c + 49 * c)
+    gate = rand(b, c)
+    add("channel_scaling_forward", lambda: B.channelScalingForward(ctx, x, gate, y), 2 * act_bytes + b * c * 2)
     ctx.close()
 
 
