@@ -89,6 +89,10 @@ class Context:
     def set_fusion(self, enabled):
         lib.mb200_set_fusion(self.handle, 1 if enabled else 0)
 
+    def enable_tf32(self, enabled):
+        """ml::Context::enableTF32: fp32 matrix products may then run on the tensor cores in TF32 (off by default, as in the reference)."""
+        lib.cuda_enable_tf32(self.handle, bool(enabled))
+
     def wait_for_torch(self):
         """Orders this context's stream after work torch has queued on its current stream."""
         torch.cuda.current_stream().synchronize()

@@ -85,10 +85,13 @@ namespace
 		flush_pending(ctx);
 
 		const void *c_in = (beta != 0.0f) ? (Cin != nullptr ? Cin : D.data) : nullptr;
-		if (!ta && tb && (A.dtype == DTYPE_FLOAT16 || A.dtype == DTYPE_INT8))
+		// fp32 operands go to the tensor cores only when the host has allowed TF32 on this context (cuda_enable_tf32), the
+		// condition under which the reference asks cuBLAS for CUBLAS_COMPUTE_32F_FAST_TF32 (src/backend/cuda/gemms.cpp:150-153)
+		const bool tf32 = A.dtype == DTYPE_FLOAT32 && D.dtype == DTYPE_FLOAT32 && get(ctx)->allow_tf32;
+		if (!ta && tb && (A.dtype == DTYPE_FLOAT16 || A.dtype == DTYPE_INT8 || tf32))
 		{
 			GemmTcProblem g;
-			g.kind = (A.dtype == DTYPE_FLOAT16) ? 0 : 1;
+			g.kind = (A.dtype == DTYPE_FLOAT16) ? 0 : (A.dtype == DTYPE_INT8 ? 1 : 2);
 			g.M = rows;
 			g.N = cols;
 			g.K = K;

@@ -120,7 +120,7 @@ namespace mb200
 			const int m_tiles = (p.M + BM - 1) / BM;
 			const int n_tiles = (p.N + BN - 1) / BN;
 			const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * p.batch;
-			const int elems_per_kblock = (KIND == 0) ? 64 : 128;
+			const int elems_per_kblock = (KIND == 0) ? 64 : (KIND == 1 ? 128 : 32); // 128 bytes of K per row
 			const int k_blocks = (p.K + elems_per_kblock - 1) / elems_per_kblock;
 
 			if (threadIdx.x == 0)
@@ -186,7 +186,7 @@ namespace mb200
 			{ /* ------------------------------------------- MMA issuer */
 				if (elect_one())
 				{
-					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN);
+					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : (KIND == 1 ? make_idesc_i8(BN) : make_idesc_tf32(BN));
 					uint32_t it = 0;
 					uint32_t local_tile = 0;
 					bool ok = true;
@@ -326,7 +326,7 @@ namespace mb200
 						}
 						if (!row_ok)
 							continue;
-						if (KIND == 0)
+						if (KIND == 0 || KIND == 2)
 						{
 #pragma unroll
 							for (int j = 0; j < 32; j++)
@@ -510,7 +510,7 @@ namespace mb200
 	{
 		if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0)
 			return false;
-		const int elem = (g.kind == 0) ? 2 : 1;
+		const int elem = (g.kind == 0) ? 2 : (g.kind == 1 ? 1 : 4);
 		// TMA: 16-byte aligned bases and row strides
 		if (!aligned_to(g.A, 16) || !aligned_to(g.B, 16))
 			return false;
@@ -525,6 +525,8 @@ namespace mb200
 		}
 		if (g.kind == 0 && g.out_dtype != DTYPE_FLOAT16 && g.out_dtype != DTYPE_FLOAT32)
 			return false;
+		if (g.kind == 2 && g.out_dtype != DTYPE_FLOAT32)
+			return false;
 		if (g.kind == 1 && g.out_dtype != DTYPE_INT32 && g.out_dtype != DTYPE_INT8 && g.out_dtype != DTYPE_FLOAT16
 				&& g.out_dtype != DTYPE_FLOAT32)
 			return false;
@@ -535,10 +537,11 @@ namespace mb200
 	{
 		Context *c = get(ctx);
 		cudaStream_t stream = use_stream(ctx);
-		const int elem = (g.kind == 0) ? 2 : 1;
-		const CUtensorMapDataType dt = (g.kind == 0) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+		const int elem = (g.kind == 0) ? 2 : (g.kind == 1 ? 1 : 4);
+		const CUtensorMapDataType dt = (g.kind == 0) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+				: (g.kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
 		const int bn = (g.N > 128) ? 256 : 128;
-		const uint32_t box_k = (g.kind == 0) ? 64 : 128;
+		const uint32_t box_k = 128 / elem;
 
 		const bool a_bcast = (g.batch > 1 && g.stride_a == 0);
 		const bool b_bcast = (g.batch > 1 && g.stride_b == 0);
@@ -590,6 +593,9 @@ namespace mb200
 		p.status = c->dev_status;
 		c->kernels_with_waits = true;
 
+		if (g.kind == 2)
+			return (bn == 256) ? launch<2, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<2, 128>(ctx, stream, map_a, map_b, p,
+							c->sm_count);
 		if (g.kind == 0)
 			return (bn == 256) ? launch<0, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128>(ctx, stream, map_a, map_b, p,
 							c->sm_count);

@@ -176,10 +176,22 @@ namespace mb200
 		{
 			return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 		}
-		template<int KIND> // 0: kind::f16, 1: kind::i8
+		/* D fp32 <- tf32 x tf32: fp32 operands in shared memory, of which the tensor core reads the upper 19 bits. */
+		__host__ __device__ constexpr uint32_t make_idesc_tf32(int n)
+		{
+			return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+		}
+		template<int KIND> // 0: kind::f16, 1: kind::i8, 2: kind::tf32
 		__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 		{
-			if (KIND == 0)
+			if (KIND == 2)
+				asm volatile(
+						"{\n\t"
+						".reg .pred p;\n\t"
+						"setp.ne.b32 p, %4, 0;\n\t"
+						"tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+			else if (KIND == 0)
 				asm volatile(
 						"{\n\t"
 						".reg .pred p;\n\t"

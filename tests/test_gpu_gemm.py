@@ -145,3 +145,47 @@ def test_shape_mismatch_is_reported(ctx):
     with pytest.raises(B.BackendError):
         B.gemm(ctx, "n", torch.zeros(4, 5, device="cuda"), "n", torch.zeros(6, 7, device="cuda"), torch.zeros(4, 7, device="cuda"))
     ctx.synchronize()
+
+
+TF32_REL = 2e-3  # 10 explicit mantissa bits on each operand, fp32 accumulation
+
+
+@pytest.mark.parametrize("shape", [(300, 200, 128), (129, 257, 40), (4096, 256, 256)])
+def test_fp32_nt_on_tensor_cores_when_tf32_is_enabled(ctx, oracle, shape):
+    """cuda_enable_tf32 moves fp32 'n','t' products to tcgen05 kind::tf32 (the reference then asks cuBLAS for FAST_TF32,
+    src/backend/cuda/gemms.cpp:150-153); with it off the result is plain fp32."""
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(sum(shape))
+    a, b = r.standard_normal((m, k)).astype(np.float32), r.standard_normal((n, k)).astype(np.float32)
+    bias, c0 = r.standard_normal(n).astype(np.float32), r.standard_normal((m, n)).astype(np.float32)
+    want = oracle.add_bias_act(oracle.gemm("n", a, "t", b) + c0, bias, "relu")
+    launches = []
+    for tf32 in (False, True):
+        ctx.enable_tf32(tf32)
+        d = torch.zeros((m, n), device="cuda")
+        before = B.launch_count()
+        B.gemm_ex(ctx, d, 1.0, "n", dev(a), "t", dev(b), 1.0, dev(c0), dev(bias), "relu")
+        ctx.synchronize()
+        launches.append(B.launch_count() - before)
+        err = max_rel_err(host(d), want)
+        assert err <= (TF32_REL if tf32 else 1e-5)
+    ctx.enable_tf32(False)
+    assert launches[1] == 1  # one fused tensor-core kernel
+
+
+def test_fp32_winograd_layer_with_tf32(ctx, oracle):
+    from minml_b200 import layers as L
+    x = np.random.default_rng(2).uniform(-1, 1, (8, 15, 15, 128)).astype(np.float32)
+    wt = (np.random.default_rng(3).standard_normal((128, 3, 3, 128)) * np.sqrt(2.0 / (9 * 128))).astype(np.float32)
+    bias = (np.random.default_rng(4).standard_normal(128) * 0.01).astype(np.float32)
+    conv = L.Conv2D(ctx, wt, bias, "relu", torch.float32)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    y = torch.empty((8, 15, 15, 128), device="cuda")
+    ctx.enable_tf32(True)
+    conv.forward([dev(x)], y, ws)
+    ctx.synchronize()
+    ctx.enable_tf32(False)
+    err = max_rel_err(host(y), oracle.conv2d(x, wt, bias, None, "relu"))
+    assert err <= 1.5e-2  # measured 8.4e-3: F(4x4,3x3) amplifies the TF32 rounding of V and U (fp16 V / M give 1.2e-2 on such layers)
