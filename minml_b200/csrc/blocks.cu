@@ -189,21 +189,21 @@ namespace
 	/* grid (row tiles x column tiles, batch, ceil(groups / blockDim.x)), block (32 channel groups, rows).  QUANT: int8 in / out.
 	 * The CTA first copies its input patch -- (rows + K - 1) x (tile_w + K - 1) positions of its channels, positions outside the
 	 * image holding the padding value -- into shared memory; the arithmetic then needs no bounds checks and no global latency.
-	 * A thread owns one output row of one group of VEC channels and walks along it: input column c feeds the K output columns
+	 * A thread owns R consecutive output rows of one group of VEC channels and walks along them: input column c feeds the K output columns
 	 * c - K + 1 .. c through the K filter columns, so K partial sums live in a ring of register accumulators (the ring index is a
 	 * compile-time constant because the column loop is unrolled K times). */
-	template<typename T, int VEC, int K, bool QUANT>
-	__global__ void __launch_bounds__(256, 2) kernel_depthwise_conv(T *y, const T *x, const T *w, const T *bias, const DepthwiseParams p,
+	template<typename T, int VEC, int K, int R, bool QUANT>
+	__global__ void __launch_bounds__(256) kernel_depthwise_conv(T *y, const T *x, const T *w, const T *bias, const DepthwiseParams p,
 			int tile_w, int tiles_w)
 	{
 		constexpr int PAD = (K - 1) / 2;
 		extern __shared__ __align__(16) unsigned char smem_raw[];
 		Group<T, VEC> *tile = reinterpret_cast<Group<T, VEC>*>(smem_raw);
 		const int tx = threadIdx.x, ty = threadIdx.y, ntx = blockDim.x, nty = blockDim.y;
-		const int h0 = (blockIdx.x / tiles_w) * nty, w0 = (blockIdx.x % tiles_w) * tile_w;
+		const int h0 = (blockIdx.x / tiles_w) * nty * R, w0 = (blockIdx.x % tiles_w) * tile_w;
 		const int c0 = (blockIdx.z * ntx + tx) * VEC;
 		const bool lane_ok = c0 < p.channels;
-		const int in_rows = nty + K - 1, in_cols = tile_w + K - 1;
+		const int in_rows = nty * R + K - 1, in_cols = tile_w + K - 1;
 		const long long image = static_cast<long long>(blockIdx.y) * p.height * p.width * p.channels + c0;
 		const T *xb = x + image;
 		T *yb = y + image;
@@ -212,17 +212,20 @@ namespace
 #pragma unroll
 		for (int k = 0; k < VEC; k++)
 			pad_group.v[k] = from_float<T>(p.pad_value);
-		for (int pix = ty; pix < in_rows * in_cols; pix += nty)
-		{
-			const int r = pix / in_cols, cc = pix - r * in_cols;
-			const int hh = h0 + r - PAD, ww = w0 + cc - PAD;
-			Group<T, VEC> g = pad_group;
-			if (lane_ok && hh >= 0 && hh < p.height && ww >= 0 && ww < p.width)
-				g = *reinterpret_cast<const Group<T, VEC>*>(xb + (static_cast<long long>(hh) * p.width + ww) * p.channels);
-			tile[pix * ntx + tx] = g;
+		for (int r = ty; r < in_rows; r += nty)
+		{ // one patch row per step of threadIdx.y; the lanes of a warp copy consecutive channel groups of one position
+			const int hh = h0 + r - PAD;
+			const bool row_inside = lane_ok && hh >= 0 && hh < p.height;
+			const T *src = xb + (static_cast<long long>(hh) * p.width + (w0 - PAD)) * p.channels;
+			Group<T, VEC> *dst = tile + static_cast<long long>(r) * in_cols * ntx + tx;
+			for (int cc = 0; cc < in_cols; cc++, src += p.channels, dst += ntx)
+			{
+				const int ww = w0 + cc - PAD;
+				*dst = (row_inside && ww >= 0 && ww < p.width) ? *reinterpret_cast<const Group<T, VEC>*>(src) : pad_group;
+			}
 		}
 		__syncthreads();
-		const int h = h0 + ty;
+		const int h = h0 + ty * R; // first of this thread's R output rows
 		if (!lane_ok || h >= p.height)
 			return;
 
@@ -245,16 +248,18 @@ namespace
 				post_shift[k] = (bias != nullptr) ? to_float(bias[c0 + k]) : 0.0f;
 			}
 		}
-		float acc[K][VEC]; // ring: output column o of the tile lives in acc[o mod K]
+		float acc[R][K][VEC]; // per output row a ring: output column o of the tile lives in slot o mod K
 #pragma unroll
-		for (int s = 0; s < K; s++)
+		for (int r = 0; r < R; r++)
 #pragma unroll
-			for (int k = 0; k < VEC; k++)
-				acc[s][k] = 0.0f;
+			for (int s = 0; s < K; s++)
+#pragma unroll
+				for (int k = 0; k < VEC; k++)
+					acc[r][s][k] = 0.0f;
 
 		const int out_cols = min(tile_w, p.width - w0);
-		const int ncols = out_cols + K - 1; // input columns of the patch this row needs
-		const Group<T, VEC> *row0 = tile + static_cast<long long>(ty) * in_cols * ntx + tx;
+		const int ncols = out_cols + K - 1; // input columns of the patch these rows need
+		const Group<T, VEC> *row0 = tile + static_cast<long long>(ty) * R * in_cols * ntx + tx;
 		for (int col0 = 0; col0 < ncols; col0 += K)
 		{
 #pragma unroll
@@ -264,52 +269,66 @@ namespace
 				if (col < ncols)
 				{
 #pragma unroll
-					for (int i = 0; i < K; i++)
-					{
+					for (int i = 0; i < K + R - 1; i++)
+					{ // patch row i feeds output row r through filter row i - r
+						float in[VEC];
 						const Group<T, VEC> g = row0[(i * in_cols + col) * ntx];
 #pragma unroll
-						for (int j = 0; j < K; j++) // filter column j: output column col - j, ring slot (u - j) mod K
+						for (int k = 0; k < VEC; k++)
+							in[k] = to_float(g.v[k]);
 #pragma unroll
-							for (int k = 0; k < VEC; k++)
-								acc[(u - j + K) % K][k] = fmaf(to_float(g.v[k]), filt[i * K + j][k], acc[(u - j + K) % K][k]);
-					}
-					if (col >= K - 1)
-					{ // output column col - (K - 1) is complete; its slot is (u + 1) mod K
-						float (&done)[VEC] = acc[(u + 1) % K];
-						const long long off = (static_cast<long long>(h) * p.width + (w0 + col - (K - 1))) * p.channels;
-						float out[VEC];
-						if (QUANT)
+						for (int r = 0; r < R; r++)
 						{
+							if (i - r < 0 || i - r >= K)
+								continue;
 #pragma unroll
-							for (int k = 0; k < VEC; k++)
-							{ // the host's CPU loop, operation for operation, without fused multiply-adds
-								const float t = __fadd_rn(__fmul_rn(done[k], post_scale[k]), post_shift[k]);
-								out[k] = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(t, p.inv_scale), p.inv_shift))));
-							}
+							for (int j = 0; j < K; j++) // filter column j: output column col - j, ring slot (u - j) mod K
+#pragma unroll
+								for (int k = 0; k < VEC; k++)
+									acc[r][(u - j + K) % K][k] = fmaf(in[k], filt[(i - r) * K + j][k], acc[r][(u - j + K) % K][k]);
 						}
-						else
-						{
-							if (p.beta != 0.0f)
-								load_group<T, VEC>(yb + off, out);
+					}
 #pragma unroll
-							for (int k = 0; k < VEC; k++)
+					for (int r = 0; r < R; r++)
+					{
+						float (&done)[VEC] = acc[r][(u + 1) % K]; // output column col - (K - 1): complete after this input column
+						if (col >= K - 1 && h + r < p.height)
+						{
+							const long long off = (static_cast<long long>(h + r) * p.width + (w0 + col - (K - 1))) * p.channels;
+							float out[VEC];
+							if (QUANT)
 							{
-								const float v = done[k] * post_scale[k] + post_shift[k];
-								out[k] = (p.beta != 0.0f) ? v + p.beta * out[k] : v;
-							}
-						}
-						store_group<T, VEC>(yb + off, out);
-					}
 #pragma unroll
-					for (int k = 0; k < VEC; k++)
-						acc[(u + 1) % K][k] = 0.0f; // the slot that the next column opens (or the one just emitted)
+								for (int k = 0; k < VEC; k++)
+								{ // the host's CPU loop, operation for operation, without fused multiply-adds
+									const float t = __fadd_rn(__fmul_rn(done[k], post_scale[k]), post_shift[k]);
+									out[k] = fmaxf(-128.0f, fminf(127.0f, roundf(__fadd_rn(__fmul_rn(t, p.inv_scale), p.inv_shift))));
+								}
+							}
+							else
+							{
+								if (p.beta != 0.0f)
+									load_group<T, VEC>(yb + off, out);
+#pragma unroll
+								for (int k = 0; k < VEC; k++)
+								{
+									const float v = done[k] * post_scale[k] + post_shift[k];
+									out[k] = (p.beta != 0.0f) ? v + p.beta * out[k] : v;
+								}
+							}
+							store_group<T, VEC>(yb + off, out);
+						}
+#pragma unroll
+						for (int k = 0; k < VEC; k++)
+							done[k] = 0.0f; // the slot the next input column opens
+					}
 				}
 			}
 		}
 	}
 
 	/* Shared-memory opt-in above 48 KB and the large carve-out, once per device and kernel instantiation. */
-	template<typename T, int VEC, int K, bool QUANT>
+	template<typename T, int VEC, int K, int R, bool QUANT>
 	bool depthwise_opt_in(int device)
 	{
 		static bool done[MAX_DEVICES] = { false };
@@ -317,8 +336,8 @@ namespace
 			return false;
 		if (!done[device])
 		{
-			if (cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEPTHWISE_SMEM_LIMIT)
-					!= cudaSuccess || cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, QUANT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+			if (cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEPTHWISE_SMEM_LIMIT)
+					!= cudaSuccess || cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT>, cudaFuncAttributePreferredSharedMemoryCarveout,
 							cudaSharedmemCarveoutMaxShared) != cudaSuccess)
 			{
 				cudaGetLastError();
@@ -331,28 +350,31 @@ namespace
 	template<typename T, int VEC, int K, bool QUANT>
 	bool launch_depthwise_kv(cudaStream_t stream, int device, int batch, T *y, const T *x, const T *w, const T *bias, const DepthwiseParams &p)
 	{
+		constexpr int R = 2; // output rows per thread: every patch element read feeds two rows' multiply-adds
 		const int groups = p.channels / VEC;
 		const int tx = std::min(groups, 32);
-		// the largest patch (rows x columns) that fits the shared-memory budget
-		int ty = std::max(1, std::min(p.height, 256 / tx)), tile_w = std::min(p.width, 32);
-		auto patch_bytes = [&](int rows, int cols)
+		// rows of the image split evenly over as few CTAs as 8 x R rows each allow; then the widest column tile that fits
+		const int max_ty = std::max(1, 256 / tx);
+		const int row_blocks = ceil_div(p.height, std::min(8, max_ty) * R);
+		int ty = ceil_div(ceil_div(p.height, row_blocks), R), tile_w = std::min(p.width, 32);
+		auto patch_bytes = [&](int threads_y, int cols)
 		{
-			return static_cast<size_t>(rows + K - 1) * (cols + K - 1) * tx * VEC * sizeof(T);
+			return static_cast<size_t>(threads_y * R + K - 1) * (cols + K - 1) * tx * VEC * sizeof(T);
 		};
 		while (patch_bytes(ty, tile_w) > static_cast<size_t>(DEPTHWISE_SMEM_LIMIT) && (ty > 1 || tile_w > 1))
 		{
-			if (tile_w >= ty && tile_w > 1)
+			if (tile_w >= ty * R && tile_w > 1)
 				tile_w = (tile_w + 1) / 2;
 			else
 				ty = (ty + 1) / 2;
 		}
 		const size_t smem = patch_bytes(ty, tile_w);
-		if (!depthwise_opt_in<T, VEC, K, QUANT>(device)) // also asks for the large shared-memory carve-out: several patches per SM
+		if (!depthwise_opt_in<T, VEC, K, R, QUANT>(device)) // also asks for the large shared-memory carve-out: several patches per SM
 			return false;
 		const int tiles_w = ceil_div(p.width, tile_w);
 		const dim3 block(tx, ty);
-		const dim3 grid(ceil_div(p.height, ty) * tiles_w, batch, ceil_div(groups, tx));
-		kernel_depthwise_conv<T, VEC, K, QUANT> <<<grid, block, smem, stream>>>(y, x, w, bias, p, tile_w, tiles_w);
+		const dim3 grid(ceil_div(p.height, ty * R) * tiles_w, batch, ceil_div(groups, tx));
+		kernel_depthwise_conv<T, VEC, K, R, QUANT> <<<grid, block, smem, stream>>>(y, x, w, bias, p, tile_w, tiles_w);
 		return true;
 	}
 	/* The widest channel group that keeps the k x k fp32 filter taps in registers: 8 / 4 / 2 channels for k = 3 / 5 / 7. */
