@@ -37,6 +37,14 @@ namespace mb200
 		}
 
 		/* D = head dimension (multiple of 16). */
+		constexpr float LOG2E = 1.4426950408889634f;
+		__device__ __forceinline__ float exp2_approx(float x)
+		{
+			float y;
+			asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+			return y;
+		}
+
 		template<int D>
 		__global__ void __launch_bounds__(WARPS * 32) kernel_mha_mma(__half *__restrict__ output, const __half *__restrict__ input,
 				const __half *__restrict__ table, int height, int width, int heads, int parts, int table_n, int table_pad)
@@ -75,13 +83,20 @@ namespace mb200
 				*reinterpret_cast<uint4*>(sv + t * LD + ch * 8) = vv;
 			}
 			for (int i = threadIdx.x; i < table_n * table_pad; i += blockDim.x)
-				st[i] = __half2float(table[static_cast<long long>(head) * table_n * table_pad + i]);
+				st[i] = __half2float(table[static_cast<long long>(head) * table_n * table_pad + i]) * LOG2E; // scores live in the log2 domain
+			// Relative offsets never leave the table when the board is no larger than the table's range + 1 (the usual case: the
+			// table is built for the board).  The index is then linear in the two positions and needs no clamping:
+			// (jh - qh + range) * pad + (jw - qw + range) = lin(j) - lin(q) + range * (pad + 1), lin(t) = th * pad + tw.
+			const int range = (table_n - 1) / 2;
+			const bool linear_bias = (height - 1 <= range) && (width - 1 <= range);
 			for (int i = threadIdx.x; i < padded; i += blockDim.x)
-				spos[i] = ((i / width) << 16) | (i % width);
+			{ // slots beyond the last token repeat the last token's position, so that every index formed from them stays in the table
+				const int t = min(i, tokens - 1);
+				spos[i] = linear_bias ? (t / width) * table_pad + (t % width) : (((t / width) << 16) | (t % width));
+			}
 			__syncthreads();
 
-			const float scale = rsqrtf(static_cast<float>(D));
-			const int range = (table_n - 1) / 2;
+			const float scale = rsqrtf(static_cast<float>(D)) * LOG2E; // exp(x) = 2^(x log2 e): one multiply less per score
 			const uint32_t sv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(sv));
 
 			for (int q0 = warp * 16; q0 < tokens; q0 += WARPS * 16)
@@ -98,8 +113,9 @@ namespace mb200
 					qa[kc][2] = (r0 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r0) * stride + col + 8) : 0u;
 					qa[kc][3] = (r1 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r1) * stride + col + 8) : 0u;
 				}
-				const int p0 = spos[min(r0, padded - 1)], p1 = spos[min(r1, padded - 1)];
-				const int qh0 = p0 >> 16, qw0 = p0 & 0xFFFF, qh1 = p1 >> 16, qw1 = p1 & 0xFFFF;
+				const int p0 = spos[min(r0, tokens - 1)], p1 = spos[min(r1, tokens - 1)];
+				const int qh0 = p0 >> 16, qw0 = p0 & 0xFFFF, qh1 = p1 >> 16, qw1 = p1 & 0xFFFF; // clamped form
+				const int lin0 = range * (table_pad + 1) - p0, lin1 = range * (table_pad + 1) - p1; // linear form
 
 				float o[NT][4];
 #pragma unroll
@@ -139,11 +155,19 @@ namespace mb200
 							if (table != nullptr)
 							{
 								const int pj = spos[j];
-								const int jh = pj >> 16, jw = pj & 0xFFFF;
-								v0 += st[(min(max(jh - qh0, -range), range) + range) * table_pad + min(max(jw - qw0, -range), range) + range];
-								v1 += st[(min(max(jh - qh1, -range), range) + range) * table_pad + min(max(jw - qw1, -range), range) + range];
+								if (linear_bias)
+								{
+									v0 += st[pj + lin0];
+									v1 += st[pj + lin1];
+								}
+								else
+								{
+									const int jh = pj >> 16, jw = pj & 0xFFFF;
+									v0 += st[(min(max(jh - qh0, -range), range) + range) * table_pad + min(max(jw - qw0, -range), range) + range];
+									v1 += st[(min(max(jh - qh1, -range), range) + range) * table_pad + min(max(jw - qw1, -range), range) + range];
+								}
 							}
-							if (j >= tokens)
+							if (kb + KEY_BLOCK > tokens && j >= tokens)
 							{
 								v0 = -1.0e30f;
 								v1 = -1.0e30f;
@@ -158,7 +182,7 @@ namespace mb200
 					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
 					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
 					const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);
-					const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1);
+					const float c0 = exp2_approx(m0 - n0), c1 = exp2_approx(m1 - n1);
 					m0 = n0;
 					m1 = n1;
 					float sum0 = 0.0f, sum1 = 0.0f;
@@ -167,7 +191,7 @@ namespace mb200
 #pragma unroll
 						for (int e = 0; e < 2; e++)
 						{
-							const float e0 = __expf(s[nt][e] - n0), e1 = __expf(s[nt][2 + e] - n1);
+							const float e0 = exp2_approx(s[nt][e] - n0), e1 = exp2_approx(s[nt][2 + e] - n1);
 							s[nt][e] = e0;
 							s[nt][2 + e] = e1;
 							sum0 += e0;
