@@ -58,6 +58,78 @@ namespace mb200
 			}
 		}
 
+		/* fp16 rows of 256 * ITERS channels: one warp per row, every lane keeps its 8 * ITERS values in registers (16-byte loads),
+		 * so the row is read from memory once; the statistics are the same two passes (mean, then squared deviations) in fp32. */
+		template<int ITERS>
+		__global__ void __launch_bounds__(256) kernel_layernorm_rows_fp16(__half *__restrict__ output, const __half *__restrict__ input,
+				const __half *__restrict__ gamma, const __half *__restrict__ beta, const __half *__restrict__ ext, long long rows)
+		{
+			constexpr int CHANNELS = 256 * ITERS;
+			const int lane = threadIdx.x % 32;
+			float g[ITERS][8], b[ITERS][8];
+#pragma unroll
+			for (int i = 0; i < ITERS; i++)
+			{
+				const int c = (i * 32 + lane) * 8;
+				uint4 gr = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u), br = make_uint4(0, 0, 0, 0); // ones, zeros
+				if (gamma != nullptr)
+					gr = *reinterpret_cast<const uint4*>(gamma + c);
+				if (beta != nullptr)
+					br = *reinterpret_cast<const uint4*>(beta + c);
+#pragma unroll
+				for (int k = 0; k < 8; k++)
+				{
+					g[i][k] = __half2float(reinterpret_cast<const __half*>(&gr)[k]);
+					b[i][k] = __half2float(reinterpret_cast<const __half*>(&br)[k]);
+				}
+			}
+			const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
+			for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r < rows; r += warps)
+			{
+				float v[ITERS][8];
+				float sum = 0.0f;
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+				{
+					const long long off = r * CHANNELS + (i * 32 + lane) * 8;
+					const uint4 raw = *reinterpret_cast<const uint4*>(input + off);
+					uint4 er = make_uint4(0, 0, 0, 0);
+					if (ext != nullptr)
+						er = *reinterpret_cast<const uint4*>(ext + off);
+#pragma unroll
+					for (int k = 0; k < 8; k++)
+					{
+						v[i][k] = __half2float(reinterpret_cast<const __half*>(&raw)[k]) + __half2float(reinterpret_cast<const __half*>(&er)[k]);
+						sum += v[i][k];
+					}
+				}
+				for (int k = 16; k >= 1; k /= 2)
+					sum += __shfl_xor_sync(0xffffffffu, sum, k);
+				const float mean = sum / static_cast<float>(CHANNELS);
+				float var = 0.0f;
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+#pragma unroll
+					for (int k = 0; k < 8; k++)
+					{
+						const float d = v[i][k] - mean;
+						var += d * d;
+					}
+				for (int k = 16; k >= 1; k /= 2)
+					var += __shfl_xor_sync(0xffffffffu, var, k);
+				const float inv_stddev = 1.0f / sqrtf(1.0e-6f + var / static_cast<float>(CHANNELS - 1));
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+				{
+					uint4 out;
+#pragma unroll
+					for (int k = 0; k < 8; k++)
+						reinterpret_cast<__half*>(&out)[k] = __float2half_rn(g[i][k] * (v[i][k] - mean) * inv_stddev + b[i][k]);
+					*reinterpret_cast<uint4*>(output + r * CHANNELS + (i * 32 + lane) * 8) = out;
+				}
+			}
+		}
+
 		constexpr int MHA_WARPS = 8;
 		/* dynamic shared memory: K [tokens][d + 1] fp32, V [tokens][d] fp32, bias table [n * n_pad] fp32,
 		 * per-warp: q [d] and p [tokens] */
@@ -160,10 +232,22 @@ extern "C"
 		switch (dtype)
 		{
 			case DTYPE_FLOAT16:
-				kernel_layernorm<__half> <<<grid, 256, 0, stream>>>(reinterpret_cast<__half*>(output), reinterpret_cast<const __half*>(input),
-						reinterpret_cast<const __half*>(weights), reinterpret_cast<const __half*>(bias), reinterpret_cast<const __half*>(ext), rows,
-						channels);
+			{
+				__half *yp = reinterpret_cast<__half*>(output);
+				const __half *xp = reinterpret_cast<const __half*>(input), *gp = reinterpret_cast<const __half*>(weights),
+						*bp = reinterpret_cast<const __half*>(bias), *ep = reinterpret_cast<const __half*>(ext);
+				const bool aligned = aligned_to(xp, 16) && aligned_to(yp, 16) && (gp == nullptr || aligned_to(gp, 16)) && (bp == nullptr || aligned_to(bp, 16))
+						&& (ep == nullptr || aligned_to(ep, 16));
+				if (aligned && channels == 256)
+					kernel_layernorm_rows_fp16<1> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+				else if (aligned && channels == 512)
+					kernel_layernorm_rows_fp16<2> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+				else if (aligned && channels == 1024)
+					kernel_layernorm_rows_fp16<4> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+				else
+					kernel_layernorm<__half> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows, channels);
 				break;
+			}
 			case DTYPE_FLOAT32:
 				kernel_layernorm<float> <<<grid, 256, 0, stream>>>(reinterpret_cast<float*>(output), reinterpret_cast<const float*>(input),
 						reinterpret_cast<const float*>(weights), reinterpret_cast<const float*>(bias), reinterpret_cast<const float*>(ext), rows,

@@ -119,7 +119,7 @@ def test_softmax(ctx, oracle, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
-@pytest.mark.parametrize("shape", [(3, 5, 7, 36), (2, 15, 15, 256), (11, 33)])
+@pytest.mark.parametrize("shape", [(3, 5, 7, 36), (2, 15, 15, 256), (11, 33), (37, 512), (5, 3, 1024)])
 def test_layernorm(ctx, oracle, dtype, shape):
     from minml_b200 import backend as B
     r = np.random.default_rng(1)
