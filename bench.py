@@ -355,12 +355,24 @@ def gpu_arm(args, cfg):
     h2d = in_host.numel() * in_host.element_size()
     d2h = sum(t.numel() * t.element_size() for t in out_hosts)
 
+    # One step = the whole network on one batch.  The calls of a step are recorded once into a CUDA graph on the context's
+    # stream and replayed: the small configurations would otherwise be paced by the Python host (about 50 us per layer of
+    # ctypes calls against 25 us of kernel), which minml's C++ host is not.  --no-graph issues the calls one by one.
+    graph = {"g": None, "outs": None, "launches": 0, "note": "calls issued one by one"}
+
+    def run_step(x):
+        if graph["g"] is not None and x is in_stage:
+            with torch.cuda.stream(graph["stream"]):
+                graph["g"].replay()
+            return graph["outs"]
+        return predict(x)
+
     def step_device():
-        return predict(in_dev)
+        return run_step(in_stage)
 
     def step_e2e():
         B.lib.cuda_memcpy_from_host(ctx.handle, ctypes.c_void_p(in_stage.data_ptr()), 0, ctypes.c_void_p(in_host.data_ptr()), h2d)
-        outs = predict(in_stage)
+        outs = run_step(in_stage)
         for dst, src in zip(out_hosts, outs):
             B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(src.data_ptr()), 0, src.numel() * src.element_size())
         ctx.synchronize()  # the caller reads the result of every step
@@ -386,15 +398,33 @@ def gpu_arm(args, cfg):
         dev_max, wall_max = replicas.max_over_ranks([dev_s, wall])
         return dev_max, wall_max
 
+    in_stage.copy_(in_dev)
+    torch.cuda.synchronize()
     for _ in range(max(args.warmup, 3)):
         step_device()
     ctx.synchronize()
+    if not args.no_graph:
+        try:
+            graph["stream"] = ctx.torch_stream()
+            g = torch.cuda.CUDAGraph()
+            before = B.launch_count()
+            with torch.cuda.graph(g, stream=graph["stream"]):
+                graph["outs"] = predict(in_stage)
+            graph["launches"] = B.launch_count() - before
+            graph["g"] = g
+            graph["note"] = "CUDA graph of one step (%d kernels) replayed on the context's stream" % graph["launches"]
+            for _ in range(3):
+                step_device()
+            ctx.synchronize()
+        except Exception as exc:  # capture is an optimisation of the launch path only
+            graph["g"] = None
+            graph["note"] = "calls issued one by one (graph capture failed: %s)" % str(exc)[:120]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = B.launch_count()
     dev_s, _ = timed(step_device, args.steps)
-    launches = B.launch_count() - launches0
+    launches = (B.launch_count() - launches0) if graph["g"] is None else graph["launches"] * args.steps
     resident = [host_copy(t) for t in step_device()]
     for _ in range(2):
         step_e2e()
@@ -419,7 +449,7 @@ def gpu_arm(args, cfg):
             "metric": METRIC.get(kind, METRIC["trunk"]), "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "i8" if kind == "int8_trunk" else "f16", "data": "synthetic", "outputs_finite_and_equal": outputs_ok,
-            "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world, "conv3x3": "three-kernel Winograd" if args.eager else "fused implicit GEMM",
+            "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world, "conv3x3": "three-kernel Winograd" if args.eager else "fused implicit GEMM", "launch": graph["note"],
                        "l2": "activations of every layer (%.0f MB) exceed the 126 MB L2, no flush needed" % (
                            batch * cfg["height"] * cfg["width"] * cfg["channels"] * 2 / 1e6)},
             "algorithmic_tflops": value * fpp / 1e12, "frac_of_nominal_dense_peak": value * fpp / world / (4.5e15 if kind == "int8_trunk" else 2.25e15),
@@ -440,6 +470,7 @@ def main():
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="issue every backend call from the host each step instead of replaying a CUDA graph")
     ap.add_argument("--eager", action="store_true", help="three kernels per 3x3 layer (fusion off) instead of the fused convolution")
     ap.add_argument("--layer", action="store_true", help="time only one channels -> channels 3x3 layer (the roofline record); used for ncu captures")
     ap.add_argument("--layer-batch", type=int, default=0, help="batch size for --layer (default: the config's)")

@@ -93,6 +93,17 @@ class Context:
         """ml::Context::enableTF32: fp32 matrix products may then run on the tensor cores in TF32 (off by default, as in the reference)."""
         lib.cuda_enable_tf32(self.handle, bool(enabled))
 
+    def torch_stream(self):
+        """The context's own CUDA stream as a torch stream object (for graph capture, or for queuing torch work behind backend calls)."""
+        lib.mb200_get_stream.restype = ctypes.c_void_p
+        return torch.cuda.ExternalStream(int(lib.mb200_get_stream(self.handle)), device=torch.device("cuda", self.device_index))
+
+    def hold_stream(self, milliseconds):
+        """Queues a busy-wait of about `milliseconds` on the context's stream, so that launches issued right after it pile up behind
+        it and then run back to back: device time of short kernels can then be measured without the host's launch pace in it."""
+        with torch.cuda.stream(self.torch_stream()):
+            torch.cuda._sleep(int(milliseconds * 1.5e6))
+
     def wait_for_torch(self):
         """Orders this context's stream after work torch has queued on its current stream."""
         torch.cuda.current_stream().synchronize()

@@ -70,16 +70,21 @@ namespace mb200
 		/* CTAS: 1 = every CTA computes 128 x BN tiles on its own; 2 = the two CTAs of a cluster compute a 256 x BN tile with
 		 * tcgen05 cta_group::2: each holds its own 128 rows of A and HALF of the weight slice, so the weight bytes a CTA pulls
 		 * from L2 per tile are halved (the operand fetch from L2, not the tensor pipe, is what limits the single-CTA kernel). */
-		template<int KIND, int BN, bool TMA_A, int CTAS = 1>
+		/* MT: 128-row tiles per CTA and work unit (1 or 2).  With 128 output channels a 128 x 128 tile does only 128 multiply-adds per
+		 * operand byte fetched and the L2 -> SM path caps the tensor pipe near half its rate; two row tiles that share every weight
+		 * slice fetch a quarter less per multiply-add and keep each stage busy twice as long (deeper effective prefetch). */
+		template<int KIND, int BN, bool TMA_A, int CTAS = 1, int MT = 1>
 		struct Cfg
 		{
+				static constexpr int a_stage_bytes = A_STAGE_BYTES * MT;
 				static constexpr int b_stage_bytes = BN / CTAS * 128;
 				// The two operand rings are sized separately: the gathered A slices (cp.async, many small requests) need more
 				// slices in flight to cover their latency than the weight slices that one TMA request fetches.
-				static constexpr int a_stages = (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
+				static constexpr int a_stages = (MT == 2) ? 4 : (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
 				static constexpr int b_stages = TMA_A ? a_stages : ((BN == 256) ? 3 : 6);
-				static constexpr int smem_bytes = a_stages * A_STAGE_BYTES + b_stages * b_stage_bytes + Roles<KIND, TMA_A>::staging_bytes + 1024;
-				static constexpr int tmem_columns = 2 * BN;
+				static constexpr int smem_bytes = a_stages * a_stage_bytes + b_stages * b_stage_bytes + Roles<KIND, TMA_A>::staging_bytes + 1024;
+				static constexpr int tmem_columns = 2 * BN * MT;
+				static_assert(tmem_columns <= 512 && smem_bytes <= 227 * 1024, "tile configuration exceeds the SM");
 		};
 
 		struct ConvParams
@@ -146,12 +151,13 @@ namespace mb200
 					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
 		}
 
-		template<int KIND, int BN, bool TMA_A, int CTAS>
+		template<int KIND, int BN, bool TMA_A, int CTAS, int MT>
 		__global__ void __launch_bounds__((Roles<KIND, TMA_A>::threads), 1) kernel_conv3x3_igemm(const __grid_constant__ CUtensorMap map_w,
 				const __grid_constant__ CUtensorMap map_x, const ConvParams p)
 		{
 			static_assert(CTAS == 1 || TMA_A, "the paired kernel fetches both operands by TMA");
-			using C = Cfg<KIND, BN, TMA_A, CTAS>;
+			static_assert(MT == 1 || (TMA_A && CTAS == 1), "two row tiles per CTA: TMA operands, single CTAs");
+			using C = Cfg<KIND, BN, TMA_A, CTAS, MT>;
 			constexpr int EPI_WARPS = Roles<KIND, TMA_A>::epi_warps;
 			constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
 			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
@@ -160,7 +166,7 @@ namespace mb200
 			__shared__ ConvBarriers bars;
 
 			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-			const uint32_t b_base = smem_base + C::a_stages * A_STAGE_BYTES;
+			const uint32_t b_base = smem_base + C::a_stages * C::a_stage_bytes;
 			const uint32_t epi_base = b_base + C::b_stages * C::b_stage_bytes;
 			const int warp = threadIdx.x / 32;
 			const int lane = threadIdx.x % 32;
@@ -173,7 +179,7 @@ namespace mb200
 			const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
 			const bool leader = cta_rank == 0;
 			const int first_unit = blockIdx.x / CTAS, unit_step = gridDim.x / CTAS;
-			const int total_units = ((m_tiles + CTAS - 1) / CTAS) * n_tiles;
+			const int total_units = ((m_tiles + CTAS * MT - 1) / (CTAS * MT)) * n_tiles;
 
 			if (threadIdx.x == 0)
 			{
@@ -222,12 +228,18 @@ namespace mb200
 					{
 						const int nt = unit % n_tiles;
 						// first output position of the tile -> (image, row, column); im2col TMA walks on from there
-						int m0 = ((unit / n_tiles) * CTAS + static_cast<int>(cta_rank)) * BM;
+						int m0 = ((unit / n_tiles) * CTAS + static_cast<int>(cta_rank)) * MT * BM;
 						if (CTAS == 2 && m0 >= p.M)
 							m0 = 0; // a tile wholly beyond M: fetch rows that exist, the epilogue stores none of them
 						const int img0 = m0 / (p.height * p.width);
 						const int h0 = (m0 - img0 * p.height * p.width) / p.width;
 						const int w0 = m0 - img0 * p.height * p.width - h0 * p.width;
+						int m1 = m0 + BM; // second row tile of the unit (MT == 2)
+						if (m1 >= p.M)
+							m1 = 0;
+						const int img1 = m1 / (p.height * p.width);
+						const int h1 = (m1 - img1 * p.height * p.width) / p.width;
+						const int w1 = m1 - img1 * p.height * p.width - h1 * p.width;
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
 							const int s = it % C::b_stages;
@@ -249,13 +261,16 @@ namespace mb200
 								tma_load_3d_pair(b_base + s * C::b_stage_bytes, &map_w, full_leader, k0, nt * BN + static_cast<int>(cta_rank) * (BN / 2), 0);
 								continue;
 							}
-							mbar_arrive_expect_tx(full, C::b_stage_bytes + (TMA_A ? A_STAGE_BYTES : 0));
+							mbar_arrive_expect_tx(full, C::b_stage_bytes + (TMA_A ? C::a_stage_bytes : 0));
 							if (TMA_A)
 							{
 								const int k0 = kb * (128 / ES);
 								const int tap = k0 / p.cin;
-								tma_load_im2col_4d(smem_base + s * A_STAGE_BYTES, &map_x, full, k0 - tap * p.cin, w0 - 1, h0 - 1, img0,
+								tma_load_im2col_4d(smem_base + s * C::a_stage_bytes, &map_x, full, k0 - tap * p.cin, w0 - 1, h0 - 1, img0,
 										static_cast<uint16_t>(tap % 3), static_cast<uint16_t>(tap / 3));
+								if (MT == 2)
+									tma_load_im2col_4d(smem_base + s * C::a_stage_bytes + A_STAGE_BYTES, &map_x, full, k0 - tap * p.cin, w1 - 1, h1 - 1, img1,
+											static_cast<uint16_t>(tap % 3), static_cast<uint16_t>(tap / 3));
 							}
 							tma_load_3d(b_base + s * C::b_stage_bytes, &map_w, full, kb * (128 / ES), nt * BN, 0);
 						}
@@ -278,7 +293,7 @@ namespace mb200
 						if (!((CTAS == 2) ? mbar_wait_cluster(empty_bar, empty_parity, abort_flag) : mbar_wait(empty_bar, empty_parity, abort_flag)))
 							break;
 						tcgen05_fence_after();
-						const uint32_t tmem_d = tmem_base + buf * BN;
+						const uint32_t tmem_d = tmem_base + buf * (BN * MT);
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
 							const int sa = it % C::a_stages, sb = it % C::b_stages;
@@ -291,7 +306,7 @@ namespace mb200
 							tcgen05_fence_after();
 							if (!TMA_A)
 								fence_proxy_async_smem(); // the A slice was written through the generic proxy by other threads
-							const uint64_t desc_a = make_desc_k_sw128(smem_base + sa * A_STAGE_BYTES);
+							const uint64_t desc_a = make_desc_k_sw128(smem_base + sa * C::a_stage_bytes);
 							const uint64_t desc_b = make_desc_k_sw128(b_base + sb * C::b_stage_bytes);
 							if (CTAS == 2)
 							{
@@ -305,6 +320,13 @@ namespace mb200
 #pragma unroll
 								for (int k = 0; k < 4; k++)
 									mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+								if (MT == 2)
+								{ // the second row tile: next 16 KB of the stage, next BN columns of tensor memory, same weight slice
+									const uint64_t desc_a1 = make_desc_k_sw128(smem_base + sa * C::a_stage_bytes + A_STAGE_BYTES);
+#pragma unroll
+									for (int k = 0; k < 4; k++)
+										mma_ss<KIND>(tmem_d + BN, desc_a1 + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+								}
 								if (!TMA_A)
 									mma_commit(smem_u32(&bars.empty_a[sa]));
 								mma_commit(smem_u32(&bars.empty_b[sb]));
@@ -334,22 +356,25 @@ namespace mb200
 				for (int unit = first_unit; unit < total_units; unit += unit_step, local_tile++)
 				{
 					const int nt = unit % n_tiles;
-					const int mt = (unit / n_tiles) * CTAS + static_cast<int>(cta_rank);
 					const uint32_t buf = local_tile & 1u;
 					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), (local_tile >> 1) & 1u, abort_flag))
 						break;
 					tcgen05_fence_after();
-					const int row0 = mt * BM + q * 32; // first row of this warp
-					const int row = row0 + lane;
-					const bool row_ok = row < p.M;
-					const long long off = static_cast<long long>(row) * p.cout;
 					const int col_begin = col_part * COLS_PER_WARP;
 					const int n_valid_tile = min(BN, p.cout - nt * BN);
-					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-					for (int c = col_begin / 32; c < (col_begin + COLS_PER_WARP) / 32; c++)
+					constexpr int CHUNKS_PER_WARP = COLS_PER_WARP / 32;
+					for (int cc = 0; cc < MT * CHUNKS_PER_WARP; cc++)
 					{
+						const int sub = cc / CHUNKS_PER_WARP; // which of the unit's row tiles
+						const int c = col_begin / 32 + cc % CHUNKS_PER_WARP;
+						const int mt = ((unit / n_tiles) * CTAS + static_cast<int>(cta_rank)) * MT + sub;
+						const int row0 = mt * BM + q * 32; // first row of this warp
+						const int row = row0 + lane;
+						const bool row_ok = row < p.M;
+						const long long off = static_cast<long long>(row) * p.cout;
+						const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * (BN * MT) + sub * BN;
 						if (c * 32 >= n_valid_tile)
-							break; // warp-uniform
+							continue; // warp-uniform
 						const int n0 = nt * BN + c * 32;
 						const int n_valid = min(32, p.cout - n0);
 						const bool fast = (KIND == 0) && rows_vectorisable && n_valid == 32;
@@ -699,10 +724,10 @@ namespace mb200
 			}
 		}
 
-		template<int KIND, int BN, bool TMA_A>
+		template<int KIND, int BN, bool TMA_A, int MT = 1>
 		bool launch(mlContext_t ctx, const CUtensorMap &map_w, const CUtensorMap &map_x, const ConvParams &p)
 		{
-			using C = Cfg<KIND, BN, TMA_A>;
+			using C = Cfg<KIND, BN, TMA_A, 1, MT>;
 			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
 			const int device = get(ctx)->device;
 			if (device < 0 || device >= MAX_DEVICES)
@@ -710,14 +735,14 @@ namespace mb200
 			bool &configured = configured_on[device];
 			if (!configured)
 			{
-				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, TMA_A, 1, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
 						"conv_igemm: shared memory opt-in"))
 					return false;
 				configured = true;
 			}
-			const int tiles = ((p.M + BM - 1) / BM) * ((p.cout + BN - 1) / BN);
+			const int tiles = (((p.M + BM - 1) / BM + MT - 1) / MT) * ((p.cout + BN - 1) / BN);
 			const int grid = std::min(tiles, get(ctx)->sm_count);
-			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1> <<<grid, Roles<KIND, TMA_A>::threads, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
+			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1, MT> <<<grid, Roles<KIND, TMA_A>::threads, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
 			MB200_COUNT_LAUNCH();
 			get(ctx)->kernels_with_waits = true;
 			return check_cuda(ctx, cudaGetLastError(), "conv_igemm launch");
@@ -746,12 +771,12 @@ namespace mb200
 				return false;
 			if (max_clusters[device] == 0)
 			{
-				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
+				if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_conv3x3_igemm<KIND, BN, true, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_bytes),
 						"conv_igemm pair: shared memory opt-in"))
 					return false;
 				config.gridDim = dim3(2 * (get(ctx)->sm_count / 2), 1, 1);
 				int n = 0;
-				if (cudaOccupancyMaxActiveClusters(&n, kernel_conv3x3_igemm<KIND, BN, true, 2>, &config) != cudaSuccess || n <= 0)
+				if (cudaOccupancyMaxActiveClusters(&n, kernel_conv3x3_igemm<KIND, BN, true, 2, 1>, &config) != cudaSuccess || n <= 0)
 				{
 					cudaGetLastError();
 					n = -1;
@@ -762,7 +787,7 @@ namespace mb200
 				return false;
 			const int units = (((p.M + BM - 1) / BM + 1) / 2) * ((p.cout + BN - 1) / BN);
 			config.gridDim = dim3(2 * std::min(units, max_clusters[device]), 1, 1);
-			const cudaError_t status = cudaLaunchKernelEx(&config, kernel_conv3x3_igemm<KIND, BN, true, 2>, map_w, map_x, p);
+			const cudaError_t status = cudaLaunchKernelEx(&config, kernel_conv3x3_igemm<KIND, BN, true, 2, 1>, map_w, map_x, p);
 			MB200_COUNT_LAUNCH();
 			get(ctx)->kernels_with_waits = true;
 			return check_cuda(ctx, status, "conv_igemm pair launch") && check_cuda(ctx, cudaGetLastError(), "conv_igemm pair launch");
@@ -876,6 +901,10 @@ namespace mb200
 					return bn == 256 ? launch_pair<0, 256>(ctx, map_w, map_x, p) : launch_pair<0, 128>(ctx, map_w, map_x, p);
 				return bn == 256 ? launch_pair<1, 256>(ctx, map_w, map_x, p) : launch_pair<1, 128>(ctx, map_w, map_x, p);
 			}
+			static const bool force_narrow = env_flag("MINML_B200_CONV_ONE_ROW_TILE");
+			const bool wide = tma_a && bn == 128 && !force_narrow && p.M > 2 * BM * get(ctx)->sm_count; // enough work for 256-row units on every SM
+			if (wide)
+				return kind == 0 ? launch<0, 128, true, 2>(ctx, map_w, map_x, p) : launch<1, 128, true, 2>(ctx, map_w, map_x, p);
 			if (kind == 0)
 			{
 				if (tma_a)
