@@ -212,6 +212,7 @@ def layer_roofline(B, L, ctx, cfg, peaks, torch, fused=True):
         for _ in range(3):
             fn()
         ctx.synchronize()
+        ctx.hold_stream(0.12 * reps + 0.2)  # the timed launches queue up behind this wait and then run back to back
         e0 = B.lib.cuda_create_event(ctx.handle)
         for _ in range(reps):
             fn()
@@ -238,6 +239,7 @@ def layer_roofline(B, L, ctx, cfg, peaks, torch, fused=True):
         for _ in range(3):
             layer()
         ctx.synchronize()
+        ctx.hold_stream(0.12 * reps + 0.2)  # the timed launches queue up behind this wait and then run back to back
         e0 = B.lib.cuda_create_event(ctx.handle)
         for _ in range(reps):
             layer()
@@ -278,6 +280,7 @@ def int8_layer_roofline(B, L, ctx, cfg, peaks, torch):
     for _ in range(3):
         conv.forward([x, res], y, ws, (0.03, 0.0))
     ctx.synchronize()
+    ctx.hold_stream(0.12 * reps + 0.2)  # the timed launches queue up behind this wait and then run back to back
     e0 = B.lib.cuda_create_event(ctx.handle)
     for _ in range(reps):
         conv.forward([x, res], y, ws, (0.03, 0.0))
