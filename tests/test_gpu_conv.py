@@ -195,3 +195,39 @@ def test_quantized_trunk(ctx, oracle, cfg):
     ref_p, ref_v = oracle_trunk(oracle, weights, x, blocks)
     assert max_rel_err(host(policy), ref_p) <= 0.1
     assert max_rel_err(host(value), ref_v) <= 0.1
+
+
+def test_trunk_step_replayed_as_cuda_graph(ctx, oracle):
+    """The calls of one trunk step recorded into a CUDA graph on the context's stream and replayed on new input give the same bits
+    as issuing them one by one (the deferred call triples are resolved at record time; nothing in the path allocates or
+    synchronises once the layers are warm)."""
+    from minml_b200 import layers as L
+    b, h, w, planes, channels, blocks = 8, 15, 15, 32, 128, 2
+    weights = L.make_trunk_weights(99, planes, channels, blocks)
+    net = L.ResNetTrunk(ctx, weights, b, h, w, planes, channels, blocks)
+    rng = np.random.default_rng(5)
+    x1 = (rng.random((b, h, w, planes)) < 0.3).astype(np.float32)
+    x2 = (rng.random((b, h, w, planes)) < 0.3).astype(np.float32)
+    stage = dev(pack_planes(x1).view(np.int32))
+    policy, value = net.predict(stage)  # warm: transformed weights, kernel attributes
+    ctx.synchronize()
+    stream = ctx.torch_stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        policy, value = net.predict(stage)
+    results = []
+    for x in (x1, x2):
+        stage.copy_(dev(pack_planes(x).view(np.int32)))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            graph.replay()
+        ctx.synchronize()
+        replayed = (policy.clone(), value.clone())
+        eager = net.predict(stage)
+        ctx.synchronize()
+        assert torch.equal(replayed[0], eager[0]) and torch.equal(replayed[1], eager[1])
+        results.append(replayed)
+    assert not torch.equal(results[0][0], results[1][0])  # the replay really consumed the new input
+    weights16 = {k: v.astype(np.float16).astype(np.float32) for k, v in weights.items()}
+    want_p, want_v = oracle_trunk(oracle, weights16, x2, blocks)
+    assert max_rel_err(host(results[1][0]), want_p) <= FP16_REL and max_rel_err(host(results[1][1]), want_v) <= FP16_REL
