@@ -10,7 +10,8 @@
  * Status tags:
  *   [hot]    implemented with hand-written sm_100a kernels (the convolution / matrix-multiply inference path)
  *   [next]   implemented: the layers adjacent to that path in minml's current architectures (batch-norm inference and
- *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling)
+ *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling, and the backward-pass Winograd
+ *            transforms with the fused activation / bias-gradient step)
  *   [infra]  thin native wrapper over the CUDA runtime
  *   [stub]   exported so that minml links; records the sticky error "not implemented" on the context and
  *            launches nothing (training, MoE, pooling variants, ...)
@@ -96,8 +97,8 @@ void cuda_depth_to_space(mlContext_t context, mlDataType_t dtype, mlShape_t inpu
 void cuda_winograd_weight_transform(mlContext_t context, int tile_size, const mlTensor_t w, mlTensor_t matrices, bool invert); /* [hot] [96] */
 void cuda_winograd_input_transform(mlContext_t context, int tile_size, const mlTensor_t x, mlTensor_t matrices); /* [hot] [97] */
 void cuda_winograd_output_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, const mlTensor_t bias, const mlTensor_t ext, mlTensor_t y, mlActivationType_t act); /* [hot] [98] */
-void cuda_winograd_gradient_transform(mlContext_t context, int tile_size, const mlTensor_t dy, mlTensor_t matrices); /* [stub] [100] */
-void cuda_winograd_update_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, mlTensor_t dw); /* [stub] [101] */
+void cuda_winograd_gradient_transform(mlContext_t context, int tile_size, const mlTensor_t dy, mlTensor_t matrices); /* [next] [100] */
+void cuda_winograd_update_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, mlTensor_t dw); /* [next] [101] */
 
 /* ---- Fused convolution: y = act(conv(x, w) + bias + add)
  *      replaces src/backend/cuda/cudnn_math.cpp:374-476,691-694 ---- */
@@ -169,10 +170,10 @@ void cuda_window_merging(mlContext_t context, mlDataType_t dtype, mlShape_t inpu
 /* ---- Activations and softmax
  *      replaces src/backend/cuda/kernels/activations.cu:190-257, src/backend/cuda/kernels/softmax.cu ---- */
 void cuda_activation_forward(mlContext_t context, float alpha, const mlTensor_t x, float beta, mlTensor_t y, mlActivationType_t act); /* [hot] [226] */
-void cuda_activation_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t y, float beta, mlTensor_t dx, mlActivationType_t act); /* [stub] [228] */
+void cuda_activation_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t y, float beta, mlTensor_t dx, mlActivationType_t act); /* [next] [228] */
 void cuda_softmax_forward(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *output, const void *input); /* [hot] [230] */
 void cuda_softmax_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t y, float beta, mlTensor_t dx); /* [stub] [231] */
-void cuda_fused_act_bias_copy_backward(mlContext_t context, mlTensor_t dy, const mlTensor_t y, float beta_dx, mlTensor_t dx, float beta_dw, mlTensor_t dw, mlActivationType_t act); /* [stub] [232] */
+void cuda_fused_act_bias_copy_backward(mlContext_t context, mlTensor_t dy, const mlTensor_t y, float beta_dx, mlTensor_t dx, float beta_dw, mlTensor_t dw, mlActivationType_t act); /* [next] [232] */
 
 /* ---- Channel shuffle and grouped GEMM
  *      replaces src/backend/cuda/kernels/group_conv.cu ---- */

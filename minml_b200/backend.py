@@ -299,3 +299,27 @@ def quantized_depthwise_conv_forward(ctx, x, w, scales, bias, y, output_qd, padd
 def channelScalingForward(ctx, x, scales, y, alpha=1.0, beta=0.0):
     lib.cuda_channel_scaling_forward(ctx.handle, alpha, desc(x), desc(scales), beta, desc(y))
     ctx.check()
+
+
+# ---------------------------------------------------------------------------------------------- backward pass of the Winograd convolution
+def winogradGradientTransform(ctx, weight_shape, dy, matrices, tile_size=None):
+    tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
+    lib.cuda_winograd_gradient_transform(ctx.handle, tile, desc(dy), desc(matrices))
+    ctx.check()
+
+
+def winogradUpdateTransform(ctx, matrices, dw, tile_size=None):
+    tile = tile_size if tile_size is not None else _tile_size(matrices, dw.shape[1])
+    lib.cuda_winograd_update_transform(ctx.handle, tile, desc(matrices), desc(dw))
+    ctx.check()
+
+
+def fusedBiasActCopyBackward(ctx, dy, y, dx=None, db=None, act="linear", beta_dx=0.0, beta_db=0.0):
+    """ml::fusedBiasActCopyBackward (src/core/math.cpp:1046-1063): dy is updated in place when act is not linear."""
+    lib.cuda_fused_act_bias_copy_backward(ctx.handle, desc(dy), desc(y), beta_dx, desc(dx), beta_db, desc(db), act_code(act))
+    ctx.check()
+
+
+def activationBackward(ctx, dy, y, dx, act="linear", alpha=1.0, beta=0.0):
+    lib.cuda_activation_backward(ctx.handle, alpha, desc(dy), desc(y), beta, desc(dx), act_code(act))
+    ctx.check()

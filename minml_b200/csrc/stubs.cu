@@ -22,14 +22,6 @@ extern "C"
 	{
 		NOT_IMPLEMENTED(context, "cuda_depth_to_space");
 	}
-	void cuda_winograd_gradient_transform(mlContext_t context, int tile_size, const mlTensor_t dy, mlTensor_t matrices) /* [100] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_winograd_gradient_transform");
-	}
-	void cuda_winograd_update_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, mlTensor_t dw) /* [101] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_winograd_update_transform");
-	}
 	void cuda_depthwise_conv_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t w, float beta, mlTensor_t dx) /* [113] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_depthwise_conv_backward");
@@ -118,17 +110,9 @@ extern "C"
 	{
 		NOT_IMPLEMENTED(context, "cuda_window_merging");
 	}
-	void cuda_activation_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t y, float beta, mlTensor_t dx, mlActivationType_t act) /* [228] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_activation_backward");
-	}
 	void cuda_softmax_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t y, float beta, mlTensor_t dx) /* [231] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_softmax_backward");
-	}
-	void cuda_fused_act_bias_copy_backward(mlContext_t context, mlTensor_t dy, const mlTensor_t y, float beta_dx, mlTensor_t dx, float beta_dw, mlTensor_t dw, mlActivationType_t act) /* [232] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_fused_act_bias_copy_backward");
 	}
 	void cuda_channel_shuffle(mlContext_t context, const mlTensor_t x, float beta, mlTensor_t y, int groups, bool invert) /* [238] */
 	{

@@ -617,3 +617,131 @@ void oracle_channel_scaling(const float *x, const float *scales, float *y, float
 				y[off] = v;
 			}
 }
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Backward pass of the Winograd convolution: gradient transform (dy tiles -> matrices), update transform
+ * (accumulated matrices -> weight gradient) and the fused activation-backward / bias-gradient / copy step.
+ * Matrices restated from src/backend/cuda/kernels/winograd_transforms.cuh:95-135 (F(2x2,3x3)), :205-250 (F(4x4,3x3)),
+ * :304-352 (F(2x2,5x5)); the CPU twins are src/backend/cpu/winograd/def_winograd_kernels.cpp.
+ * ------------------------------------------------------------------------------------------------------------- */
+static const double GR_23[4][2] = { { 1, 0 }, { 1, 1 }, { 1, -1 }, { 0, 1 } };
+static const double GR_43[6][4] = { { 1, 0, 0, 0 }, { 2.0 / 3, 2.0 / 3, 2.0 / 3, 2.0 / 3 }, { 2.0 / 3, -2.0 / 3, 2.0 / 3, -2.0 / 3 },
+		{ 1.0 / 3, 2.0 / 3, 4.0 / 3, 8.0 / 3 }, { 1.0 / 3, -2.0 / 3, 4.0 / 3, -8.0 / 3 }, { 0, 0, 0, 2 } };
+static const double GR_25[6][2] = { { 1, 0 }, { 2.0 / 3, 2.0 / 3 }, { 2.0 / 3, -2.0 / 3 }, { 1.0 / 3, 2.0 / 3 }, { 1.0 / 3, -2.0 / 3 }, { 0, 1 } };
+static const double UP_23[3][4] = { { 1, 0.5, 0.5, 0 }, { 0, 0.5, -0.5, 0 }, { 0, 0.5, 0.5, 1 } };
+static const double UP_43[3][6] = { { 1, 1, 1, 0.25, 0.25, 0 }, { 0, 1, -1, 0.5, -0.5, 0 }, { 0, 1, 1, 1, 1, 2 } };
+static const double UP_25[5][6] = { { 1, 1, 1, 0.25, 0.25, 0 }, { 0, 1, -1, 0.5, -0.5, 0 }, { 0, 1, 1, 1, 1, 0 }, { 0, 1, -1, 2, -2, 0 },
+		{ 0, 1, 1, 4, 4, 4 } };
+static double gr_at(int tile, int k, int r, int c) { return k == 5 ? GR_25[r][c] : (tile == 4 ? GR_43[r][c] : GR_23[r][c]); }
+static double up_at(int tile, int k, int r, int c) { return k == 5 ? UP_25[r][c] : (tile == 4 ? UP_43[r][c] : UP_23[r][c]); }
+
+/* M[p, tile, c] = (Gr d Gr^T)[p] for the tile x tile pieces of dy (zero beyond the border), tile order (b, th, tw)
+ * (winograd_nonfused.cu:182-212) */
+void oracle_winograd_gradient_transform(int tile, int k, const float *dy, float *m, int batch, int height, int width, int channels)
+{
+	const int p = tile + k - 1;
+	const int th_n = (height + tile - 1) / tile, tw_n = (width + tile - 1) / tile;
+	const size_t tiles = (size_t) batch * th_n * tw_n;
+	for (int b = 0; b < batch; b++)
+		for (int th = 0; th < th_n; th++)
+			for (int tw = 0; tw < tw_n; tw++)
+			{
+				const size_t t = ((size_t) b * th_n + th) * tw_n + tw;
+				for (int c = 0; c < channels; c++)
+				{
+					double d[4][4], tmp[6][4];
+					for (int r = 0; r < tile; r++)
+						for (int q = 0; q < tile; q++)
+						{
+							const int h = tile * th + r, w = tile * tw + q;
+							d[r][q] = (h < height && w < width) ? dy[(((size_t) b * height + h) * width + w) * channels + c] : 0.0;
+						}
+					for (int i = 0; i < p; i++)
+						for (int q = 0; q < tile; q++)
+						{
+							double s = 0.0;
+							for (int r = 0; r < tile; r++)
+								s += gr_at(tile, k, i, r) * d[r][q];
+							tmp[i][q] = s;
+						}
+					for (int i = 0; i < p; i++)
+						for (int j = 0; j < p; j++)
+						{
+							double s = 0.0;
+							for (int q = 0; q < tile; q++)
+								s += tmp[i][q] * gr_at(tile, k, j, q);
+							m[((size_t) (i * p + j) * tiles + t) * channels + c] = (float) s;
+						}
+				}
+			}
+}
+/* dw[co, :, :, ci] = Up M[:, co, ci] Up^T with M [p*p, cout, cin] (winograd_nonfused.cu:214-239) */
+void oracle_winograd_update_transform(int tile, int k, const float *m, float *dw, int cout, int cin)
+{
+	const int p = tile + k - 1;
+	for (int co = 0; co < cout; co++)
+		for (int ci = 0; ci < cin; ci++)
+		{
+			double d[6][6], tmp[5][6];
+			for (int r = 0; r < p; r++)
+				for (int q = 0; q < p; q++)
+					d[r][q] = m[((size_t) (r * p + q) * cout + co) * cin + ci];
+			for (int i = 0; i < k; i++)
+				for (int q = 0; q < p; q++)
+				{
+					double s = 0.0;
+					for (int r = 0; r < p; r++)
+						s += up_at(tile, k, i, r) * d[r][q];
+					tmp[i][q] = s;
+				}
+			for (int i = 0; i < k; i++)
+				for (int j = 0; j < k; j++)
+				{
+					double s = 0.0;
+					for (int q = 0; q < p; q++)
+						s += tmp[i][q] * up_at(tile, k, j, q);
+					dw[(((size_t) co * k + i) * k + j) * cin + ci] = (float) s;
+				}
+		}
+}
+/* dy <- dy * act'(y) (in place); db <- beta_db * db + column sums of the new dy; dx <- dy + beta_dx * dx
+ * (src/backend/cuda/kernels/tensor_op.cu:195-270,527-580; the CPU backend has no counterpart) */
+void oracle_act_bias_copy_backward(float *dy, const float *y, float *dx, float *db, float beta_dx, float beta_db, int act, size_t rows,
+		int channels)
+{
+	if (db)
+		for (int c = 0; c < channels; c++)
+			db[c] *= beta_db;
+	for (int c = 0; c < channels; c++)
+	{
+		double sum = 0.0;
+		for (size_t r = 0; r < rows; r++)
+		{
+			const size_t i = r * channels + c;
+			float g = dy[i];
+			switch (act)
+			{
+				case 1:
+					g *= y[i] * (1.0f - y[i]);
+					break;
+				case 2:
+					g *= 1.0f - y[i] * y[i];
+					break;
+				case 3:
+					g = (y[i] > 0.0f) ? g : 0.0f;
+					break;
+				case 4:
+					g = (y[i] > 0.0f) ? g : g * 0.1f;
+					break;
+				default:
+					break;
+			}
+			dy[i] = g;
+			sum += g;
+			if (dx)
+				dx[i] = (beta_dx != 0.0f) ? g + beta_dx * dx[i] : g;
+		}
+		if (db)
+			db[c] += (float) sum;
+	}
+}

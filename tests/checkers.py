@@ -65,6 +65,32 @@ class Oracle:
         self.lib.oracle_winograd_input_transform(tile, k, _fp(x), _fp(v), b, h, w, c)
         return v
 
+    def winograd_gradient_transform(self, dy, tile=4, k=3):
+        dy = _f32(dy)
+        b, h, w, c = dy.shape
+        p = tile + k - 1
+        tiles = b * ((h + tile - 1) // tile) * ((w + tile - 1) // tile)
+        m = np.empty((p * p, tiles, c), np.float32)
+        self.lib.oracle_winograd_gradient_transform(tile, k, _fp(dy), _fp(m), b, h, w, c)
+        return m
+
+    def winograd_update_transform(self, m, tile=4, k=3):
+        m = _f32(m)
+        _, cout, cin = m.shape
+        dw = np.empty((cout, k, k, cin), np.float32)
+        self.lib.oracle_winograd_update_transform(tile, k, _fp(m), _fp(dw), cout, cin)
+        return dw
+
+    def act_bias_copy_backward(self, dy, y, dx=None, db=None, beta_dx=0.0, beta_db=0.0, act="linear", with_dx=True, with_db=True):
+        """Returns (dy after the activation derivative, dx or None, db or None)."""
+        dy, y = _f32(dy).copy(), _f32(y)
+        c = dy.shape[-1]
+        dx_out = (np.zeros_like(dy) if dx is None else _f32(dx).copy()) if with_dx else None
+        db_out = (np.zeros(c, np.float32) if db is None else _f32(db).copy()) if with_db else None
+        self.lib.oracle_act_bias_copy_backward(_fp(dy), _fp(y), _fp(dx_out), _fp(db_out), ctypes.c_float(beta_dx), ctypes.c_float(beta_db), ACT[act],
+                                               ctypes.c_size_t(dy.size // c), c)
+        return dy, dx_out, db_out
+
     def winograd_output_transform(self, m, out_shape, bias=None, ext=None, act="linear", tile=4, k=3):
         m, bias, ext = _f32(m), _f32(bias), _f32(ext)
         b, h, w, c = out_shape
@@ -274,6 +300,8 @@ class ReferenceCpu:
             "cpu_winograd_weight_transform": [V, I, I, S, V, V, B],
             "cpu_winograd_input_transform": [V, I, I, S, S, V, V],
             "cpu_winograd_output_transform": [V, I, I, S, S, V, V, V, V, I],
+            "cpu_winograd_gradient_transform": [V, I, I, S, S, V, V],
+            "cpu_winograd_update_transform": [V, I, I, S, V, V],
             "cpu_gemm": [V, I, S, V, S, V, S, V, C, C, F, F],
             "cpu_gemm_batched": [V, I, S, V, S, V, S, V, C, C, F, F],
             "cpu_gemm_ex": [V, I, S, V, F, C, S, V, C, S, V, F, S, V, V, I],
@@ -312,6 +340,21 @@ class ReferenceCpu:
         v = np.zeros((p * p, tiles, c), np.float32)
         self.lib.cpu_winograd_input_transform(self.ctx, tile, DTYPE_FLOAT32, _shape(weight_shape), _shape(x.shape), _vp(x), _vp(v))
         return v
+
+    def winograd_gradient_transform(self, dy, weight_shape, tile=4):
+        dy = _f32(dy)
+        b, h, w, c = dy.shape
+        p = tile + weight_shape[1] - 1
+        tiles = b * ((h + tile - 1) // tile) * ((w + tile - 1) // tile)
+        m = np.zeros((p * p, tiles, c), np.float32)
+        self.lib.cpu_winograd_gradient_transform(self.ctx, tile, DTYPE_FLOAT32, _shape(weight_shape), _shape(dy.shape), _vp(dy), _vp(m))
+        return m
+
+    def winograd_update_transform(self, m, weight_shape, tile=4):
+        m = _f32(m)
+        dw = np.zeros(weight_shape, np.float32)
+        self.lib.cpu_winograd_update_transform(self.ctx, tile, DTYPE_FLOAT32, _shape(weight_shape), _vp(m), _vp(dw))
+        return dw
 
     def winograd_output_transform(self, m, weight_shape, out_shape, bias=None, ext=None, act="linear", tile=4):
         m, bias, ext = _f32(m), _f32(bias), _f32(ext)

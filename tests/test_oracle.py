@@ -249,3 +249,33 @@ def test_int8_depthwise_restatement_matches_a_plain_numpy_loop(oracle):
     y8, yf = oracle.depthwise_conv_int8(x, wt, scales, bias, out_qd, zero)
     assert np.array_equal(yf, want_f)
     assert np.array_equal(y8, want_8)
+
+
+def test_gradient_and_update_transforms_against_reference_cpu(oracle, refcpu):
+    """The backward-pass transforms against minml's CPU backend (F(4x4,3x3) and F(2x2,5x5), the two it implements), and the
+    defining identity of the pair: sum over tiles of <gradient transform, input transform> pushed through the update transform is
+    the weight gradient of the convolution."""
+    r = np.random.default_rng(21)
+    for tile, k in ((4, 3), (2, 5)):
+        dy = r.standard_normal((3, 9, 11, 20)).astype(np.float32)
+        wshape = (20, k, k, 12)
+        assert np.max(np.abs(oracle.winograd_gradient_transform(dy, tile, k) - refcpu.winograd_gradient_transform(dy, wshape, tile))) <= 1e-5
+        p = tile + k - 1
+        m = r.standard_normal((p * p, 20, 12)).astype(np.float32)
+        got, want = oracle.winograd_update_transform(m, tile, k), refcpu.winograd_update_transform(m, wshape, tile)
+        assert np.max(np.abs(got - want)) <= 2e-6 * np.max(np.abs(want))  # the oracle sums in double, the backend in fp32
+    # dL/dw of y = conv(x, w) for L = sum(y * dy), by the transforms and directly
+    for tile, k in ((4, 3), (2, 3), (2, 5)):
+        x = r.standard_normal((2, 8, 8, 5)).astype(np.float32)
+        dy = r.standard_normal((2, 8, 8, 7)).astype(np.float32)
+        v = oracle.winograd_input_transform(x, tile, k)         # [p*p, tiles, cin]
+        g = oracle.winograd_gradient_transform(dy, tile, k)     # [p*p, tiles, cout]
+        m = np.einsum("ptc,ptd->pcd", g, v).astype(np.float32)  # [p*p, cout, cin]
+        dw = oracle.winograd_update_transform(m, tile, k)
+        pad = k // 2
+        xp = np.pad(x, ((0, 0), (pad, pad), (pad, pad), (0, 0)))
+        want = np.zeros((7, k, k, 5), np.float32)
+        for i in range(k):
+            for j in range(k):
+                want[:, i, j, :] = np.einsum("bhwo,bhwc->oc", dy, xp[:, i:i + 8, j:j + 8, :])
+        assert np.max(np.abs(dw - want)) <= 1e-3 * np.max(np.abs(want))
