@@ -24,6 +24,11 @@
  *                 covers whole 64-byte row segments
  *   warps 10, 11, 14, 15   A-operand gather (cp.async variant only)
  *
+ * The int8 TMA variant runs sixteen epilogue warps (its requantisation is the expensive part).  Tile shapes on top of that:
+ *   256 output channels, TMA operands: clusters of two CTAs, tcgen05.mma.cta_group::2 (M = 256, each CTA fetches half of every
+ *       weight slice) -- the single-CTA kernel was limited by the operand fetch from L2;
+ *   up to 128 output channels, TMA operands, enough rows: two 128-row tiles per CTA and work unit sharing every weight slice.
+ *
  * Two variants of the A operand path:
  *   TMA_A = true   im2col-mode TMA: one request per K slice delivers 128 output positions x 128 bytes of channels of one
  *                  filter tap, zero-filled outside the image.  Needs cin * element size to be a multiple of 128 bytes and
@@ -120,15 +125,6 @@ namespace mb200
 		__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes)
 		{
 			asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(src_bytes) : "memory");
-		}
-		__device__ __forceinline__ void cp_async_commit()
-		{
-			asm volatile("cp.async.commit_group;" ::: "memory");
-		}
-		template<int N>
-		__device__ __forceinline__ void cp_async_wait()
-		{
-			asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory");
 		}
 		__device__ __forceinline__ void cp_async_wait_all()
 		{

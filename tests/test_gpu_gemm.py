@@ -189,3 +189,27 @@ def test_fp32_winograd_layer_with_tf32(ctx, oracle):
     ctx.enable_tf32(False)
     err = max_rel_err(host(y), oracle.conv2d(x, wt, bias, None, "relu"))
     assert err <= 1.5e-2  # measured 8.4e-3: F(4x4,3x3) amplifies the TF32 rounding of V and U (fp16 V / M give 1.2e-2 on such layers)
+
+
+@pytest.mark.parametrize("ops", ["nn", "nt", "tn", "tt"])
+@pytest.mark.parametrize("shape", [(300, 260, 72), (128, 128, 16), (515, 129, 203), (256, 384, 4)])
+def test_fp32_register_tiled_engine(ctx, oracle, ops, shape):
+    """fp32 products large enough for the 128 x 128 register-tiled kernel: every transposition, tails in all three dimensions,
+    alpha / beta, and a batch."""
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(sum(shape) + ord(ops[0]))
+    batch = 3
+    a = r.standard_normal((batch, k, m) if ops[0] == "t" else (batch, m, k)).astype(np.float32)
+    b = r.standard_normal((batch, n, k) if ops[1] == "t" else (batch, k, n)).astype(np.float32)
+    c0 = r.standard_normal((batch, m, n)).astype(np.float32)
+    c = dev(c0)
+    B.gemmBatched(ctx, ops[0], dev(a), ops[1], dev(b), c, 1.1, 0.1)
+    ctx.synchronize()
+    for i in range(batch):
+        want = 1.1 * oracle.gemm(ops[0], a[i], ops[1], b[i]) + 0.1 * c0[i]
+        assert np.max(np.abs(host(c[i]) - want)) <= 1e-4 * max(1.0, np.max(np.abs(want)))
+    c1 = torch.full((m, n), float("nan"), device="cuda")
+    B.gemm(ctx, ops[0], dev(a[0]), ops[1], dev(b[0]), c1)
+    ctx.synchronize()
+    assert np.max(np.abs(host(c1) - oracle.gemm(ops[0], a[0], ops[1], b[0]))) <= 1e-4 * max(1.0, float(np.max(np.abs(host(c1)))))
