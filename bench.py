@@ -12,7 +12,9 @@ rank runs the same per-GPU batch on its own GPU: weak scaling, no collective on 
 The JSON line printed by rank 0 carries:
   value       positions/s with the packed input already resident in HBM (device time, CUDA events, max over ranks)
   e2e         positions/s through the C ABI with HOST buffers: pinned host -> device copy of the packed planes,
-              forward, device -> host copy of policy and value, inside the timed region
+              forward, device -> host copy of policy and value, inside the timed region (wall clock).  Two contexts take
+              the steps in turn so that one step's copies overlap the other's arithmetic (--no-overlap: one context);
+              with small configurations their kernels also overlap, so e2e can exceed the single-stream `value`
   roofline    the dominant kernel of a 256 -> 256 layer, timed alone with CUDA events on the context's stream
   cpu_baseline  minml's own CPU backend (oracle/_ref, else the C port) on the host cores, on a bounded sample
 `--impl reference` times only that CPU implementation and prints the same line shape with "impl": "reference".
@@ -325,119 +327,127 @@ def gpu_arm(args, cfg):
     replicas = Replicas("nccl")
     world, rank = replicas.world, replicas.rank
     barrier = replicas.barrier
-
-    ctx = B.Context(local)
-    ctx.set_fusion(not args.eager)
     batch = cfg["batch"]
     kind = cfg.get("kind", "trunk")
-    if kind == "hybrid":
-        weights = L.make_hybrid_weights(SEED, cfg["channels"], cfg["heads"], cfg["ffn"], max(cfg["height"], cfg["width"]))
-        net = L.HybridBlock(ctx, weights, batch, cfg["height"], cfg["width"], cfg["channels"], cfg["heads"], cfg["ffn"])
-        tokens = np.random.default_rng(replicas.input_seed(SEED)).standard_normal((batch, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float16)
-        in_host = torch.from_numpy(tokens).pin_memory()
-        in_stage = torch.empty_like(in_host, device="cuda")
-        out_hosts = [torch.empty(tokens.shape, dtype=torch.float16).pin_memory()]
 
-        def predict(x):
-            return (net.predict(x),)
-    else:
-        weights = L.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
-        shape = (batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
-        if kind == "int8_trunk":
-            from minml_b200 import networks as N
-            net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64)
-        else:
-            net = L.ResNetTrunk(ctx, weights, *shape)
-        _, packed = synthetic_input(cfg, batch, replicas.input_seed(SEED))
-        in_host = torch.from_numpy(packed).pin_memory()
-        in_stage = torch.empty_like(in_host, device="cuda")
-        out_hosts = [torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory(),
-                     torch.empty((batch, 3), dtype=torch.float16).pin_memory()]
-        predict = net.predict
-    in_dev = in_host.cuda()
-    h2d = in_host.numel() * in_host.element_size()
-    d2h = sum(t.numel() * t.element_size() for t in out_hosts)
+    class Pipe:
+        """One backend context with its own copy of the network, staging buffer, pinned host buffers and (unless --no-graph) the
+        CUDA graph of one step recorded on the context's stream.  One step = the whole network on one batch: the calls of a step
+        are recorded once and replayed, because the small configurations would otherwise be paced by the Python host (about 50 us
+        per layer of ctypes calls against 25 us of kernel), which minml's C++ host is not."""
 
-    # One step = the whole network on one batch.  The calls of a step are recorded once into a CUDA graph on the context's
-    # stream and replayed: the small configurations would otherwise be paced by the Python host (about 50 us per layer of
-    # ctypes calls against 25 us of kernel), which minml's C++ host is not.  --no-graph issues the calls one by one.
-    graph = {"g": None, "outs": None, "launches": 0, "note": "calls issued one by one"}
+        def __init__(self):
+            self.ctx = B.Context(local)
+            self.ctx.set_fusion(not args.eager)
+            ctx = self.ctx
+            if kind == "hybrid":
+                weights = L.make_hybrid_weights(SEED, cfg["channels"], cfg["heads"], cfg["ffn"], max(cfg["height"], cfg["width"]))
+                net = L.HybridBlock(ctx, weights, batch, cfg["height"], cfg["width"], cfg["channels"], cfg["heads"], cfg["ffn"])
+                tokens = np.random.default_rng(replicas.input_seed(SEED)).standard_normal((batch, cfg["height"], cfg["width"], cfg["channels"])).astype(np.float16)
+                self.in_host = torch.from_numpy(tokens).pin_memory()
+                self.out_hosts = [torch.empty(tokens.shape, dtype=torch.float16).pin_memory()]
+                self.predict = lambda x: (net.predict(x),)
+            else:
+                weights = L.make_trunk_weights(SEED, cfg["planes"], cfg["channels"], cfg["blocks"])
+                shape = (batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
+                if kind == "int8_trunk":
+                    from minml_b200 import networks as N
+                    net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64)
+                else:
+                    net = L.ResNetTrunk(ctx, weights, *shape)
+                _, packed = synthetic_input(cfg, batch, replicas.input_seed(SEED))
+                self.in_host = torch.from_numpy(packed).pin_memory()
+                self.out_hosts = [torch.empty((batch, cfg["height"], cfg["width"], 1), dtype=torch.float16).pin_memory(),
+                                  torch.empty((batch, 3), dtype=torch.float16).pin_memory()]
+                self.predict = net.predict
+            self.net = net
+            self.in_stage = self.in_host.cuda()
+            self.h2d = self.in_host.numel() * self.in_host.element_size()
+            self.d2h = sum(t.numel() * t.element_size() for t in self.out_hosts)
+            self.graph, self.outs, self.launches_per_step, self.note = None, None, 0, "calls issued one by one"
+            torch.cuda.synchronize()
+            for _ in range(max(args.warmup, 3)):
+                self.step()
+            ctx.synchronize()
+            if not args.no_graph:
+                try:
+                    self.stream = ctx.torch_stream()
+                    g = torch.cuda.CUDAGraph()
+                    before = B.launch_count()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self.outs = self.predict(self.in_stage)
+                    self.launches_per_step = B.launch_count() - before
+                    self.graph = g
+                    self.note = "CUDA graph of one step (%d kernels) replayed on the context's stream" % self.launches_per_step
+                    for _ in range(3):
+                        self.step()
+                    ctx.synchronize()
+                except Exception as exc:  # capture is an optimisation of the launch path only
+                    self.graph = None
+                    self.note = "calls issued one by one (graph capture failed: %s)" % str(exc)[:120]
 
-    def run_step(x):
-        if graph["g"] is not None and x is in_stage:
-            with torch.cuda.stream(graph["stream"]):
-                graph["g"].replay()
-            return graph["outs"]
-        return predict(x)
+        def step(self):
+            """The network on what the staging buffer holds (device resident)."""
+            if self.graph is not None:
+                with torch.cuda.stream(self.stream):
+                    self.graph.replay()
+                return self.outs
+            return self.predict(self.in_stage)
 
-    def step_device():
-        return run_step(in_stage)
+        def step_from_host(self):
+            """Pinned host input -> device, the network, results -> pinned host; all queued on the context's stream, nothing waited for."""
+            B.lib.cuda_memcpy_from_host(self.ctx.handle, ctypes.c_void_p(self.in_stage.data_ptr()), 0, ctypes.c_void_p(self.in_host.data_ptr()), self.h2d)
+            outs = self.step()
+            for dst, src in zip(self.out_hosts, outs):
+                B.lib.cuda_memcpy_to_host(self.ctx.handle, ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(src.data_ptr()), 0,
+                                          src.numel() * src.element_size())
 
-    def step_e2e():
-        B.lib.cuda_memcpy_from_host(ctx.handle, ctypes.c_void_p(in_stage.data_ptr()), 0, ctypes.c_void_p(in_host.data_ptr()), h2d)
-        outs = run_step(in_stage)
-        for dst, src in zip(out_hosts, outs):
-            B.lib.cuda_memcpy_to_host(ctx.handle, ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(src.data_ptr()), 0, src.numel() * src.element_size())
-        ctx.synchronize()  # the caller reads the result of every step
-        return outs
+    pipe = Pipe()
+    ctx = pipe.ctx
 
-    def host_copy(t):
-        ctx.synchronize()
-        return t.detach().cpu().clone()
-
-    def timed(fn, steps):
+    def timed_device(steps):
         barrier()
         e0 = B.lib.cuda_create_event(ctx.handle)
-        t0 = time.perf_counter()
         for _ in range(steps):
-            fn()
+            pipe.step()
         e1 = B.lib.cuda_create_event(ctx.handle)
         ctx.synchronize()
-        wall = time.perf_counter() - t0
         dev_s = B.lib.cuda_get_time_between_events(e0, e1)
         B.lib.cuda_destroy_event(e0)
         B.lib.cuda_destroy_event(e1)
         barrier()
-        dev_max, wall_max = replicas.max_over_ranks([dev_s, wall])
-        return dev_max, wall_max
+        return replicas.max_over_ranks([dev_s])[0]
 
-    in_stage.copy_(in_dev)
-    torch.cuda.synchronize()
-    for _ in range(max(args.warmup, 3)):
-        step_device()
-    ctx.synchronize()
-    if not args.no_graph:
-        try:
-            graph["stream"] = ctx.torch_stream()
-            g = torch.cuda.CUDAGraph()
-            before = B.launch_count()
-            with torch.cuda.graph(g, stream=graph["stream"]):
-                graph["outs"] = predict(in_stage)
-            graph["launches"] = B.launch_count() - before
-            graph["g"] = g
-            graph["note"] = "CUDA graph of one step (%d kernels) replayed on the context's stream" % graph["launches"]
-            for _ in range(3):
-                step_device()
-            ctx.synchronize()
-        except Exception as exc:  # capture is an optimisation of the launch path only
-            graph["g"] = None
-            graph["note"] = "calls issued one by one (graph capture failed: %s)" % str(exc)[:120]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = B.launch_count()
-    dev_s, _ = timed(step_device, args.steps)
-    launches = (B.launch_count() - launches0) if graph["g"] is None else graph["launches"] * args.steps
-    resident = [host_copy(t) for t in step_device()]
-    for _ in range(2):
-        step_e2e()
-    e2e_dev_s, e2e_wall = timed(step_e2e, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
-    e2e_s = max(e2e_dev_s, e2e_wall)  # the step ends when the host holds the result
+    dev_s = timed_device(args.steps)
+    launches = (B.launch_count() - launches0) if pipe.graph is None else pipe.launches_per_step * args.steps
+    resident = [t.detach().cpu().clone() for t in pipe.step()]
 
-    # sanity: the host-fed run computed what the resident run computed, and nothing overflowed
-    ctx.synchronize()
-    outputs_ok = all(bool(torch.isfinite(h.float()).all()) and torch.equal(h, r) for h, r in zip(out_hosts, resident))
+    # End to end through the C ABI with host buffers.  Two contexts (two streams, two copies of the network) take the steps in
+    # turn, so that the copies of one step overlap the arithmetic of the other; the caller collects the result of step i when it
+    # comes back to that context for step i + 2, i.e. every step's result is waited for inside the timed region.
+    pipes = [pipe] if args.no_overlap else [pipe, Pipe()]
+    for p in pipes:
+        p.step_from_host()
+        p.ctx.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        p = pipes[i % len(pipes)]
+        p.ctx.synchronize()  # the result of this context's previous step is in host memory now
+        p.step_from_host()
+    for p in pipes:
+        p.ctx.synchronize()
+    e2e_wall = time.perf_counter() - t0
+    barrier()
+    e2e_s = replicas.max_over_ranks([e2e_wall])[0]
+    clocks = sampler.stop() if rank == 0 else None
+
+    # sanity: the host-fed runs computed what the resident run computed, and nothing overflowed
+    outputs_ok = all(bool(torch.isfinite(h.float()).all()) and torch.equal(h, r) for p in pipes for h, r in zip(p.out_hosts, resident))
     result = None
     if rank == 0:
         peaks = load_peaks()
@@ -452,15 +462,18 @@ def gpu_arm(args, cfg):
             "metric": METRIC.get(kind, METRIC["trunk"]), "value": value, "unit": "positions/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "i8" if kind == "int8_trunk" else "f16", "data": "synthetic", "outputs_finite_and_equal": outputs_ok,
-            "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world, "conv3x3": "three-kernel Winograd" if args.eager else "fused implicit GEMM", "launch": graph["note"],
+            "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world,
+                       "conv3x3": "three-kernel Winograd" if args.eager else "fused implicit GEMM", "launch": pipe.note,
+                       "e2e_overlap": "two contexts alternate steps (copies of one overlap the arithmetic of the other)" if len(pipes) == 2 else "none",
                        "l2": "activations of every layer (%.0f MB) exceed the 126 MB L2, no flush needed" % (
                            batch * cfg["height"] * cfg["width"] * cfg["channels"] * 2 / 1e6)},
             "algorithmic_tflops": value * fpp / 1e12, "frac_of_nominal_dense_peak": value * fpp / world / (4.5e15 if kind == "int8_trunk" else 2.25e15),
-            "e2e": {"value": total_positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "e2e": {"value": total_positions / e2e_s, "unit": "positions/s", "h2d_bytes_per_step": pipe.h2d, "d2h_bytes_per_step": pipe.d2h,
                     "ms_per_step": e2e_s / args.steps * 1e3},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
         }
-    ctx.close()
+    for p in pipes:
+        p.ctx.close()
     replicas.close()
     return result
 
@@ -474,6 +487,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue every backend call from the host each step instead of replaying a CUDA graph")
+    ap.add_argument("--no-overlap", action="store_true", help="end-to-end steps on one context, one after the other")
     ap.add_argument("--eager", action="store_true", help="three kernels per 3x3 layer (fusion off) instead of the fused convolution")
     ap.add_argument("--layer", action="store_true", help="time only one channels -> channels 3x3 layer (the roofline record); used for ncu captures")
     ap.add_argument("--layer-batch", type=int, default=0, help="batch size for --layer (default: the config's)")
