@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c3|c1] [--impl ours|reference]
 
 One "step" is one forward pass of the trunk over one batch of synthetic positions (bit-packed planes in, policy and
-value out).  Default workload: BASELINE config 3 -- 20x20 board, 32 input planes (Bernoulli p = 0.3), stem 3x3 32 -> 256,
+value out).  Default workload: benchmark configuration 3 -- 20x20 board, 32 input planes (Bernoulli p = 0.3), stem 3x3 32 -> 256,
 20 residual blocks of two 3x3 256 -> 256 convolutions with bias and ReLU, 1x1 policy head, global-average-pool + dense
 value head, fp16, batch 1024 per GPU, He-normal random weights.  With N > 1 (launched by torch.distributed.run) every
 rank runs the same per-GPU batch on its own GPU: weak scaling, no collective on the forward path.

@@ -1,4 +1,4 @@
-"""The int8 trunk of BASELINE config 2, assembled the way minml's `Quantize` graph pass assembles it
+"""The int8 trunk of benchmark configuration 2, assembled the way minml's `Quantize` graph pass assembles it
 (src/graph/graph_optimizers.cpp:220-242, src/layers/Layer.cpp:147-160, src/layers/quantization.cpp:59-97):
 
   * weights: per-output-channel symmetric int8, q = clamp(round(w * 127 / max|w_co|)); channel_scale = s_in * max|w_co| / 127;

@@ -19,7 +19,7 @@ def _case(seed, b, h, w, cin, cout, k=3):
 
 
 def test_config0_fp32_three_call_path(ctx, oracle, refcpu):
-    """BASELINE config 0 at a reduced batch: fp32, 15x15, 128 -> 128, bias + ReLU, via the reference's own call triple."""
+    """Benchmark configuration 0 at a reduced batch: fp32, 15x15, 128 -> 128, bias + ReLU, via the reference's own call triple."""
     from minml_b200 import layers as L
     x, wt, bias, _ = _case(1234, 8, 15, 15, 128, 128)
     conv = L.Conv2D(ctx, wt, bias, "relu", torch.float32)
@@ -159,7 +159,7 @@ def test_trunk_matches_fp32_oracle(ctx, oracle, cfg):
 
 @pytest.mark.parametrize("cfg", [(2, 15, 15, 256, 8, 1024), (1, 9, 7, 64, 4, 128)])
 def test_hybrid_block_matches_fp32_oracle(ctx, oracle, cfg):
-    """BASELINE config 4 topology (3x3 residual block, pre-LN attention with relative-position bias, ReLU feed-forward) at a small batch."""
+    """Benchmark configuration 4 topology (3x3 residual block, pre-LN attention with relative-position bias, ReLU feed-forward) at a small batch."""
     from minml_b200 import layers as L
     from tests.util import oracle_hybrid
     b, h, w, embed, heads, ffn = cfg
@@ -176,7 +176,7 @@ def test_hybrid_block_matches_fp32_oracle(ctx, oracle, cfg):
 
 @pytest.mark.parametrize("cfg", [(4, 15, 15, 32, 128, 2), (2, 20, 20, 32, 256, 3)])
 def test_quantized_trunk(ctx, oracle, cfg):
-    """BASELINE config 2 topology (int8 activations and weights between the 3x3 layers, fp16 heads): the heads' outputs against the
+    """Benchmark configuration 2 topology (int8 activations and weights between the 3x3 layers, fp16 heads): the heads' outputs against the
     oracle's integer chain with the same calibrated scales, and, loosely, against the fp32 trunk (the quantisation error itself)."""
     from minml_b200 import layers as L
     from minml_b200 import networks as N

@@ -1,4 +1,4 @@
-"""The BASELINE configurations at their FULL sizes.  The oracle is scalar C, so a whole full-size tensor is out of its reach;
+"""The benchmark configurations at their FULL sizes.  The oracle is scalar C, so a whole full-size tensor is out of its reach;
 what is checked instead holds at any size:
 
   * positions (batch items) are independent, so the oracle on a handful of SAMPLED items -- first, last, and items that
