@@ -245,6 +245,11 @@ void *mb200_get_stream(mlContext_t context);
 void mb200_set_fusion(mlContext_t context, int enabled);
 /* Library build identification: "minml_b200 <version> sm_100a". */
 const char *mb200_version(void);
+/* Failure-path self test: launches one small kernel that waits, with a limit of `polls` polls (1 .. 2^20), on a barrier that
+ * nothing completes.  The wait gives up, the kernel writes the context's status word and retires; the next
+ * cuda_synchronize_with_context records the same sticky error a tensor-core kernel whose wait ran out would produce.  The
+ * context stays usable.  Nothing in the call can hang. */
+void mb200_selftest_bounded_wait(mlContext_t context, int polls);
 
 /* No counterpart in the reference.
  * y = act(conv3x3(x, w) + bias + add) by F(4x4,3x3) Winograd, for callers that must never allocate device memory: a

@@ -62,9 +62,9 @@ namespace mb200
 			return done != 0;
 		}
 		/* Bounded wait.  `abort_flag` lives in shared memory and is shared by all roles of the CTA. */
-		__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+		__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t limit)
 		{
-			for (uint32_t it = 0; it < SPIN_LIMIT; ++it)
+			for (uint32_t it = 0; it < limit; ++it)
 			{
 				if (mbar_try_wait(bar, parity))
 					return true;
@@ -73,6 +73,10 @@ namespace mb200
 			}
 			*abort_flag = 1;
 			return false;
+		}
+		__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+		{
+			return mbar_wait_limited(bar, parity, abort_flag, SPIN_LIMIT);
 		}
 
 		/* ---------------------------------------------------------------- TMA */

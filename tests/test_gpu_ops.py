@@ -204,3 +204,26 @@ def test_dequantize(ctx):
     B.dequantize(ctx, q, out, 0.05, -0.3)
     ctx.synchronize()
     assert torch.allclose(out, q.float() * 0.05 - 0.3, atol=1e-6)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(ctx, oracle):
+    """The failure path of the tensor-core kernels, driven without any of them misbehaving: a small kernel waits (bounded) on a
+    barrier nothing completes, gives up and writes the context's status word; synchronize reports the sticky error; after that the
+    same context computes a correct convolution."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    ctx.synchronize()
+    B.lib.mb200_selftest_bounded_wait(ctx.handle, 2000)
+    with pytest.raises(B.BackendError, match="gave up on a bounded wait"):
+        ctx.synchronize()
+    ctx.synchronize()  # the error was reported once and cleared
+    r = np.random.default_rng(0)
+    x = r.uniform(-1, 1, (2, 9, 9, 64)).astype(np.float16).astype(np.float32)
+    wt = (r.standard_normal((64, 3, 3, 64)) * 0.05).astype(np.float16).astype(np.float32)
+    conv = L.Conv2D(ctx, wt, None, "relu", torch.float16)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    y = torch.empty((2, 9, 9, 64), device="cuda", dtype=torch.float16)
+    conv.forward([dev(x, torch.float16)], y, ws)
+    ctx.synchronize()
+    assert max_rel_err(host(y), oracle.conv2d(x, wt, None, None, "relu")) <= 1e-2
