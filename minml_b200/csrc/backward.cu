@@ -291,6 +291,8 @@ extern "C"
 	void cuda_winograd_gradient_transform(mlContext_t context, int tile_size, const mlTensor_t dy, mlTensor_t matrices)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_winograd_gradient_transform: null context");
+		if (volume(dy) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, dy.rank == 4 && matrices.rank == 3 && dy.data != nullptr && matrices.data != nullptr && dy.dtype == matrices.dtype,
 				"cuda_winograd_gradient_transform: dy [b,h,w,c] and matrices [p*p,tiles,c] of one type");
 		const int p = patch_of(matrices), k = p - tile_size + 1;
@@ -316,6 +318,8 @@ extern "C"
 	void cuda_winograd_update_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, mlTensor_t dw)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_winograd_update_transform: null context");
+		if (volume(dw) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, matrices.rank == 3 && dw.rank == 4 && matrices.data != nullptr && dw.data != nullptr,
 				"cuda_winograd_update_transform: matrices [p*p,cout,cin] and dw [cout,k,k,cin]");
 		const int p = patch_of(matrices), k = p - tile_size + 1;
@@ -342,6 +346,8 @@ extern "C"
 			mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_activation_backward: null context");
+		if (volume(dy) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, dy.data != nullptr && y.data != nullptr && dx.data != nullptr && volume(dy) == volume(y) && volume(dy) == volume(dx)
 				&& dy.dtype == y.dtype && dy.dtype == dx.dtype, "cuda_activation_backward: dy, y and dx must match");
 		flush_pending(context);
@@ -368,6 +374,8 @@ extern "C"
 			mlTensor_t dw, mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_fused_act_bias_copy_backward: null context");
+		if (volume(dy) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, dy.data != nullptr && y.data != nullptr && volume(dy) == volume(y) && dy.dtype == y.dtype,
 				"cuda_fused_act_bias_copy_backward: dy and y must match");
 		MB200_REQUIRE(context, dx.data == nullptr || (volume(dx) == volume(dy) && dx.dtype == dy.dtype),

@@ -421,6 +421,8 @@ extern "C"
 			const mlTensor_t avg_var, float beta, mlTensor_t y, mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_batchnorm_inference: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.data != nullptr && y.data != nullptr && avg_var.data != nullptr, "cuda_batchnorm_inference: null tensor");
 		MB200_REQUIRE(context, x.dtype == y.dtype && volume(x) == volume(y), "cuda_batchnorm_inference: x and y do not match");
 		MB200_REQUIRE(context, avg_var.dtype == DTYPE_FLOAT32 && volume(avg_var) == 2LL * last_dim(x),
@@ -508,6 +510,8 @@ extern "C"
 	void cuda_channel_scaling_forward(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t scales, float beta, mlTensor_t y)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_channel_scaling_forward: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.data != nullptr && y.data != nullptr && scales.data != nullptr && x.rank >= 2 && scales.rank == 2,
 				"cuda_channel_scaling_forward: x [b, ..., c], scales [b, c]");
 		MB200_REQUIRE(context, x.dtype == y.dtype && x.dtype == scales.dtype && volume(x) == volume(y) && scales.dim[0] == x.dim[0]
@@ -557,6 +561,8 @@ extern "C"
 			mlTensor_t y)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_depthwise_conv_forward: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.rank == 4 && y.rank == 4 && w.rank == 3 && x.data != nullptr && y.data != nullptr && w.data != nullptr,
 				"cuda_depthwise_conv_forward: x, y [b,h,w,c], w [k,k,c]");
 		MB200_REQUIRE(context, w.dim[0] == w.dim[1] && (w.dim[0] == 3 || w.dim[0] == 5 || w.dim[0] == 7), "cuda_depthwise_conv_forward: filter %d x %d not supported (3, 5, 7)",
@@ -598,6 +604,8 @@ extern "C"
 			int padding_value)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_quantized_depthwise_conv_forward: null context");
+		if (volume(input_shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, dtype == DTYPE_INT8, "cuda_quantized_depthwise_conv_forward: only int8 is supported");
 		MB200_REQUIRE(context, input_shape.rank == 4 && weights_shape.rank == 3 && input != nullptr && weights != nullptr && output != nullptr,
 				"cuda_quantized_depthwise_conv_forward: input [b,h,w,c], weights [k,k,c]");

@@ -21,6 +21,8 @@ extern "C"
 			const void *input, const void *weights, void *output, const void *bias, const void *add, mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_convolution_implicit_gemm_forward: null context");
+		if (volume(input_shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, input_shape.rank == 4 && weights_shape.rank == 4, "cuda_convolution_implicit_gemm_forward: rank-4 shapes expected");
 		MB200_REQUIRE(context, input != nullptr && weights != nullptr && output != nullptr, "cuda_convolution_implicit_gemm_forward: null pointer");
 		MB200_REQUIRE(context, dtype == DTYPE_FLOAT16 || dtype == DTYPE_FLOAT32, "cuda_convolution_implicit_gemm_forward: dtype %d not supported",

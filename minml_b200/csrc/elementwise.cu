@@ -342,6 +342,8 @@ extern "C"
 	void cuda_add_bias_act(mlContext_t context, float alpha, const mlTensor_t x, const mlTensor_t b, float beta, mlTensor_t y, mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_add_bias_act: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.data != nullptr && y.data != nullptr && b.data != nullptr, "cuda_add_bias_act: null tensor data");
 		MB200_REQUIRE(context, x.dtype == y.dtype && x.dtype == b.dtype, "cuda_add_bias_act: dtypes differ");
 		MB200_REQUIRE(context, volume(x) == volume(y) && last_dim(b) == last_dim(x), "cuda_add_bias_act: shapes do not match");
@@ -370,6 +372,8 @@ extern "C"
 	void cuda_activation_forward(mlContext_t context, float alpha, const mlTensor_t x, float beta, mlTensor_t y, mlActivationType_t act)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_activation_forward: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.data != nullptr && y.data != nullptr, "cuda_activation_forward: null tensor data");
 		MB200_REQUIRE(context, x.dtype == y.dtype && volume(x) == volume(y), "cuda_activation_forward: x and y differ in dtype or size");
 		const long long elements = volume(x);
@@ -406,6 +410,8 @@ extern "C"
 			const mlTensor_t x3, float beta, mlTensor_t y)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_add_tensors: null context");
+		if (volume(y) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		const long long elements = volume(y);
 		if (elements == 0 || y.data == nullptr)
 			return;
@@ -443,6 +449,8 @@ extern "C"
 	void cuda_unpack_input(mlContext_t context, mlShape_t shape, mlDataType_t dst_dtype, void *dst, const void *src)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_unpack_input: null context");
+		if (volume(shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, dst != nullptr && src != nullptr, "cuda_unpack_input: null pointer");
 		flush_pending(context);
 		const long long rows = volume_without_last_dim(shape);
@@ -518,6 +526,8 @@ extern "C"
 	void cuda_transpose_021(mlContext_t context, mlDataType_t dtype, mlShape_t shape, const void *input, void *output)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_transpose_021: null context");
+		if (volume(shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, shape.rank == 3 && input != nullptr && output != nullptr && input != output,
 				"cuda_transpose_021: needs a rank-3 shape and distinct non-null buffers");
 		flush_pending(context);
@@ -555,6 +565,8 @@ extern "C"
 	void cuda_global_average_pooling_forward(mlContext_t context, float alpha, const mlTensor_t x, float beta, mlTensor_t y)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_global_average_pooling_forward: null context");
+		if (volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, x.rank == 4 && y.rank == 2 && x.data != nullptr && y.data != nullptr,
 				"cuda_global_average_pooling_forward: x must be [b,h,w,c] and y [b,c]");
 		MB200_REQUIRE(context, x.dim[0] == y.dim[0] && x.dim[3] == y.dim[1] && x.dtype == y.dtype,
@@ -593,6 +605,8 @@ extern "C"
 	void cuda_softmax_forward(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *output, const void *input)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_softmax_forward: null context");
+		if (volume(shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, output != nullptr && input != nullptr, "cuda_softmax_forward: null pointer");
 		flush_pending(context);
 		const long long rows = volume_without_last_dim(shape);

@@ -26,10 +26,11 @@ namespace
 			mlDataType_t dtype;
 			int rows, cols;
 			long long batch_stride;
+			bool matrix; // rank 2 or 3
 	};
 	Operand operand_of(const mlTensor_t &t)
 	{
-		Operand r { t.data, t.dtype, 0, 0, 0 };
+		Operand r { t.data, t.dtype, 0, 0, 0, t.rank == 2 || t.rank == 3 };
 		if (t.rank == 2)
 		{
 			r.rows = t.dim[0];
@@ -53,8 +54,10 @@ namespace
 			const void *Cin, const void *bias, mlActivationType_t act, int batch)
 	{
 		MB200_REQUIRE(ctx, ctx != nullptr, "%s: null context", who);
+		MB200_REQUIRE(ctx, A.matrix && B.matrix && D.matrix, "%s: operands must have rank 2 or 3", who);
+		if (static_cast<long long>(D.rows) * D.cols == 0 || batch == 0)
+			return; // an empty product: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(ctx, A.data != nullptr && B.data != nullptr && D.data != nullptr, "%s: null tensor data", who);
-		MB200_REQUIRE(ctx, A.rows > 0 && B.rows > 0 && D.rows > 0, "%s: operands must have rank 2 or 3", who);
 		const bool ta = is_transpose(opA), tb = is_transpose(opB);
 		const int rows = ta ? A.cols : A.rows;
 		const int cols = tb ? B.rows : B.cols;

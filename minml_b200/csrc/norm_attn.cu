@@ -220,6 +220,8 @@ extern "C"
 			const void *bias, const void *ext)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_layernorm_forward: null context");
+		if (volume(shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, input != nullptr && output != nullptr, "cuda_layernorm_forward: null pointer");
 		flush_pending(context);
 		const long long rows = volume_without_last_dim(shape);
@@ -287,6 +289,8 @@ extern "C"
 		(void) workspace;
 		(void) backward_data;
 		MB200_REQUIRE(context, context != nullptr, "cuda_multi_head_attention_forward: null context");
+		if (volume(input_shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, input_shape.rank == 4 && input != nullptr && output != nullptr,
 				"cuda_multi_head_attention_forward: needs a rank-4 input and buffers");
 		MB200_REQUIRE(context, num_heads > 0, "cuda_multi_head_attention_forward: %d heads", num_heads);

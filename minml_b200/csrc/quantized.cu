@@ -164,6 +164,8 @@ extern "C"
 			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_quantized_scale_shift_act: null context");
+		if (volume(shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, output != nullptr && input != nullptr && scales != nullptr && bias != nullptr,
 				"cuda_quantized_scale_shift_act: null pointer");
 		if (requant_complete_fused(context, dtype, shape, output, output_qd, input, scales, bias, act, ext, ext_qd))
@@ -209,6 +211,8 @@ extern "C"
 	void cuda_dequantize(mlContext_t context, mlDataType_t dtype, const void *input, void *output, int elements, float scale, float shift)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_dequantize: null context");
+		if (elements == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		if (elements <= 0)
 			return;
 		MB200_REQUIRE(context, input != nullptr && output != nullptr, "cuda_dequantize: null pointer");
@@ -240,6 +244,8 @@ extern "C"
 			const void *padding)
 	{
 		MB200_REQUIRE(context, context != nullptr, "cuda_im2row: null context");
+		if (volume(input_shape) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		MB200_REQUIRE(context, input_shape.rank == 4 && output != nullptr && input != nullptr, "cuda_im2row: needs a rank-4 input and buffers");
 		MB200_REQUIRE(context, kernel_size >= 1 && kernel_size % 2 == 1, "cuda_im2row: kernel size %d must be odd", kernel_size);
 		const int elem = size_of(dtype);

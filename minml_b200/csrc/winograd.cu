@@ -569,6 +569,8 @@ extern "C"
 	}
 	void cuda_winograd_input_transform(mlContext_t context, int tile_size, const mlTensor_t x, mlTensor_t matrices)
 	{
+		if (context != nullptr && volume(x) == 0)
+			return; // an empty problem: nothing to validate or launch (its tensors may have null data)
 		if (!winograd_check_common(context, "cuda_winograd_input_transform", tile_size, matrices))
 			return;
 		MB200_REQUIRE(context, x.rank == 4 && x.data != nullptr && x.dtype == matrices.dtype,
@@ -586,6 +588,11 @@ extern "C"
 	void cuda_winograd_output_transform(mlContext_t context, int tile_size, const mlTensor_t matrices, const mlTensor_t bias, const mlTensor_t ext,
 			mlTensor_t y, mlActivationType_t act)
 	{
+		if (context != nullptr && volume(y) == 0)
+		{ // an empty problem: drop what an (equally empty) recorded input transform / product may have left pending
+			flush_pending(context);
+			return;
+		}
 		if (!winograd_check_common(context, "cuda_winograd_output_transform", tile_size, matrices))
 			return;
 		MB200_REQUIRE(context, y.rank == 4 && y.data != nullptr && y.dtype == matrices.dtype,

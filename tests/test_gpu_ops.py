@@ -227,3 +227,27 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(ctx, orac
     conv.forward([dev(x, torch.float16)], y, ws)
     ctx.synchronize()
     assert max_rel_err(host(y), oracle.conv2d(x, wt, None, None, "relu")) <= 1e-2
+
+
+def test_empty_tensors_launch_nothing_and_record_no_error(ctx):
+    """Zero-sized batches, as the reference's layers may see them for an empty request: every entry point returns without a launch."""
+    from minml_b200 import backend as B
+    f16 = torch.float16
+    before = B.launch_count()
+    x = torch.empty((0, 15, 15, 128), device="cuda", dtype=f16)
+    y = torch.empty((0, 15, 15, 128), device="cuda", dtype=f16)
+    w = torch.zeros((128, 3, 3, 128), device="cuda", dtype=f16)
+    bias = torch.zeros(128, device="cuda", dtype=f16)
+    B.convolutionImplicitGemmForward(ctx, x, w, y, bias, None, "relu")
+    B.addBiasAct(ctx, x, bias, y, "relu")
+    B.activationForward(ctx, x, y, "relu")
+    B.addTensors(ctx, y, 1.0, x, 1.0, x)
+    B.layernormForward(ctx, x, y, bias, bias)
+    B.globalAveragePoolingForward(ctx, x, torch.empty((0, 128), device="cuda", dtype=f16))
+    B.gemm(ctx, "n", torch.empty((0, 64), device="cuda", dtype=f16), "t", torch.zeros((32, 64), device="cuda", dtype=f16),
+           torch.empty((0, 32), device="cuda", dtype=f16))
+    B.softmaxForward(ctx, torch.empty((0, 10), device="cuda", dtype=f16), torch.empty((0, 10), device="cuda", dtype=f16))
+    B.depthwiseConvForward(ctx, x, torch.zeros((7, 7, 128), device="cuda", dtype=f16), y, bias)
+    B.batchnormInference(ctx, x, y, bias, bias, torch.zeros((2, 128), device="cuda"), "relu")
+    ctx.synchronize()
+    assert B.launch_count() == before
