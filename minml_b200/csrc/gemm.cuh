@@ -12,7 +12,8 @@ namespace mb200
 	 * Leading dimensions and batch strides are in elements; a batch stride of 0 broadcasts the operand. */
 	struct GemmTcProblem
 	{
-			int kind = 0; // 0: fp16 operands, fp32 accumulation; 1: int8 operands, int32 accumulation; 2: fp32 operands read as tf32
+			int kind = 0; // 0: fp16 operands, fp32 accumulation; 1: int8 operands, int32 accumulation; 2: fp32 operands read as tf32;
+			// 3: fp32 operands split into two tf32 terms each (three tensor-core products, close to fp32 accuracy)
 			int M = 0, N = 0, K = 0, batch = 1;
 			const void *A = nullptr;
 			int lda = 0;

@@ -11,6 +11,7 @@
  * generic kernel.  cuda_gemm_ex fuses beta * C, bias and activation into the tensor-core epilogue (the reference's
  * non-cuDNN build needs three extra passes over D: src/backend/cuda/cudnn_math.cpp:696-715).
  */
+#include <cstdlib>
 #include "common.cuh"
 #include "gemm.cuh"
 #include "winograd.cuh"
@@ -88,13 +89,17 @@ namespace
 		flush_pending(ctx);
 
 		const void *c_in = (beta != 0.0f) ? (Cin != nullptr ? Cin : D.data) : nullptr;
-		// fp32 operands go to the tensor cores only when the host has allowed TF32 on this context (cuda_enable_tf32), the
-		// condition under which the reference asks cuBLAS for CUBLAS_COMPUTE_32F_FAST_TF32 (src/backend/cuda/gemms.cpp:150-153)
-		const bool tf32 = A.dtype == DTYPE_FLOAT32 && D.dtype == DTYPE_FLOAT32 && get(ctx)->allow_tf32;
-		if (!ta && tb && (A.dtype == DTYPE_FLOAT16 || A.dtype == DTYPE_INT8 || tf32))
+		// fp32 operands are read as plain TF32 only when the host has allowed TF32 on this context (cuda_enable_tf32), the
+		// condition under which the reference asks cuBLAS for CUBLAS_COMPUTE_32F_FAST_TF32 (src/backend/cuda/gemms.cpp:150-153);
+		// otherwise they run as three TF32 products of split operands, which keeps the result within fp32 rounding noise
+		// (MINML_B200_FP32_SIMT=1 sends them to the plain fp32 engine instead)
+		static const bool fp32_simt = std::getenv("MINML_B200_FP32_SIMT") != nullptr && std::getenv("MINML_B200_FP32_SIMT")[0] == '1';
+		const bool fp32 = A.dtype == DTYPE_FLOAT32 && D.dtype == DTYPE_FLOAT32;
+		const bool tf32 = fp32 && get(ctx)->allow_tf32;
+		if (!ta && tb && (A.dtype == DTYPE_FLOAT16 || A.dtype == DTYPE_INT8 || tf32 || (fp32 && !fp32_simt)))
 		{
 			GemmTcProblem g;
-			g.kind = (A.dtype == DTYPE_FLOAT16) ? 0 : (A.dtype == DTYPE_INT8 ? 1 : 2);
+			g.kind = (A.dtype == DTYPE_FLOAT16) ? 0 : (A.dtype == DTYPE_INT8 ? 1 : (tf32 ? 2 : 3));
 			g.M = rows;
 			g.N = cols;
 			g.K = K;

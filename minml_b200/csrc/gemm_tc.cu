@@ -79,13 +79,26 @@ namespace mb200
 		constexpr int BM = 128;
 		constexpr int BK_BYTES = 128; // one swizzle row: 64 fp16 or 128 int8
 		constexpr int EPI_WARPS = 8;
-		constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+		constexpr int SPLIT_WARPS = 4; // only in the split-fp32 kernel
+		constexpr int num_threads(int kind)
+		{
+			return (2 + EPI_WARPS + (kind == 3 ? SPLIT_WARPS : 0)) * 32;
+		}
 
-		template<int BN>
+		/*
+		 * KIND 3 multiplies fp32 operands at (nearly) fp32 accuracy on the TF32 tensor cores: every element x is split in shared
+		 * memory into hi = x rounded to a TF32 number (low 13 mantissa bits clear) and lo = x - hi (exact in fp32), and
+		 * the product is accumulated as hi*hi + hi*lo + lo*hi in fp32. The dropped lo*lo term and the truncation of lo to TF32
+		 * are both of relative size 2^-21, a little above the 2^-24 of an fp32 multiply and far below TF32's 2^-11. Each stage
+		 * holds the operands twice (the landed tile, overwritten with hi, and the lo tile), so there are fewer stages.
+		 */
+		template<int KIND, int BN>
 		struct Tiling
 		{
-				static constexpr int stage_bytes = BM * BK_BYTES + BN * BK_BYTES;
-				static constexpr int stages = (BN == 256) ? 4 : 6;
+				static constexpr bool split = (KIND == 3);
+				static constexpr int operand_bytes = BM * BK_BYTES + BN * BK_BYTES;
+				static constexpr int stage_bytes = operand_bytes * (split ? 2 : 1);
+				static constexpr int stages = split ? 3 : ((BN == 256) ? 4 : 6);
 				static constexpr int smem_bytes = stages * stage_bytes + EPI_WARPS * epi::WARP_BYTES + 1024;
 				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
 		};
@@ -94,11 +107,21 @@ namespace mb200
 		{
 				uint64_t full[6];
 				uint64_t empty[6];
+				uint64_t split[6]; // KIND 3: the stage's hi and lo tiles are written
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
 				int abort_flag;
 		};
+
+		/* hi = x rounded to the nearest TF32 number (13 low mantissa bits clear); lo = x - hi (exact, either sign, so the
+		 * truncation of lo by the tensor core does not bias the sum). An infinite x turns into NaN in the product (inf * 0 in
+		 * the cross terms) where fp32 arithmetic would give an infinity. */
+		__device__ __forceinline__ void split_tf32(uint32_t x, uint32_t &hi, uint32_t &lo)
+		{
+			hi = (x + 0x1000u) & 0xFFFFE000u;
+			lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
+		}
 
 		__device__ __forceinline__ float requant_prepare(int acc, float scale, float shift)
 		{
@@ -106,10 +129,10 @@ namespace mb200
 		}
 
 		template<int KIND, int BN>
-		__global__ void __launch_bounds__(NUM_THREADS, 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
+		__global__ void __launch_bounds__(num_threads(KIND), 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
 				const __grid_constant__ CUtensorMap map_b, const GemmTcParams p)
 		{
-			using T = Tiling<BN>;
+			using T = Tiling<KIND, BN>;
 			extern __shared__ uint8_t smem_raw[];
 			__shared__ Barriers bars;
 
@@ -120,7 +143,7 @@ namespace mb200
 			const int m_tiles = (p.M + BM - 1) / BM;
 			const int n_tiles = (p.N + BN - 1) / BN;
 			const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * p.batch;
-			const int elems_per_kblock = (KIND == 0) ? 64 : (KIND == 1 ? 128 : 32); // 128 bytes of K per row
+			const int elems_per_kblock = (KIND == 0) ? 64 : (KIND == 1 ? 128 : 32); // 128 bytes of K per row (fp32 for KIND 2 and 3)
 			const int k_blocks = (p.K + elems_per_kblock - 1) / elems_per_kblock;
 
 			if (threadIdx.x == 0)
@@ -129,6 +152,7 @@ namespace mb200
 				{
 					mbar_init(smem_u32(&bars.full[s]), 1);
 					mbar_init(smem_u32(&bars.empty[s]), 1);
+					mbar_init(smem_u32(&bars.split[s]), SPLIT_WARPS);
 				}
 				for (int a = 0; a < 2; a++)
 				{
@@ -172,7 +196,7 @@ namespace mb200
 								break;
 							}
 							const uint32_t full = smem_u32(&bars.full[s]);
-							mbar_arrive_expect_tx(full, T::stage_bytes);
+							mbar_arrive_expect_tx(full, T::operand_bytes);
 							const uint32_t dst_a = smem_base + s * T::stage_bytes;
 							const uint32_t dst_b = dst_a + BM * BK_BYTES;
 							tma_load_3d(dst_a, &map_a, full, kb * elems_per_kblock, mt * BM, p.a_broadcast ? 0 : b);
@@ -187,6 +211,7 @@ namespace mb200
 				if (elect_one())
 				{
 					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : (KIND == 1 ? make_idesc_i8(BN) : make_idesc_tf32(BN));
+					uint64_t *const ready = T::split ? bars.split : bars.full; // what the tensor core may read
 					uint32_t it = 0;
 					uint32_t local_tile = 0;
 					bool ok = true;
@@ -202,12 +227,14 @@ namespace mb200
 						{
 							const int s = it % T::stages;
 							const uint32_t parity = (it / T::stages) & 1u;
-							if (!mbar_wait(smem_u32(&bars.full[s]), parity, abort_flag))
+							if (!mbar_wait(smem_u32(&ready[s]), parity, abort_flag))
 							{
 								ok = false;
 								break;
 							}
 							tcgen05_fence_after();
+							if (T::split)
+								fence_proxy_async_smem(); // the hi and lo tiles were plain stores of the split warps
 							const uint32_t addr_a = smem_base + s * T::stage_bytes;
 							const uint32_t addr_b = addr_a + BM * BK_BYTES;
 							const uint64_t desc_a = make_desc_k_sw128(addr_a);
@@ -215,6 +242,17 @@ namespace mb200
 #pragma unroll
 							for (int k = 0; k < 4; k++) // 4 x 32 bytes of K per stage; +2 in descriptor units of 16 bytes
 								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+							if (T::split)
+							{
+								const uint64_t lo_a = make_desc_k_sw128(addr_a + T::operand_bytes);
+								const uint64_t lo_b = make_desc_k_sw128(addr_b + T::operand_bytes);
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									mma_ss<KIND>(tmem_d, desc_a + 2 * k, lo_b + 2 * k, idesc, 1u);
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									mma_ss<KIND>(tmem_d, lo_a + 2 * k, desc_b + 2 * k, idesc, 1u);
+							}
 							mma_commit(smem_u32(&bars.empty[s]));
 						}
 						if (ok)
@@ -222,6 +260,41 @@ namespace mb200
 					}
 				}
 				__syncwarp();
+			}
+			else if (T::split && warp >= 2 + EPI_WARPS)
+			{ /* ------------------------------------------- split warps (KIND 3): x -> hi (in place) and lo */
+				const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
+				uint32_t it = 0;
+				bool ok = true;
+				for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+					for (int kb = 0; kb < k_blocks; kb++, it++)
+					{
+						const int s = it % T::stages;
+						if (!mbar_wait(smem_u32(&bars.full[s]), (it / T::stages) & 1u, abort_flag))
+						{
+							ok = false;
+							break;
+						}
+						// the split is elementwise, so it keeps whatever swizzled layout the copy engine wrote
+						const uint32_t hi = smem_base + s * T::stage_bytes;
+						const uint32_t lo = hi + T::operand_bytes;
+#pragma unroll 4
+						for (int i = t; i < T::operand_bytes / 16; i += SPLIT_WARPS * 32)
+						{
+							const uint4 x = ld_shared_v4(hi + i * 16);
+							uint4 h, l;
+							split_tf32(x.x, h.x, l.x);
+							split_tf32(x.y, h.y, l.y);
+							split_tf32(x.z, h.z, l.z);
+							split_tf32(x.w, h.w, l.w);
+							st_shared_v4(hi + i * 16, h);
+							st_shared_v4(lo + i * 16, l);
+						}
+						fence_proxy_async_smem(); // plain stores -> visible to the tensor core's reads
+						__syncwarp();
+						if (lane == 0)
+							mbar_arrive(smem_u32(&bars.split[s]));
+					}
 			}
 			else
 			{ /* ------------------------------------------------------------ epilogue */
@@ -326,7 +399,7 @@ namespace mb200
 						}
 						if (!row_ok)
 							continue;
-						if (KIND == 0 || KIND == 2)
+						if (KIND == 0 || KIND >= 2)
 						{
 #pragma unroll
 							for (int j = 0; j < 32; j++)
@@ -484,7 +557,7 @@ namespace mb200
 		template<int KIND, int BN>
 		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const GemmTcParams &p, int sm_count)
 		{
-			using T = Tiling<BN>;
+			using T = Tiling<KIND, BN>;
 			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
 			const int device = get(ctx)->device;
 			if (device < 0 || device >= MAX_DEVICES)
@@ -500,7 +573,7 @@ namespace mb200
 			}
 			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
 			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
-			kernel_gemm_tc<KIND, BN> <<<grid, NUM_THREADS, T::smem_bytes, stream>>>(map_a, map_b, p);
+			kernel_gemm_tc<KIND, BN> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, p);
 			MB200_COUNT_LAUNCH();
 			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
 		}
@@ -525,7 +598,7 @@ namespace mb200
 		}
 		if (g.kind == 0 && g.out_dtype != DTYPE_FLOAT16 && g.out_dtype != DTYPE_FLOAT32)
 			return false;
-		if (g.kind == 2 && g.out_dtype != DTYPE_FLOAT32)
+		if (g.kind >= 2 && g.out_dtype != DTYPE_FLOAT32)
 			return false;
 		if (g.kind == 1 && g.out_dtype != DTYPE_INT32 && g.out_dtype != DTYPE_INT8 && g.out_dtype != DTYPE_FLOAT16
 				&& g.out_dtype != DTYPE_FLOAT32)
@@ -540,7 +613,7 @@ namespace mb200
 		const int elem = (g.kind == 0) ? 2 : (g.kind == 1 ? 1 : 4);
 		const CUtensorMapDataType dt = (g.kind == 0) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
 				: (g.kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
-		const int bn = (g.N > 128) ? 256 : 128;
+		const int bn = (g.N > 128 && g.kind != 3) ? 256 : 128; // the split-fp32 kernel holds each stage twice: narrow tiles only
 		const uint32_t box_k = 128 / elem;
 
 		const bool a_bcast = (g.batch > 1 && g.stride_a == 0);
@@ -593,6 +666,8 @@ namespace mb200
 		p.status = c->dev_status;
 		c->kernels_with_waits = true;
 
+		if (g.kind == 3)
+			return launch<3, 128>(ctx, stream, map_a, map_b, p, c->sm_count);
 		if (g.kind == 2)
 			return (bn == 256) ? launch<2, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<2, 128>(ctx, stream, map_a, map_b, p,
 							c->sm_count);

@@ -185,10 +185,10 @@ namespace mb200
 		{
 			return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
 		}
-		template<int KIND> // 0: kind::f16, 1: kind::i8, 2: kind::tf32
+		template<int KIND> // 0: kind::f16, 1: kind::i8, 2 and above: kind::tf32
 		__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 		{
-			if (KIND == 2)
+			if (KIND >= 2)
 				asm volatile(
 						"{\n\t"
 						".reg .pred p;\n\t"

@@ -171,7 +171,7 @@ def test_fp32_nt_on_tensor_cores_when_tf32_is_enabled(ctx, oracle, shape):
         err = max_rel_err(host(d), want)
         assert err <= (TF32_REL if tf32 else 1e-5)
     ctx.enable_tf32(False)
-    assert launches[1] == 1  # one fused tensor-core kernel
+    assert launches == [1, 1]  # one fused tensor-core kernel either way (split operands when TF32 is not allowed)
 
 
 def test_fp32_winograd_layer_with_tf32(ctx, oracle):
@@ -213,3 +213,26 @@ def test_fp32_register_tiled_engine(ctx, oracle, ops, shape):
     B.gemm(ctx, ops[0], dev(a[0]), ops[1], dev(b[0]), c1)
     ctx.synchronize()
     assert np.max(np.abs(host(c1) - oracle.gemm(ops[0], a[0], ops[1], b[0]))) <= 1e-4 * max(1.0, float(np.max(np.abs(host(c1)))))
+
+
+@pytest.mark.parametrize("shape", [(1000, 256, 256), (130, 384, 36), (64, 72, 1024)])
+def test_fp32_nt_split_operands_keep_fp32_accuracy(ctx, shape):
+    """fp32 'n','t' products without TF32 permission run on the tensor cores as hi*hi + hi*lo + lo*hi of operands split into
+    two TF32 terms. Checked against a float64 product, relative to sum |a||b|: the error has to stay at the level the other
+    fp32 tests allow (1e-5), two orders of magnitude below plain TF32."""
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(k)
+    a = (r.standard_normal((m, k)) * np.exp(r.uniform(-6, 6, (m, k)))).astype(np.float32)  # wide dynamic range
+    b = (r.standard_normal((n, k)) * np.exp(r.uniform(-6, 6, (n, k)))).astype(np.float32)
+    d = torch.full((m, n), float("nan"), device="cuda")
+    before = B.launch_count()
+    B.gemm(ctx, "n", dev(a), "t", dev(b), d)
+    ctx.synchronize()
+    assert B.launch_count() - before == 1
+    exact = a.astype(np.float64) @ b.astype(np.float64).T
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64).T
+    err = float(np.max(np.abs(host(d) - exact) / scale))
+    # measured 1.2e-6 (k = 36), 3.6e-6 (k = 256), 5.9e-6 (k = 1024): a few 2^-22 per product (dropped lo*lo, lo truncated to
+    # TF32) plus the tensor core's truncating fp32 accumulation, which grows slowly with k; plain TF32 gives about 1e-3 here
+    assert err <= 1e-5, err
