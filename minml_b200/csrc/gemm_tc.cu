@@ -89,17 +89,23 @@ namespace mb200
 		 * KIND 3 multiplies fp32 operands at (nearly) fp32 accuracy on the TF32 tensor cores: every element x is split in shared
 		 * memory into hi = x rounded to a TF32 number (low 13 mantissa bits clear) and lo = x - hi (exact in fp32), and
 		 * the product is accumulated as hi*hi + hi*lo + lo*hi in fp32. The dropped lo*lo term and the truncation of lo to TF32
-		 * are both of relative size 2^-21, a little above the 2^-24 of an fp32 multiply and far below TF32's 2^-11. Each stage
-		 * holds the operands twice (the landed tile, overwritten with hi, and the lo tile), so there are fewer stages.
+		 * are both of relative size 2^-21, a little above the 2^-24 of an fp32 multiply and far below TF32's 2^-11. The landed
+		 * tile is overwritten with hi; lo goes to a ring of its own, two deep, which only has to live from the split to the end
+		 * of that slice's products, so most of shared memory stays with the copies in flight (the kernel streams fp32 operands
+		 * and is short of bytes in flight before it is short of anything else). It has no use for the epilogue staging.
 		 */
 		template<int KIND, int BN>
 		struct Tiling
 		{
 				static constexpr bool split = (KIND == 3);
 				static constexpr int operand_bytes = BM * BK_BYTES + BN * BK_BYTES;
-				static constexpr int stage_bytes = operand_bytes * (split ? 2 : 1);
-				static constexpr int stages = split ? 3 : ((BN == 256) ? 4 : 6);
-				static constexpr int smem_bytes = stages * stage_bytes + EPI_WARPS * epi::WARP_BYTES + 1024;
+				static constexpr int stage_bytes = operand_bytes;
+				static constexpr int stages = split ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
+				static constexpr int lo_stages = split ? ((BN == 256) ? 1 : 2) : 0;
+				static constexpr int lo_ring = (lo_stages > 0) ? lo_stages : 1; // divisor that is never zero
+				static constexpr int lo_offset = stages * stage_bytes;
+				static constexpr int staging_offset = lo_offset + lo_stages * operand_bytes;
+				static constexpr int smem_bytes = staging_offset + (split ? 0 : EPI_WARPS * epi::WARP_BYTES) + 1024;
 				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
 		};
 
@@ -108,6 +114,7 @@ namespace mb200
 				uint64_t full[6];
 				uint64_t empty[6];
 				uint64_t split[6]; // KIND 3: the stage's hi and lo tiles are written
+				uint64_t lo_empty[2]; // KIND 3: the products that read this lo tile are done
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
@@ -156,6 +163,7 @@ namespace mb200
 				}
 				for (int a = 0; a < 2; a++)
 				{
+					mbar_init(smem_u32(&bars.lo_empty[a]), 1);
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
 					mbar_init(smem_u32(&bars.tmem_empty[a]), EPI_WARPS);
 				}
@@ -244,14 +252,16 @@ namespace mb200
 								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
 							if (T::split)
 							{
-								const uint64_t lo_a = make_desc_k_sw128(addr_a + T::operand_bytes);
-								const uint64_t lo_b = make_desc_k_sw128(addr_b + T::operand_bytes);
+								const uint32_t lo = smem_base + T::lo_offset + (it % T::lo_ring) * T::operand_bytes;
+								const uint64_t lo_a = make_desc_k_sw128(lo);
+								const uint64_t lo_b = make_desc_k_sw128(lo + BM * BK_BYTES);
 #pragma unroll
 								for (int k = 0; k < 4; k++)
 									mma_ss<KIND>(tmem_d, desc_a + 2 * k, lo_b + 2 * k, idesc, 1u);
 #pragma unroll
 								for (int k = 0; k < 4; k++)
 									mma_ss<KIND>(tmem_d, lo_a + 2 * k, desc_b + 2 * k, idesc, 1u);
+								mma_commit(smem_u32(&bars.lo_empty[it % T::lo_ring]));
 							}
 							mma_commit(smem_u32(&bars.empty[s]));
 						}
@@ -270,25 +280,36 @@ namespace mb200
 					for (int kb = 0; kb < k_blocks; kb++, it++)
 					{
 						const int s = it % T::stages;
-						if (!mbar_wait(smem_u32(&bars.full[s]), (it / T::stages) & 1u, abort_flag))
+						if (!mbar_wait(smem_u32(&bars.lo_empty[it % T::lo_ring]), ((it / T::lo_ring) & 1u) ^ 1u, abort_flag)
+								|| !mbar_wait(smem_u32(&bars.full[s]), (it / T::stages) & 1u, abort_flag))
 						{
 							ok = false;
 							break;
 						}
 						// the split is elementwise, so it keeps whatever swizzled layout the copy engine wrote
 						const uint32_t hi = smem_base + s * T::stage_bytes;
-						const uint32_t lo = hi + T::operand_bytes;
-#pragma unroll 4
-						for (int i = t; i < T::operand_bytes / 16; i += SPLIT_WARPS * 32)
+						const uint32_t lo = smem_base + T::lo_offset + (it % T::lo_ring) * T::operand_bytes;
+						constexpr int PER_THREAD = T::operand_bytes / 16 / (SPLIT_WARPS * 32);
+						constexpr int GROUP = 8; // loads issued back to back before the first is used
+						static_assert(PER_THREAD % GROUP == 0, "the split loop assumes whole groups");
+#pragma unroll 1
+						for (int g = 0; g < PER_THREAD; g += GROUP)
 						{
-							const uint4 x = ld_shared_v4(hi + i * 16);
-							uint4 h, l;
-							split_tf32(x.x, h.x, l.x);
-							split_tf32(x.y, h.y, l.y);
-							split_tf32(x.z, h.z, l.z);
-							split_tf32(x.w, h.w, l.w);
-							st_shared_v4(hi + i * 16, h);
-							st_shared_v4(lo + i * 16, l);
+							uint4 x[GROUP];
+#pragma unroll
+							for (int u = 0; u < GROUP; u++)
+								x[u] = ld_shared_v4(hi + (t + (g + u) * SPLIT_WARPS * 32) * 16);
+#pragma unroll
+							for (int u = 0; u < GROUP; u++)
+							{
+								uint4 h, l;
+								split_tf32(x[u].x, h.x, l.x);
+								split_tf32(x[u].y, h.y, l.y);
+								split_tf32(x[u].z, h.z, l.z);
+								split_tf32(x[u].w, h.w, l.w);
+								st_shared_v4(hi + (t + (g + u) * SPLIT_WARPS * 32) * 16, h);
+								st_shared_v4(lo + (t + (g + u) * SPLIT_WARPS * 32) * 16, l);
+							}
 						}
 						fence_proxy_async_smem(); // plain stores -> visible to the tensor core's reads
 						__syncwarp();
@@ -300,7 +321,7 @@ namespace mb200
 			{ /* ------------------------------------------------------------ epilogue */
 				const int q = warp % 4; // tensor-memory lane quarter this warp may read
 				const int col_part = (warp - 2) / 4; // which half of the tile's columns
-				const uint32_t sbuf = smem_base + T::stages * T::stage_bytes + (warp - 2) * epi::WARP_BYTES;
+				const uint32_t sbuf = smem_base + T::staging_offset + (warp - 2) * epi::WARP_BYTES; // fp16 fast path only
 				const int rr = lane / 4, seg = lane % 4; // cooperative access: 8 rows x 4 segments of 16 bytes per instruction
 				const bool use_c = p.beta != 0.0f && p.C != nullptr;
 				// fp16 rows can be moved in 16-byte pieces when every row (of every batch item) starts on a 16-byte boundary
@@ -613,7 +634,9 @@ namespace mb200
 		const int elem = (g.kind == 0) ? 2 : (g.kind == 1 ? 1 : 4);
 		const CUtensorMapDataType dt = (g.kind == 0) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
 				: (g.kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
-		const int bn = (g.N > 128 && g.kind != 3) ? 256 : 128; // the split-fp32 kernel holds each stage twice: narrow tiles only
+		// the split-fp32 kernel is bound by shared-memory bandwidth either way; 256-wide tiles (three landing stages, one lo
+		// buffer) measured no faster than 128-wide ones (five and two)
+		const int bn = (g.N > 128 && g.kind != 3) ? 256 : 128;
 		const uint32_t box_k = 128 / elem;
 
 		const bool a_bcast = (g.batch > 1 && g.stride_a == 0);
