@@ -136,8 +136,20 @@ def main():
             rows * (k_in + n_out * (2 if ext is not None else 1)) * 2 + n_out * k_in * 2, 2.0 * rows * n_out * k_in)
         del a_in, w_in, out, ext
 
+    # ---- fp32 operands: three TF32 products of split operands by default, one TF32 product once the host allows TF32
+    rows32 = rows // 2
+    a32, w32 = torch.randn((rows32, c), device="cuda"), torch.randn((c, c), device="cuda")
+    d32 = torch.empty((rows32, c), device="cuda")
+    add("gemm fp32 [rows/2,c] x [c,c]^T split operands", lambda: B.gemm(ctx, "n", a32, "t", w32, d32), 2 * rows32 * c * 4 + c * c * 4,
+        2.0 * rows32 * c * c, note="tensor_frac is against the bf16 peak; TF32 runs at half of it and this path needs 3 products")
+    ctx.enable_tf32(True)
+    add("gemm fp32 [rows/2,c] x [c,c]^T as TF32", lambda: B.gemm(ctx, "n", a32, "t", w32, d32), 2 * rows32 * c * 4 + c * c * 4,
+        2.0 * rows32 * c * c, note="tensor_frac is against the bf16 peak; TF32 runs at half of it")
+    ctx.enable_tf32(False)
+    del a32, d32
+
     # ---- elementwise / layout
-    packed = torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
+    packed =torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
     x0 = torch.empty((b, h, w, planes), device="cuda", dtype=f16)
     add("unpack_input (32 planes)", lambda: B.unpackInput(ctx, packed, x0), rows * 4 + rows * planes * 2)
     add("add_bias_act (relu)", lambda: B.addBiasAct(ctx, x, bias, y, "relu"), 2 * act_bytes)
