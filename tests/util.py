@@ -89,3 +89,34 @@ def oracle_hybrid(oracle, w, x, heads):
     a2 = conv1x1(att, "proj_w", "proj_b", a)
     n2 = oracle.layernorm(a2, w["ln2_g"], w["ln2_b"])
     return conv1x1(conv1x1(n2, "ffn1_w", "ffn1_b", None, "relu"), "ffn2_w", "ffn2_b", a2)
+
+
+def forward_loaded_network_on_cpu(oracle, description, blob, x):
+    """Runs a network file (minml_b200.checkpoint's description + blob) through the CPU oracle, node by node; returns the
+    output nodes' values. Only the layer kinds of the convolution path."""
+    from minml_b200 import checkpoint as C
+    values = []
+    nodes = C.nodes_of(description)
+    for node in nodes:
+        layer, ins = node["layer"], node["input_nodes"]
+        kind, act = layer["name"], layer["nonlinearity"]
+        w, b = C.read_tensor(layer.get("weights"), blob), C.read_tensor(layer.get("bias"), blob)
+        if kind == "Input":
+            y = x
+        elif kind == "Conv2D":
+            y = oracle.conv2d(values[ins[0]], w, b if b is not None else np.zeros(w.shape[0], np.float32), None, act)
+        elif kind == "BatchNormalization":
+            y = oracle.batchnorm_inference(values[ins[0]], w, b, C.read_tensor(layer["avg_var"], blob), act)
+        elif kind == "Add":
+            y = oracle.add_bias_act(values[ins[0]] + values[ins[1]], np.zeros(values[ins[0]].shape[-1], np.float32), act)
+        elif kind == "GlobalAveragePooling":
+            y = oracle.global_average_pooling(values[ins[0]])
+        elif kind == "Dense":
+            rows = values[ins[0]].reshape(values[ins[0]].shape[0], -1)
+            y = oracle.add_bias_act(oracle.gemm("n", rows, "t", w), b if b is not None else np.zeros(w.shape[0], np.float32), act)
+        elif kind == "Softmax":
+            y = oracle.softmax(values[ins[0]].reshape(values[ins[0]].shape[0], -1))
+        else:
+            raise NotImplementedError(kind)
+        values.append(np.asarray(y, np.float32))
+    return [values[i] for i, n in enumerate(nodes) if n["is_output_node"]]
