@@ -10,8 +10,8 @@
  * Status tags:
  *   [hot]    implemented with hand-written sm_100a kernels (the convolution / matrix-multiply inference path)
  *   [next]   implemented: the layers adjacent to that path in minml's current architectures (batch-norm inference and
- *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling, and the backward-pass Winograd
- *            transforms with the fused activation / bias-gradient step)
+ *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling, RMS normalisation, space-to-depth
+ *            and depth-to-space, and the backward-pass Winograd transforms with the fused activation / bias-gradient step)
  *   [infra]  thin native wrapper over the CUDA runtime
  *   [stub]   exported so that minml links; records the sticky error "not implemented" on the context and
  *            launches nothing (training, MoE, pooling variants, ...)
@@ -89,8 +89,8 @@ void cuda_memcpy_to_host(mlContext_t context, void *dst, const void *src, size_t
 void cuda_unpack_input(mlContext_t context, mlShape_t shape, mlDataType_t dst_dtype, void *dst, const void *src); /* [hot] [86] */
 void cuda_convert_type(mlContext_t context, void *dst, mlDataType_t dst_dtype, const void *src, mlDataType_t src_dtype, int elements); /* [hot] [87] */
 void cuda_transpose_021(mlContext_t context, mlDataType_t dtype, mlShape_t shape, const void *input, void *output); /* [hot] [89] */
-void cuda_space_to_depth(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output); /* [stub] [90] */
-void cuda_depth_to_space(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output); /* [stub] [92] */
+void cuda_space_to_depth(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output); /* [next] [90] */
+void cuda_depth_to_space(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output); /* [next] [92] */
 
 /* ---- Winograd transforms
  *      replaces src/backend/cuda/kernels/winograd_nonfused.cu:417-520 ---- */
@@ -153,7 +153,7 @@ void cuda_fold_batchnorm(mlContext_t context, mlTensor_t layer_weights, mlTensor
  *      replaces src/backend/cuda/kernels/layernorm.cu:480-527, src/backend/cuda/kernels/rmsnorm.cu ---- */
 void cuda_layernorm_forward(mlContext_t context, mlShape_t shape, mlDataType_t dtype, const void *input, void *output, const void *weights, const void *bias, const void *ext); /* [hot] [191] */
 void cuda_layernorm_backward(mlContext_t context, mlShape_t shape, const void *input, void *gradient_prev, void *gradient_next, const void *weights, void *weights_update, void *bias_update); /* [stub] [193] */
-void cuda_rmsnorm_forward(mlContext_t context, mlShape_t shape, mlDataType_t dtype, const void *input, void *output, const void *weights); /* [stub] [199] */
+void cuda_rmsnorm_forward(mlContext_t context, mlShape_t shape, mlDataType_t dtype, const void *input, void *output, const void *weights); /* [next] [199] */
 void cuda_rmsnorm_backward(mlContext_t context, mlShape_t shape, const void *input, void *gradient_prev, void *gradient_next, const void *weights, void *weights_update); /* [stub] [201] */
 
 /* ---- Multi-head attention

@@ -231,6 +231,24 @@ def layernormForward(ctx, x, y, weights, bias, ext=None):
     ctx.check()
 
 
+def rmsnormForward(ctx, x, y, weights=None):
+    """ml::rmsnormForward (src/core/math.cpp): y = weights * x / (1e-6 + rms(x)) over the last axis; weights may be None."""
+    lib.cuda_rmsnorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x), ptr(y), ptr(weights))
+    ctx.check()
+
+
+def spaceToDepth(ctx, x, y):
+    """ml::spaceToDepth: [b, h, w, c] -> [b, ceil(h/p), ceil(w/q), p*q*c]; the patch size follows from the two shapes."""
+    lib.cuda_space_to_depth(ctx.handle, dtype_of(x), shape_of(x), ptr(x), shape_of(y), ptr(y))
+    ctx.check()
+
+
+def depthToSpace(ctx, x, y):
+    """ml::depthToSpace: the inverse of spaceToDepth."""
+    lib.cuda_depth_to_space(ctx.handle, dtype_of(x), shape_of(x), ptr(x), shape_of(y), ptr(y))
+    ctx.check()
+
+
 def multiHeadAttentionGetWorkspaceSize(x_shape, weights_shape, num_heads, training=False):
     return lib.cuda_multi_head_attention_get_workspace_size(shape_of(x_shape), shape_of(weights_shape), num_heads, training)
 

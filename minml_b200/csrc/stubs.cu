@@ -14,14 +14,6 @@ using namespace mb200;
 
 extern "C"
 {
-	void cuda_space_to_depth(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output) /* [90] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_space_to_depth");
-	}
-	void cuda_depth_to_space(mlContext_t context, mlDataType_t dtype, mlShape_t input_shape, const void *input, mlShape_t output_shape, void *output) /* [92] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_depth_to_space");
-	}
 	void cuda_depthwise_conv_backward(mlContext_t context, float alpha, const mlTensor_t dy, const mlTensor_t w, float beta, mlTensor_t dx) /* [113] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_depthwise_conv_backward");
@@ -89,10 +81,6 @@ extern "C"
 	void cuda_layernorm_backward(mlContext_t context, mlShape_t shape, const void *input, void *gradient_prev, void *gradient_next, const void *weights, void *weights_update, void *bias_update) /* [193] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_layernorm_backward");
-	}
-	void cuda_rmsnorm_forward(mlContext_t context, mlShape_t shape, mlDataType_t dtype, const void *input, void *output, const void *weights) /* [199] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_rmsnorm_forward");
 	}
 	void cuda_rmsnorm_backward(mlContext_t context, mlShape_t shape, const void *input, void *gradient_prev, void *gradient_next, const void *weights, void *weights_update) /* [201] */
 	{

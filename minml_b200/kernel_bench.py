@@ -200,6 +200,11 @@ def main():
     dscale, dbias = torch.full((c,), 1e-4, device="cuda"), torch.zeros(c, device="cuda")
     add("quantized_depthwise_conv_forward 7x7 int8", lambda: B.quantized_depthwise_conv_forward(ctx, xq, wdq, dscale, dbias, yq, (0.05, 0.0), 0),
         2 * rows * c + 49 * c)
+    add("rmsnorm_forward", lambda: B.rmsnormForward(ctx, x, y, gamma), 2 * act_bytes)
+    deep = torch.empty((b, (h + 1) // 2, (w + 1) // 2, 4 * c), device="cuda", dtype=f16)
+    add("space_to_depth 2x2", lambda: B.spaceToDepth(ctx, x, deep), act_bytes + deep.numel() * 2)
+    add("depth_to_space 2x2", lambda: B.depthToSpace(ctx, deep, y), act_bytes + deep.numel() * 2)
+    del deep
     gate = rand(b, c)
     add("channel_scaling_forward", lambda: B.channelScalingForward(ctx, x, gate, y), 2 * act_bytes + b * c * 2)
     ctx.close()

@@ -745,3 +745,76 @@ void oracle_act_bias_copy_backward(float *dy, const float *y, float *dx, float *
 			db[c] += (float) sum;
 	}
 }
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Layers between the convolution blocks: RMS normalisation and the space <-> depth rearrangements.
+ * --------------------------------------------------------------------------------------------------------------- */
+/* y[r, c] = gamma[c] * x[r, c] / (1e-6 + sqrt(mean_c x^2))  (src/backend/cpu/normalization.cpp:452-486; gamma may be NULL) */
+void oracle_rmsnorm(const float *x, float *y, const float *gamma, size_t rows, int channels)
+{
+	for (size_t r = 0; r < rows; r++)
+	{
+		float sum = 0.0f;
+		for (int c = 0; c < channels; c++)
+			sum += x[r * channels + c] * x[r * channels + c];
+		const float inv_rms = 1.0f / (1.0e-6f + sqrtf(sum / (float) channels));
+		for (int c = 0; c < channels; c++)
+			y[r * channels + c] = (gamma ? gamma[c] : 1.0f) * x[r * channels + c] * inv_rms;
+	}
+}
+/* The smallest p with ceil(larger / p) == smaller, 0 if none (src/backend/cpu/dispatcher.cpp:125-137). */
+static int patch_size(int smaller, int larger)
+{
+	for (int p = 1; smaller > 0 && larger >= smaller; p++)
+	{
+		const int tmp = (larger + p - 1) / p;
+		if (tmp == smaller)
+			return p;
+		if (tmp < smaller)
+			break;
+	}
+	return 0;
+}
+/* [b, h, w, c] -> [b, oh, ow, p*q*c] with zero fill past the edge; element size in bytes so that any dtype can be checked
+ * (src/backend/cpu/dispatcher.cpp:190-219). Returns 0 when the shapes do not fit. */
+int oracle_space_to_depth(const uint8_t *x, uint8_t *y, int elem, int batch, int h, int w, int c, int oh, int ow)
+{
+	const int p = patch_size(oh, h), q = patch_size(ow, w);
+	if (p == 0 || q == 0)
+		return 0;
+	const size_t block = (size_t) elem * c;
+	for (int b = 0; b < batch; b++)
+		for (int i = 0; i < oh; i++)
+			for (int j = 0; j < ow; j++)
+				for (int dx = 0; dx < p; dx++)
+					for (int dy = 0; dy < q; dy++)
+					{
+						const int hh = i * p + dx, ww = j * q + dy;
+						if (hh < h && ww < w)
+							memcpy(y, x + (((size_t) b * h + hh) * w + ww) * block, block);
+						else
+							memset(y, 0, block);
+						y += block;
+					}
+	return 1;
+}
+/* The inverse: [b, ih, iw, p*q*c] -> [b, h, w, c]  (src/backend/cpu/dispatcher.cpp:220-247). */
+int oracle_depth_to_space(const uint8_t *x, uint8_t *y, int elem, int batch, int ih, int iw, int h, int w, int c)
+{
+	const int p = patch_size(ih, h), q = patch_size(iw, w);
+	if (p == 0 || q == 0)
+		return 0;
+	const size_t block = (size_t) elem * c;
+	for (int b = 0; b < batch; b++)
+		for (int i = 0; i < ih; i++)
+			for (int j = 0; j < iw; j++)
+				for (int dx = 0; dx < p; dx++)
+					for (int dy = 0; dy < q; dy++)
+					{
+						const int hh = i * p + dx, ww = j * q + dy;
+						if (hh < h && ww < w)
+							memcpy(y + (((size_t) b * h + hh) * w + ww) * block, x, block);
+						x += block;
+					}
+	return 1;
+}

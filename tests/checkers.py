@@ -208,6 +208,39 @@ class Oracle:
         self.lib.oracle_channel_scaling(_fp(x), _fp(_f32(scales)), _fp(out), ctypes.c_float(alpha), ctypes.c_float(beta), b, x.size // (b * c), c)
         return out
 
+    def rmsnorm(self, x, gamma=None):
+        x = _f32(x)
+        y = np.empty_like(x)
+        c = x.shape[-1]
+        self.lib.oracle_rmsnorm(_fp(x), _fp(y), _fp(_f32(gamma)), ctypes.c_size_t(x.size // c), c)
+        return y
+
+    def space_to_depth(self, x, out_hw):
+        """x [b, h, w, c] of any dtype -> [b, oh, ow, p*q*c]; raises when the shapes do not fit."""
+        x = np.ascontiguousarray(x)
+        b, h, w, c = x.shape
+        oh, ow = out_hw
+        p, q = -(-h // oh), -(-w // ow)
+        y = np.empty((b, oh, ow, p * q * c), x.dtype)
+        self.lib.oracle_space_to_depth.restype = ctypes.c_int
+        ok = self.lib.oracle_space_to_depth(ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(y.ctypes.data), x.dtype.itemsize, b, h, w, c, oh, ow)
+        if not ok or y.shape[3] != p * q * c:
+            raise ValueError("shapes do not fit")
+        return y
+
+    def depth_to_space(self, x, out_hw, fill=0):
+        """x [b, ih, iw, p*q*c] -> [b, h, w, c]."""
+        x = np.ascontiguousarray(x)
+        b, ih, iw, deep = x.shape
+        h, w = out_hw
+        p, q = -(-h // ih), -(-w // iw)
+        y = np.full((b, h, w, deep // (p * q)), fill, x.dtype)
+        self.lib.oracle_depth_to_space.restype = ctypes.c_int
+        if not self.lib.oracle_depth_to_space(ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(y.ctypes.data), x.dtype.itemsize, b, ih, iw, h, w,
+                                              y.shape[3]):
+            raise ValueError("shapes do not fit")
+        return y
+
     def global_average_pooling(self, x, alpha=1.0, beta=0.0, y=None):
         x = _f32(x)
         b, h, w, c = x.shape
@@ -316,6 +349,9 @@ class ReferenceCpu:
             "cpu_fold_batchnorm": [V, T, T, T, T, T],
             "cpu_depthwise_conv_forward": [V, F, T, T, T, F, T],
             "cpu_channel_scaling_forward": [V, F, T, T, F, T],
+            "cpu_rmsnorm_forward": [V, S, I, V, V, V],
+            "cpu_space_to_depth": [V, I, S, V, S, V],
+            "cpu_depth_to_space": [V, I, S, V, S, V],
         }
         for name, argtypes in sigs.items():
             fn = getattr(lib, name)
@@ -425,6 +461,24 @@ class ReferenceCpu:
         x = _f32(x)
         y = np.zeros((x.shape[0], x.shape[3]), np.float32)
         self.lib.cpu_global_average_pooling_forward(self.ctx, 1.0, _tensor(x), 0.0, _tensor(y))
+        return y
+
+    def rmsnorm(self, x, gamma=None):
+        x = _f32(x)
+        y = np.zeros_like(x)
+        self.lib.cpu_rmsnorm_forward(self.ctx, _shape(x.shape), DTYPE_FLOAT32, _vp(x), _vp(y), _vp(_f32(gamma)))
+        return y
+
+    def space_to_depth(self, x, out_shape):
+        x = _f32(x)
+        y = np.full(out_shape, np.nan, np.float32)
+        self.lib.cpu_space_to_depth(self.ctx, DTYPE_FLOAT32, _shape(x.shape), _vp(x), _shape(out_shape), _vp(y))
+        return y
+
+    def depth_to_space(self, x, out_shape):
+        x = _f32(x)
+        y = np.zeros(out_shape, np.float32)
+        self.lib.cpu_depth_to_space(self.ctx, DTYPE_FLOAT32, _shape(x.shape), _vp(x), _shape(out_shape), _vp(y))
         return y
 
     def layernorm(self, x, gamma, beta, ext=None):

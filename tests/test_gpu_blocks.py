@@ -135,3 +135,31 @@ def test_squeeze_and_excitation_block(ctx, oracle):
     hid_ref = oracle.add_bias_act(oracle.gemm("n", p_ref, "t", w1), b1, "relu")
     gate_ref = oracle.add_bias_act(oracle.gemm("n", hid_ref, "t", w2), b2, "sigmoid")
     assert max_rel_err(host(y), oracle.channel_scaling(t_ref, gate_ref)) <= FP16_REL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_fused_conv_block_call_sequence(ctx, oracle, dtype):
+    """FusedConvBlock::forward on a CUDA device (src/layers/FusedConvBlock.cpp:192-213): depthwise 7x7 convolution with bias,
+    1x1 convolution + ReLU into the workspace, 1x1 convolution back with the block's input as the residual -- three ABI
+    calls, the last two each one fused tensor-core kernel."""
+    from minml_b200 import backend as B
+    r = np.random.default_rng(11)
+    b, h, w, c = 4, 15, 15, 128
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if dtype == torch.float16 else (lambda a: a.astype(np.float32))
+    x = rnd(r.standard_normal((b, h, w, c)))
+    wd, bd = rnd(r.standard_normal((7, 7, c)) * 0.1), rnd(r.standard_normal(c) * 0.1)
+    w1, b1 = rnd(r.standard_normal((c, c)) * 0.1), rnd(r.standard_normal(c) * 0.1)
+    w2, b2 = rnd(r.standard_normal((c, c)) * 0.1), rnd(r.standard_normal(c) * 0.1)
+    xd = dev(x, dtype)
+    out = torch.empty((b, h, w, c), device="cuda", dtype=dtype)
+    tmp = torch.empty((b * h * w, c), device="cuda", dtype=dtype)
+    B.depthwiseConvForward(ctx, xd, dev(wd, dtype), out, dev(bd, dtype))
+    before = B.launch_count()
+    B.gemm_ex(ctx, tmp, 1.0, "n", out.view(b * h * w, c), "t", dev(w1, dtype), 0.0, tmp, dev(b1, dtype), "relu")
+    B.gemm_ex(ctx, out.view(b * h * w, c), 1.0, "n", tmp, "t", dev(w2, dtype), 1.0, xd.view(b * h * w, c), dev(b2, dtype), "linear")
+    ctx.synchronize()
+    assert B.launch_count() - before == 2
+    t = oracle.depthwise_conv(x, wd, bd).reshape(b * h * w, c)
+    t = oracle.add_bias_act(oracle.gemm("n", t, "t", w1), b1, "relu")
+    want = oracle.add_bias_act(oracle.gemm("n", t, "t", w2) + x.reshape(b * h * w, c), b2, "linear").reshape(b, h, w, c)
+    assert _tol(dtype, host(out), want)

@@ -279,3 +279,34 @@ def test_gradient_and_update_transforms_against_reference_cpu(oracle, refcpu):
             for j in range(k):
                 want[:, i, j, :] = np.einsum("bhwo,bhwc->oc", dy, xp[:, i:i + 8, j:j + 8, :])
         assert np.max(np.abs(dw - want)) <= 1e-3 * np.max(np.abs(want))
+
+
+def test_rmsnorm_and_space_depth_rearrangements_against_reference_cpu(oracle, refcpu):
+    """The restatements against minml's own CPU functions (cpu_rmsnorm_forward, cpu_space_to_depth, cpu_depth_to_space), on the
+    shapes of the reference's tests (test_normalization.cpp:977-1013: 123 x 43; test_convert.cpp:282-360: ragged patches)."""
+    x = init_for_test((123, 43))
+    gamma = init_for_test((43,)) + 1.1
+    assert np.abs(oracle.rmsnorm(x, gamma) - refcpu.rmsnorm(x, gamma)).max() <= 1e-6
+    assert np.abs(oracle.rmsnorm(x) - refcpu.rmsnorm(x)).max() <= 1e-6
+    direct = gamma * x / (1e-6 + np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True)))
+    assert np.abs(oracle.rmsnorm(x, gamma) - direct).max() <= 1e-6
+    for (b, h, w, c), (oh, ow) in (((3, 8, 8, 5), (4, 4)), ((2, 15, 15, 4), (8, 8)), ((2, 13, 14, 3), (5, 7)), ((1, 6, 9, 2), (6, 3))):
+        x = init_for_test((b, h, w, c))
+        p, q = -(-h // oh), -(-w // ow)
+        deep = oracle.space_to_depth(x, (oh, ow))
+        assert deep.shape == (b, oh, ow, p * q * c)
+        assert np.array_equal(deep, refcpu.space_to_depth(x, deep.shape))
+        back = oracle.depth_to_space(deep, (h, w))
+        assert np.array_equal(back, x)  # the round trip loses nothing: only the zero fill past the edge is dropped
+        assert np.array_equal(back, refcpu.depth_to_space(deep, x.shape))
+    with pytest.raises(ValueError):
+        oracle.space_to_depth(init_for_test((1, 10, 10, 2)), (4, 6))  # ceil(10/3) = 4 but ceil(10/2) = 5, ceil(10/1) = 10: no patch gives 6
+
+
+def test_space_to_depth_moves_bytes_for_any_element_size(oracle):
+    x = np.arange(2 * 5 * 7 * 3, dtype=np.int8).reshape(2, 5, 7, 3)
+    deep = oracle.space_to_depth(x, (3, 4))
+    assert deep.dtype == np.int8 and deep.shape == (2, 3, 4, 2 * 2 * 3)
+    assert np.array_equal(deep[1, 0, 0, :3], x[1, 0, 0]) and np.array_equal(deep[1, 0, 0, 3:6], x[1, 0, 1])
+    assert np.array_equal(deep[1, 0, 0, 6:9], x[1, 1, 0]) and np.array_equal(deep[0, 2, 3, 3:], np.zeros(9, np.int8))  # past both edges
+    assert np.array_equal(oracle.depth_to_space(deep, (5, 7)), x)
