@@ -70,50 +70,99 @@ namespace mb200
 			return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, static_cast<long long>(sm_count) * 16)));
 		}
 
-		/* y = act(x + bias[c]) * alpha + beta * y  over [rows, channels] */
-		template<typename T, bool VECTOR>
+		/* y = act(x + bias[c]) * alpha + beta * y  over [rows, channels].
+		 * These kernels are bound by instruction issue before they are bound by memory when written naively (a 64-bit modulo
+		 * and a switch over the activation per element cost more than the 16-byte load they accompany), so: ACT is a compile-time
+		 * class (0 linear, 1 ReLU, 2 decided at run time), PLAIN drops alpha and beta, and the channel offset of a thread's next
+		 * packet is advanced by a precomputed step instead of being recomputed with a division. */
+		template<typename T, bool VECTOR, int ACT, bool PLAIN>
 		__global__ void __launch_bounds__(256) kernel_bias_act(T *__restrict__ y, const T *__restrict__ x, const T *__restrict__ bias, long long rows,
 				int channels, float alpha, float beta, int act)
 		{
 			constexpr int N = VECTOR ? Vec16<T>::N : 1;
 			const long long total = rows * channels / N;
 			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+			const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+			const int groups = channels / N; // packets per row
+			int g = static_cast<int>(first % groups);
+			const int g_step = static_cast<int>(stride % groups);
+			for (long long i = first; i < total; i += stride)
 			{
 				const long long e = i * N;
-				const int c = static_cast<int>(e % channels);
-				float v[N], b[N];
+				float v[N];
 				if constexpr (VECTOR)
-				{
 					Vec16<T>::load(x + e, reinterpret_cast<float (&)[Vec16<T>::N]>(v));
-					if (bias != nullptr)
-						Vec16<T>::load(bias + c, reinterpret_cast<float (&)[Vec16<T>::N]>(b));
-				}
 				else
-				{
 					v[0] = to_float(x[e]);
-					if (bias != nullptr)
-						b[0] = to_float(bias[c]);
+				if (bias != nullptr)
+				{
+					float b[N];
+					if constexpr (VECTOR)
+						Vec16<T>::load(bias + g * N, reinterpret_cast<float (&)[Vec16<T>::N]>(b));
+					else
+						b[0] = to_float(bias[g]);
+#pragma unroll
+					for (int k = 0; k < N; k++)
+						v[k] += b[k];
 				}
 #pragma unroll
 				for (int k = 0; k < N; k++)
-					v[k] = apply_activation(bias != nullptr ? v[k] + b[k] : v[k], act) * alpha;
-				if (beta != 0.0f)
 				{
-					float o[N];
-					if constexpr (VECTOR)
-						Vec16<T>::load(y + e, reinterpret_cast<float (&)[Vec16<T>::N]>(o));
-					else
-						o[0] = to_float(y[e]);
+					if (ACT == 1)
+						v[k] = fmaxf(v[k], 0.0f);
+					else if (ACT == 2)
+						v[k] = apply_activation(v[k], act);
+				}
+				if (!PLAIN)
+				{
 #pragma unroll
 					for (int k = 0; k < N; k++)
-						v[k] += beta * o[k];
+						v[k] *= alpha;
+					if (beta != 0.0f)
+					{
+						float o[N];
+						if constexpr (VECTOR)
+							Vec16<T>::load(y + e, reinterpret_cast<float (&)[Vec16<T>::N]>(o));
+						else
+							o[0] = to_float(y[e]);
+#pragma unroll
+						for (int k = 0; k < N; k++)
+							v[k] += beta * o[k];
+					}
 				}
 				if constexpr (VECTOR)
 					Vec16<T>::store(y + e, reinterpret_cast<const float (&)[Vec16<T>::N]>(v));
 				else
 					y[e] = from_float<T>(v[0]);
+				g += g_step;
+				if (g >= groups)
+					g -= groups;
 			}
+		}
+		template<typename T, bool VECTOR>
+		void launch_bias_act_variant(cudaStream_t stream, int grid, T *y, const T *x, const T *bias, long long rows, int channels, float alpha,
+				float beta, int act)
+		{
+			const bool plain = alpha == 1.0f && beta == 0.0f;
+			const int cls = (act == ACTIVATION_LINEAR) ? 0 : (act == ACTIVATION_RELU ? 1 : 2);
+#define VARIANT(A, P) kernel_bias_act<T, VECTOR, A, P> <<<grid, 256, 0, stream>>>(y, x, bias, rows, channels, alpha, beta, act)
+			if (plain)
+			{
+				if (cls == 0)
+					VARIANT(0, true);
+				else if (cls == 1)
+					VARIANT(1, true);
+				else
+					VARIANT(2, true);
+			}
+			else
+			{
+				if (cls == 1)
+					VARIANT(1, false);
+				else
+					VARIANT(2, false); // apply_activation passes linear through
+			}
+#undef VARIANT
 		}
 		template<typename T>
 		void launch_bias_act(mlContext_t ctx, void *y, const void *x, const void *bias, long long rows, int channels, float alpha, float beta,
@@ -123,11 +172,11 @@ namespace mb200
 			const int sm = get(ctx)->sm_count;
 			const bool vec = channels % Vec16<T>::N == 0 && aligned_to(y, 16) && aligned_to(x, 16) && (bias == nullptr || aligned_to(bias, 16));
 			if (vec)
-				kernel_bias_act<T, true> <<<grid_for(rows * channels / Vec16<T>::N, 256, sm), 256, 0, stream>>>(reinterpret_cast<T*>(y),
+				launch_bias_act_variant<T, true>(stream, grid_for(rows * channels / Vec16<T>::N, 256, sm), reinterpret_cast<T*>(y),
 						reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(bias), rows, channels, alpha, beta, act);
 			else
-				kernel_bias_act<T, false> <<<grid_for(rows * channels, 256, sm), 256, 0, stream>>>(reinterpret_cast<T*>(y),
-						reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(bias), rows, channels, alpha, beta, act);
+				launch_bias_act_variant<T, false>(stream, grid_for(rows * channels, 256, sm), reinterpret_cast<T*>(y), reinterpret_cast<const T*>(x),
+						reinterpret_cast<const T*>(bias), rows, channels, alpha, beta, act);
 			MB200_COUNT_LAUNCH();
 		}
 
@@ -217,11 +266,50 @@ namespace mb200
 			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < elements; i += stride)
 				dst[i] = float_as<D>(as_float<S>(src[i])); // always through fp32, as the reference does (conversion.cu:53)
 		}
+		/* The same in groups of 8 consecutive elements per thread, two groups loaded before the first is converted. */
+		template<typename T>
+		struct alignas(sizeof(T) * 8 > 16 ? 16 : sizeof(T) * 8) Group8
+		{
+				T v[8];
+		};
+		template<typename D, typename S>
+		__global__ void __launch_bounds__(256) kernel_convert_groups(D *__restrict__ dst, const S *__restrict__ src, long long groups)
+		{
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < groups; i += 2 * stride)
+			{
+				const bool second = i + stride < groups;
+				const Group8<S> a = reinterpret_cast<const Group8<S>*>(src)[i];
+				Group8<S> b;
+				if (second)
+					b = reinterpret_cast<const Group8<S>*>(src)[i + stride];
+				Group8<D> out;
+#pragma unroll
+				for (int k = 0; k < 8; k++)
+					out.v[k] = float_as<D>(as_float<S>(a.v[k]));
+				reinterpret_cast<Group8<D>*>(dst)[i] = out;
+				if (second)
+				{
+#pragma unroll
+					for (int k = 0; k < 8; k++)
+						out.v[k] = float_as<D>(as_float<S>(b.v[k]));
+					reinterpret_cast<Group8<D>*>(dst)[i + stride] = out;
+				}
+			}
+		}
+		template<typename D, typename S>
+		void launch_convert(cudaStream_t stream, int sm, void *dst, const void *src, long long elements)
+		{
+			if (elements % 8 == 0 && aligned_to(dst, 16) && aligned_to(src, 16))
+				kernel_convert_groups<D, S> <<<grid_for(elements / 16, 256, sm), 256, 0, stream>>>(reinterpret_cast<D*>(dst),
+						reinterpret_cast<const S*>(src), elements / 8);
+			else
+				kernel_convert<D, S> <<<grid_for(elements, 256, sm), 256, 0, stream>>>(reinterpret_cast<D*>(dst), reinterpret_cast<const S*>(src), elements);
+		}
 		template<typename D>
 		bool convert_from(cudaStream_t stream, int sm, void *dst, const void *src, mlDataType_t src_dtype, long long elements)
 		{
-			const int grid = grid_for(elements, 256, sm);
-#define CASE(E, S) case E: kernel_convert<D, S> <<<grid, 256, 0, stream>>>(reinterpret_cast<D*>(dst), reinterpret_cast<const S*>(src), elements); break
+#define CASE(E, S) case E: launch_convert<D, S>(stream, sm, dst, src, elements); break
 			switch (src_dtype)
 			{
 				CASE(DTYPE_FLOAT16, __half);
@@ -331,6 +419,80 @@ namespace mb200
 				for (int j = lane; j < channels; j += 32)
 					y[r * channels + j] = from_float<T>(expf(to_float(px[j]) - m) * inv);
 			}
+		}
+		/* Rows of up to 32 * N * ITERS channels (N elements per 16-byte access, channels a multiple of N): every lane keeps its
+		 * pieces of the row in registers, so the row is read once and all of a lane's loads are in flight together. */
+		template<typename T, int ITERS>
+		__global__ void __launch_bounds__(256) kernel_softmax_rows(T *__restrict__ y, const T *__restrict__ x, long long rows, int channels)
+		{
+			constexpr int N = Vec16<T>::N;
+			const int lane = threadIdx.x % 32;
+			const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
+			for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r < rows; r += warps)
+			{
+				float v[ITERS][N];
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+				{
+					const int c = (i * 32 + lane) * N;
+					if (c < channels)
+						Vec16<T>::load(x + r * channels + c, reinterpret_cast<float (&)[Vec16<T>::N]>(v[i]));
+				}
+				float m = -3.0e38f;
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+					if ((i * 32 + lane) * N < channels)
+					{
+#pragma unroll
+						for (int k = 0; k < N; k++)
+							m = fmaxf(m, v[i][k]);
+					}
+				for (int k = 16; k >= 1; k /= 2)
+					m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, k));
+				float s = 0.0f;
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+					if ((i * 32 + lane) * N < channels)
+					{
+#pragma unroll
+						for (int k = 0; k < N; k++)
+						{
+							v[i][k] = expf(v[i][k] - m);
+							s += v[i][k];
+						}
+					}
+				for (int k = 16; k >= 1; k /= 2)
+					s += __shfl_xor_sync(0xffffffffu, s, k);
+				const float inv = 1.0f / s;
+#pragma unroll
+				for (int i = 0; i < ITERS; i++)
+				{
+					const int c = (i * 32 + lane) * N;
+					if (c < channels)
+					{
+#pragma unroll
+						for (int k = 0; k < N; k++)
+							v[i][k] *= inv;
+						Vec16<T>::store(y + r * channels + c, reinterpret_cast<const float (&)[Vec16<T>::N]>(v[i]));
+					}
+				}
+			}
+		}
+		template<typename T>
+		void launch_softmax(cudaStream_t stream, int grid, void *output, const void *input, long long rows, int channels)
+		{
+			T *yp = reinterpret_cast<T*>(output);
+			const T *xp = reinterpret_cast<const T*>(input);
+			constexpr int N = Vec16<T>::N;
+			const bool wide = channels % N == 0 && aligned_to(yp, 16) && aligned_to(xp, 16);
+			if (wide && channels <= 32 * N)
+				kernel_softmax_rows<T, 1> <<<grid, 256, 0, stream>>>(yp, xp, rows, channels);
+			else if (wide && channels <= 64 * N)
+				kernel_softmax_rows<T, 2> <<<grid, 256, 0, stream>>>(yp, xp, rows, channels);
+			else if (wide && channels <= 128 * N)
+				kernel_softmax_rows<T, 4> <<<grid, 256, 0, stream>>>(yp, xp, rows, channels);
+			else
+				kernel_softmax<T> <<<grid, 256, 0, stream>>>(yp, xp, rows, channels);
 		}
 	}
 } /* namespace mb200 */
@@ -618,12 +780,10 @@ extern "C"
 		switch (dtype)
 		{
 			case DTYPE_FLOAT16:
-				kernel_softmax<__half> <<<grid, 256, 0, stream>>>(reinterpret_cast<__half*>(output), reinterpret_cast<const __half*>(input), rows,
-						channels);
+				launch_softmax<__half>(stream, grid, output, input, rows, channels);
 				break;
 			case DTYPE_FLOAT32:
-				kernel_softmax<float> <<<grid, 256, 0, stream>>>(reinterpret_cast<float*>(output), reinterpret_cast<const float*>(input), rows,
-						channels);
+				launch_softmax<float>(stream, grid, output, input, rows, channels);
 				break;
 			default:
 				record_error(context, "cuda_softmax_forward: dtype %d not supported", static_cast<int>(dtype));

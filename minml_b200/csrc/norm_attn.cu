@@ -83,49 +83,70 @@ namespace mb200
 					b[i][k] = __half2float(reinterpret_cast<const __half*>(&br)[k]);
 				}
 			}
+			// ROWS rows per pass, so that every lane has four 16-byte loads in flight whatever the row length
+			constexpr int ROWS = (ITERS == 1) ? 4 : (ITERS == 2 ? 2 : 1);
 			const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
-			for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r < rows; r += warps)
+			for (long long r0 = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r0 < rows; r0 += warps * ROWS)
 			{
-				float v[ITERS][8];
-				float sum = 0.0f;
+				uint4 raw[ROWS][ITERS], er[ROWS][ITERS];
 #pragma unroll
-				for (int i = 0; i < ITERS; i++)
+				for (int q = 0; q < ROWS; q++)
 				{
-					const long long off = r * CHANNELS + (i * 32 + lane) * 8;
-					const uint4 raw = *reinterpret_cast<const uint4*>(input + off);
-					uint4 er = make_uint4(0, 0, 0, 0);
-					if (ext != nullptr)
-						er = *reinterpret_cast<const uint4*>(ext + off);
+					const long long r = r0 + q * warps;
 #pragma unroll
-					for (int k = 0; k < 8; k++)
+					for (int i = 0; i < ITERS; i++)
 					{
-						v[i][k] = __half2float(reinterpret_cast<const __half*>(&raw)[k]) + __half2float(reinterpret_cast<const __half*>(&er)[k]);
-						sum += v[i][k];
+						const long long off = r * CHANNELS + (i * 32 + lane) * 8;
+						raw[q][i] = make_uint4(0, 0, 0, 0);
+						er[q][i] = make_uint4(0, 0, 0, 0);
+						if (r < rows)
+						{
+							raw[q][i] = *reinterpret_cast<const uint4*>(input + off);
+							if (ext != nullptr)
+								er[q][i] = *reinterpret_cast<const uint4*>(ext + off);
+						}
 					}
 				}
-				for (int k = 16; k >= 1; k /= 2)
-					sum += __shfl_xor_sync(0xffffffffu, sum, k);
-				const float mean = sum / static_cast<float>(CHANNELS);
-				float var = 0.0f;
 #pragma unroll
-				for (int i = 0; i < ITERS; i++)
-#pragma unroll
-					for (int k = 0; k < 8; k++)
-					{
-						const float d = v[i][k] - mean;
-						var += d * d;
-					}
-				for (int k = 16; k >= 1; k /= 2)
-					var += __shfl_xor_sync(0xffffffffu, var, k);
-				const float inv_stddev = 1.0f / sqrtf(1.0e-6f + var / static_cast<float>(CHANNELS - 1));
-#pragma unroll
-				for (int i = 0; i < ITERS; i++)
+				for (int q = 0; q < ROWS; q++)
 				{
-					uint4 out;
+					const long long r = r0 + q * warps;
+					if (r >= rows)
+						break; // warp-uniform
+					float v[ITERS][8];
+					float sum = 0.0f;
 #pragma unroll
-					for (int k = 0; k < 8; k++)
-						reinterpret_cast<__half*>(&out)[k] = __float2half_rn(g[i][k] * (v[i][k] - mean) * inv_stddev + b[i][k]);
-					*reinterpret_cast<uint4*>(output + r * CHANNELS + (i * 32 + lane) * 8) = out;
+					for (int i = 0; i < ITERS; i++)
+#pragma unroll
+						for (int k = 0; k < 8; k++)
+						{
+							v[i][k] = __half2float(reinterpret_cast<const __half*>(&raw[q][i])[k]) + __half2float(reinterpret_cast<const __half*>(&er[q][i])[k]);
+							sum += v[i][k];
+						}
+					for (int k = 16; k >= 1; k /= 2)
+						sum += __shfl_xor_sync(0xffffffffu, sum, k);
+					const float mean = sum / static_cast<float>(CHANNELS);
+					float var = 0.0f;
+#pragma unroll
+					for (int i = 0; i < ITERS; i++)
+#pragma unroll
+						for (int k = 0; k < 8; k++)
+						{
+							const float d = v[i][k] - mean;
+							var += d * d;
+						}
+					for (int k = 16; k >= 1; k /= 2)
+						var += __shfl_xor_sync(0xffffffffu, var, k);
+					const float inv_stddev = 1.0f / sqrtf(1.0e-6f + var / static_cast<float>(CHANNELS - 1));
+#pragma unroll
+					for (int i = 0; i < ITERS; i++)
+					{
+						uint4 out;
+#pragma unroll
+						for (int k = 0; k < 8; k++)
+							reinterpret_cast<__half*>(&out)[k] = __float2half_rn(g[i][k] * (v[i][k] - mean) * inv_stddev + b[i][k]);
+						*reinterpret_cast<uint4*>(output + r * CHANNELS + (i * 32 + lane) * 8) = out;
+					}
 				}
 			}
 		}

@@ -37,75 +37,94 @@ namespace
 	};
 
 	/* One warp per row. Rows of up to 32 * VEC * ITERS channels stay in registers between the sum of squares and the scaling, so
-	 * the row is read from memory once; longer rows are read a second time (from L1 / L2). */
-	template<typename T, int VEC, int ITERS>
+	 * the row is read from memory once, and ROWS rows are in flight per warp (four 16-byte loads per lane whatever the row length);
+	 * longer rows are read a second time (from L1 / L2). */
+	template<typename T, int VEC, int ITERS, int ROWS>
 	__global__ void __launch_bounds__(256) kernel_rmsnorm(T *__restrict__ output, const T *__restrict__ input, const T *__restrict__ gamma,
 			long long rows, int channels)
 	{
 		const int lane = threadIdx.x % 32;
 		const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
 		const bool cached = channels <= 32 * VEC * ITERS;
-		for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r < rows; r += warps)
+		for (long long r0 = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r0 < rows; r0 += warps * ROWS)
 		{
-			const T *px = input + r * channels;
-			T *py = output + r * channels;
-			Pack<T, VEC> keep[ITERS];
-			float sum = 0.0f;
 			if (cached)
 			{
+				Pack<T, VEC> keep[ROWS][ITERS];
 #pragma unroll
-				for (int i = 0; i < ITERS; i++)
-				{
-					const int c = (i * 32 + lane) * VEC;
-					if (c < channels)
+				for (int q = 0; q < ROWS; q++)
+#pragma unroll
+					for (int i = 0; i < ITERS; i++)
 					{
-						keep[i] = *reinterpret_cast<const Pack<T, VEC>*>(px + c);
+						const int c = (i * 32 + lane) * VEC;
+						if (r0 + q * warps < rows && c < channels)
+							keep[q][i] = *reinterpret_cast<const Pack<T, VEC>*>(input + (r0 + q * warps) * channels + c);
+					}
 #pragma unroll
-						for (int k = 0; k < VEC; k++)
-							sum += to_f(keep[i].v[k]) * to_f(keep[i].v[k]);
+				for (int q = 0; q < ROWS; q++)
+				{
+					const long long r = r0 + q * warps;
+					if (r >= rows)
+						break; // warp-uniform
+					float sum = 0.0f;
+#pragma unroll
+					for (int i = 0; i < ITERS; i++)
+						if ((i * 32 + lane) * VEC < channels)
+						{
+#pragma unroll
+							for (int k = 0; k < VEC; k++)
+								sum += to_f(keep[q][i].v[k]) * to_f(keep[q][i].v[k]);
+						}
+					for (int k = 16; k >= 1; k /= 2)
+						sum += __shfl_xor_sync(0xffffffffu, sum, k);
+					const float inv_rms = 1.0f / (1.0e-6f + sqrtf(sum / static_cast<float>(channels)));
+#pragma unroll
+					for (int i = 0; i < ITERS; i++)
+					{
+						const int c = (i * 32 + lane) * VEC;
+						if (c < channels)
+						{
+							Pack<T, VEC> g, out;
+							if (gamma != nullptr)
+								g = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
+#pragma unroll
+							for (int k = 0; k < VEC; k++)
+								out.v[k] = from_f<T>((gamma != nullptr ? to_f(g.v[k]) : 1.0f) * to_f(keep[q][i].v[k]) * inv_rms);
+							*reinterpret_cast<Pack<T, VEC>*>(output + r * channels + c) = out;
+						}
 					}
 				}
 			}
 			else
-				for (int c = lane * VEC; c < channels; c += 32 * VEC)
+				for (int q = 0; q < ROWS; q++)
 				{
-					const Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(px + c);
-#pragma unroll
-					for (int k = 0; k < VEC; k++)
-						sum += to_f(p.v[k]) * to_f(p.v[k]);
-				}
-			for (int k = 16; k >= 1; k /= 2)
-				sum += __shfl_xor_sync(0xffffffffu, sum, k);
-			const float inv_rms = 1.0f / (1.0e-6f + sqrtf(sum / static_cast<float>(channels)));
-			if (cached)
-			{
-#pragma unroll
-				for (int i = 0; i < ITERS; i++)
-				{
-					const int c = (i * 32 + lane) * VEC;
-					if (c < channels)
+					const long long r = r0 + q * warps;
+					if (r >= rows)
+						break;
+					const T *px = input + r * channels;
+					T *py = output + r * channels;
+					float sum = 0.0f;
+					for (int c = lane * VEC; c < channels; c += 32 * VEC)
 					{
+						const Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(px + c);
+#pragma unroll
+						for (int k = 0; k < VEC; k++)
+							sum += to_f(p.v[k]) * to_f(p.v[k]);
+					}
+					for (int k = 16; k >= 1; k /= 2)
+						sum += __shfl_xor_sync(0xffffffffu, sum, k);
+					const float inv_rms = 1.0f / (1.0e-6f + sqrtf(sum / static_cast<float>(channels)));
+					for (int c = lane * VEC; c < channels; c += 32 * VEC)
+					{
+						const Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(px + c);
 						Pack<T, VEC> g, out;
 						if (gamma != nullptr)
 							g = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
 #pragma unroll
 						for (int k = 0; k < VEC; k++)
-							out.v[k] = from_f<T>((gamma != nullptr ? to_f(g.v[k]) : 1.0f) * to_f(keep[i].v[k]) * inv_rms);
+							out.v[k] = from_f<T>((gamma != nullptr ? to_f(g.v[k]) : 1.0f) * to_f(p.v[k]) * inv_rms);
 						*reinterpret_cast<Pack<T, VEC>*>(py + c) = out;
 					}
-				}
-			}
-			else
-				for (int c = lane * VEC; c < channels; c += 32 * VEC)
-				{
-					const Pack<T, VEC> p = *reinterpret_cast<const Pack<T, VEC>*>(px + c);
-					Pack<T, VEC> g, out;
-					if (gamma != nullptr)
-						g = *reinterpret_cast<const Pack<T, VEC>*>(gamma + c);
-#pragma unroll
-					for (int k = 0; k < VEC; k++)
-						out.v[k] = from_f<T>((gamma != nullptr ? to_f(g.v[k]) : 1.0f) * to_f(p.v[k]) * inv_rms);
-					*reinterpret_cast<Pack<T, VEC>*>(py + c) = out;
 				}
 		}
 	}
@@ -120,10 +139,14 @@ namespace
 		constexpr int WIDE = 16 / static_cast<int>(sizeof(T)); // elements per 16-byte access
 		const bool wide = channels % WIDE == 0 && reinterpret_cast<uintptr_t>(xp) % 16 == 0 && reinterpret_cast<uintptr_t>(yp) % 16 == 0
 				&& reinterpret_cast<uintptr_t>(gp) % 16 == 0;
-		if (wide)
-			kernel_rmsnorm<T, WIDE, 4> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
+		if (wide && channels <= 32 * WIDE)
+			kernel_rmsnorm<T, WIDE, 1, 4> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
+		else if (wide && channels <= 64 * WIDE)
+			kernel_rmsnorm<T, WIDE, 2, 2> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
+		else if (wide)
+			kernel_rmsnorm<T, WIDE, 4, 1> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
 		else
-			kernel_rmsnorm<T, 1, 8> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
+			kernel_rmsnorm<T, 1, 8, 1> <<<grid, 256, 0, stream>>>(yp, xp, gp, rows, channels);
 		MB200_COUNT_LAUNCH();
 	}
 
@@ -142,47 +165,77 @@ namespace
 		}
 	}
 
+	/* Division of a 31-bit number by a run-time constant as a multiply-high and a shift (the divisor's magic number is found
+	 * once on the host): the copy kernels below would otherwise spend more instructions on index arithmetic than on copying. */
+	struct FastDiv
+	{
+			uint32_t divisor = 1, multiplier = 0, shift = 0;
+			FastDiv() = default;
+			explicit FastDiv(uint32_t d) :
+					divisor(d)
+			{
+				if (d > 1)
+				{
+					uint32_t log2_ceil = 0;
+					while ((1ull << log2_ceil) < d)
+						log2_ceil++;
+					const uint32_t p = 31 + log2_ceil;
+					multiplier = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+					shift = p - 32;
+				}
+			}
+			__device__ __forceinline__ uint32_t div(uint32_t n) const
+			{
+				return (divisor == 1) ? n : (__umulhi(n, multiplier) >> shift);
+			}
+			__device__ __forceinline__ void divmod(uint32_t n, uint32_t &q, uint32_t &r) const
+			{
+				q = div(n);
+				r = n - q * divisor;
+			}
+	};
+
 	struct Geometry
 	{
 			int batch, height, width; // of the spatially larger tensor
 			int ph, pw; // patch size
 			int coarse_h, coarse_w; // of the spatially smaller tensor
 			int pieces; // pieces of V bytes per channel block of the larger tensor
+			FastDiv by_pieces, by_pw, by_ph;
 	};
 
-	/* One thread per piece of the smaller (deep) tensor; TO_DEPTH picks the copy direction. */
+	/* A block walks over rows of coarse pixels (batch item b, coarse row i); within one, consecutive threads take consecutive
+	 * pieces of the deep tensor, which is contiguous there. TO_DEPTH picks the copy direction. */
 	template<typename V, bool TO_DEPTH>
 	__global__ void __launch_bounds__(256) kernel_rearrange(V *__restrict__ deep, V *__restrict__ flat, const Geometry g)
 	{
-		const long long total = static_cast<long long>(g.batch) * g.coarse_h * g.coarse_w * g.ph * g.pw * g.pieces;
-		const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-		for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride)
+		const uint32_t inner = static_cast<uint32_t>(g.coarse_w) * g.ph * g.pw * g.pieces;
+		const int coarse_rows = g.batch * g.coarse_h;
+		for (int row = blockIdx.x; row < coarse_rows; row += gridDim.x)
 		{
-			long long t = idx;
-			const int piece = static_cast<int>(t % g.pieces);
-			t /= g.pieces;
-			const int y = static_cast<int>(t % g.pw);
-			t /= g.pw;
-			const int x = static_cast<int>(t % g.ph);
-			t /= g.ph;
-			const int j = static_cast<int>(t % g.coarse_w);
-			t /= g.coarse_w;
-			const int i = static_cast<int>(t % g.coarse_h);
-			const int b = static_cast<int>(t / g.coarse_h);
-			const int h = i * g.ph + x, w = j * g.pw + y;
-			const bool inside = h < g.height && w < g.width;
-			const long long flat_idx = ((static_cast<long long>(b) * g.height + h) * g.width + w) * g.pieces + piece;
-			if (TO_DEPTH)
+			const int b = row / g.coarse_h, i = row - b * g.coarse_h;
+			V *deep_row = deep + static_cast<long long>(row) * inner;
+			V *flat_image = flat + static_cast<long long>(b) * g.height * g.width * g.pieces;
+			for (uint32_t t = threadIdx.x; t < inner; t += blockDim.x)
 			{
-				V value;
-				if (inside)
-					value = flat[flat_idx];
-				else
+				uint32_t rest, piece, y, x, j;
+				g.by_pieces.divmod(t, rest, piece);
+				g.by_pw.divmod(rest, rest, y);
+				g.by_ph.divmod(rest, j, x);
+				const int h = i * g.ph + static_cast<int>(x), w = static_cast<int>(j) * g.pw + static_cast<int>(y);
+				const bool inside = h < g.height && w < g.width;
+				V *flat_at = flat_image + (static_cast<long long>(h) * g.width + w) * g.pieces + piece;
+				if (TO_DEPTH)
+				{
+					V value;
 					memset(&value, 0, sizeof(V));
-				deep[idx] = value;
+					if (inside)
+						value = *flat_at;
+					deep_row[t] = value;
+				}
+				else if (inside)
+					*flat_at = deep_row[t];
 			}
-			else if (inside)
-				flat[flat_idx] = deep[idx];
 		}
 	}
 
@@ -216,8 +269,13 @@ namespace
 		while (piece > 1 && (block_bytes % piece != 0 || addresses % piece != 0))
 			piece /= 2;
 		g.pieces = static_cast<int>(block_bytes / piece);
-		const long long total = static_cast<long long>(g.batch) * g.coarse_h * g.coarse_w * g.ph * g.pw * g.pieces;
-		const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((total + 255) / 256, static_cast<long long>(get(context)->sm_count) * 16)));
+		g.by_pieces = FastDiv(static_cast<uint32_t>(g.pieces));
+		g.by_pw = FastDiv(static_cast<uint32_t>(g.pw));
+		g.by_ph = FastDiv(static_cast<uint32_t>(g.ph));
+		const long long inner = static_cast<long long>(g.coarse_w) * g.ph * g.pw * g.pieces;
+		MB200_REQUIRE(context, inner < (1ll << 31), "%s: a row of %lld pieces is too long", who, inner);
+		const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(static_cast<long long>(g.batch) * g.coarse_h,
+				static_cast<long long>(get(context)->sm_count) * 16)));
 		cudaStream_t stream = use_stream(context);
 		void *d = const_cast<void*>(deep), *f = const_cast<void*>(flat);
 		switch (piece)

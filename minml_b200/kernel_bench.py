@@ -149,7 +149,7 @@ def main():
     del a32, d32
 
     # ---- elementwise / layout
-    packed =torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
+    packed = torch.randint(0, 2 ** 31 - 1, (b, h, w, 1), device="cuda", dtype=torch.int32)
     x0 = torch.empty((b, h, w, planes), device="cuda", dtype=f16)
     add("unpack_input (32 planes)", lambda: B.unpackInput(ctx, packed, x0), rows * 4 + rows * planes * 2)
     add("add_bias_act (relu)", lambda: B.addBiasAct(ctx, x, bias, y, "relu"), 2 * act_bytes)
