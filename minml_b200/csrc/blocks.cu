@@ -74,7 +74,13 @@ namespace
 
 	/* ------------------------------------------------------------------------------------------------ batch norm */
 	/* block = (channel groups, rows): thread (tx, ty) owns channel group blockIdx.y * blockDim.x + tx and the rows ty, ty + step, ... */
-	template<typename T, int VEC>
+	/* ACT is a compile-time class (0 linear, 1 ReLU, 2 decided at run time through a call): with the transcendental activations
+	 * inlined per element and per unrolled row the kernel outgrew the instruction cache and stalled on instruction fetch. */
+	__device__ __noinline__ float activation_by_call(float v, int act)
+	{
+		return apply_activation(v, act);
+	}
+	template<typename T, int VEC, int ACT>
 	__global__ void __launch_bounds__(256) kernel_batchnorm_inference(T *y, const T *x, const T *gamma, const T *beta_bn, const float *avg_var,
 			long long rows, int channels, float alpha, float beta, int act)
 	{
@@ -90,25 +96,39 @@ namespace
 			scale[k] = g / sqrtf(avg_var[channels + c0 + k] + 1.0e-6f);
 			shift[k] = -avg_var[c0 + k] * scale[k] + b;
 		}
-		for (long long r = blockIdx.x * static_cast<long long>(blockDim.y) + threadIdx.y; r < rows; r += static_cast<long long>(gridDim.x) * blockDim.y)
+		// The per-channel constants take half of the registers a full-occupancy kernel may use, so fewer warps are resident;
+		// each thread therefore keeps the loads of UNROLL rows in flight.
+		constexpr int UNROLL = 2;
+		const long long row_step = static_cast<long long>(gridDim.x) * blockDim.y;
+		for (long long r0 = blockIdx.x * static_cast<long long>(blockDim.y) + threadIdx.y; r0 < rows; r0 += row_step * UNROLL)
 		{
-			const long long off = r * channels + c0;
-			float in[VEC], out[VEC];
-			load_group<T, VEC>(x + off, in);
-			if (beta != 0.0f)
-				load_group<T, VEC>(y + off, out);
+			float in[UNROLL][VEC], out[UNROLL][VEC];
 #pragma unroll
-			for (int k = 0; k < VEC; k++)
-			{
-				float v = in[k] * scale[k] + shift[k];
-				if (act == ACTIVATION_RELU)
-					v = fmaxf(v, 0.0f);
-				else if (act != ACTIVATION_LINEAR)
-					v = apply_activation(v, act);
-				v *= alpha;
-				out[k] = (beta != 0.0f) ? v + beta * out[k] : v;
-			}
-			store_group<T, VEC>(y + off, out);
+			for (int u = 0; u < UNROLL; u++)
+				if (r0 + u * row_step < rows)
+				{
+					const long long off = (r0 + u * row_step) * channels + c0;
+					load_group<T, VEC>(x + off, in[u]);
+					if (beta != 0.0f)
+						load_group<T, VEC>(y + off, out[u]);
+				}
+#pragma unroll
+			for (int u = 0; u < UNROLL; u++)
+				if (r0 + u * row_step < rows)
+				{
+#pragma unroll
+					for (int k = 0; k < VEC; k++)
+					{
+						float v = in[u][k] * scale[k] + shift[k];
+						if (ACT == 1)
+							v = fmaxf(v, 0.0f);
+						else if (ACT == 2)
+							v = activation_by_call(v, act);
+						v *= alpha;
+						out[u][k] = (beta != 0.0f) ? v + beta * out[u][k] : v;
+					}
+					store_group<T, VEC>(y + (r0 + u * row_step) * channels + c0, out[u]);
+				}
 		}
 	}
 	template<typename T, int VEC>
@@ -121,7 +141,12 @@ namespace
 		const dim3 block(tx, ty);
 		const int row_blocks = static_cast<int>(std::max<long long>(1, std::min<long long>((rows + ty - 1) / ty, static_cast<long long>(sm_count) * 8)));
 		const dim3 grid(row_blocks, ceil_div(groups, tx));
-		kernel_batchnorm_inference<T, VEC> <<<grid, block, 0, stream>>>(y, x, w, b, av, rows, channels, alpha, beta, act);
+		if (act == ACTIVATION_LINEAR)
+			kernel_batchnorm_inference<T, VEC, 0> <<<grid, block, 0, stream>>>(y, x, w, b, av, rows, channels, alpha, beta, act);
+		else if (act == ACTIVATION_RELU)
+			kernel_batchnorm_inference<T, VEC, 1> <<<grid, block, 0, stream>>>(y, x, w, b, av, rows, channels, alpha, beta, act);
+		else
+			kernel_batchnorm_inference<T, VEC, 2> <<<grid, block, 0, stream>>>(y, x, w, b, av, rows, channels, alpha, beta, act);
 	}
 
 	/* weights viewed as [outer, inner]; channel = row (per_row) or column.  One thread per element; the bias is updated by the

@@ -195,6 +195,36 @@ namespace mb200
 	template<> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
 	template<> __device__ __forceinline__ double from_float<double>(float x) { return static_cast<double>(x); }
 
+	/* Division of a 31-bit number by a run-time constant as a multiply-high and a shift (the divisor's magic number is found
+	 * once on the host): copy kernels would otherwise spend more instructions on index arithmetic than on copying. */
+	struct FastDiv
+	{
+			uint32_t divisor = 1, multiplier = 0, shift = 0;
+			FastDiv() = default;
+			explicit FastDiv(uint32_t d) :
+					divisor(d)
+			{
+				if (d > 1)
+				{
+					uint32_t log2_ceil = 0;
+					while ((1ull << log2_ceil) < d)
+						log2_ceil++;
+					const uint32_t p = 31 + log2_ceil;
+					multiplier = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+					shift = p - 32;
+				}
+			}
+			__device__ __forceinline__ uint32_t div(uint32_t n) const
+			{
+				return (divisor == 1) ? n : (__umulhi(n, multiplier) >> shift);
+			}
+			__device__ __forceinline__ void divmod(uint32_t n, uint32_t &q, uint32_t &r) const
+			{
+				q = div(n);
+				r = n - q * divisor;
+			}
+	};
+
 	/* Activation set of the reference (src/backend/cuda/vec/vector_math.cuh:40-80): leaky slope 0.1. */
 	__device__ __forceinline__ float apply_activation(float x, int act)
 	{

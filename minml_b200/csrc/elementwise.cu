@@ -254,6 +254,51 @@ namespace mb200
 			}
 		}
 
+		/* The same for 8 consecutive channels per thread (channels a multiple of 8, aligned destination): one byte of the
+		 * position's word becomes one store of 8 elements; row and channel group advance without divisions. */
+		template<typename T>
+		struct alignas(sizeof(T) * 8 > 16 ? 16 : sizeof(T) * 8) Unpacked8
+		{
+				T v[8];
+		};
+		template<typename T>
+		__global__ void __launch_bounds__(256) kernel_unpack_groups(T *__restrict__ dst, const uint32_t *__restrict__ src, long long rows, int channels)
+		{
+			const int words = (channels + 31) / 32;
+			const int groups = channels / 8;
+			const long long total = rows * groups;
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+			long long r = first / groups;
+			int g = static_cast<int>(first - r * groups);
+			const long long r_step = stride / groups;
+			const int g_step = static_cast<int>(stride - r_step * groups);
+			for (long long i = first; i < total; i += stride)
+			{
+				const uint32_t bits = src[r * words + g / 4] >> ((g % 4) * 8);
+				Unpacked8<T> out;
+#pragma unroll
+				for (int k = 0; k < 8; k++)
+					out.v[k] = ((bits >> k) & 1u) ? one_of<T>() : zero_of<T>();
+				reinterpret_cast<Unpacked8<T>*>(dst)[i] = out;
+				r += r_step;
+				g += g_step;
+				if (g >= groups)
+				{
+					g -= groups;
+					r++;
+				}
+			}
+		}
+		template<typename T>
+		void launch_unpack(cudaStream_t stream, int sm, void *dst, const uint32_t *src, long long rows, int channels)
+		{
+			if (channels % 8 == 0 && aligned_to(dst, 16))
+				kernel_unpack_groups<T> <<<grid_for(rows * (channels / 8), 256, sm), 256, 0, stream>>>(reinterpret_cast<T*>(dst), src, rows, channels);
+			else
+				kernel_unpack<T> <<<grid_for(rows * channels, 256, sm), 256, 0, stream>>>(reinterpret_cast<T*>(dst), src, rows, channels);
+		}
+
 		template<typename T> __device__ __forceinline__ float as_float(T x) { return static_cast<float>(x); }
 		template<> __device__ __forceinline__ float as_float<__half>(__half x) { return __half2float(x); }
 		template<typename T> __device__ __forceinline__ T float_as(float x) { return static_cast<T>(x); }
@@ -620,9 +665,8 @@ extern "C"
 		if (rows == 0 || channels == 0)
 			return;
 		cudaStream_t stream = use_stream(context);
-		const int grid = grid_for(rows * channels, 256, get(context)->sm_count);
 		const uint32_t *s = reinterpret_cast<const uint32_t*>(src);
-#define CASE(E, T) case E: kernel_unpack<T> <<<grid, 256, 0, stream>>>(reinterpret_cast<T*>(dst), s, rows, channels); break
+#define CASE(E, T) case E: launch_unpack<T>(stream, get(context)->sm_count, dst, s, rows, channels); break
 		switch (dst_dtype)
 		{
 			CASE(DTYPE_FLOAT16, __half);

@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "conv.cuh"
 
+#include <algorithm>
 #include <cstring>
 
 namespace mb200
@@ -39,10 +40,14 @@ namespace mb200
 			const long long total = rows * channels / VEC;
 			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
 			const bool act_on = (act == ACTIVATION_SIGMOID || act == ACTIVATION_TANH || act == ACTIVATION_RELU);
-			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+			const int groups = channels / VEC;
+			const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+			int g = static_cast<int>(first % groups); // channel group of the thread's item, advanced without a division
+			const int g_step = static_cast<int>(stride % groups);
+			for (long long i = first; i < total; i += stride, g = (g + g_step >= groups) ? g + g_step - groups : g + g_step)
 			{
 				const long long e = i * VEC;
-				const int c = static_cast<int>(e % channels);
+				const int c = g * VEC;
 				int acc[VEC];
 				float sc[VEC], sh[VEC];
 				int ex[VEC];
@@ -144,13 +149,59 @@ namespace mb200
 				dst[i] = v;
 			}
 		}
+		/* The same copy with one warp per output position: the position is decomposed once per warp (multiply-high divisions),
+		 * the lanes walk over its kernel x kernel x packets pieces, which are contiguous in the output. */
+		template<int VB>
+		__global__ void __launch_bounds__(256) kernel_im2row_positions(void *__restrict__ output, const void *__restrict__ input, int positions,
+				int height, int width, int packets, int kernel, bool invert, typename PacketOf<VB>::type pad, FastDiv by_hw, FastDiv by_w,
+				FastDiv by_packets, FastDiv by_kernel)
+		{
+			using P = typename PacketOf<VB>::type;
+			const int pad_hw = (kernel - 1) / 2;
+			const uint32_t per_position = static_cast<uint32_t>(kernel) * kernel * packets;
+			const P *src = reinterpret_cast<const P*>(input);
+			P *dst = reinterpret_cast<P*>(output);
+			const int lane = threadIdx.x % 32;
+			const int warps = gridDim.x * (blockDim.x / 32);
+			for (int pos = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32; pos < positions; pos += warps)
+			{
+				uint32_t b, rem, h, w;
+				by_hw.divmod(static_cast<uint32_t>(pos), b, rem);
+				by_w.divmod(rem, h, w);
+				P *dst_row = dst + static_cast<long long>(pos) * per_position;
+				const P *src_image = src + static_cast<long long>(b) * height * width * packets;
+#pragma unroll 4
+				for (uint32_t t = lane; t < per_position; t += 32)
+				{
+					uint32_t tap, pk, kh, kw;
+					by_packets.divmod(t, tap, pk);
+					by_kernel.divmod(tap, kh, kw);
+					const int ih = static_cast<int>(h) - pad_hw + static_cast<int>(invert ? (kernel - 1 - kh) : kh);
+					const int iw = static_cast<int>(w) - pad_hw + static_cast<int>(invert ? (kernel - 1 - kw) : kw);
+					P v = pad;
+					if (ih >= 0 && ih < height && iw >= 0 && iw < width)
+						v = src_image[(static_cast<long long>(ih) * width + iw) * packets + pk];
+					dst_row[t] = v;
+				}
+			}
+		}
 		template<int VB>
 		void launch_im2row(cudaStream_t stream, int grid, void *output, const void *input, int batch, int height, int width, int row_bytes,
 				int kernel, bool invert, const uint8_t (&pattern)[16])
 		{
 			typename PacketOf<VB>::type pad;
 			std::memcpy(&pad, pattern, VB);
-			kernel_im2row<VB> <<<grid, 256, 0, stream>>>(output, input, batch, height, width, row_bytes, kernel, invert, pad);
+			const long long positions = static_cast<long long>(batch) * height * width;
+			const long long per_position = static_cast<long long>(kernel) * kernel * (row_bytes / VB);
+			if (positions < (1ll << 31) && per_position < (1ll << 31))
+			{
+				const int warp_grid = static_cast<int>(std::max<long long>(1, std::min<long long>((positions + 7) / 8, static_cast<long long>(grid))));
+				kernel_im2row_positions<VB> <<<warp_grid, 256, 0, stream>>>(output, input, static_cast<int>(positions), height, width, row_bytes / VB,
+						kernel, invert, pad, FastDiv(static_cast<uint32_t>(height) * width), FastDiv(static_cast<uint32_t>(width)),
+						FastDiv(static_cast<uint32_t>(row_bytes / VB)), FastDiv(static_cast<uint32_t>(kernel)));
+			}
+			else
+				kernel_im2row<VB> <<<grid, 256, 0, stream>>>(output, input, batch, height, width, row_bytes, kernel, invert, pad);
 			MB200_COUNT_LAUNCH();
 		}
 	}
