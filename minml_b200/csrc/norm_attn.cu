@@ -60,7 +60,7 @@ namespace mb200
 
 		/* fp16 rows of 256 * ITERS channels: one warp per row, every lane keeps its 8 * ITERS values in registers (16-byte loads),
 		 * so the row is read from memory once; the statistics are the same two passes (mean, then squared deviations) in fp32. */
-		template<int ITERS>
+		template<int ITERS, bool HAS_EXT>
 		__global__ void __launch_bounds__(256) kernel_layernorm_rows_fp16(__half *__restrict__ output, const __half *__restrict__ input,
 				const __half *__restrict__ gamma, const __half *__restrict__ beta, const __half *__restrict__ ext, long long rows)
 		{
@@ -88,7 +88,7 @@ namespace mb200
 			const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
 			for (long long r0 = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; r0 < rows; r0 += warps * ROWS)
 			{
-				uint4 raw[ROWS][ITERS], er[ROWS][ITERS];
+				uint4 raw[ROWS][ITERS], er[HAS_EXT ? ROWS : 1][HAS_EXT ? ITERS : 1];
 #pragma unroll
 				for (int q = 0; q < ROWS; q++)
 				{
@@ -98,11 +98,12 @@ namespace mb200
 					{
 						const long long off = r * CHANNELS + (i * 32 + lane) * 8;
 						raw[q][i] = make_uint4(0, 0, 0, 0);
-						er[q][i] = make_uint4(0, 0, 0, 0);
+						if (HAS_EXT)
+							er[q][i] = make_uint4(0, 0, 0, 0);
 						if (r < rows)
 						{
 							raw[q][i] = *reinterpret_cast<const uint4*>(input + off);
-							if (ext != nullptr)
+							if (HAS_EXT)
 								er[q][i] = *reinterpret_cast<const uint4*>(ext + off);
 						}
 					}
@@ -120,7 +121,9 @@ namespace mb200
 #pragma unroll
 						for (int k = 0; k < 8; k++)
 						{
-							v[i][k] = __half2float(reinterpret_cast<const __half*>(&raw[q][i])[k]) + __half2float(reinterpret_cast<const __half*>(&er[q][i])[k]);
+							v[i][k] = __half2float(reinterpret_cast<const __half*>(&raw[q][i])[k]);
+							if (HAS_EXT)
+								v[i][k] += __half2float(reinterpret_cast<const __half*>(&er[q][i])[k]);
 							sum += v[i][k];
 						}
 					for (int k = 16; k >= 1; k /= 2)
@@ -261,12 +264,14 @@ extern "C"
 						*bp = reinterpret_cast<const __half*>(bias), *ep = reinterpret_cast<const __half*>(ext);
 				const bool aligned = aligned_to(xp, 16) && aligned_to(yp, 16) && (gp == nullptr || aligned_to(gp, 16)) && (bp == nullptr || aligned_to(bp, 16))
 						&& (ep == nullptr || aligned_to(ep, 16));
+#define ROWS_KERNEL(I) do { if (ep != nullptr) kernel_layernorm_rows_fp16<I, true> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows); \
+		else kernel_layernorm_rows_fp16<I, false> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows); } while (0)
 				if (aligned && channels == 256)
-					kernel_layernorm_rows_fp16<1> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+					ROWS_KERNEL(1);
 				else if (aligned && channels == 512)
-					kernel_layernorm_rows_fp16<2> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+					ROWS_KERNEL(2);
 				else if (aligned && channels == 1024)
-					kernel_layernorm_rows_fp16<4> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows);
+					ROWS_KERNEL(4);
 				else
 					kernel_layernorm<__half> <<<grid, 256, 0, stream>>>(yp, xp, gp, bp, ep, rows, channels);
 				break;
