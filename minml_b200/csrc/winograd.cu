@@ -224,11 +224,16 @@ namespace mb200
 			const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
 			if (idx >= total_tiles * cvecs)
 				return;
-			const long long tile = idx / cvecs;
-			const int c0 = static_cast<int>(idx % cvecs) * VEC;
-			const int tw = static_cast<int>(tile % tiles_w);
-			const int th = static_cast<int>((tile / tiles_w) % tiles_h);
-			const int b = static_cast<int>(tile / (static_cast<long long>(tiles_w) * tiles_h));
+			// 32-bit index arithmetic (the launcher checks that the thread count fits): five 64-bit divisions cost about as many
+			// instructions as the transform itself
+			const unsigned idx32 = static_cast<unsigned>(idx);
+			const unsigned tile32 = idx32 / static_cast<unsigned>(cvecs);
+			const int c0 = static_cast<int>(idx32 - tile32 * static_cast<unsigned>(cvecs)) * VEC;
+			const unsigned row32 = tile32 / static_cast<unsigned>(tiles_w);
+			const int tw = static_cast<int>(tile32 - row32 * static_cast<unsigned>(tiles_w));
+			const int b = static_cast<int>(row32 / static_cast<unsigned>(tiles_h));
+			const int th = static_cast<int>(row32 - static_cast<unsigned>(b) * static_cast<unsigned>(tiles_h));
+			const long long tile = tile32;
 
 			// 1. fetch the whole zero-padded patch: P*P independent loads (a position outside the image reads element 0 and is masked)
 			R raw[P][P];
@@ -305,11 +310,16 @@ namespace mb200
 			const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
 			if (idx >= total_tiles * cvecs)
 				return;
-			const long long tile = idx / cvecs;
-			const int c0 = static_cast<int>(idx % cvecs) * VEC;
-			const int tw = static_cast<int>(tile % tiles_w);
-			const int th = static_cast<int>((tile / tiles_w) % tiles_h);
-			const int b = static_cast<int>(tile / (static_cast<long long>(tiles_w) * tiles_h));
+			// 32-bit index arithmetic (the launcher checks that the thread count fits): five 64-bit divisions cost about as many
+			// instructions as the transform itself
+			const unsigned idx32 = static_cast<unsigned>(idx);
+			const unsigned tile32 = idx32 / static_cast<unsigned>(cvecs);
+			const int c0 = static_cast<int>(idx32 - tile32 * static_cast<unsigned>(cvecs)) * VEC;
+			const unsigned row32 = tile32 / static_cast<unsigned>(tiles_w);
+			const int tw = static_cast<int>(tile32 - row32 * static_cast<unsigned>(tiles_w));
+			const int b = static_cast<int>(row32 / static_cast<unsigned>(tiles_h));
+			const int th = static_cast<int>(row32 - static_cast<unsigned>(b) * static_cast<unsigned>(tiles_h));
+			const long long tile = tile32;
 
 			// 1. all P*P matrix elements and the T*T residual values of this tile are fetched before any arithmetic
 			R raw[P][P];
@@ -464,6 +474,7 @@ namespace mb200
 		const int batch = x.dim[0], height = x.dim[1], width = x.dim[2], channels = x.dim[3];
 		const int tiles_h = (height + tile_size - 1) / tile_size, tiles_w = (width + tile_size - 1) / tile_size;
 		const long long tiles = static_cast<long long>(batch) * tiles_h * tiles_w;
+		MB200_REQUIRE(ctx, tiles * channels < (1ll << 31), "cuda_winograd_input_transform: %lld tiles x %d channels exceed one launch", tiles, channels);
 		cudaStream_t stream = use_stream(ctx);
 #define ARGS(D) reinterpret_cast<D*>(matrices.data), reinterpret_cast<const D*>(x.data), batch, height, width, channels, tiles_h, tiles_w
 		if (x.dtype == DTYPE_FLOAT16)
@@ -494,6 +505,7 @@ namespace mb200
 		const int batch = y.dim[0], height = y.dim[1], width = y.dim[2], channels = y.dim[3];
 		const int tiles_h = (height + tile_size - 1) / tile_size, tiles_w = (width + tile_size - 1) / tile_size;
 		const long long tiles = static_cast<long long>(batch) * tiles_h * tiles_w;
+		MB200_REQUIRE(ctx, tiles * channels < (1ll << 31), "cuda_winograd_output_transform: %lld tiles x %d channels exceed one launch", tiles, channels);
 		cudaStream_t stream = use_stream(ctx);
 #define ARGS(D) reinterpret_cast<const D*>(matrices.data), reinterpret_cast<D*>(y.data), reinterpret_cast<const D*>(ext.data), \
 		reinterpret_cast<const D*>(bias.data), static_cast<int>(act), batch, height, width, channels, tiles_h, tiles_w
