@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 using namespace mb200;
 
@@ -217,10 +218,15 @@ namespace
 	 * A thread owns R consecutive output rows of one group of VEC channels and walks along them: input column c feeds the K output columns
 	 * c - K + 1 .. c through the K filter columns, so K partial sums live in a ring of register accumulators (the ring index is a
 	 * compile-time constant because the column loop is unrolled K times). */
-	template<typename T, int VEC, int K, int R, bool QUANT>
+	/* H2 (fp16 only): taps, ring accumulators and multiply-adds in half2, two channels per instruction and no conversions in the
+	 * inner loop; sums are then rounded to fp16 after every tap, as in the reference's kernel (depthwise_conv.cu accumulates fp16
+	 * convolutions in half2), instead of being kept in fp32. Scaling, bias and the beta term stay in fp32. */
+	template<typename T, int VEC, int K, int R, bool QUANT, bool H2 = false>
 	__global__ void __launch_bounds__(256) kernel_depthwise_conv(T *y, const T *x, const T *w, const T *bias, const DepthwiseParams p,
 			int tile_w, int tiles_w)
 	{
+		static_assert(!H2 || (sizeof(T) == 2 && VEC % 2 == 0 && !QUANT), "half2 arithmetic needs pairs of fp16 channels");
+		constexpr int PAIRS = H2 ? VEC / 2 : 1;
 		constexpr int PAD = (K - 1) / 2;
 		extern __shared__ __align__(16) unsigned char smem_raw[];
 		Group<T, VEC> *tile = reinterpret_cast<Group<T, VEC>*>(smem_raw);
@@ -254,10 +260,21 @@ namespace
 		if (!lane_ok || h >= p.height)
 			return;
 
-		float filt[K * K][VEC];
+		float filt[H2 ? 1 : K * K][VEC];
+		__half2 filt2[H2 ? K * K : 1][PAIRS];
 #pragma unroll
 		for (int t = 0; t < K * K; t++)
-			load_group<T, VEC>(w + static_cast<long long>(t) * p.channels + c0, filt[t]);
+		{
+			if constexpr (H2)
+			{
+				const Group<T, VEC> g = *reinterpret_cast<const Group<T, VEC>*>(w + static_cast<long long>(t) * p.channels + c0);
+#pragma unroll
+				for (int q = 0; q < PAIRS; q++)
+					filt2[t][q] = reinterpret_cast<const __half2*>(&g)[q];
+			}
+			else
+				load_group<T, VEC>(w + static_cast<long long>(t) * p.channels + c0, filt[t]);
+		}
 		float post_scale[VEC], post_shift[VEC];
 #pragma unroll
 		for (int k = 0; k < VEC; k++)
@@ -273,14 +290,20 @@ namespace
 				post_shift[k] = (bias != nullptr) ? to_float(bias[c0 + k]) : 0.0f;
 			}
 		}
-		float acc[R][K][VEC]; // per output row a ring: output column o of the tile lives in slot o mod K
+		float acc[R][K][H2 ? 1 : VEC]; // per output row a ring: output column o of the tile lives in slot o mod K
+		__half2 acc2[R][K][PAIRS];
 #pragma unroll
 		for (int r = 0; r < R; r++)
 #pragma unroll
 			for (int s = 0; s < K; s++)
+			{
 #pragma unroll
-				for (int k = 0; k < VEC; k++)
+				for (int k = 0; k < (H2 ? 1 : VEC); k++)
 					acc[r][s][k] = 0.0f;
+#pragma unroll
+				for (int q = 0; q < PAIRS; q++)
+					acc2[r][s][q] = __float2half2_rn(0.0f);
+			}
 
 		const int out_cols = min(tile_w, p.width - w0);
 		const int ncols = out_cols + K - 1; // input columns of the patch these rows need
@@ -298,9 +321,12 @@ namespace
 					{ // patch row i feeds output row r through filter row i - r
 						float in[VEC];
 						const Group<T, VEC> g = row0[(i * in_cols + col) * ntx];
+						if constexpr (!H2)
+						{
 #pragma unroll
-						for (int k = 0; k < VEC; k++)
-							in[k] = to_float(g.v[k]);
+							for (int k = 0; k < VEC; k++)
+								in[k] = to_float(g.v[k]);
+						}
 #pragma unroll
 						for (int r = 0; r < R; r++)
 						{
@@ -308,15 +334,43 @@ namespace
 								continue;
 #pragma unroll
 							for (int j = 0; j < K; j++) // filter column j: output column col - j, ring slot (u - j) mod K
+							{
+								if constexpr (H2)
+								{
 #pragma unroll
-								for (int k = 0; k < VEC; k++)
-									acc[r][(u - j + K) % K][k] = fmaf(in[k], filt[(i - r) * K + j][k], acc[r][(u - j + K) % K][k]);
+									for (int q = 0; q < PAIRS; q++)
+										acc2[r][(u - j + K) % K][q] = __hfma2(reinterpret_cast<const __half2*>(&g)[q], filt2[(i - r) * K + j][q],
+												acc2[r][(u - j + K) % K][q]);
+								}
+								else
+								{
+#pragma unroll
+									for (int k = 0; k < VEC; k++)
+										acc[r][(u - j + K) % K][k] = fmaf(in[k], filt[(i - r) * K + j][k], acc[r][(u - j + K) % K][k]);
+								}
+							}
 						}
 					}
 #pragma unroll
 					for (int r = 0; r < R; r++)
 					{
-						float (&done)[VEC] = acc[r][(u + 1) % K]; // output column col - (K - 1): complete after this input column
+						float done[VEC]; // output column col - (K - 1): complete after this input column
+						if constexpr (H2)
+						{
+#pragma unroll
+							for (int q = 0; q < PAIRS; q++)
+							{
+								const float2 f = __half22float2(acc2[r][(u + 1) % K][q]);
+								done[2 * q] = f.x;
+								done[2 * q + 1] = f.y;
+							}
+						}
+						else
+						{
+#pragma unroll
+							for (int k = 0; k < VEC; k++)
+								done[k] = acc[r][(u + 1) % K][k];
+						}
 						if (col >= K - 1 && h + r < p.height)
 						{
 							const long long off = (static_cast<long long>(h + r) * p.width + (w0 + col - (K - 1))) * p.channels;
@@ -343,9 +397,13 @@ namespace
 							}
 							store_group<T, VEC>(yb + off, out);
 						}
+						// the slot the next input column opens
 #pragma unroll
-						for (int k = 0; k < VEC; k++)
-							done[k] = 0.0f; // the slot the next input column opens
+						for (int k = 0; k < (H2 ? 1 : VEC); k++)
+							acc[r][(u + 1) % K][k] = 0.0f;
+#pragma unroll
+						for (int q = 0; q < PAIRS; q++)
+							acc2[r][(u + 1) % K][q] = __float2half2_rn(0.0f);
 					}
 				}
 			}
@@ -353,7 +411,7 @@ namespace
 	}
 
 	/* Shared-memory opt-in above 48 KB and the large carve-out, once per device and kernel instantiation. */
-	template<typename T, int VEC, int K, int R, bool QUANT>
+	template<typename T, int VEC, int K, int R, bool QUANT, bool H2>
 	bool depthwise_opt_in(int device)
 	{
 		static bool done[MAX_DEVICES] = { false };
@@ -361,8 +419,8 @@ namespace
 			return false;
 		if (!done[device])
 		{
-			if (cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEPTHWISE_SMEM_LIMIT)
-					!= cudaSuccess || cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+			if (cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT, H2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEPTHWISE_SMEM_LIMIT)
+					!= cudaSuccess || cudaFuncSetAttribute(kernel_depthwise_conv<T, VEC, K, R, QUANT, H2>, cudaFuncAttributePreferredSharedMemoryCarveout,
 							cudaSharedmemCarveoutMaxShared) != cudaSuccess)
 			{
 				cudaGetLastError();
@@ -372,7 +430,7 @@ namespace
 		}
 		return true;
 	}
-	template<typename T, int VEC, int K, bool QUANT>
+	template<typename T, int VEC, int K, bool QUANT, bool H2 = false>
 	bool launch_depthwise_kv(cudaStream_t stream, int device, int batch, T *y, const T *x, const T *w, const T *bias, const DepthwiseParams &p)
 	{
 		constexpr int R = 2; // output rows per thread: every patch element read feeds two rows' multiply-adds
@@ -394,12 +452,12 @@ namespace
 				ty = (ty + 1) / 2;
 		}
 		const size_t smem = patch_bytes(ty, tile_w);
-		if (!depthwise_opt_in<T, VEC, K, R, QUANT>(device)) // also asks for the large shared-memory carve-out: several patches per SM
+		if (!depthwise_opt_in<T, VEC, K, R, QUANT, H2>(device)) // also asks for the large shared-memory carve-out: several patches per SM
 			return false;
 		const int tiles_w = ceil_div(p.width, tile_w);
 		const dim3 block(tx, ty);
 		const dim3 grid(ceil_div(p.height, ty * R) * tiles_w, batch, ceil_div(groups, tx));
-		kernel_depthwise_conv<T, VEC, K, R, QUANT> <<<grid, block, smem, stream>>>(y, x, w, bias, p, tile_w, tiles_w);
+		kernel_depthwise_conv<T, VEC, K, R, QUANT, H2> <<<grid, block, smem, stream>>>(y, x, w, bias, p, tile_w, tiles_w);
 		return true;
 	}
 	/* The widest channel group that keeps the k x k fp32 filter taps in registers: 8 / 4 / 2 channels for k = 3 / 5 / 7. */
@@ -412,6 +470,19 @@ namespace
 			return p.channels % vec == 0 && aligned_to(x, bytes) && aligned_to(y, bytes) && aligned_to(w, bytes);
 		};
 		constexpr int WIDEST = (sizeof(T) == 4) ? 4 : 8;
+		if constexpr (sizeof(T) == 2 && !QUANT)
+		{ // fp16: half2 arithmetic for the widest group of each kernel size, unless MINML_B200_DEPTHWISE_FP32=1 asks for fp32 sums
+			static const bool fp32_sums = std::getenv("MINML_B200_DEPTHWISE_FP32") != nullptr && std::getenv("MINML_B200_DEPTHWISE_FP32")[0] == '1';
+			if (!fp32_sums)
+			{
+				if (k == 3 && ok(8))
+					return launch_depthwise_kv<T, 8, 3, QUANT, true>(stream, device, batch, y, x, w, bias, p);
+				if (k == 5 && ok(4))
+					return launch_depthwise_kv<T, 4, 5, QUANT, true>(stream, device, batch, y, x, w, bias, p);
+				if (k == 7 && ok(2))
+					return launch_depthwise_kv<T, 2, 7, QUANT, true>(stream, device, batch, y, x, w, bias, p);
+			}
+		}
 		if (k == 3)
 		{
 			if (ok(WIDEST))
