@@ -21,9 +21,10 @@
  * the tensor cores): a thread owns one output row of a small group of channels and walks along it.  Input column ww feeds the k
  * output columns ww - pad .. ww + pad, whose partial sums sit in k register accumulators that shift by one per step; the k x k
  * filter taps of the thread's channels stay in registers as fp32 for the whole row.  Every input element is therefore loaded k
- * times (once per filter row), not k x k times, and the inner loop is k multiply-adds per loaded value.  Accumulation is fp32 (the
- * reference accumulates fp16 depthwise convolutions in half2); the int8 variant runs on the same fp32 path, which is exact there:
- * every partial sum is an integer below 49 * 128 * 128 < 2^24.
+ * times (once per filter row), not k x k times, and the inner loop is k multiply-adds per loaded value.  fp32 tensors accumulate in
+ * fp32; fp16 tensors by default multiply and accumulate in half2 like the reference's kernel (two channels per instruction, no
+ * conversions in the inner loop), or in fp32 when MINML_B200_DEPTHWISE_FP32=1; the int8 variant runs on the fp32 path, which is
+ * exact there: every partial sum is an integer below 49 * 128 * 128 < 2^24.
  */
 #include "common.cuh"
 
