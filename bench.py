@@ -359,7 +359,7 @@ def gpu_arm(args, cfg):
                 shape = (batch, cfg["height"], cfg["width"], cfg["planes"], cfg["channels"], cfg["blocks"])
                 if kind == "int8_trunk":
                     from minml_b200 import networks as N
-                    net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64)
+                    net = N.QuantizedTrunk(ctx, weights, *shape, calibration_batches=64, calibrator=args.calibrator)
                 else:
                     net = L.ResNetTrunk(ctx, weights, *shape)
                 _, packed = synthetic_input(cfg, batch, replicas.input_seed(SEED))
@@ -494,6 +494,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue every backend call from the host each step instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="end-to-end steps on one context, one after the other")
+    ap.add_argument("--calibrator", default="max_abs", choices=["max_abs", "histogram"],
+                    help="int8 configuration: activation transforms by the max-abs rule the configuration states, or by minml's histogram calibrator")
     ap.add_argument("--eager", action="store_true", help="three kernels per 3x3 layer (fusion off) instead of the fused convolution")
     ap.add_argument("--layer", action="store_true", help="time only one channels -> channels 3x3 layer (the roofline record); used for ncu captures")
     ap.add_argument("--layer-batch", type=int, default=0, help="batch size for --layer (default: the config's)")

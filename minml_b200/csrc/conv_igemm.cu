@@ -31,8 +31,11 @@
  *
  * Two variants of the A operand path:
  *   TMA_A = true   im2col-mode TMA: one request per K slice delivers 128 output positions x 128 bytes of channels of one
- *                  filter tap, zero-filled outside the image.  Needs cin * element size to be a multiple of 128 bytes and
- *                  a zero padding value.  This is the fast path (256 -> 256 fp16: 1.23 PFLOP/s against 0.92 for the gather).
+ *                  filter tap, zero-filled outside the image.  Needs cin * element size to be a multiple of 128 bytes.  A non-zero
+ *                  int8 padding value z (the quantised zero of an asymmetric input) is made up for in the epilogue: positions on
+ *                  the border get z * (sum of the weights of the taps that fell outside) from a 9 x cout table computed per call
+ *                  (kernel_border_table), which keeps the int32 accumulators exact.  This is the fast path (256 -> 256 fp16:
+ *                  1.23 PFLOP/s against 0.92 for the gather).
  *   TMA_A = false  cp.async gather of 16-byte channel chunks: any cin that is a multiple of 8 (fp16) / 16 (int8), any
  *                  int8 padding value.
  * Every wait is bounded (tc.cuh); on a timeout the kernel sets its status word and drains.
@@ -107,6 +110,9 @@ namespace mb200
 				float ext_scale, ext_shift, out_scale, out_shift;
 				float inv_out_scale, inv_out_shift; // 1 / out_scale and -out_shift / out_scale, rounded like AffineTransform::get_inverse
 				int pad_byte;
+				// int8, non-zero padding value on the TMA path (which can only fill with zeros): [9][cout] corrections, already
+				// multiplied by the padding value, for the nine kinds of position (3 x 3: first / inner / last row and column)
+				const int *border;
 				int *status;
 		};
 
@@ -399,6 +405,21 @@ namespace mb200
 						uint32_t r[32];
 						tmem_ld_32x32(taddr + c * 32, r);
 						tmem_wait_ld();
+						if (KIND == 1 && p.border != nullptr && row_ok)
+						{ /* The copy engine filled positions outside the image with zeros where the host asked for the quantised zero z:
+						   * add z * (sum of the weights of the taps that fell outside), which depends only on the kind of position. */
+							const int pos = row % (p.height * p.width);
+							const int ph = pos / p.width, pw = pos - ph * p.width;
+							const int kind_of_position = (ph == 0 ? 1 : (ph == p.height - 1 ? 2 : 0)) * 3 + (pw == 0 ? 1 : (pw == p.width - 1 ? 2 : 0));
+							if (kind_of_position != 0)
+							{
+								const int *bt = p.border + kind_of_position * p.cout + n0;
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										r[j] += static_cast<uint32_t>(bt[j]);
+							}
+						}
 
 						if (fast)
 						{
@@ -859,6 +880,36 @@ namespace mb200
 			return true;
 		}
 
+		/* table[kind][co] = pad * sum over the taps outside the image for that kind of position of sum_ci w[co][tap][ci];
+		 * one CTA per output channel, one warp per tap. */
+		__global__ void __launch_bounds__(9 * 32) kernel_border_table(int *__restrict__ table, const int8_t *__restrict__ w, int cin, int cout, int pad)
+		{
+			__shared__ int tap_sum[9];
+			const int co = blockIdx.x, tap = threadIdx.x / 32, lane = threadIdx.x % 32;
+			const int8_t *src = w + (static_cast<long long>(co) * 9 + tap) * cin;
+			int s = 0;
+			for (int i = lane; i < cin; i += 32)
+				s += src[i];
+			for (int k = 16; k >= 1; k /= 2)
+				s += __shfl_xor_sync(0xffffffffu, s, k);
+			if (lane == 0)
+				tap_sum[tap] = s;
+			__syncthreads();
+			if (threadIdx.x < 9)
+			{
+				const int hk = threadIdx.x / 3, wk = threadIdx.x % 3; // 0 inner, 1 first, 2 last row / column
+				int total = 0;
+				for (int kh = 0; kh < 3; kh++)
+					for (int kw = 0; kw < 3; kw++)
+					{
+						const bool outside = (hk == 1 && kh == 0) || (hk == 2 && kh == 2) || (wk == 1 && kw == 0) || (wk == 2 && kw == 2);
+						if (outside)
+							total += tap_sum[kh * 3 + kw];
+					}
+				table[threadIdx.x * cout + co] = total * pad;
+			}
+		}
+
 		bool run(mlContext_t ctx, int kind, const mlTensor_t &x, const void *w, int cout, ConvParams p)
 		{
 			const int es = (kind == 0) ? 2 : 1;
@@ -875,7 +926,17 @@ namespace mb200
 			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
 			static const bool force_gather = env_flag("MINML_B200_CONV_GATHER"); // measurement switches: each forces the slower variant
 			static const bool force_single = env_flag("MINML_B200_CONV_SINGLE_CTA");
-			const bool tma_a = (p.cin * es) % 128 == 0 && p.pad_byte == 0 && !force_gather;
+			// (int8 with a non-zero padding value: still by TMA when the caller supplied room for the border corrections)
+			const bool zero_fill_ok = p.pad_byte == 0 || (kind == 1 && p.border != nullptr && p.height >= 2 && p.width >= 2);
+			const bool tma_a = (p.cin * es) % 128 == 0 && zero_fill_ok && !force_gather;
+			if (tma_a && p.pad_byte != 0)
+			{
+				kernel_border_table<<<cout, 9 * 32, 0, use_stream(ctx)>>>(const_cast<int*>(p.border), reinterpret_cast<const int8_t*>(w), p.cin, cout,
+						p.pad_byte);
+				MB200_COUNT_LAUNCH();
+			}
+			else
+				p.border = nullptr; // the gather variant stores the padding value itself
 			// Pairs pay off where the operand fetch is the limit (256-column tiles: 0.383 -> 0.353 ms on the 256 -> 256 layer); with
 			// 128-column tiles the epilogue is, and coupling two CTAs' accumulator hand-offs costs more than it saves (measured).
 			static const bool force_pair = env_flag("MINML_B200_CONV_PAIR");
@@ -1001,6 +1062,10 @@ namespace mb200
 		p.inv_out_scale = 1.0f / output_qd.scale;
 		p.inv_out_shift = -output_qd.shift / output_qd.scale;
 		p.pad_byte = c->pending_i8.pad;
+		// the int32 matrix the host set aside for the accumulators is not written by the fused kernel: its first 9 x cout words
+		// hold the border corrections when the padding value is not zero
+		if (p.pad_byte != 0 && volume(c->pending_i8.acc) >= 9LL * cout && aligned_to(c->pending_i8.acc.data, 4))
+			p.border = reinterpret_cast<const int*>(c->pending_i8.acc.data);
 		c->pending_i8.stage = 0;
 		return run(ctx, 1, x, c->pending_i8.w.data, cout, p);
 	}

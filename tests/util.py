@@ -45,18 +45,23 @@ def oracle_trunk(oracle, weights, x, blocks):
     return policy, value
 
 
-def oracle_quantized_trunk(oracle, weights, x01, blocks, scales):
+def oracle_quantized_trunk(oracle, weights, x01, blocks, transforms):
     """The int8 trunk (minml_b200.networks.QuantizedTrunk) layer by layer on the oracle's integer convolution.
-    `scales[t]` is the per-tensor activation scale of tensor t (stem output, then two per block); shifts are 0."""
-    def qconv(xq, wn, bn, s_in, s_out, ext=None, s_ext=1.0):
-        q, cs, qb = oracle.quantize_weights(weights[wn], weights[bn], s_in, 0.0)
-        return oracle.conv2d_int8(xq, q, cs, qb, 0, (s_out, 0.0), "relu", ext, (s_ext, 0.0))
-    a, _, _ = qconv(x01.astype(np.int8), "stem_w", "stem_b", 1.0, scales[0])
+    `transforms[t]` is the per-tensor (scale, shift) of tensor t (stem output, then two per block), or a bare scale (shift 0)."""
+    qd = [t if isinstance(t, tuple) else (t, 0.0) for t in transforms]
+
+    def zero_of(t):  # the int8 value that dequantises to 0, as layers.QuantizedConv2D computes it
+        return int(np.clip(np.round(-np.float32(t[1]) / np.float32(t[0])), -128, 127))
+
+    def qconv(xq, wn, bn, t_in, t_out, ext=None, t_ext=(1.0, 0.0)):
+        q, cs, qb = oracle.quantize_weights(weights[wn], weights[bn], t_in[0], t_in[1])
+        return oracle.conv2d_int8(xq, q, cs, qb, zero_of(t_in), t_out, "relu", ext, t_ext)
+    a, _, _ = qconv(x01.astype(np.int8), "stem_w", "stem_b", (1.0, 0.0), qd[0])
     real = None
     for i in range(blocks):
-        s_in, s_mid, s_out = scales[2 * i], scales[1 + 2 * i], scales[2 + 2 * i]
-        t, _, _ = qconv(a, "b%d_w1" % i, "b%d_b1" % i, s_in, s_mid)
-        a, real, _ = qconv(t, "b%d_w2" % i, "b%d_b2" % i, s_mid, s_out, a, s_in)
+        t_in, t_mid, t_out = qd[2 * i], qd[1 + 2 * i], qd[2 + 2 * i]
+        t, _, _ = qconv(a, "b%d_w1" % i, "b%d_b1" % i, t_in, t_mid)
+        a, real, _ = qconv(t, "b%d_w2" % i, "b%d_b2" % i, t_mid, t_out, a, t_in)
     real = real.astype(np.float16).astype(np.float32)  # the last block hands fp16 to the heads
     policy = oracle.conv2d(real, weights["policy_w"], weights["policy_b"], None, "linear")
     pooled = oracle.global_average_pooling(real)
