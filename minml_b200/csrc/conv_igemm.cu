@@ -113,6 +113,7 @@ namespace mb200
 				// int8, non-zero padding value on the TMA path (which can only fill with zeros): [9][cout] corrections, already
 				// multiplied by the padding value, for the nine kinds of position (3 x 3: first / inner / last row and column)
 				const int *border;
+				FastDiv by_board, by_width; // position -> (row, column) of the board without divisions (border table only)
 				int *status;
 		};
 
@@ -408,16 +409,33 @@ namespace mb200
 						if (KIND == 1 && p.border != nullptr && row_ok)
 						{ /* The copy engine filled positions outside the image with zeros where the host asked for the quantised zero z:
 						   * add z * (sum of the weights of the taps that fell outside), which depends only on the kind of position. */
-							const int pos = row % (p.height * p.width);
-							const int ph = pos / p.width, pw = pos - ph * p.width;
-							const int kind_of_position = (ph == 0 ? 1 : (ph == p.height - 1 ? 2 : 0)) * 3 + (pw == 0 ? 1 : (pw == p.width - 1 ? 2 : 0));
+							uint32_t image, pos, ph, pw;
+							p.by_board.divmod(static_cast<uint32_t>(row), image, pos);
+							p.by_width.divmod(pos, ph, pw);
+							const int kind_of_position = (ph == 0 ? 1 : (static_cast<int>(ph) == p.height - 1 ? 2 : 0)) * 3
+									+ (pw == 0 ? 1 : (static_cast<int>(pw) == p.width - 1 ? 2 : 0));
 							if (kind_of_position != 0)
 							{
 								const int *bt = p.border + kind_of_position * p.cout + n0;
+								if (n_valid == 32 && (p.cout % 4) == 0)
+								{ // the table starts on a 16-byte boundary (it is the head of the host's accumulator matrix) and n0 is a multiple of 32
 #pragma unroll
-								for (int j = 0; j < 32; j++)
-									if (j < n_valid)
-										r[j] += static_cast<uint32_t>(bt[j]);
+									for (int j4 = 0; j4 < 8; j4++)
+									{
+										const int4 t = reinterpret_cast<const int4*>(bt)[j4];
+										r[4 * j4] += static_cast<uint32_t>(t.x);
+										r[4 * j4 + 1] += static_cast<uint32_t>(t.y);
+										r[4 * j4 + 2] += static_cast<uint32_t>(t.z);
+										r[4 * j4 + 3] += static_cast<uint32_t>(t.w);
+									}
+								}
+								else
+								{
+#pragma unroll
+									for (int j = 0; j < 32; j++)
+										if (j < n_valid)
+											r[j] += static_cast<uint32_t>(bt[j]);
+								}
 							}
 						}
 
@@ -922,6 +940,8 @@ namespace mb200
 			p.M = x.dim[0] * x.dim[1] * x.dim[2];
 			p.K = 9 * x.dim[3];
 			p.status = get(ctx)->dev_status;
+			p.by_board = FastDiv(static_cast<uint32_t>(p.height) * p.width);
+			p.by_width = FastDiv(static_cast<uint32_t>(p.width));
 			const int bn = (cout > 128) ? 256 : 128;
 			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
 			static const bool force_gather = env_flag("MINML_B200_CONV_GATHER"); // measurement switches: each forces the slower variant
@@ -1064,7 +1084,7 @@ namespace mb200
 		p.pad_byte = c->pending_i8.pad;
 		// the int32 matrix the host set aside for the accumulators is not written by the fused kernel: its first 9 x cout words
 		// hold the border corrections when the padding value is not zero
-		if (p.pad_byte != 0 && volume(c->pending_i8.acc) >= 9LL * cout && aligned_to(c->pending_i8.acc.data, 4))
+		if (p.pad_byte != 0 && volume(c->pending_i8.acc) >= 9LL * cout && aligned_to(c->pending_i8.acc.data, 16))
 			p.border = reinterpret_cast<const int*>(c->pending_i8.acc.data);
 		c->pending_i8.stage = 0;
 		return run(ctx, 1, x, c->pending_i8.w.data, cout, p);
