@@ -11,7 +11,7 @@
  *   [hot]    implemented with hand-written sm_100a kernels (the convolution / matrix-multiply inference path)
  *   [next]   implemented: the layers adjacent to that path in minml's current architectures (batch-norm inference and
  *            folding, depthwise convolution fp / int8, squeeze-and-excitation channel scaling, RMS normalisation, space-to-depth
- *            and depth-to-space, and the backward-pass Winograd transforms with the fused activation / bias-gradient step)
+ *            and depth-to-space, the elementwise product of the Multiply layer, and the backward-pass Winograd transforms with the fused activation / bias-gradient step)
  *   [infra]  thin native wrapper over the CUDA runtime
  *   [stub]   exported so that minml links; records the sticky error "not implemented" on the context and
  *            launches nothing (training, MoE, pooling variants, ...)
@@ -205,7 +205,7 @@ void cuda_learnable_scaling_backward(mlContext_t context, float alpha, const mlT
 void cuda_emulate_low_precision(mlContext_t context, mlShape_t shape, mlDataType_t dtype, void *dst, const void *src, mlQuantizationData_t qd); /* [stub] [278] */
 void cuda_scale_tensor(mlContext_t context, float alpha, mlTensor_t x); /* [hot] [281] */
 void cuda_add_tensors(mlContext_t context, float alpha1, const mlTensor_t x1, float alpha2, const mlTensor_t x2, float alpha3, const mlTensor_t x3, float beta, mlTensor_t y); /* [hot] [283] */
-void cuda_multiply_tensors(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *dst, const void *src1, const void *src2); /* [stub] [285] */
+void cuda_multiply_tensors(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *dst, const void *src1, const void *src2); /* [next] [285] */
 void cuda_sum_over_first_dim(mlContext_t context, float alpha, const mlTensor_t src, float beta, mlTensor_t dst); /* [stub] [287] */
 
 /* ---- Training: losses and optimisers

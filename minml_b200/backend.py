@@ -200,6 +200,12 @@ def addTensors(ctx, y, alpha1=0.0, x1=None, alpha2=0.0, x2=None, alpha3=0.0, x3=
     ctx.check()
 
 
+def multiplyTensors(ctx, dst, src1, src2):
+    """ml::multiplyTensors: dst = src1 * src2 element by element (the Multiply layer)."""
+    lib.cuda_multiply_tensors(ctx.handle, dtype_of(dst), shape_of(dst), ptr(dst), ptr(src1), ptr(src2))
+    ctx.check()
+
+
 def globalAveragePoolingForward(ctx, x, y, alpha=1.0, beta=0.0):
     lib.cuda_global_average_pooling_forward(ctx.handle, alpha, desc(x), beta, desc(y))
     ctx.check()

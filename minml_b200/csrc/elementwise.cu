@@ -539,6 +539,30 @@ namespace mb200
 			else
 				kernel_softmax<T> <<<grid, 256, 0, stream>>>(yp, xp, rows, channels);
 		}
+		/* dst = src1 * src2, element by element (fp16 through fp32; fp64 stays fp64) */
+		template<typename T>
+		__global__ void __launch_bounds__(256) kernel_multiply_packets(T *__restrict__ dst, const T *__restrict__ a, const T *__restrict__ b, long long packets)
+		{
+			constexpr int N = Vec16<T>::N;
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < packets; i += stride)
+			{
+				float x[N], y[N];
+				Vec16<T>::load(a + i * N, x);
+				Vec16<T>::load(b + i * N, y);
+#pragma unroll
+				for (int k = 0; k < N; k++)
+					x[k] *= y[k];
+				Vec16<T>::store(dst + i * N, x);
+			}
+		}
+		template<typename T, typename ACC>
+		__global__ void __launch_bounds__(256) kernel_multiply_elements(T *__restrict__ dst, const T *__restrict__ a, const T *__restrict__ b, long long elements)
+		{
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < elements; i += stride)
+				dst[i] = static_cast<T>(static_cast<ACC>(a[i]) * static_cast<ACC>(b[i]));
+		}
 	}
 } /* namespace mb200 */
 
@@ -835,5 +859,45 @@ extern "C"
 		}
 		MB200_COUNT_LAUNCH();
 		check_cuda(context, cudaGetLastError(), "cuda_softmax_forward");
+	}
+	void cuda_multiply_tensors(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *dst, const void *src1, const void *src2)
+	{
+		MB200_REQUIRE(context, context != nullptr, "cuda_multiply_tensors: null context");
+		const long long elements = volume(shape);
+		if (elements == 0)
+			return; // an empty problem: nothing to validate or launch
+		MB200_REQUIRE(context, dst != nullptr && src1 != nullptr && src2 != nullptr, "cuda_multiply_tensors: null pointer");
+		flush_pending(context);
+		cudaStream_t stream = use_stream(context);
+		const int sm = get(context)->sm_count;
+		const bool packets = aligned_to(dst, 16) && aligned_to(src1, 16) && aligned_to(src2, 16);
+		switch (dtype)
+		{
+			case DTYPE_FLOAT16:
+				if (packets && elements % 8 == 0)
+					kernel_multiply_packets<__half> <<<grid_for(elements / 8, 256, sm), 256, 0, stream>>>(reinterpret_cast<__half*>(dst),
+							reinterpret_cast<const __half*>(src1), reinterpret_cast<const __half*>(src2), elements / 8);
+				else
+					kernel_multiply_elements<__half, float> <<<grid_for(elements, 256, sm), 256, 0, stream>>>(reinterpret_cast<__half*>(dst),
+							reinterpret_cast<const __half*>(src1), reinterpret_cast<const __half*>(src2), elements);
+				break;
+			case DTYPE_FLOAT32:
+				if (packets && elements % 4 == 0)
+					kernel_multiply_packets<float> <<<grid_for(elements / 4, 256, sm), 256, 0, stream>>>(reinterpret_cast<float*>(dst),
+							reinterpret_cast<const float*>(src1), reinterpret_cast<const float*>(src2), elements / 4);
+				else
+					kernel_multiply_elements<float, float> <<<grid_for(elements, 256, sm), 256, 0, stream>>>(reinterpret_cast<float*>(dst),
+							reinterpret_cast<const float*>(src1), reinterpret_cast<const float*>(src2), elements);
+				break;
+			case DTYPE_FLOAT64:
+				kernel_multiply_elements<double, double> <<<grid_for(elements, 256, sm), 256, 0, stream>>>(reinterpret_cast<double*>(dst),
+						reinterpret_cast<const double*>(src1), reinterpret_cast<const double*>(src2), elements);
+				break;
+			default:
+				record_error(context, "cuda_multiply_tensors: dtype %d not supported", static_cast<int>(dtype));
+				return;
+		}
+		MB200_COUNT_LAUNCH();
+		check_cuda(context, cudaGetLastError(), "cuda_multiply_tensors");
 	}
 }

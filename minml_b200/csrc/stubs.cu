@@ -170,10 +170,6 @@ extern "C"
 	{
 		NOT_IMPLEMENTED(context, "cuda_emulate_low_precision");
 	}
-	void cuda_multiply_tensors(mlContext_t context, mlDataType_t dtype, mlShape_t shape, void *dst, const void *src1, const void *src2) /* [285] */
-	{
-		NOT_IMPLEMENTED(context, "cuda_multiply_tensors");
-	}
 	void cuda_sum_over_first_dim(mlContext_t context, float alpha, const mlTensor_t src, float beta, mlTensor_t dst) /* [287] */
 	{
 		NOT_IMPLEMENTED(context, "cuda_sum_over_first_dim");

@@ -85,3 +85,19 @@ def test_shapes_that_do_not_fit_are_refused(ctx):
     with pytest.raises(B.BackendError):
         B.spaceToDepth(ctx, x, torch.zeros((1, 5, 5, 6), device="cuda"))  # 2 x 2 patches of 2 channels are 8, not 6
     ctx.synchronize()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
+@pytest.mark.parametrize("shape", [(4, 15, 15, 128), (7, 33), (1, 5)])
+def test_multiply_tensors(ctx, dtype, shape):
+    """cuda_multiply_tensors (the Multiply layer): dst = src1 * src2; one rounding of the exact product in the tensor's type
+    (the reference's CPU twin: src/backend/cpu/training.cpp:102-121)."""
+    from minml_b200 import backend as B
+    r = np.random.default_rng(sum(shape))
+    np_dtype = {torch.float32: np.float32, torch.float16: np.float16, torch.float64: np.float64}[dtype]
+    a, b = r.standard_normal(shape).astype(np_dtype), r.standard_normal(shape).astype(np_dtype)
+    y = torch.full(shape, float("nan"), device="cuda", dtype=dtype)
+    B.multiplyTensors(ctx, y, torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda())
+    ctx.synchronize()
+    want = (a.astype(np.float64) * b.astype(np.float64)).astype(np_dtype)
+    assert np.array_equal(y.cpu().numpy(), want)
