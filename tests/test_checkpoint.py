@@ -71,3 +71,21 @@ def test_oracle_forward_of_the_file_matches_the_outputs_minml_computed(oracle):
     assert float(want_value.max()) > 0.9 and np.ptp(want_value, axis=0).max() > 1e-3  # outputs depend on the input
     assert np.abs(policy - want_policy).max() <= 1e-5
     assert np.abs(value - want_value).max() <= 1e-5
+
+
+def test_old_format_and_other_dtypes():
+    """Files written before the header existed are the bare array of nodes (Graph::load, src/graph/Graph.cpp:502-510); tensors
+    may be fp16 or int8 (a quantised network)."""
+    import json
+    d, blob = C.load_file(golden("toy_network.bin"))
+    old = json.dumps(d["nodes"]).encode() + b"\n" + blob
+    d2, blob2 = C.load_bytes(old)
+    assert isinstance(d2, list) and C.nodes_of(d2) == d["nodes"] and blob2 == blob
+    half = np.arange(6, dtype=np.float16).tobytes()
+    q = np.array([-128, -1, 0, 127], np.int8).tobytes()
+    payload = half + q
+    t16 = C.read_tensor({"shape": [2, 3], "dtype": "FLOAT16", "binary_offset": 0}, payload)
+    t8 = C.read_tensor({"param": {"shape": [4], "dtype": "INT8", "binary_offset": len(half)}}, payload)
+    assert t16.dtype == np.float16 and t16.tolist() == [[0, 1, 2], [3, 4, 5]]
+    assert t8.dtype == np.int8 and t8.tolist() == [-128, -1, 0, 127]
+    assert C.read_tensor(None, payload) is None
