@@ -13,7 +13,8 @@ and a layer carries its configuration (`Layer::getConfig`, `src/layers/Layer.cpp
 its parameters `weights` / `bias` (`{"param": tensor, ...}`), `channel_scales`, and `avg_var` for batch normalisation.
 
 `load_file` parses a file; `LoadedNetwork` runs the layer kinds this library accelerates (Input, Conv2D, Dense, Add,
-BatchNormalization, GlobalAveragePooling, Softmax) through the C ABI, in fp32 or fp16. Any other layer kind raises.
+BatchNormalization, GlobalAveragePooling, Softmax, DepthwiseConv2D, RMSNormalization, ChannelScaling, SpaceToDepth,
+DepthToSpace) through the C ABI, in fp32 or fp16. Any other layer kind raises.
 """
 import json
 import zlib
@@ -78,7 +79,8 @@ def nodes_of(description):
     return description if isinstance(description, list) else description["nodes"]
 
 
-SUPPORTED = ("Input", "Conv2D", "Dense", "Add", "BatchNormalization", "GlobalAveragePooling", "Softmax")
+SUPPORTED = ("Input", "Conv2D", "Dense", "Add", "BatchNormalization", "GlobalAveragePooling", "Softmax", "DepthwiseConv2D",
+             "RMSNormalization", "ChannelScaling", "SpaceToDepth", "DepthToSpace")
 
 
 class LoadedNetwork:
@@ -141,6 +143,29 @@ class LoadedNetwork:
             elif kind == "GlobalAveragePooling":
                 shape = (self.shapes[ins[0]][0], self.shapes[ins[0]][-1])
                 step = ("pool", ins)
+            elif kind == "DepthwiseConv2D":
+                shape = self.shapes[ins[0]]
+                params = [torch.from_numpy(np.ascontiguousarray(w, np.float32)).to(dev).to(self.dtype),
+                          None if b is None else torch.from_numpy(np.ascontiguousarray(b, np.float32)).to(dev).to(self.dtype)]
+                step = ("depthwise", params, ins)
+            elif kind == "RMSNormalization":
+                shape = self.shapes[ins[0]]
+                gamma = None if w is None else torch.from_numpy(np.ascontiguousarray(w, np.float32)).to(dev).to(self.dtype)
+                step = ("rmsnorm", gamma, ins)
+            elif kind == "ChannelScaling":
+                shape = self.shapes[ins[0]]
+                step = ("channel_scaling", ins)
+            elif kind == "SpaceToDepth":
+                bsz, h, wd, c = self.shapes[ins[0]]
+                ph, pw = int(layer["patch_size_h"]), int(layer["patch_size_w"])
+                shape = (bsz, -(-h // ph), -(-wd // pw), c * ph * pw)
+                step = ("space_to_depth", ins)
+            elif kind == "DepthToSpace":
+                bsz, h, wd, c = self.shapes[ins[0]]
+                ph, pw = int(layer["patch_size_h"]), int(layer["patch_size_w"])
+                out_h, out_w = (int(v) for v in layer["output_shape"])
+                shape = (bsz, out_h, out_w, c // (ph * pw))
+                step = ("depth_to_space", ins)
             else:  # Softmax over all the axes after the first: rows of the flattened rest
                 axis = [int(a) for a in layer.get("axis", [])]
                 rank = len(self.shapes[ins[0]])
@@ -179,6 +204,16 @@ class LoadedNetwork:
                 B.batchnormInference(ctx, out[step[3][0]], out[index], gamma, beta, stats, step[2])
             elif step[0] == "pool":
                 B.globalAveragePoolingForward(ctx, out[step[1][0]], out[index])
+            elif step[0] == "depthwise":
+                B.depthwiseConvForward(ctx, out[step[2][0]], step[1][0], out[index], step[1][1])
+            elif step[0] == "rmsnorm":
+                B.rmsnormForward(ctx, out[step[2][0]], out[index], step[1])
+            elif step[0] == "channel_scaling":
+                B.channelScalingForward(ctx, out[step[1][0]], out[step[1][1]], out[index])
+            elif step[0] == "space_to_depth":
+                B.spaceToDepth(ctx, out[step[1][0]], out[index])
+            elif step[0] == "depth_to_space":
+                B.depthToSpace(ctx, out[step[1][0]], out[index])
             elif step[0] == "softmax":
                 src = out[step[1][0]]
                 B.softmaxForward(ctx, src.view(src.shape[0], -1), out[index])

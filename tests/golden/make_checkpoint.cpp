@@ -7,9 +7,13 @@
  *
  * Built by `make -C oracle checkpoint_fixture` against the reference checkout, run as
  *     oracle/_ref/make_checkpoint tests/golden
- * Topology (the trunk's layer kinds at toy size, 9x9 board, 4 planes, 16 channels, batch 3):
+ * toy_network: the trunk's layer kinds at toy size (9x9 board, 4 planes, 16 channels, batch 3):
  *     input -> conv3x3+relu -> batchnorm(relu) -> [conv3x3+relu -> conv3x3 -> add(relu)] x 2
  *           -> policy: conv1x1 -> softmax       -> value: global average pooling -> dense 3 -> softmax
+ * toy_block_network: the block of minml's current architectures (12x12 board, 4 planes, batch 2):
+ *     input -> space-to-depth 2x2 -> conv1x1 32 +relu
+ *           -> [depthwise 7x7 -> RMS norm -> conv1x1+relu -> conv1x1 -> squeeze-and-excitation (pooling, dense 8 relu, dense 32
+ *               sigmoid, channel scaling) -> add] -> policy: depth-to-space 2x2 -> conv1x1 -> softmax; value as above
  */
 #include <minml/core/Context.hpp>
 #include <minml/core/Device.hpp>
@@ -19,10 +23,15 @@
 #include <minml/graph/graph_optimizers.hpp>
 #include <minml/layers/Add.hpp>
 #include <minml/layers/BatchNormalization.hpp>
+#include <minml/layers/ChannelScaling.hpp>
 #include <minml/layers/Conv2D.hpp>
 #include <minml/layers/Dense.hpp>
+#include <minml/layers/DepthToSpace.hpp>
+#include <minml/layers/DepthwiseConv2D.hpp>
 #include <minml/layers/GlobalAveragePooling.hpp>
+#include <minml/layers/RMSNormalization.hpp>
 #include <minml/layers/Softmax.hpp>
+#include <minml/layers/SpaceToDepth.hpp>
 #include <minml/utils/file_util.hpp>
 #include <minml/utils/json.hpp>
 #include <minml/utils/serialization.hpp>
@@ -146,6 +155,71 @@ int main(int argc, char *argv[])
 	{
 		FileSaver fs(dir + "/toy_network_io.bin");
 		fs.save(io, io_binary, -1, false);
+	}
+
+	/* ---- the second network */
+	{
+		const int b2 = 2, board = 12, ch = 32;
+		Graph g2;
+		auto in = g2.addInput(Shape( { b2, board, board, planes }));
+		auto y2 = g2.add(SpaceToDepth(2), in);
+		y2 = g2.add(Conv2D(ch, 1, "relu"), y2);
+		auto t = g2.add(DepthwiseConv2D(ch, 7), y2);
+		t = g2.add(RMSNormalization(), t);
+		t = g2.add(Conv2D(ch, 1, "relu"), t);
+		t = g2.add(Conv2D(ch, 1, "linear"), t);
+		auto se = g2.add(GlobalAveragePooling(), t);
+		se = g2.add(Dense(8, "relu"), se);
+		se = g2.add(Dense(ch, "sigmoid"), se);
+		t = g2.add(ChannelScaling(), { t, se });
+		y2 = g2.add(Add("linear"), { t, y2 });
+		auto p2 = g2.add(DepthToSpace(2, Shape( { board, board })), y2);
+		p2 = g2.add(Conv2D(1, 1, "linear"), p2);
+		p2 = g2.add(Softmax( { 1, 2, 3 }), p2);
+		auto v2 = g2.add(GlobalAveragePooling(), y2);
+		v2 = g2.add(Dense(3, "linear"), v2);
+		v2 = g2.add(Softmax( { 1 }), v2);
+		g2.addOutput(p2);
+		g2.addOutput(v2);
+		g2.init();
+		for (int i = 0; i < g2.numberOfNodes(); i++)
+		{
+			Layer &layer = g2.getNode(i).getLayer();
+			Tensor &w = layer.getWeights().getParam();
+			if (layer.getBias().getParam().volume() > 0)
+				randomize(layer.getBias().getParam(), rng, -0.1f, 0.1f);
+			if (layer.name() == "Conv2D" or layer.name() == "Dense")
+			{
+				const bool head = w.dim(0) <= 3;
+				const float limit = head ? 1.0f : std::sqrt(6.0f / (w.volume() / w.dim(0)));
+				randomize(w, rng, -limit, limit);
+			}
+			else if (layer.name() == "DepthwiseConv2D")
+				randomize(w, rng, -0.25f, 0.25f);
+			else if (layer.name() == "RMSNormalization")
+				randomize(w, rng, 0.5f, 1.5f);
+		}
+		g2.makeTrainable(false);
+		SerializedObject binary2;
+		const Json description2 = g2.save(binary2);
+		{
+			FileSaver fs(dir + "/toy_block_network.bin");
+			fs.save(description2, binary2, 2, false);
+		}
+		std::vector<float> input2(static_cast<size_t>(b2) * board * board * planes);
+		for (float &v : input2)
+			v = (rng() % 10) < 3 ? 1.0f : 0.0f;
+		g2.getInput().copyFromHost(input2.data(), sizeof(float) * input2.size());
+		g2.predict(b2);
+		g2.context().synchronize();
+		SerializedObject io_binary2;
+		Json io2;
+		io2["input"] = g2.getInput().serialize(io_binary2);
+		io2["policy"] = g2.getOutput(0).serialize(io_binary2);
+		io2["value"] = g2.getOutput(1).serialize(io_binary2);
+		FileSaver fs(dir + "/toy_block_network_io.bin");
+		fs.save(io2, io_binary2, -1, false);
+		std::printf("wrote %s/toy_block_network{.bin,_io.bin}: %d nodes, %zu bytes of parameters\n", dir.c_str(), g2.numberOfNodes(), binary2.size());
 	}
 	std::printf("wrote %s/toy_network{.bin,_compressed.bin,_io.bin}: %d nodes, %zu bytes of parameters\n", dir.c_str(), g.numberOfNodes(),
 			binary.size());

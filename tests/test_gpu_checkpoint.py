@@ -12,12 +12,12 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-@pytest.mark.parametrize("name", ["toy_network.bin", "toy_network_compressed.bin"])
+@pytest.mark.parametrize("name", ["toy_network.bin", "toy_network_compressed.bin", "toy_block_network.bin"])
 @pytest.mark.parametrize("dtype,tolerance", [(torch.float32, 1e-4), (torch.float16, 1e-2)])
 @pytest.mark.parametrize("fused", [False, True])
 def test_loaded_network_reproduces_the_outputs_minml_computed(ctx, name, dtype, tolerance, fused):
     d, blob = C.load_file(os.path.join(GOLDEN, name))
-    io, io_blob = C.load_file(os.path.join(GOLDEN, "toy_network_io.bin"))
+    io, io_blob = C.load_file(os.path.join(GOLDEN, "toy_block_network_io.bin" if "block" in name else "toy_network_io.bin"))
     x = C.read_tensor(io["input"], io_blob)
     ctx.set_fusion(fused)
     try:

@@ -121,6 +121,17 @@ def forward_loaded_network_on_cpu(oracle, description, blob, x):
             y = oracle.add_bias_act(oracle.gemm("n", rows, "t", w), b if b is not None else np.zeros(w.shape[0], np.float32), act)
         elif kind == "Softmax":
             y = oracle.softmax(values[ins[0]].reshape(values[ins[0]].shape[0], -1))
+        elif kind == "DepthwiseConv2D":
+            y = oracle.depthwise_conv(values[ins[0]], w, b)
+        elif kind == "RMSNormalization":
+            y = oracle.rmsnorm(values[ins[0]], w)
+        elif kind == "ChannelScaling":
+            y = oracle.channel_scaling(values[ins[0]], values[ins[1]])
+        elif kind == "SpaceToDepth":
+            h, wd = values[ins[0]].shape[1:3]
+            y = oracle.space_to_depth(values[ins[0]], (-(-h // int(layer["patch_size_h"])), -(-wd // int(layer["patch_size_w"]))))
+        elif kind == "DepthToSpace":
+            y = oracle.depth_to_space(values[ins[0]], tuple(int(v) for v in layer["output_shape"]))
         else:
             raise NotImplementedError(kind)
         values.append(np.asarray(y, np.float32))
