@@ -1,5 +1,7 @@
 """Bandwidth-bound entry points on the GPU against the oracle: bias/activation, tensor sums, pooling, unpacking,
 conversion, transposition, softmax, layer norm, attention, and the eager int8 steps."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -251,3 +253,22 @@ def test_empty_tensors_launch_nothing_and_record_no_error(ctx):
     B.batchnormInference(ctx, x, y, bias, bias, torch.zeros((2, 128), device="cuda"), "relu")
     ctx.synchronize()
     assert B.launch_count() == before
+
+
+def test_kernel_bench_tool_runs_and_reports_every_kernel():
+    """The per-kernel timing tool (python -m minml_b200.kernel_bench) at the smallest configuration: one JSON line per kernel,
+    finite positive times, fractions of the peaks in range."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "minml_b200.kernel_bench", "--config", "c1", "--reps", "2"], cwd=root, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    records = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    names = [r["kernel"] for r in records]
+    assert len(records) >= 30 and len(set(names)) == len(names)
+    for needle in ("conv3x3 fused (fp16", "conv3x3 fused (int8", "gemm_batched", "multi_head_attention", "depthwise_conv_forward", "rmsnorm"):
+        assert any(needle in n for n in names), needle
+    for r in records:
+        assert 0.0 < r["ms"] < 100.0 and 0.0 < r["hbm_frac"] < 1.5, r
