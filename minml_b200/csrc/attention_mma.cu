@@ -14,12 +14,13 @@
  */
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace mb200
 {
 	namespace
 	{
 		constexpr int WARPS = 4;
-		constexpr int KEY_BLOCK = 64;
 
 		__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 		{
@@ -36,7 +37,6 @@ namespace mb200
 			return *reinterpret_cast<const uint32_t*>(&h);
 		}
 
-		/* D = head dimension (multiple of 16). */
 		constexpr float LOG2E = 1.4426950408889634f;
 		__device__ __forceinline__ float exp2_approx(float x)
 		{
@@ -45,7 +45,10 @@ namespace mb200
 			return y;
 		}
 
-		template<int D>
+		/* D = head dimension (multiple of 16); QT = query tiles of 16 rows a warp carries at once (every K and V fragment it loads
+		 * from shared memory then feeds QT products, and QT independent softmax chains hide each other's latencies); KB = keys per
+		 * block of the running softmax. */
+		template<int D, int QT, int KB>
 		__global__ void __launch_bounds__(WARPS * 32) kernel_mha_mma(__half *__restrict__ output, const __half *__restrict__ input,
 				const __half *__restrict__ table, int height, int width, int heads, int parts, int table_n, int table_pad)
 		{
@@ -54,7 +57,7 @@ namespace mb200
 			constexpr int NT = D / 8; // n-tiles of the second product
 			extern __shared__ __align__(16) unsigned char smem_raw[];
 			const int tokens = height * width;
-			const int padded = (tokens + KEY_BLOCK - 1) / KEY_BLOCK * KEY_BLOCK;
+			const int padded = (tokens + KB - 1) / KB * KB;
 			__half *sk = reinterpret_cast<__half*>(smem_raw);
 			__half *sv = sk + padded * LD;
 			float *st = reinterpret_cast<float*>(sv + padded * LD);
@@ -99,171 +102,232 @@ namespace mb200
 			const float scale = rsqrtf(static_cast<float>(D)) * LOG2E; // exp(x) = 2^(x log2 e): one multiply less per score
 			const uint32_t sv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(sv));
 
-			for (int q0 = warp * 16; q0 < tokens; q0 += WARPS * 16)
+			for (int q0 = warp * 16 * QT; q0 < tokens; q0 += WARPS * 16 * QT)
 			{
-				// Q fragments of rows q0 + g and q0 + g + 8
-				uint32_t qa[KC][4];
-				const int r0 = q0 + g, r1 = q0 + g + 8;
+				// per query tile t: Q fragments of rows r[t][0] = q0 + 16 t + g and r[t][1] = r[t][0] + 8
+				uint32_t qa[QT][KC][4];
+				int r[QT][2], lin[QT][2], qh[QT][2], qw[QT][2];
+				float o[QT][NT][4], m[QT][2], l[QT][2];
 #pragma unroll
-				for (int kc = 0; kc < KC; kc++)
+				for (int t = 0; t < QT; t++)
 				{
-					const int col = head * D + kc * 16 + tig * 2;
-					qa[kc][0] = (r0 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r0) * stride + col) : 0u;
-					qa[kc][1] = (r1 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r1) * stride + col) : 0u;
-					qa[kc][2] = (r0 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r0) * stride + col + 8) : 0u;
-					qa[kc][3] = (r1 < tokens) ? *reinterpret_cast<const uint32_t*>(base + static_cast<long long>(r1) * stride + col + 8) : 0u;
-				}
-				const int p0 = spos[min(r0, tokens - 1)], p1 = spos[min(r1, tokens - 1)];
-				const int qh0 = p0 >> 16, qw0 = p0 & 0xFFFF, qh1 = p1 >> 16, qw1 = p1 & 0xFFFF; // clamped form
-				const int lin0 = range * (table_pad + 1) - p0, lin1 = range * (table_pad + 1) - p1; // linear form
-
-				float o[NT][4];
+					r[t][0] = q0 + t * 16 + g;
+					r[t][1] = r[t][0] + 8;
 #pragma unroll
-				for (int n = 0; n < NT; n++)
-#pragma unroll
-					for (int k = 0; k < 4; k++)
-						o[n][k] = 0.0f;
-				float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
-
-				for (int kb = 0; kb < padded; kb += KEY_BLOCK)
-				{
-					float s[KEY_BLOCK / 8][4];
-#pragma unroll
-					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
+					for (int kc = 0; kc < KC; kc++)
 					{
+						const int col = head * D + kc * 16 + tig * 2;
+#pragma unroll
+						for (int half = 0; half < 2; half++)
+						{
+							const bool ok = r[t][half] < tokens;
+							const __half *src = base + static_cast<long long>(r[t][half]) * stride + col;
+							qa[t][kc][half] = ok ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+							qa[t][kc][2 + half] = ok ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+						}
+					}
+#pragma unroll
+					for (int half = 0; half < 2; half++)
+					{
+						const int pq = spos[min(r[t][half], tokens - 1)];
+						qh[t][half] = pq >> 16; // clamped form
+						qw[t][half] = pq & 0xFFFF;
+						lin[t][half] = range * (table_pad + 1) - pq; // linear form
+						m[t][half] = -1.0e30f;
+						l[t][half] = 0.0f;
+					}
+#pragma unroll
+					for (int n = 0; n < NT; n++)
 #pragma unroll
 						for (int k = 0; k < 4; k++)
-							s[nt][k] = 0.0f;
+							o[t][n][k] = 0.0f;
+				}
+
+				for (int kb = 0; kb < padded; kb += KB)
+				{
+					float s[QT][KB / 8][4];
+#pragma unroll
+					for (int nt = 0; nt < KB / 8; nt++)
+					{
+#pragma unroll
+						for (int t = 0; t < QT; t++)
+#pragma unroll
+							for (int k = 0; k < 4; k++)
+								s[t][nt][k] = 0.0f;
 						const __half *krow = sk + (kb + nt * 8 + g) * LD + tig * 2;
 #pragma unroll
 						for (int kc = 0; kc < KC; kc++)
 						{
 							const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kc * 16);
 							const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kc * 16 + 8);
-							mma_16816(s[nt], qa[kc], b0, b1);
+#pragma unroll
+							for (int t = 0; t < QT; t++)
+								mma_16816(s[t][nt], qa[t][kc], b0, b1);
 						}
 					}
-					// scale, relative-position bias, mask keys beyond the last token; block maxima
-					float bm0 = -1.0e30f, bm1 = -1.0e30f;
 #pragma unroll
-					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
-#pragma unroll
-						for (int e = 0; e < 2; e++)
-						{
-							const int j = kb + nt * 8 + tig * 2 + e;
-							float v0 = s[nt][e] * scale, v1 = s[nt][2 + e] * scale;
-							if (table != nullptr)
-							{
-								const int pj = spos[j];
-								if (linear_bias)
-								{
-									v0 += st[pj + lin0];
-									v1 += st[pj + lin1];
-								}
-								else
-								{
-									const int jh = pj >> 16, jw = pj & 0xFFFF;
-									v0 += st[(min(max(jh - qh0, -range), range) + range) * table_pad + min(max(jw - qw0, -range), range) + range];
-									v1 += st[(min(max(jh - qh1, -range), range) + range) * table_pad + min(max(jw - qw1, -range), range) + range];
-								}
-							}
-							if (kb + KEY_BLOCK > tokens && j >= tokens)
-							{
-								v0 = -1.0e30f;
-								v1 = -1.0e30f;
-							}
-							s[nt][e] = v0;
-							s[nt][2 + e] = v1;
-							bm0 = fmaxf(bm0, v0);
-							bm1 = fmaxf(bm1, v1);
-						}
-					bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
-					bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
-					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
-					bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
-					const float n0 = fmaxf(m0, bm0), n1 = fmaxf(m1, bm1);
-					const float c0 = exp2_approx(m0 - n0), c1 = exp2_approx(m1 - n1);
-					m0 = n0;
-					m1 = n1;
-					float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-					for (int nt = 0; nt < KEY_BLOCK / 8; nt++)
-#pragma unroll
-						for (int e = 0; e < 2; e++)
-						{
-							const float e0 = exp2_approx(s[nt][e] - n0), e1 = exp2_approx(s[nt][2 + e] - n1);
-							s[nt][e] = e0;
-							s[nt][2 + e] = e1;
-							sum0 += e0;
-							sum1 += e1;
-						}
-					l0 = l0 * c0 + sum0;
-					l1 = l1 * c1 + sum1;
-#pragma unroll
-					for (int n = 0; n < NT; n++)
+					for (int t = 0; t < QT; t++)
 					{
-						o[n][0] *= c0;
-						o[n][1] *= c0;
-						o[n][2] *= c1;
-						o[n][3] *= c1;
+						// scale, relative-position bias, mask keys beyond the last token; block maxima
+						float bm0 = -1.0e30f, bm1 = -1.0e30f;
+#pragma unroll
+						for (int nt = 0; nt < KB / 8; nt++)
+#pragma unroll
+							for (int e = 0; e < 2; e++)
+							{
+								const int j = kb + nt * 8 + tig * 2 + e;
+								float v0 = s[t][nt][e] * scale, v1 = s[t][nt][2 + e] * scale;
+								if (table != nullptr)
+								{
+									const int pj = spos[j];
+									if (linear_bias)
+									{
+										v0 += st[pj + lin[t][0]];
+										v1 += st[pj + lin[t][1]];
+									}
+									else
+									{
+										const int jh = pj >> 16, jw = pj & 0xFFFF;
+										v0 += st[(min(max(jh - qh[t][0], -range), range) + range) * table_pad + min(max(jw - qw[t][0], -range), range) + range];
+										v1 += st[(min(max(jh - qh[t][1], -range), range) + range) * table_pad + min(max(jw - qw[t][1], -range), range) + range];
+									}
+								}
+								if (kb + KB > tokens && j >= tokens)
+								{
+									v0 = -1.0e30f;
+									v1 = -1.0e30f;
+								}
+								s[t][nt][e] = v0;
+								s[t][nt][2 + e] = v1;
+								bm0 = fmaxf(bm0, v0);
+								bm1 = fmaxf(bm1, v1);
+							}
+						bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 1));
+						bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, 2));
+						bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 1));
+						bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, 2));
+						const float n0 = fmaxf(m[t][0], bm0), n1 = fmaxf(m[t][1], bm1);
+						const float c0 = exp2_approx(m[t][0] - n0), c1 = exp2_approx(m[t][1] - n1);
+						m[t][0] = n0;
+						m[t][1] = n1;
+						float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+						for (int nt = 0; nt < KB / 8; nt++)
+#pragma unroll
+							for (int e = 0; e < 2; e++)
+							{
+								const float e0 = exp2_approx(s[t][nt][e] - n0), e1 = exp2_approx(s[t][nt][2 + e] - n1);
+								s[t][nt][e] = e0;
+								s[t][nt][2 + e] = e1;
+								sum0 += e0;
+								sum1 += e1;
+							}
+						l[t][0] = l[t][0] * c0 + sum0;
+						l[t][1] = l[t][1] * c1 + sum1;
+#pragma unroll
+						for (int n = 0; n < NT; n++)
+						{
+							o[t][n][0] *= c0;
+							o[t][n][1] *= c0;
+							o[t][n][2] *= c1;
+							o[t][n][3] *= c1;
+						}
 					}
 					// O += P V: the accumulator layout of two neighbouring score tiles is the A-fragment layout of one k16 step
 #pragma unroll
-					for (int kc = 0; kc < KEY_BLOCK / 16; kc++)
+					for (int kc = 0; kc < KB / 16; kc++)
 					{
-						uint32_t pa[4];
-						pa[0] = pack_half2(s[2 * kc][0], s[2 * kc][1]);
-						pa[1] = pack_half2(s[2 * kc][2], s[2 * kc][3]);
-						pa[2] = pack_half2(s[2 * kc + 1][0], s[2 * kc + 1][1]);
-						pa[3] = pack_half2(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+						uint32_t pa[QT][4];
+#pragma unroll
+						for (int t = 0; t < QT; t++)
+						{
+							pa[t][0] = pack_half2(s[t][2 * kc][0], s[t][2 * kc][1]);
+							pa[t][1] = pack_half2(s[t][2 * kc][2], s[t][2 * kc][3]);
+							pa[t][2] = pack_half2(s[t][2 * kc + 1][0], s[t][2 * kc + 1][1]);
+							pa[t][3] = pack_half2(s[t][2 * kc + 1][2], s[t][2 * kc + 1][3]);
+						}
 #pragma unroll
 						for (int n = 0; n < NT; n++)
 						{
 							uint32_t b0, b1;
 							// lanes 0-15 name the 16 key rows of this step; the transposing load returns V^T fragments
 							ldmatrix_x2_trans(b0, b1, sv_addr + static_cast<uint32_t>(((kb + kc * 16 + (lane & 15)) * LD + n * 8) * 2));
-							mma_16816(o[n], pa, b0, b1);
+#pragma unroll
+							for (int t = 0; t < QT; t++)
+								mma_16816(o[t][n], pa[t], b0, b1);
 						}
 					}
 				}
-				// the row sums live in the four lanes of a quad
-				l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-				l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-				l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-				l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-				const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
 				__half *out = output + static_cast<long long>(b) * tokens * heads * D + head * D;
 #pragma unroll
-				for (int n = 0; n < NT; n++)
+				for (int t = 0; t < QT; t++)
 				{
-					if (r0 < tokens)
-						*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r0) * heads * D + n * 8 + tig * 2) = pack_half2(o[n][0] * inv0,
-								o[n][1] * inv0);
-					if (r1 < tokens)
-						*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r1) * heads * D + n * 8 + tig * 2) = pack_half2(o[n][2] * inv1,
-								o[n][3] * inv1);
+					// the row sums live in the four lanes of a quad
+					float l0 = l[t][0], l1 = l[t][1];
+					l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+					l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+					l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+					l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+					const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+#pragma unroll
+					for (int n = 0; n < NT; n++)
+					{
+						if (r[t][0] < tokens)
+							*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r[t][0]) * heads * D + n * 8 + tig * 2) = pack_half2(o[t][n][0] * inv0,
+									o[t][n][1] * inv0);
+						if (r[t][1] < tokens)
+							*reinterpret_cast<uint32_t*>(out + static_cast<long long>(r[t][1]) * heads * D + n * 8 + tig * 2) = pack_half2(o[t][n][2] * inv1,
+									o[t][n][3] * inv1);
+					}
 				}
 			}
 		}
 
-		template<int D>
+		template<int D, int QT, int KB>
 		bool launch(mlContext_t ctx, __half *output, const __half *input, const __half *table, int batch, int height, int width, int heads, int parts,
 				int table_n, int table_pad)
 		{
 			const int tokens = height * width;
-			const int padded = (tokens + KEY_BLOCK - 1) / KEY_BLOCK * KEY_BLOCK;
+			const int padded = (tokens + KB - 1) / KB * KB;
 			const size_t smem = static_cast<size_t>(2) * padded * (D + 8) * sizeof(__half) + static_cast<size_t>(table_n) * table_pad * sizeof(float)
 					+ static_cast<size_t>(padded) * sizeof(int);
 			if (smem > 200 * 1024)
 				return false;
-			if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_mha_mma<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+			if (!check_cuda(ctx, cudaFuncSetAttribute(kernel_mha_mma<D, QT, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
 					"attention: shared memory opt-in"))
 				return false;
-			kernel_mha_mma<D> <<<dim3(heads, batch), WARPS * 32, smem, use_stream(ctx)>>>(output, input, table, height, width, heads, parts, table_n,
-					table_pad);
+			kernel_mha_mma<D, QT, KB> <<<dim3(heads, batch), WARPS * 32, smem, use_stream(ctx)>>>(output, input, table, height, width, heads, parts,
+					table_n, table_pad);
 			MB200_COUNT_LAUNCH();
 			check_cuda(ctx, cudaGetLastError(), "cuda_multi_head_attention_forward");
 			return true;
+		}
+		/* Variant by environment for measurements: MINML_B200_MHA_VARIANT = 0 (one query tile, 64 keys), 1 (two tiles, 64 keys),
+		 * 2 (two tiles, 32 keys: the default), 3 (one tile, 32 keys). */
+		int mha_variant()
+		{
+			static const int v = []
+			{
+				const char *e = std::getenv("MINML_B200_MHA_VARIANT");
+				return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 2;
+			}();
+			return v;
+		}
+		template<int D>
+		bool launch_small_head(mlContext_t ctx, __half *o, const __half *x, const __half *t, int batch, int height, int width, int heads, int parts,
+				int table_n, int table_pad)
+		{
+			switch (mha_variant())
+			{
+				case 0:
+					return launch<D, 1, 64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				case 1:
+					return launch<D, 2, 64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				case 3:
+					return launch<D, 1, 32>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				default:
+					return launch<D, 2, 32>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+			}
 		}
 	}
 
@@ -281,13 +345,13 @@ namespace mb200
 		switch (head_dim)
 		{
 			case 16:
-				return launch<16>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				return launch_small_head<16>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
 			case 32:
-				return launch<32>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				return launch_small_head<32>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
 			case 64:
-				return launch<64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				return launch<64, 1, 64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
 			case 128:
-				return launch<128>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
+				return launch<128, 1, 64>(ctx, o, x, t, batch, height, width, heads, parts, table_n, table_pad);
 			default:
 				return false;
 		}
