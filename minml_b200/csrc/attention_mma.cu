@@ -6,8 +6,9 @@
  *   input  [b, h, w, parts * heads * d]   packed [q | k | v] (parts = 3) or [q = k | v] (parts = 2)
  *   S = Q K^T / sqrt(d);  S[i, j] += table[head, r + clamp(hj - hi, -r, r), r + clamp(wj - wi, -r, r)];  P = softmax(S);  O = P V
  *
- * One CTA per (head, batch item) stages K and V of that head in shared memory once; each of its 4 warps owns 16 queries at
- * a time and walks the keys in blocks of 64 with a running maximum and sum, keeping S, P and O in registers.
+ * One CTA per (head, batch item) stages K and V of that head in shared memory once; each of its 4 warps owns one or two tiles
+ * of 16 queries at a time and walks the keys in blocks of 32 or 64 with a running maximum and sum, keeping S, P and O in
+ * registers (head dimensions up to 32: two tiles, 32 keys; larger ones: one tile, 64 keys).
  * Tokens here are at most a few hundred (a 20x20 board has 400) with head dimensions of 16-128, shapes for which a
  * tcgen05 tile (M = 128, accumulators in tensor memory, both operands from shared memory) would spend most of its cycles on
  * layout changes between the two products; the warp-level instruction keeps P in the accumulator registers it came from.
