@@ -258,7 +258,9 @@ void mb200_selftest_bounded_wait(mlContext_t context, int polls);
  * (fp16 or fp32, 3x3 weights [cout, 3, 3, cin]); the transformed weights, transformed input and products live in a fixed
  * MB200_NOALLOC_SCRATCH_BYTES array inside the library image (held by every GPU that loads the library until the process
  * exits) instead of the context workspace.  A problem needing more than that (36 * elem * (cout*cin + tiles*cin + tiles*cout),
- * tiles = b * ceil(h/4) * ceil(w/4)) is refused with an error on the context.  The call performs no cudaMalloc / cudaFree.
+ * tiles = b * ceil(h/4) * ceil(w/4)) is refused with an error on the context.  The call performs no cudaMalloc / cudaFree;
+ * the CUDA runtime itself loads each kernel's code on its first launch, so warm up once per data type and shape class (or
+ * set CUDA_MODULE_LOADING=EAGER) before the phase in which nothing may be allocated.
  * All calls on a device share the array: calls on one context are ordered by its stream, calls that overlap on the GPU
  * (different contexts) race.  The first call on each device resolves the array's device address; issue it before any
  * stream capture begins. */

@@ -1,6 +1,6 @@
 """Per-kernel timing of every hot entry point of the backend at the sizes of the benchmark configurations.
 
-    python -m minml_b200.kernel_bench [--config c3|c1|c2|c4] [--reps N] [--only substring]
+    python kernel_bench.py [--config c3|c1|c2|c4] [--reps N] [--only substring]
 
 Each entry point is timed alone with CUDA events on the context's stream (3 warm-up calls, N timed calls).  For every kernel
 the line gives the time, the algorithmic bytes (each input read once, each output written once) and FLOPs of one call, and
@@ -11,14 +11,17 @@ c3 exceed the L2 cache; smaller configurations are noted as L2-resident in the o
 import argparse
 import json
 import os
+import sys
 
 import numpy as np
 import torch
 
-from . import backend as B
-from . import layers as L
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from minml_b200 import backend as B  # noqa: E402
+from minml_b200 import layers as L  # noqa: E402
 
 SIZES = {
     "c3": dict(batch=1024, h=20, w=20, c=256, planes=32),

@@ -39,7 +39,14 @@ def shape_of(t_or_dims):
     return s
 
 
-def desc(t):
+def _check_device(t, ctx):
+    """A tensor handed to a context must live on that context's device: a kernel launched on one GPU's stream with another GPU's
+    pointer faults (or, with peer access, silently reads across NVLink).  Raised here, on the host, before any launch."""
+    if ctx is not None and t.is_cuda and t.device.index != ctx.device_index:
+        raise BackendError("tensor on cuda:%d passed to a context of cuda:%d" % (t.device.index, ctx.device_index))
+
+
+def desc(t, ctx=None):
     """mlTensor_t for a dense torch tensor; None gives the empty descriptor (null data, rank 0)."""
     d = mlTensor_t()
     if t is None:
@@ -48,6 +55,7 @@ def desc(t):
         d.rank = 0
         return d
     assert t.is_contiguous(), "the backend ABI addresses dense row-major tensors only"
+    _check_device(t, ctx)
     d.data = t.data_ptr()
     d.dtype = dtype_of(t)
     d.rank = t.dim()
@@ -56,8 +64,11 @@ def desc(t):
     return d
 
 
-def ptr(t):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+def ptr(t, ctx=None):
+    if t is None:
+        return None
+    _check_device(t, ctx)
+    return ctypes.c_void_p(t.data_ptr())
 
 
 def act_code(act):
@@ -72,6 +83,7 @@ class Context:
         if n == 0:
             raise BackendError("no CUDA device: libminml_b200 has no CPU fallback")
         self.device_index = device_index
+        self.device = torch.device("cuda", device_index)  # where tensors handed to this context must live
         self.handle = lib.cuda_create_context(device_index)
         if not self.handle:
             raise BackendError("cuda_create_context failed: %s" % _last_error(None))
@@ -132,19 +144,19 @@ def launch_count():
 # ---------------------------------------------------------------------------------------------- Winograd
 def winogradWeightTransform(ctx, weight, matrices, invert=False, tile_size=None):
     tile = tile_size if tile_size is not None else _tile_size(matrices, weight.shape[1])
-    lib.cuda_winograd_weight_transform(ctx.handle, tile, desc(weight), desc(matrices), bool(invert))
+    lib.cuda_winograd_weight_transform(ctx.handle, tile, desc(weight, ctx), desc(matrices, ctx), bool(invert))
     ctx.check()
 
 
 def winogradInputTransform(ctx, weight_shape, x, matrices, tile_size=None):
     tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
-    lib.cuda_winograd_input_transform(ctx.handle, tile, desc(x), desc(matrices))
+    lib.cuda_winograd_input_transform(ctx.handle, tile, desc(x, ctx), desc(matrices, ctx))
     ctx.check()
 
 
 def winogradOutputTransform(ctx, weight_shape, matrices, output, bias=None, ext=None, act="linear", tile_size=None):
     tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
-    lib.cuda_winograd_output_transform(ctx.handle, tile, desc(matrices), desc(bias), desc(ext), desc(output), act_code(act))
+    lib.cuda_winograd_output_transform(ctx.handle, tile, desc(matrices, ctx), desc(bias, ctx), desc(ext, ctx), desc(output, ctx), act_code(act))
     ctx.check()
 
 
@@ -156,102 +168,102 @@ def _tile_size(matrices, kernel):
 
 # ---------------------------------------------------------------------------------------------- GEMM
 def gemm(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0):
-    lib.cuda_gemm_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A), desc(B), beta, desc(C))
+    lib.cuda_gemm_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A, ctx), desc(B, ctx), beta, desc(C, ctx))
     ctx.check()
 
 
 def gemmBatched(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0):
-    lib.cuda_gemm_batched_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A), desc(B), beta, desc(C))
+    lib.cuda_gemm_batched_v2(ctx.handle, opA.encode(), opB.encode(), alpha, desc(A, ctx), desc(B, ctx), beta, desc(C, ctx))
     ctx.check()
 
 
 def gemm_legacy(ctx, opA, A, opB, B, C, alpha=1.0, beta=0.0, batched=False):
     fn = lib.cuda_gemm_batched if batched else lib.cuda_gemm
-    fn(ctx.handle, dtype_of(C), shape_of(C), ptr(C), shape_of(A), ptr(A), shape_of(B), ptr(B), opA.encode(), opB.encode(), alpha, beta)
+    fn(ctx.handle, dtype_of(C), shape_of(C), ptr(C, ctx), shape_of(A), ptr(A, ctx), shape_of(B), ptr(B, ctx), opA.encode(), opB.encode(), alpha, beta)
     ctx.check()
 
 
 def gemm_ex(ctx, D, alpha, opA, A, opB, B, beta, C, bias, act):
-    lib.cuda_gemm_ex(ctx.handle, dtype_of(D), shape_of(D), ptr(D), alpha, opA.encode(), shape_of(A), ptr(A), opB.encode(), shape_of(B), ptr(B),
-                     beta, shape_of(C if C is not None else D), ptr(C), ptr(bias), act_code(act))
+    lib.cuda_gemm_ex(ctx.handle, dtype_of(D), shape_of(D), ptr(D, ctx), alpha, opA.encode(), shape_of(A), ptr(A, ctx), opB.encode(), shape_of(B), ptr(B, ctx),
+                     beta, shape_of(C if C is not None else D), ptr(C, ctx), ptr(bias, ctx), act_code(act))
     ctx.check()
 
 
 # ---------------------------------------------------------------------------------------------- fused convolution
 def convolutionImplicitGemmForward(ctx, x, weights, output, bias=None, add=None, act="linear"):
-    lib.cuda_convolution_implicit_gemm_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(weights), ptr(x), ptr(weights), ptr(output),
-                                               ptr(bias), ptr(add), act_code(act))
+    lib.cuda_convolution_implicit_gemm_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(weights), ptr(x, ctx), ptr(weights, ctx), ptr(output, ctx),
+                                               ptr(bias, ctx), ptr(add, ctx), act_code(act))
     ctx.check()
 
 
 # ---------------------------------------------------------------------------------------------- elementwise
 def addBiasAct(ctx, x, bias, y, act="linear", alpha=1.0, beta=0.0):
-    lib.cuda_add_bias_act(ctx.handle, alpha, desc(x), desc(bias), beta, desc(y), act_code(act))
+    lib.cuda_add_bias_act(ctx.handle, alpha, desc(x, ctx), desc(bias, ctx), beta, desc(y, ctx), act_code(act))
     ctx.check()
 
 
 def activationForward(ctx, x, y, act, alpha=1.0, beta=0.0):
-    lib.cuda_activation_forward(ctx.handle, alpha, desc(x), beta, desc(y), act_code(act))
+    lib.cuda_activation_forward(ctx.handle, alpha, desc(x, ctx), beta, desc(y, ctx), act_code(act))
     ctx.check()
 
 
 def addTensors(ctx, y, alpha1=0.0, x1=None, alpha2=0.0, x2=None, alpha3=0.0, x3=None, beta=0.0):
-    lib.cuda_add_tensors(ctx.handle, alpha1, desc(x1), alpha2, desc(x2), alpha3, desc(x3), beta, desc(y))
+    lib.cuda_add_tensors(ctx.handle, alpha1, desc(x1, ctx), alpha2, desc(x2, ctx), alpha3, desc(x3, ctx), beta, desc(y, ctx))
     ctx.check()
 
 
 def multiplyTensors(ctx, dst, src1, src2):
     """ml::multiplyTensors: dst = src1 * src2 element by element (the Multiply layer)."""
-    lib.cuda_multiply_tensors(ctx.handle, dtype_of(dst), shape_of(dst), ptr(dst), ptr(src1), ptr(src2))
+    lib.cuda_multiply_tensors(ctx.handle, dtype_of(dst), shape_of(dst), ptr(dst, ctx), ptr(src1, ctx), ptr(src2, ctx))
     ctx.check()
 
 
 def globalAveragePoolingForward(ctx, x, y, alpha=1.0, beta=0.0):
-    lib.cuda_global_average_pooling_forward(ctx.handle, alpha, desc(x), beta, desc(y))
+    lib.cuda_global_average_pooling_forward(ctx.handle, alpha, desc(x, ctx), beta, desc(y, ctx))
     ctx.check()
 
 
 def softmaxForward(ctx, x, y):
-    lib.cuda_softmax_forward(ctx.handle, dtype_of(x), shape_of(x), ptr(y), ptr(x))
+    lib.cuda_softmax_forward(ctx.handle, dtype_of(x), shape_of(x), ptr(y, ctx), ptr(x, ctx))
     ctx.check()
 
 
 def unpackInput(ctx, packed, dst):
-    lib.cuda_unpack_input(ctx.handle, shape_of(dst), dtype_of(dst), ptr(dst), ptr(packed))
+    lib.cuda_unpack_input(ctx.handle, shape_of(dst), dtype_of(dst), ptr(dst, ctx), ptr(packed, ctx))
     ctx.check()
 
 
 def convertType(ctx, dst, src):
-    lib.cuda_convert_type(ctx.handle, ptr(dst), dtype_of(dst), ptr(src), dtype_of(src), src.numel())
+    lib.cuda_convert_type(ctx.handle, ptr(dst, ctx), dtype_of(dst), ptr(src, ctx), dtype_of(src), src.numel())
     ctx.check()
 
 
 def transpose_021(ctx, src, dst):
-    lib.cuda_transpose_021(ctx.handle, dtype_of(src), shape_of(src), ptr(src), ptr(dst))
+    lib.cuda_transpose_021(ctx.handle, dtype_of(src), shape_of(src), ptr(src, ctx), ptr(dst, ctx))
     ctx.check()
 
 
 # ---------------------------------------------------------------------------------------------- norms, attention
 def layernormForward(ctx, x, y, weights, bias, ext=None):
-    lib.cuda_layernorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x), ptr(y), ptr(weights), ptr(bias), ptr(ext))
+    lib.cuda_layernorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x, ctx), ptr(y, ctx), ptr(weights, ctx), ptr(bias, ctx), ptr(ext, ctx))
     ctx.check()
 
 
 def rmsnormForward(ctx, x, y, weights=None):
     """ml::rmsnormForward (src/core/math.cpp): y = weights * x / (1e-6 + rms(x)) over the last axis; weights may be None."""
-    lib.cuda_rmsnorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x), ptr(y), ptr(weights))
+    lib.cuda_rmsnorm_forward(ctx.handle, shape_of(x), dtype_of(x), ptr(x, ctx), ptr(y, ctx), ptr(weights, ctx))
     ctx.check()
 
 
 def spaceToDepth(ctx, x, y):
     """ml::spaceToDepth: [b, h, w, c] -> [b, ceil(h/p), ceil(w/q), p*q*c]; the patch size follows from the two shapes."""
-    lib.cuda_space_to_depth(ctx.handle, dtype_of(x), shape_of(x), ptr(x), shape_of(y), ptr(y))
+    lib.cuda_space_to_depth(ctx.handle, dtype_of(x), shape_of(x), ptr(x, ctx), shape_of(y), ptr(y, ctx))
     ctx.check()
 
 
 def depthToSpace(ctx, x, y):
     """ml::depthToSpace: the inverse of spaceToDepth."""
-    lib.cuda_depth_to_space(ctx.handle, dtype_of(x), shape_of(x), ptr(x), shape_of(y), ptr(y))
+    lib.cuda_depth_to_space(ctx.handle, dtype_of(x), shape_of(x), ptr(x, ctx), shape_of(y), ptr(y, ctx))
     ctx.check()
 
 
@@ -261,8 +273,8 @@ def multiHeadAttentionGetWorkspaceSize(x_shape, weights_shape, num_heads, traini
 
 def multiHeadAttentionForward(ctx, x, y, weights, num_heads, symmetric=False, workspace=None):
     wshape = shape_of(weights) if weights is not None else shape_of([])
-    lib.cuda_multi_head_attention_forward(ctx.handle, shape_of(x), wshape, shape_of([]), dtype_of(x), ptr(x), ptr(y), ptr(weights), None,
-                                          ptr(workspace), None, num_heads, bool(symmetric))
+    lib.cuda_multi_head_attention_forward(ctx.handle, shape_of(x), wshape, shape_of([]), dtype_of(x), ptr(x, ctx), ptr(y, ctx), ptr(weights, ctx), None,
+                                          ptr(workspace, ctx), None, num_heads, bool(symmetric))
     ctx.check()
 
 
@@ -281,69 +293,69 @@ def im2row(ctx, x, output, kernel_size, invert=False, padding=None):
     if padding is not None:
         keep = torch.as_tensor(padding, dtype=x.dtype, device="cpu").reshape(1).contiguous()
         pad_ptr = ctypes.c_void_p(keep.data_ptr())
-    lib.cuda_im2row(ctx.handle, dtype_of(x), shape_of(x), ptr(output), ptr(x), kernel_size, bool(invert), pad_ptr)
+    lib.cuda_im2row(ctx.handle, dtype_of(x), shape_of(x), ptr(output, ctx), ptr(x, ctx), kernel_size, bool(invert), pad_ptr)
     ctx.check()
     del keep
 
 
 def quantized_scale_shift_act(ctx, output, output_qd, acc_i32, scales, bias, act="linear", ext=None, ext_qd=(1.0, 0.0)):
-    lib.cuda_quantized_scale_shift_act(ctx.handle, dtype_of(output), shape_of(output), ptr(output), qdata(*output_qd), ptr(acc_i32), ptr(scales),
-                                       ptr(bias), act_code(act), ptr(ext), qdata(*ext_qd))
+    lib.cuda_quantized_scale_shift_act(ctx.handle, dtype_of(output), shape_of(output), ptr(output, ctx), qdata(*output_qd), ptr(acc_i32, ctx), ptr(scales, ctx),
+                                       ptr(bias, ctx), act_code(act), ptr(ext, ctx), qdata(*ext_qd))
     ctx.check()
 
 
 def dequantize(ctx, src_i8, dst, scale, shift):
-    lib.cuda_dequantize(ctx.handle, dtype_of(dst), ptr(src_i8), ptr(dst), src_i8.numel(), float(scale), float(shift))
+    lib.cuda_dequantize(ctx.handle, dtype_of(dst), ptr(src_i8, ctx), ptr(dst, ctx), src_i8.numel(), float(scale), float(shift))
     ctx.check()
 
 
 # ---------------------------------------------------------------------------------------------- layers next to the convolution path
 def batchnormInference(ctx, x, y, weights, bias, avg_var, act="linear", alpha=1.0, beta=0.0):
     """ml::batchnormInference (src/core/math.cpp): avg_var is fp32 [2, channels] = (mean, variance); weights / bias may be None."""
-    lib.cuda_batchnorm_inference(ctx.handle, alpha, desc(x), desc(weights), desc(bias), desc(avg_var), beta, desc(y), act_code(act))
+    lib.cuda_batchnorm_inference(ctx.handle, alpha, desc(x, ctx), desc(weights, ctx), desc(bias, ctx), desc(avg_var, ctx), beta, desc(y, ctx), act_code(act))
     ctx.check()
 
 
 def foldBatchnorm(ctx, layer_weights, layer_bias, bn_weights, bn_bias, bn_avg_var):
-    lib.cuda_fold_batchnorm(ctx.handle, desc(layer_weights), desc(layer_bias), desc(bn_weights), desc(bn_bias), desc(bn_avg_var))
+    lib.cuda_fold_batchnorm(ctx.handle, desc(layer_weights, ctx), desc(layer_bias, ctx), desc(bn_weights, ctx), desc(bn_bias, ctx), desc(bn_avg_var, ctx))
     ctx.check()
 
 
 def depthwiseConvForward(ctx, x, w, y, bias=None, alpha=1.0, beta=0.0):
-    lib.cuda_depthwise_conv_forward(ctx.handle, alpha, desc(x), desc(w), desc(bias), beta, desc(y))
+    lib.cuda_depthwise_conv_forward(ctx.handle, alpha, desc(x, ctx), desc(w, ctx), desc(bias, ctx), beta, desc(y, ctx))
     ctx.check()
 
 
 def quantized_depthwise_conv_forward(ctx, x, w, scales, bias, y, output_qd, padding_value=0):
-    lib.cuda_quantized_depthwise_conv_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(w), ptr(x), ptr(w), ptr(scales), ptr(bias), ptr(y),
+    lib.cuda_quantized_depthwise_conv_forward(ctx.handle, dtype_of(x), shape_of(x), shape_of(w), ptr(x, ctx), ptr(w, ctx), ptr(scales, ctx), ptr(bias, ctx), ptr(y, ctx),
                                               qdata(*output_qd), int(padding_value))
     ctx.check()
 
 
 def channelScalingForward(ctx, x, scales, y, alpha=1.0, beta=0.0):
-    lib.cuda_channel_scaling_forward(ctx.handle, alpha, desc(x), desc(scales), beta, desc(y))
+    lib.cuda_channel_scaling_forward(ctx.handle, alpha, desc(x, ctx), desc(scales, ctx), beta, desc(y, ctx))
     ctx.check()
 
 
 # ---------------------------------------------------------------------------------------------- backward pass of the Winograd convolution
 def winogradGradientTransform(ctx, weight_shape, dy, matrices, tile_size=None):
     tile = tile_size if tile_size is not None else _tile_size(matrices, weight_shape[1])
-    lib.cuda_winograd_gradient_transform(ctx.handle, tile, desc(dy), desc(matrices))
+    lib.cuda_winograd_gradient_transform(ctx.handle, tile, desc(dy, ctx), desc(matrices, ctx))
     ctx.check()
 
 
 def winogradUpdateTransform(ctx, matrices, dw, tile_size=None):
     tile = tile_size if tile_size is not None else _tile_size(matrices, dw.shape[1])
-    lib.cuda_winograd_update_transform(ctx.handle, tile, desc(matrices), desc(dw))
+    lib.cuda_winograd_update_transform(ctx.handle, tile, desc(matrices, ctx), desc(dw, ctx))
     ctx.check()
 
 
 def fusedBiasActCopyBackward(ctx, dy, y, dx=None, db=None, act="linear", beta_dx=0.0, beta_db=0.0):
     """ml::fusedBiasActCopyBackward (src/core/math.cpp:1046-1063): dy is updated in place when act is not linear."""
-    lib.cuda_fused_act_bias_copy_backward(ctx.handle, desc(dy), desc(y), beta_dx, desc(dx), beta_db, desc(db), act_code(act))
+    lib.cuda_fused_act_bias_copy_backward(ctx.handle, desc(dy, ctx), desc(y, ctx), beta_dx, desc(dx, ctx), beta_db, desc(db, ctx), act_code(act))
     ctx.check()
 
 
 def activationBackward(ctx, dy, y, dx, act="linear", alpha=1.0, beta=0.0):
-    lib.cuda_activation_backward(ctx.handle, alpha, desc(dy), desc(y), beta, desc(dx), act_code(act))
+    lib.cuda_activation_backward(ctx.handle, alpha, desc(dy, ctx), desc(y, ctx), beta, desc(dx, ctx), act_code(act))
     ctx.check()

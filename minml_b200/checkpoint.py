@@ -95,7 +95,7 @@ class LoadedNetwork:
         self.torch = torch
         self.dtype = dtype if dtype is not None else torch.float32
         self.nodes = nodes_of(description)
-        self.workspace = L.Workspace()
+        self.workspace = L.Workspace(ctx)
         self.steps = []
         self.outputs = []
         self.shapes = []

@@ -58,6 +58,7 @@ namespace mb200
 			std::string error;
 			PendingWinograd pending;
 			PendingInt8 pending_i8;
+			std::recursive_mutex mutex; // guards `pending`, `pending_i8` and `fusion` (recursive: a flush re-enters the eager entry points)
 			int sm_count = 148;
 			bool kernels_with_waits = false; // a kernel that polls mbarriers ran since the last synchronize
 			int *dev_status = nullptr; // device word set to non-zero by a kernel whose bounded wait ran out
@@ -179,6 +180,11 @@ namespace mb200
 	inline bool aligned_to(const void *ptr, size_t bytes)
 	{
 		return (reinterpret_cast<uintptr_t>(ptr) % bytes) == 0;
+	}
+	inline bool ranges_overlap(const void *a, long long a_bytes, const void *b, long long b_bytes)
+	{
+		const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+		return a0 < b0 + static_cast<uintptr_t>(b_bytes) && b0 < a0 + static_cast<uintptr_t>(a_bytes);
 	}
 	inline int ceil_div(long long a, long long b)
 	{

@@ -22,10 +22,33 @@ namespace mb200
 
 	namespace
 	{
-		std::mutex g_mutex;
+		std::mutex g_mutex; // error slots
 		std::string g_global_error;
 		bool g_global_has_error = false;
+		std::mutex g_contexts_mutex; // the list of live contexts; held while flush_all_pending walks it, so that none is destroyed under it
 		std::vector<Context*> g_contexts;
+
+		/* Size in bytes of the device allocation that starts at (or contains) ptr; 1 when the driver cannot tell. */
+		size_t allocation_size(const void *ptr)
+		{
+			typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+			static const range_fn fn = []() -> range_fn
+			{
+				void *entry = nullptr;
+				cudaDriverEntryPointQueryResult result;
+				if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &result) != cudaSuccess || entry == nullptr)
+				{
+					cudaGetLastError();
+					return nullptr;
+				}
+				return reinterpret_cast<range_fn>(entry);
+			}();
+			unsigned long long base = 0;
+			size_t size = 0;
+			if (fn == nullptr || fn(&base, &size, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(ptr))) != 0 || size == 0)
+				return 1;
+			return size;
+		}
 
 		int device_count()
 		{
@@ -144,14 +167,13 @@ namespace mb200
 		}
 		return c->workspace;
 	}
+	/* Replays the recorded calls of EVERY context (a freed buffer or a null-context copy may concern any of them).  Each
+	 * context is flushed under its own mutex, so the thread that owns it either has not recorded its next call yet or finds
+	 * nothing pending and runs that call eagerly on results that exist. */
 	void flush_all_pending()
 	{
-		std::vector<Context*> copy;
-		{
-			std::lock_guard<std::mutex> lock(g_mutex);
-			copy = g_contexts;
-		}
-		for (Context *c : copy)
+		std::lock_guard<std::mutex> lock(g_contexts_mutex);
+		for (Context *c : g_contexts)
 			flush_pending(c);
 	}
 } /* namespace mb200 */
@@ -254,7 +276,7 @@ extern "C"
 		}
 		if (check_cuda(nullptr, cudaMalloc(reinterpret_cast<void**>(&c->dev_status), sizeof(int)), "cuda_create_context: status word"))
 			cudaMemset(c->dev_status, 0, sizeof(int));
-		std::lock_guard<std::mutex> lock(g_mutex);
+		std::lock_guard<std::mutex> lock(g_contexts_mutex);
 		g_contexts.push_back(c);
 		return c;
 	}
@@ -296,15 +318,8 @@ extern "C"
 			return;
 		Context *c = get(context);
 		flush_pending(context);
-		cudaSetDevice(c->device);
-		cudaStreamSynchronize(c->stream);
-		cudaStreamDestroy(c->stream);
-		if (c->workspace != nullptr)
-			cudaFree(c->workspace);
-		if (c->dev_status != nullptr)
-			cudaFree(c->dev_status);
-		{
-			std::lock_guard<std::mutex> lock(g_mutex);
+		{ // out of the list first: from here on no other thread's flush can reach this context
+			std::lock_guard<std::mutex> lock(g_contexts_mutex);
 			for (size_t i = 0; i < g_contexts.size(); i++)
 				if (g_contexts[i] == c)
 				{
@@ -312,6 +327,13 @@ extern "C"
 					break;
 				}
 		}
+		cudaSetDevice(c->device);
+		cudaStreamSynchronize(c->stream);
+		cudaStreamDestroy(c->stream);
+		if (c->workspace != nullptr)
+			cudaFree(c->workspace);
+		if (c->dev_status != nullptr)
+			cudaFree(c->dev_status);
 		delete c;
 	}
 
@@ -390,7 +412,7 @@ extern "C"
 		if (ptr != nullptr)
 		{
 			flush_all_pending(); // a deferred sequence may still reference this buffer
-			winograd_forget_pointer(ptr); // a recycled address must never alias a stale weight record
+			winograd_forget_range(ptr, allocation_size(ptr)); // a recycled address must never alias a stale weight record
 			check_cuda(nullptr, cudaFree(ptr), "cuda_free");
 		}
 	}
@@ -413,6 +435,7 @@ extern "C"
 		else
 			flush_pending(context);
 		void *tmp_dst = reinterpret_cast<uint8_t*>(dst) + dst_offset;
+		winograd_forget_range(tmp_dst, dst_count); // transformed weights written to directly are no longer described by their snapshot
 		cudaStream_t stream = use_stream(context);
 		if (src == nullptr)
 		{
@@ -455,6 +478,7 @@ extern "C"
 			return;
 		void *d = reinterpret_cast<uint8_t*>(dst) + dst_offset;
 		const void *s = reinterpret_cast<const uint8_t*>(src) + src_offset;
+		winograd_forget_range(d, count);
 		if (context == nullptr)
 		{
 			flush_all_pending();
@@ -472,6 +496,7 @@ extern "C"
 		if (count == 0)
 			return;
 		void *d = reinterpret_cast<uint8_t*>(dst) + dst_offset;
+		winograd_forget_range(d, count);
 		if (context == nullptr)
 		{
 			flush_all_pending();
@@ -536,6 +561,7 @@ extern "C"
 	{
 		if (context != nullptr)
 		{
+			std::lock_guard<std::recursive_mutex> lock(get(context)->mutex);
 			flush_pending(context);
 			get(context)->fusion = (enabled != 0);
 		}

@@ -48,7 +48,10 @@ extern "C"
 		const mlTensor_t x = make_tensor(input, dtype, input_shape);
 		const mlTensor_t w = make_tensor(weights, dtype, weights_shape);
 		const mlTensor_t y = make_tensor(output, dtype, out_shape);
-		if (conv_fused_supported(x, w, y, act))
+		// in place (y overlapping x) only the Winograd path below is correct: V is complete before y is written, whereas the fused
+		// kernel reads the 3x3 neighbourhood of positions that other CTAs are writing
+		const bool in_place = ranges_overlap(input, volume(x) * size_of(dtype), output, volume(y) * size_of(dtype));
+		if (!in_place && conv_fused_supported(x, w, y, act))
 		{
 			conv_fused_run(context, x, w, bias, add, y, act);
 			return;

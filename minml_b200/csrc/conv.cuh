@@ -9,6 +9,8 @@ namespace mb200
 {
 	/* True when an input tensor can be consumed by the fused 3x3 kernel (dtype, channel count, alignment). */
 	bool conv_fused_input_supported(const mlTensor_t &x);
+	/* True when a raw weight tensor [cout, 3, 3, cin] can be the B operand of the fused kernel (dtype, channel count). */
+	bool conv_fused_weights_supported(const mlTensor_t &w);
 	/* True when y = act(conv3x3(x, w) + bias + ext) can run as the fused kernel. */
 	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act);
 	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,

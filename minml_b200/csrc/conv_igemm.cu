@@ -107,7 +107,7 @@ namespace mb200
 				int out_dtype;
 				const float *scales; // int8 kind
 				const float *shifts;
-				float ext_scale, ext_shift, out_scale, out_shift;
+				float ext_scale, ext_shift;
 				float inv_out_scale, inv_out_shift; // 1 / out_scale and -out_shift / out_scale, rounded like AffineTransform::get_inverse
 				int pad_byte;
 				// int8, non-zero padding value on the TMA path (which can only fill with zeros): [9][cout] corrections, already
@@ -493,8 +493,7 @@ namespace mb200
 
 						if (fast_i8)
 						{ /* int8 -> int8 fast path.  The arithmetic is the scalar loop of the reference's CPU backend, operation for
-						   * operation and without fused multiply-adds: x = acc * scale[c] + shift[c] (+ ext * s_e + z_e); activation;
-						   * q = clamp(round(x * (1 / s_o) + (-z_o / s_o)))  (src/layers/Conv2D.cpp:283-304, src/layers/quantization.cpp:43-47) */
+						   * operation and without fused multiply-adds (epilogue.cuh: requant_real, requant_add_ext, requant_round) */
 							if (!row_ok)
 								continue;
 							const float4 *sp = reinterpret_cast<const float4*>(p.scales + n0);
@@ -511,19 +510,14 @@ namespace mb200
 #pragma unroll
 								for (int t = 0; t < 4; t++)
 								{
-									float x = __fadd_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[4 * g4 + t])), scs[t]), shs[t]);
+									float x = requant_real(static_cast<int>(r[4 * g4 + t]), scs[t], shs[t]);
 									if (p.ext != nullptr)
-									{
-										const int e = static_cast<int>(static_cast<int8_t>((ext_words[g4] >> (8 * t)) & 0xFFu));
-										x = __fadd_rn(x, __fadd_rn(__fmul_rn(static_cast<float>(e), p.ext_scale), p.ext_shift));
-									}
+										x = requant_add_ext(x, static_cast<int>(static_cast<int8_t>((ext_words[g4] >> (8 * t)) & 0xFFu)), p.ext_scale, p.ext_shift);
 									if (relu)
 										x = fmaxf(x, 0.0f);
 									else if (other_act)
 										x = activation_out_of_line(x, p.act);
-									// round half away from zero, then saturate: the float -> int conversion saturates at the int32 range and
-									// the packing instruction at the int8 range, which together are the reference's clamp(round(.), -128, 127)
-									q4[t] = __float2int_rz(roundf(__fadd_rn(__fmul_rn(x, p.inv_out_scale), p.inv_out_shift)));
+									q4[t] = requant_round(x, p.inv_out_scale, p.inv_out_shift);
 								}
 								packed[g4] = pack_sat_s8x4(q4[0], q4[1], q4[2], q4[3]);
 							}
@@ -590,11 +584,11 @@ namespace mb200
 							float x = 0.0f;
 							if (j < n_valid)
 							{
-								x = static_cast<float>(static_cast<int>(r[j])) * p.scales[n0 + j] + p.shifts[n0 + j];
+								x = requant_real(static_cast<int>(r[j]), p.scales[n0 + j], p.shifts[n0 + j]);
 								if (ep != nullptr)
 								{
 									const int e = ext_vec ? static_cast<int>(static_cast<int8_t>((ext_words[j / 4] >> (8 * (j % 4))) & 0xFFu)) : static_cast<int>(ep[j]);
-									x += static_cast<float>(e) * p.ext_scale + p.ext_shift;
+									x = requant_add_ext(x, e, p.ext_scale, p.ext_shift);
 								}
 							}
 							v[j] = x;
@@ -612,7 +606,7 @@ namespace mb200
 #pragma unroll
 								for (int t = 0; t < 4; t++)
 								{
-									const int qv = static_cast<int>(fmaxf(-128.0f, fminf(127.0f, roundf((v[j + t] - p.out_shift) / p.out_scale))));
+									const int qv = requant_clamp(requant_round(v[j + t], p.inv_out_scale, p.inv_out_shift));
 									w4 |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * t);
 								}
 								packed[j / 4] = w4;
@@ -764,9 +758,11 @@ namespace mb200
 		{
 			using C = Cfg<KIND, BN, TMA_A, 1, MT>;
 			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
+			static std::mutex configured_mutex; // contexts on several threads may reach a kernel for the first time together
 			const int device = get(ctx)->device;
 			if (device < 0 || device >= MAX_DEVICES)
 				return false;
+			std::unique_lock<std::mutex> configured_lock(configured_mutex);
 			bool &configured = configured_on[device];
 			if (!configured)
 			{
@@ -775,6 +771,7 @@ namespace mb200
 					return false;
 				configured = true;
 			}
+			configured_lock.unlock();
 			const int tiles = (((p.M + BM - 1) / BM + MT - 1) / MT) * ((p.cout + BN - 1) / BN);
 			const int grid = std::min(tiles, get(ctx)->sm_count);
 			kernel_conv3x3_igemm<KIND, BN, TMA_A, 1, MT> <<<grid, Roles<KIND, TMA_A>::threads, C::smem_bytes, use_stream(ctx)>>>(map_w, map_x, p);
@@ -789,6 +786,8 @@ namespace mb200
 		{
 			using C = Cfg<KIND, BN, true, 2>;
 			static int max_clusters[MAX_DEVICES] = { 0 }; // per device; 0 = not queried yet, -1 = clusters of this size cannot be placed
+			static std::mutex max_clusters_mutex;
+			std::lock_guard<std::mutex> max_clusters_lock(max_clusters_mutex);
 			const int device = get(ctx)->device;
 			cudaLaunchConfig_t config;
 			std::memset(&config, 0, sizeof(config));
@@ -998,6 +997,10 @@ namespace mb200
 	{
 		return x.dtype == DTYPE_FLOAT16 && shape_ok(0, x, 1, x.data);
 	}
+	bool conv_fused_weights_supported(const mlTensor_t &w)
+	{
+		return w.dtype == DTYPE_FLOAT16 && w.rank == 4 && w.dim[3] % 8 == 0;
+	}
 	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act)
 	{
 		(void) act;
@@ -1032,6 +1035,7 @@ namespace mb200
 		const mlTensor_t x = make_tensor(input, DTYPE_INT8, input_shape);
 		if (!shape_ok(1, x, 1, input))
 			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
 		flush_pending(ctx);
 		c->pending_i8.stage = 1;
 		c->pending_i8.x = x;
@@ -1042,7 +1046,10 @@ namespace mb200
 	bool int8_gemm_defer(mlContext_t ctx, char opA, char opB, const mlTensor_t &A, const mlTensor_t &B, const mlTensor_t &C)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending_i8.stage != 1)
+		if (c == nullptr)
+			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
+		if (c->pending_i8.stage != 1)
 			return false;
 		if (is_transpose(opA) || !is_transpose(opB) || A.data != c->pending_i8.rows || A.dtype != DTYPE_INT8 || B.dtype != DTYPE_INT8
 				|| C.dtype != DTYPE_INT32 || A.rank != 2 || B.rank != 2 || C.rank != 2)
@@ -1059,7 +1066,10 @@ namespace mb200
 			const void *input, const void *scales, const void *bias, mlActivationType_t act, const void *ext, mlQuantizationData_t ext_qd)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending_i8.stage != 2 || input != c->pending_i8.acc.data)
+		if (c == nullptr)
+			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
+		if (c->pending_i8.stage != 2 || input != c->pending_i8.acc.data)
 			return false;
 		if (dtype != DTYPE_INT8 && dtype != DTYPE_FLOAT16 && dtype != DTYPE_FLOAT32)
 			return false;
@@ -1077,8 +1087,7 @@ namespace mb200
 		p.shifts = reinterpret_cast<const float*>(bias);
 		p.ext_scale = ext_qd.scale;
 		p.ext_shift = ext_qd.shift;
-		p.out_scale = output_qd.scale;
-		p.out_shift = output_qd.shift;
+		// (the output transform reaches the kernel as its inverse, below)
 		p.inv_out_scale = 1.0f / output_qd.scale;
 		p.inv_out_shift = -output_qd.shift / output_qd.scale;
 		p.pad_byte = c->pending_i8.pad;
@@ -1092,7 +1101,10 @@ namespace mb200
 	void flush_pending_int8(mlContext_t ctx)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending_i8.stage == 0)
+		if (c == nullptr)
+			return;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
+		if (c->pending_i8.stage == 0)
 			return;
 		const PendingInt8 pend = c->pending_i8;
 		c->pending_i8.stage = 0;

@@ -16,7 +16,11 @@
  *
  * Rules that follow from that:
  *   - a problem whose U + V + M does not fit is refused with an error on the context; nothing is launched;
- *   - the call itself never calls cudaMalloc, cudaFree or any routine that allocates device memory;
+ *   - the call itself never calls cudaMalloc, cudaFree or any routine that allocates device memory.  One thing outside its
+ *     control: the CUDA runtime loads a kernel's code onto the device the first time that kernel is launched (lazy module
+ *     loading), and which kernels run depends on the data type and on the shape class (fp16 with even / odd channel counts,
+ *     fp32, tensor-core or generic product).  So run one warm-up call per data type and shape class you will use, on every
+ *     device, before the phase in which nothing may be allocated -- or start the process with CUDA_MODULE_LOADING=EAGER;
  *   - the array is shared by every call on the device and keeps whatever the last call left in it.  Nothing in it has to
  *     start at zero: U, V and M are each written completely before they are read;
  *   - two calls that are in flight on the same GPU at the same time (two contexts, two processes' worth of streams) use
@@ -112,6 +116,7 @@ extern "C"
 		const mlTensor_t bias_t = make_tensor(bias, dtype, make_shape( { cout }));
 		const mlTensor_t add_t = make_tensor(add, dtype, out_shape);
 
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
 		const bool fusion = c->fusion;
 		c->fusion = false; // the four steps run eagerly, in this order, on the context's stream
 		winograd_weight_transform_eager(context, 4, w, u, false);

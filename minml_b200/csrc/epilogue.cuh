@@ -81,6 +81,31 @@ namespace mb200
 					v[j] = activation_out_of_line(v[j], act);
 			}
 		}
+		/* Requantisation of an int32 accumulator, the one formula of every int8 output path of the library (fused convolution,
+		 * tensor-core GEMM epilogue, eager cuda_quantized_scale_shift_act).  It is the arithmetic of the reference's CPU layer
+		 * (src/layers/Conv2D.cpp:283-304 with AffineTransform::get_inverse, include/minml/layers/quantization.hpp:47-55), step
+		 * for step and with every step rounded on its own -- no fused multiply-add -- so that all paths give the same bits:
+		 *     x = acc * scale[c] + shift[c]  (+ (ext * s_e + z_e));   activation;   q = clamp(round(x * (1 / s_o) + (-z_o / s_o)))
+		 * with round-half-away-from-zero.  (The reference's CUDA kernel divides instead, round((x - z_o) / s_o),
+		 * src/backend/cuda/kernels/quantized.cu:44-47, which can differ from its CPU layer by one step.) */
+		__device__ __forceinline__ float requant_real(int acc, float scale, float shift)
+		{
+			return __fadd_rn(__fmul_rn(static_cast<float>(acc), scale), shift);
+		}
+		__device__ __forceinline__ float requant_add_ext(float x, int e, float ext_scale, float ext_shift)
+		{
+			return __fadd_rn(x, __fadd_rn(__fmul_rn(static_cast<float>(e), ext_scale), ext_shift));
+		}
+		/* Rounded but not yet saturated: the float -> int conversion saturates at the int32 range, pack_sat_s8x4 or
+		 * requant_clamp then at the int8 range, which together are the reference's clamp(round(.), -128, 127). */
+		__device__ __forceinline__ int requant_round(float x, float inv_out_scale, float inv_out_shift)
+		{
+			return __float2int_rz(roundf(__fadd_rn(__fmul_rn(x, inv_out_scale), inv_out_shift)));
+		}
+		__device__ __forceinline__ int requant_clamp(int q)
+		{
+			return max(-128, min(127, q));
+		}
 		/* Four int32 -> four int8 with saturation, byte t of the result = value t. */
 		__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d)
 		{

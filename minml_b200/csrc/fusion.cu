@@ -12,11 +12,22 @@
  *   3. the output transform on the recorded M launches ONE fused convolution kernel on x and the raw weights.
  * Any other call on the context first replays what was recorded with the eager kernels (flush_pending), so code
  * that inspects V or M -- e.g. the reference's own transform tests -- sees exactly the three-kernel behaviour.
+ *
+ * Snapshot semantics.  In the reference the transformed matrices U are a snapshot of the weights at transform time: the host may
+ * overwrite, reuse or free the raw weight tensor afterwards and the convolution still computes with what U holds.  The fused
+ * kernel works on raw weights, so cuda_winograd_weight_transform also keeps a backend-owned device copy of them (same layout,
+ * [cout, 3, 3, cin], which IS the K-major B operand of the implicit GEMM) and the fused kernel reads that copy, never the host's
+ * tensor.  The record is keyed by the address of U: it goes away when U is freed or when a copy / fill of the ABI writes into U
+ * (the snapshot would no longer describe its contents; the sequence then runs on the three eager kernels).
+ *
+ * Threads.  The recorded state of a context is guarded by the context's mutex: another thread's cuda_free or null-context copy
+ * flushes every context (context.cu) and must not interleave with the owner recording a call.
  */
 #include "common.cuh"
 #include "winograd.cuh"
 #include "conv.cuh"
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 
@@ -26,12 +37,28 @@ namespace mb200
 	{
 		struct WeightRecord
 		{
-				mlTensor_t w;
+				mlTensor_t w; // shape and dtype of the raw weights; data = the backend-owned copy (nullptr: not fusable, no copy kept)
 				int tile_size;
 				bool invert;
+				size_t matrices_bytes;
+				size_t copy_bytes;
+				int device;
 		};
 		std::mutex g_registry_mutex;
-		std::map<const void*, WeightRecord> g_registry; // transformed matrices pointer -> raw weights
+		std::map<const void*, WeightRecord> g_registry; // transformed matrices pointer -> snapshot of the raw weights
+
+		void release(WeightRecord &rec)
+		{
+			if (rec.w.data != nullptr)
+			{
+				int current = 0;
+				cudaGetDevice(&current);
+				cudaSetDevice(rec.device);
+				cudaFree(rec.w.data);
+				cudaSetDevice(current);
+				rec.w.data = nullptr;
+			}
+		}
 
 		bool lookup(const void *matrices, WeightRecord &out)
 		{
@@ -46,20 +73,67 @@ namespace mb200
 
 	void winograd_register_weights(mlContext_t ctx, const mlTensor_t &w, const mlTensor_t &matrices, int tile_size, bool invert)
 	{
-		(void) ctx;
+		Context *c = get(ctx);
+		if (c == nullptr)
+			return;
+		const bool fusable = tile_size == 4 && !invert && w.rank == 4 && w.dim[1] == 3 && w.dim[2] == 3 && conv_fused_weights_supported(w);
+		const size_t bytes = static_cast<size_t>(volume(w)) * size_of(w.dtype);
 		std::lock_guard<std::mutex> lock(g_registry_mutex);
-		g_registry[matrices.data] = WeightRecord { w, tile_size, invert };
+		auto it = g_registry.find(matrices.data);
+		void *copy = nullptr;
+		if (it != g_registry.end())
+		{ // the host transforms again whenever its weights change (Conv2D::invalidateWeightsCache): reuse the allocation when it fits
+			if (fusable && it->second.w.data != nullptr && it->second.copy_bytes == bytes && it->second.device == c->device)
+				copy = it->second.w.data;
+			else
+				release(it->second);
+			g_registry.erase(it);
+		}
+		if (!fusable)
+			return; // such a sequence always runs on the eager kernels; nothing to remember
+		cudaStream_t stream = use_stream(ctx);
+		if (copy == nullptr && cudaMalloc(&copy, bytes) != cudaSuccess)
+		{
+			cudaGetLastError();
+			return; // no memory for the snapshot: the sequence stays on the eager kernels
+		}
+		if (!check_cuda(ctx, cudaMemcpyAsync(copy, w.data, bytes, cudaMemcpyDeviceToDevice, stream), "weight snapshot"))
+		{
+			cudaFree(copy);
+			return;
+		}
+		WeightRecord rec;
+		rec.w = w;
+		rec.w.data = copy;
+		rec.tile_size = tile_size;
+		rec.invert = invert;
+		rec.matrices_bytes = static_cast<size_t>(volume(matrices)) * size_of(matrices.dtype);
+		rec.copy_bytes = bytes;
+		rec.device = c->device;
+		g_registry[matrices.data] = rec;
 	}
-	void winograd_forget_pointer(const void *ptr)
+	void winograd_forget_range(const void *ptr, size_t bytes)
 	{
 		std::lock_guard<std::mutex> lock(g_registry_mutex);
+		if (g_registry.empty())
+			return;
+		const uint8_t *lo = reinterpret_cast<const uint8_t*>(ptr);
+		const uint8_t *hi = lo + std::max<size_t>(bytes, 1);
 		for (auto it = g_registry.begin(); it != g_registry.end();)
 		{
-			if (it->first == ptr || it->second.w.data == ptr)
+			const uint8_t *m = reinterpret_cast<const uint8_t*>(it->first);
+			if (m < hi && lo < m + it->second.matrices_bytes)
+			{
+				release(it->second);
 				it = g_registry.erase(it);
+			}
 			else
 				++it;
 		}
+	}
+	void winograd_forget_pointer(const void *ptr)
+	{ // the buffer is being freed: its size is unknown here, but any record whose matrices start inside it starts AT it
+		winograd_forget_range(ptr, 1);
 	}
 
 	bool winograd_defer_input(mlContext_t ctx, int tile_size, const mlTensor_t &x, const mlTensor_t &matrices)
@@ -69,6 +143,7 @@ namespace mb200
 			return false;
 		if (!conv_fused_input_supported(x))
 			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
 		c->pending.stage = 1;
 		c->pending.x = x;
 		c->pending.v = matrices;
@@ -79,14 +154,17 @@ namespace mb200
 			const mlTensor_t &C)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending.stage != 1)
+		if (c == nullptr)
+			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
+		if (c->pending.stage != 1)
 			return false;
 		if (is_transpose(opA) || !is_transpose(opB) || alpha != 1.0f || beta != 0.0f)
 			return false;
 		if (A.data != c->pending.v.data || A.rank != 3 || B.rank != 3 || C.rank != 3 || A.dtype != B.dtype || A.dtype != C.dtype)
 			return false;
 		WeightRecord rec;
-		if (!lookup(B.data, rec) || rec.tile_size != c->pending.tile_size || rec.invert)
+		if (!lookup(B.data, rec) || rec.w.data == nullptr || rec.tile_size != c->pending.tile_size || rec.invert)
 			return false;
 		if (rec.w.dim[0] != B.dim[1] || rec.w.dim[3] != B.dim[2] || rec.w.dtype != A.dtype)
 			return false;
@@ -99,17 +177,24 @@ namespace mb200
 			const mlTensor_t &y, mlActivationType_t act)
 	{
 		Context *c = get(ctx);
-		if (c == nullptr || c->pending.stage != 2)
+		if (c == nullptr)
+			return false;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
+		if (c->pending.stage != 2)
 			return false;
 		if (matrices.data != c->pending.m.data || tile_size != c->pending.tile_size)
 			return false;
 		WeightRecord rec;
-		if (!lookup(c->pending.u.data, rec))
+		if (!lookup(c->pending.u.data, rec) || rec.w.data == nullptr)
 			return false;
 		const mlTensor_t x = c->pending.x;
 		if (y.dim[0] != x.dim[0] || y.dim[1] != x.dim[1] || y.dim[2] != x.dim[2] || y.dim[3] != rec.w.dim[0])
 			return false;
 		if (!conv_fused_supported(x, rec.w, y, act))
+			return false;
+		// In place (y overlapping x) the three-kernel path is correct -- V is complete before y is written -- but the fused kernel
+		// reads the 3x3 neighbourhood of positions that other CTAs are writing: such a call runs on the eager kernels.
+		if (ranges_overlap(x.data, volume(x) * size_of(x.dtype), y.data, volume(y) * size_of(y.dtype)))
 			return false;
 		c->pending.stage = 0;
 		return conv_fused_run(ctx, x, rec.w, bias.data, ext.data, y, act);
@@ -119,6 +204,7 @@ namespace mb200
 		Context *c = get(ctx);
 		if (c == nullptr)
 			return;
+		std::lock_guard<std::recursive_mutex> lock(c->mutex);
 		if (c->pending_i8.stage != 0)
 			flush_pending_int8(ctx);
 		if (c->pending.stage == 0)

@@ -32,7 +32,8 @@ namespace mb200
 			int act = ACTIVATION_LINEAR;
 			mlDataType_t out_dtype = DTYPE_FLOAT16;
 			/* int8 kind with out_dtype != INT32: fused requantisation epilogue
-			 * x = acc * scales[n] + shifts[n] (+ ext * ext_scale + ext_shift); act; int8 out = clamp(round((x - out_shift) / out_scale)) */
+			 * x = acc * scales[n] + shifts[n] (+ ext * ext_scale + ext_shift); act; int8 out = clamp(round(x * (1 / out_scale) + (-out_shift / out_scale))),
+			 * every step rounded on its own (epilogue.cuh) */
 			const float *scales = nullptr;
 			const float *shifts = nullptr;
 			const int8_t *ext = nullptr; // indexed like C (ldc, stride_c)
@@ -56,7 +57,7 @@ namespace mb200
 			const float *scales;
 			const float *shifts;
 			const int8_t *ext;
-			float ext_scale, ext_shift, out_scale, out_shift;
+			float ext_scale, ext_shift, inv_out_scale, inv_out_shift;
 			int *status;
 	};
 	bool gemm_tc_supported(const GemmTcProblem &g);

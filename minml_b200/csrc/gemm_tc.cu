@@ -130,10 +130,7 @@ namespace mb200
 			lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
 		}
 
-		__device__ __forceinline__ float requant_prepare(int acc, float scale, float shift)
-		{
-			return static_cast<float>(acc) * scale + shift;
-		}
+		// (requantisation arithmetic: epilogue.cuh)
 
 		template<int KIND, int BN>
 		__global__ void __launch_bounds__(num_threads(KIND), 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
@@ -472,9 +469,9 @@ namespace mb200
 							for (int j = 0; j < 32; j++)
 								if (j < n_valid)
 								{
-									float x = requant_prepare(static_cast<int>(r[j]), p.scales[n0 + j], p.shifts[n0 + j]);
+									float x = requant_real(static_cast<int>(r[j]), p.scales[n0 + j], p.shifts[n0 + j]);
 									if (ep != nullptr)
-										x += static_cast<float>(ep[j]) * p.ext_scale + p.ext_shift;
+										x = requant_add_ext(x, static_cast<int>(ep[j]), p.ext_scale, p.ext_shift);
 									v[j] = x;
 								}
 							if (p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH || p.act == ACTIVATION_RELU)
@@ -549,7 +546,7 @@ namespace mb200
 #pragma unroll
 							for (int j = 0; j < 32; j++)
 								if (j < n_valid)
-									dp[j] = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, roundf((v[j] - p.out_shift) / p.out_scale))));
+									dp[j] = static_cast<int8_t>(requant_clamp(requant_round(v[j], p.inv_out_scale, p.inv_out_shift)));
 						}
 					}
 					tcgen05_fence_before();
@@ -684,8 +681,8 @@ namespace mb200
 		p.ext = g.ext;
 		p.ext_scale = g.ext_scale;
 		p.ext_shift = g.ext_shift;
-		p.out_scale = g.out_scale;
-		p.out_shift = g.out_shift;
+		p.inv_out_scale = 1.0f / g.out_scale; // AffineTransform::get_inverse of the reference's host code
+		p.inv_out_shift = -g.out_shift / g.out_scale;
 		p.status = c->dev_status;
 		c->kernels_with_waits = true;
 

@@ -5,8 +5,10 @@
  *
  *   scale_shift_act:  x = acc[i, c] * scales[c] + bias[c] (+ ext[i, c] * ext_qd.scale + ext_qd.shift);
  *                     activation in {linear, sigmoid, tanh, relu} (anything else is left linear, as in the reference);
- *                     output fp16 / fp32 / fp64, or int8 = clamp(round((x - out_qd.shift) / out_qd.scale), -128, 127)
- *                     with round-half-away-from-zero.
+ *                     output fp16 / fp32 / fp64, or int8 = clamp(round(x * (1 / s_o) + (-z_o / s_o)), -128, 127) with
+ *                     round-half-away-from-zero: the formula and rounding order of the reference's CPU layer
+ *                     (src/layers/Conv2D.cpp:283-304), shared with the fused kernels through epilogue.cuh.  The reference's
+ *                     CUDA kernel divides, round((x - z_o) / s_o), which can differ from its own CPU layer by one step.
  *   im2row:           [b, h, w, c] -> [b*h*w, k*k*c], columns ordered (kh, kw, c), taps outside the image filled with
  *                     *padding (zero when the pointer is null).  Unlike the reference's active code path this one
  *                     handles int8 and honours `padding`, which the host's int8 3x3 convolution needs
@@ -14,6 +16,7 @@
  */
 #include "common.cuh"
 #include "conv.cuh"
+#include "epilogue.cuh"
 
 #include <algorithm>
 #include <cstring>
@@ -26,16 +29,16 @@ namespace mb200
 		template<> __device__ __forceinline__ void store_value<float>(float *p, float x, float, float, float) { *p = x; }
 		template<> __device__ __forceinline__ void store_value<double>(double *p, float x, float, float, float) { *p = x; }
 		template<> __device__ __forceinline__ void store_value<__half>(__half *p, float x, float, float, float) { *p = __float2half_rn(x); }
-		template<> __device__ __forceinline__ void store_value<int8_t>(int8_t *p, float x, float, float scale, float shift)
+		template<> __device__ __forceinline__ void store_value<int8_t>(int8_t *p, float x, float, float inv_scale, float inv_shift)
 		{
-			*p = static_cast<int8_t>(fmaxf(-128.0f, fminf(127.0f, roundf((x - shift) / scale))));
+			*p = static_cast<int8_t>(epi::requant_clamp(epi::requant_round(x, inv_scale, inv_shift)));
 		}
 
 		/* One thread requantises VEC consecutive channels of one row (VEC = 4: 16-byte accumulator and scale loads). */
 		template<typename T, int VEC>
 		__global__ void __launch_bounds__(256) kernel_scale_shift_act(T *__restrict__ output, const int *__restrict__ input,
 				const float *__restrict__ scales, const float *__restrict__ bias, const int8_t *__restrict__ ext, long long rows, int channels,
-				int act, float out_scale, float out_shift, float ext_scale, float ext_shift)
+				int act, float inv_out_scale, float inv_out_shift, float ext_scale, float ext_shift)
 		{
 			const long long total = rows * channels / VEC;
 			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -78,25 +81,25 @@ namespace mb200
 #pragma unroll
 				for (int k = 0; k < VEC; k++)
 				{
-					x[k] = static_cast<float>(acc[k]) * sc[k] + sh[k];
+					x[k] = epi::requant_real(acc[k], sc[k], sh[k]);
 					if (ext != nullptr)
-						x[k] += static_cast<float>(ex[k]) * ext_scale + ext_shift;
+						x[k] = epi::requant_add_ext(x[k], ex[k], ext_scale, ext_shift);
 					if (act_on)
 						x[k] = apply_activation(x[k], act);
 				}
 				if (VEC == 4 && sizeof(T) == 1)
 				{
-					uint32_t w4 = 0;
-#pragma unroll
+					int q[VEC];
+					#pragma unroll
 					for (int k = 0; k < VEC; k++)
-						w4 |= (static_cast<uint32_t>(static_cast<int>(fmaxf(-128.0f, fminf(127.0f, roundf((x[k] - out_shift) / out_scale))))) & 0xFFu) << (8 * k);
-					*reinterpret_cast<uint32_t*>(output + e) = w4;
+						q[k] = epi::requant_round(x[k], inv_out_scale, inv_out_shift);
+					*reinterpret_cast<uint32_t*>(output + e) = epi::pack_sat_s8x4(q[0], q[1 % VEC], q[2 % VEC], q[3 % VEC]);
 				}
 				else
 				{
 #pragma unroll
 					for (int k = 0; k < VEC; k++)
-						store_value<T>(output + e + k, x[k], 0.0f, out_scale, out_shift);
+						store_value<T>(output + e + k, x[k], 0.0f, inv_out_scale, inv_out_shift);
 				}
 			}
 		}
@@ -235,7 +238,7 @@ extern "C"
 		else kernel_scale_shift_act<T, 1> <<<grid, 256, 0, stream>>>(ARGS(T)); } while (0)
 #define ARGS(T) reinterpret_cast<T*>(output), reinterpret_cast<const int*>(input), reinterpret_cast<const float*>(scales), \
 		reinterpret_cast<const float*>(bias), reinterpret_cast<const int8_t*>(ext), rows, channels, static_cast<int>(act), \
-		output_qd.scale, output_qd.shift, ext_qd.scale, ext_qd.shift
+		1.0f / output_qd.scale, -output_qd.shift / output_qd.scale, ext_qd.scale, ext_qd.shift
 		switch (dtype)
 		{
 			case DTYPE_FLOAT16:

@@ -13,9 +13,11 @@ namespace mb200
 	void winograd_output_transform_eager(mlContext_t ctx, int tile_size, const mlTensor_t matrices, const mlTensor_t bias, const mlTensor_t ext,
 			mlTensor_t y, mlActivationType_t act);
 
-	/* Remembers which raw weight tensor a set of transformed matrices was computed from (evicted by cuda_free). */
+	/* Keeps a backend-owned snapshot of the raw weights a set of transformed matrices was computed from (what the fused kernel
+	 * reads); dropped when the matrices are freed (forget_pointer) or written to through the ABI (forget_range). */
 	void winograd_register_weights(mlContext_t ctx, const mlTensor_t &w, const mlTensor_t &matrices, int tile_size, bool invert);
 	void winograd_forget_pointer(const void *ptr);
+	void winograd_forget_range(const void *ptr, size_t bytes);
 
 	/* The three hooks of the deferred sequence.  Each returns true when it consumed the call. */
 	bool winograd_defer_input(mlContext_t ctx, int tile_size, const mlTensor_t &x, const mlTensor_t &matrices);

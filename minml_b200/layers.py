@@ -20,21 +20,26 @@ import numpy as np
 import torch
 
 from . import backend as B
+from .synthetic import he_normal, make_hybrid_weights, make_trunk_weights  # noqa: F401  (re-exported: callers build networks from them)
 
 
-def _dev(a, dtype):
-    return torch.from_numpy(np.ascontiguousarray(a)).cuda().to(dtype).contiguous()
+def _dev(ctx, a, dtype):
+    """numpy array -> tensor of `dtype` on the context's device (never torch's current device: a context of GPU 1 must not be
+    handed GPU 0's memory)."""
+    return torch.from_numpy(np.ascontiguousarray(a)).to(ctx.device).to(dtype).contiguous()
 
 
 class Workspace:
-    """The single scratch tensor a Graph shares between its layers (src/graph/Graph.cpp:578-587)."""
+    """The single scratch tensor a Graph shares between its layers (src/graph/Graph.cpp:578-587), on the device of the context
+    that will use it (`ctx=None`: torch's current device)."""
 
-    def __init__(self):
+    def __init__(self, ctx=None):
         self.buffer = None
+        self.device = ctx.device if ctx is not None else None
 
     def reserve(self, nbytes):
         if self.buffer is None or self.buffer.numel() < nbytes:
-            self.buffer = torch.empty(int(nbytes), dtype=torch.uint8, device="cuda")
+            self.buffer = torch.empty(int(nbytes), dtype=torch.uint8, device=self.device if self.device is not None else "cuda")
 
     def view(self, shape, dtype, byte_offset=0):
         n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
@@ -49,8 +54,8 @@ class Conv2D:
         self.activation = activation
         self.kernel = weights.shape[1]
         self.cout, self.cin = weights.shape[0], weights.shape[3]
-        self.weights = _dev(weights, dtype)
-        self.bias = None if bias is None else _dev(bias, dtype)
+        self.weights = _dev(ctx, weights, dtype)
+        self.bias = None if bias is None else _dev(ctx, bias, dtype)
         self.transformed = None  # cached, as m_transformed_weights in the reference (Conv2D.cpp:356-363)
         self.tile = 4            # CUDA, 3x3 -> WINOGRAD_NON_FUSED with F(4x4,3x3) (Conv2D.cpp:494-498)
 
@@ -76,7 +81,7 @@ class Conv2D:
             return
         assert self.kernel == 3
         if self.transformed is None:
-            self.transformed = torch.empty((36, self.cout, self.cin), dtype=self.dtype, device="cuda")
+            self.transformed = torch.empty((36, self.cout, self.cin), dtype=self.dtype, device=self.ctx.device)
             B.winogradWeightTransform(self.ctx, self.weights, self.transformed, False, self.tile)
         tiles = b * ((h + self.tile - 1) // self.tile) * ((w + self.tile - 1) // self.tile)
         elem = torch.empty((), dtype=self.dtype).element_size()
@@ -95,9 +100,9 @@ class QuantizedConv2D:
         self.ctx = ctx
         self.kernel = q_weights.shape[1]
         self.cout, self.cin = q_weights.shape[0], q_weights.shape[3]
-        self.weights = torch.from_numpy(np.ascontiguousarray(q_weights)).cuda()
-        self.channel_scales = _dev(channel_scales, torch.float32)
-        self.bias = _dev(q_bias, torch.float32)
+        self.weights = torch.from_numpy(np.ascontiguousarray(q_weights)).to(ctx.device)
+        self.channel_scales = _dev(ctx, channel_scales, torch.float32)
+        self.bias = _dev(ctx, q_bias, torch.float32)
         self.input_qd, self.output_qd = input_qd, output_qd
         self.activation = activation
         self.out_dtype = out_dtype
@@ -128,8 +133,8 @@ class QuantizedConv2D:
 class Dense:
     def __init__(self, ctx, weights, bias, activation="linear", dtype=torch.float16):
         self.ctx = ctx
-        self.weights = _dev(weights, dtype)  # [out, in]
-        self.bias = None if bias is None else _dev(bias, dtype)
+        self.weights = _dev(ctx, weights, dtype)  # [out, in]
+        self.bias = None if bias is None else _dev(ctx, bias, dtype)
         self.activation = activation
 
     def forward(self, inputs, output, workspace=None):
@@ -159,7 +164,7 @@ class Add:
 class LayerNormalization:
     def __init__(self, ctx, gamma, beta, dtype=torch.float16):
         self.ctx = ctx
-        self.gamma, self.beta = _dev(gamma, dtype), _dev(beta, dtype)
+        self.gamma, self.beta = _dev(ctx, gamma, dtype), _dev(ctx, beta, dtype)
 
     def forward(self, inputs, output, workspace=None):
         B.layernormForward(self.ctx, inputs[0], output, self.gamma, self.beta, inputs[1] if len(inputs) > 1 else None)
@@ -169,32 +174,13 @@ class MultiHeadAttention:
     def __init__(self, ctx, num_heads, table, dtype=torch.float16):
         self.ctx = ctx
         self.num_heads = num_heads
-        self.table = None if table is None else _dev(table, dtype)  # [heads, 2R-1, round_up(2R-1, 4)]
+        self.table = None if table is None else _dev(ctx, table, dtype)  # [heads, 2R-1, round_up(2R-1, 4)]
 
     def forward(self, inputs, output, workspace=None):
         B.multiHeadAttentionForward(self.ctx, inputs[0], output, self.table, self.num_heads, False)
 
 
 # ------------------------------------------------------------------------------------------------------ topologies
-def he_normal(rng, shape, fan_in):
-    return (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
-
-
-def make_trunk_weights(seed, in_planes, channels, blocks):
-    """He-normal weights, N(0, 0.01) biases; the same arrays feed the GPU run and the CPU checkers."""
-    rng = np.random.default_rng(seed)
-    w = {"stem_w": he_normal(rng, (channels, 3, 3, in_planes), 9 * in_planes), "stem_b": (rng.standard_normal(channels) * 0.01).astype(np.float32)}
-    for i in range(blocks):
-        for j in (1, 2):
-            w["b%d_w%d" % (i, j)] = he_normal(rng, (channels, 3, 3, channels), 9 * channels)
-            w["b%d_b%d" % (i, j)] = (rng.standard_normal(channels) * 0.01).astype(np.float32)
-    w["policy_w"] = he_normal(rng, (1, 1, 1, channels), channels)
-    w["policy_b"] = (rng.standard_normal(1) * 0.01).astype(np.float32)
-    w["value_w"] = he_normal(rng, (3, channels), channels)
-    w["value_b"] = (rng.standard_normal(3) * 0.01).astype(np.float32)
-    return w
-
-
 class ResNetTrunk:
     """Bit-packed input planes -> stem 3x3 -> `blocks` residual blocks of two 3x3 convolutions -> 1x1 policy head and
     global-average-pool + dense value head.  `predict` walks the nodes in insertion order like Graph::predict."""
@@ -213,15 +199,15 @@ class ResNetTrunk:
         self.value = Dense(ctx, weights["value_w"], weights["value_b"], "linear", dtype)
 
         def act():
-            return torch.empty((batch, height, width, channels), dtype=dtype, device="cuda")
+            return torch.empty((batch, height, width, channels), dtype=dtype, device=ctx.device)
         self.words = (in_planes + 31) // 32
-        self.packed = torch.empty((batch, height, width, self.words), dtype=torch.int32, device="cuda")
-        self.x0 = torch.empty((batch, height, width, in_planes), dtype=dtype, device="cuda")
+        self.packed = torch.empty((batch, height, width, self.words), dtype=torch.int32, device=ctx.device)
+        self.x0 = torch.empty((batch, height, width, in_planes), dtype=dtype, device=ctx.device)
         self.a, self.b, self.c = act(), act(), act()
-        self.policy_out = torch.empty((batch, height, width, 1), dtype=dtype, device="cuda")
-        self.pooled = torch.empty((batch, channels), dtype=dtype, device="cuda")
-        self.value_out = torch.empty((batch, 3), dtype=dtype, device="cuda")
-        self.workspace = Workspace()
+        self.policy_out = torch.empty((batch, height, width, 1), dtype=dtype, device=ctx.device)
+        self.pooled = torch.empty((batch, channels), dtype=dtype, device=ctx.device)
+        self.value_out = torch.empty((batch, 3), dtype=dtype, device=ctx.device)
+        self.workspace = Workspace(ctx)
         self.workspace.reserve(max(self.stem.workspace_bytes(self.x0.shape), self.convs[0][0].workspace_bytes(self.a.shape) if blocks else 0))
 
     def conv_flops_per_position(self):
@@ -250,24 +236,6 @@ class ResNetTrunk:
 
 
 # ------------------------------------------------------------------------------------------------------ hybrid block
-def make_hybrid_weights(seed, embed, heads, ffn, board):
-    """N(0, 0.02) weights for the conv + attention block: a 3x3 residual block, pre-LN attention with a relative-position
-    table [heads, 2R-1, round_up(2R-1, 4)] (R = board size), and a ReLU feed-forward network embed -> ffn -> embed."""
-    rng = np.random.default_rng(seed)
-
-    def n(*shape):
-        return (rng.standard_normal(shape) * 0.02).astype(np.float32)
-    size = 2 * board - 1
-    return {
-        "c1_w": n(embed, 3, 3, embed), "c1_b": n(embed), "c2_w": n(embed, 3, 3, embed), "c2_b": n(embed),
-        "ln1_g": np.ones(embed, np.float32), "ln1_b": np.zeros(embed, np.float32),
-        "qkv_w": n(3 * embed, 1, 1, embed), "qkv_b": n(3 * embed), "table": n(heads, size, (size + 3) // 4 * 4),
-        "proj_w": n(embed, 1, 1, embed), "proj_b": n(embed),
-        "ln2_g": np.ones(embed, np.float32), "ln2_b": np.zeros(embed, np.float32),
-        "ffn1_w": n(ffn, 1, 1, embed), "ffn1_b": n(ffn), "ffn2_w": n(embed, 1, 1, ffn), "ffn2_b": n(embed),
-    }
-
-
 class HybridBlock:
     """x -> 3x3 residual block -> x + proj(MHA(qkv(LN(x)))) -> x + FFN(LN(x)), every layer through the calls minml's
     Conv2D (k = 3 and k = 1), LayerNormalization and MultiHeadAttention layers make; skips ride in the convolutions' `ext`."""
@@ -285,10 +253,10 @@ class HybridBlock:
         self.ffn2 = Conv2D(ctx, weights["ffn2_w"], weights["ffn2_b"], "linear", dtype)
 
         def buf(c):
-            return torch.empty((batch, height, width, c), dtype=dtype, device="cuda")
+            return torch.empty((batch, height, width, c), dtype=dtype, device=ctx.device)
         self.t1, self.a, self.n1, self.att, self.a2, self.n2, self.out = (buf(embed) for _ in range(7))
         self.qkv_out, self.f1 = buf(3 * embed), buf(ffn)
-        self.workspace = Workspace()
+        self.workspace = Workspace(ctx)
         self.workspace.reserve(self.conv1.workspace_bytes((batch, height, width, embed)))
         self.flops_per_item = (2 * 2 * height * width * 9 * embed * embed + 2 * height * width * embed * (3 * embed + embed + 2 * ffn)
                                + 4 * (height * width) ** 2 * embed)

@@ -52,7 +52,7 @@ class QuantizedTrunk:
         from .layers import _dev
         for _ in range(calibration_batches):
             planes = (rng.random((calib_batch, height, width, in_planes)) < 0.3).astype(np.float32)
-            x0 = _dev(planes, torch.float16)
+            x0 = _dev(ctx, planes, torch.float16)
             ref.stem.forward([x0], ref.a, ref.workspace)
             ctx.synchronize()
             maxima[0] = max(maxima[0], float(ref.a.abs().max()))
@@ -98,16 +98,16 @@ class QuantizedTrunk:
         self.value = L.Dense(ctx, weights["value_w"], weights["value_b"], "linear", torch.float16)
 
         def act8():
-            return torch.empty((batch, height, width, channels), dtype=torch.int8, device="cuda")
+            return torch.empty((batch, height, width, channels), dtype=torch.int8, device=ctx.device)
         self.words = (in_planes + 31) // 32
-        self.packed = torch.empty((batch, height, width, self.words), dtype=torch.int32, device="cuda")
-        self.x0 = torch.empty((batch, height, width, in_planes), dtype=torch.int8, device="cuda")
+        self.packed = torch.empty((batch, height, width, self.words), dtype=torch.int32, device=ctx.device)
+        self.x0 = torch.empty((batch, height, width, in_planes), dtype=torch.int8, device=ctx.device)
         self.a, self.b, self.c = act8(), act8(), act8()
-        self.last = torch.empty((batch, height, width, channels), dtype=torch.float16, device="cuda")
-        self.policy_out = torch.empty((batch, height, width, 1), dtype=torch.float16, device="cuda")
-        self.pooled = torch.empty((batch, channels), dtype=torch.float16, device="cuda")
-        self.value_out = torch.empty((batch, 3), dtype=torch.float16, device="cuda")
-        self.workspace = L.Workspace()
+        self.last = torch.empty((batch, height, width, channels), dtype=torch.float16, device=ctx.device)
+        self.policy_out = torch.empty((batch, height, width, 1), dtype=torch.float16, device=ctx.device)
+        self.pooled = torch.empty((batch, channels), dtype=torch.float16, device=ctx.device)
+        self.value_out = torch.empty((batch, 3), dtype=torch.float16, device=ctx.device)
+        self.workspace = L.Workspace(ctx)
         self.workspace.reserve(self.convs[0][0].workspace_bytes(self.a.shape))
 
     def predict(self, packed_input=None):

@@ -50,6 +50,14 @@ class Replicas:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return [float(v) for v in t]
 
+    def gather_floats(self, value):
+        """This rank's number from every rank, in rank order (identical list on every rank): used to name the slowest rank."""
+        t = torch.zeros(self.world, dtype=torch.float64, device=self.device)
+        t[self.rank] = float(value)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return [float(v) for v in t]
+
     def throughput(self, units_per_rank, local_seconds):
         """Whole-job units per second: all ranks' units over the slowest rank's time."""
         slowest = self.max_over_ranks([local_seconds])[0]

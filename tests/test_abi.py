@@ -50,3 +50,34 @@ def test_stub_records_not_implemented_without_a_context():
     lib.cuda_hash_routing(None, t, t)
     assert b"not implemented" in lib.mb200_get_last_error(None)
     lib.mb200_clear_last_error(None)
+
+
+def test_tensor_on_another_device_is_refused_on_the_host():
+    """A tensor that lives on cuda:0 must not reach a context of cuda:1: the Python mirror raises before any launch.  Checked
+    here with stand-ins (no GPU needed): the test is about the host-side guard, not about device memory."""
+    import types
+
+    import pytest
+
+    from minml_b200 import backend as B
+
+    class FakeTensor:
+        def __init__(self, index):
+            self.is_cuda = True
+            self.device = types.SimpleNamespace(index=index)
+            self.shape = (2, 3)
+            self.dtype = None
+
+        def is_contiguous(self):
+            return True
+
+        def data_ptr(self):
+            return 256
+
+    fake_ctx = types.SimpleNamespace(device_index=1)
+    assert B.ptr(FakeTensor(1), fake_ctx).value == 256
+    assert B.ptr(None, fake_ctx) is None
+    with pytest.raises(B.BackendError, match="cuda:0 passed to a context of cuda:1"):
+        B.ptr(FakeTensor(0), fake_ctx)
+    with pytest.raises(B.BackendError, match="cuda:0 passed to a context of cuda:1"):
+        B.desc(FakeTensor(0), fake_ctx)

@@ -125,6 +125,71 @@ def test_int8_conv(ctx, oracle, fusion, k, shape, zero_shift):
     ctx.set_fusion(True)
 
 
+@pytest.mark.parametrize("fusion", [False, True])
+def test_int8_conv_against_the_reference_layer(ctx, fusion):
+    """Every int8 path of the library against the outputs minml's own Conv2D computed on its CPU device
+    (tests/golden/int8_conv_cases.bin, the scalar loop of src/layers/Conv2D.cpp:240-308): with ReLU or no activation the int8 and
+    fp32 outputs are equal BIT FOR BIT -- same accumulators, same requantisation formula and rounding order on every path;
+    with sigmoid / tanh (different exp implementations on the two machines) within one int8 step, and nearly all equal.
+    36-channel cases take the three kernels also with fusion on; the 32- and 128-channel cases run the fused kernel (gather and
+    copy-engine operand paths, the latter with the border corrections of a non-zero quantised zero)."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    from tests.util import load_int8_conv_cases
+    ctx.set_fusion(fusion)
+    for name, c in load_int8_conv_cases().items():
+        out_dtype = torch.int8 if c["output"].dtype == np.int8 else torch.float32
+        conv = L.QuantizedConv2D(ctx, c["weights"], c["channel_scales"], c["bias"], c["in_qd"], c["out_qd"], c["activation"], out_dtype)
+        assert conv.input_zero == c["input_zero"], name
+        ws = L.Workspace()
+        ws.reserve(conv.workspace_bytes(c["input"].shape))
+        y = torch.zeros(c["output"].shape, device="cuda", dtype=out_dtype)
+        before = B.launch_count()
+        conv.forward([dev(c["input"])] + ([dev(c["ext"])] if c["ext"] is not None else []), y, ws, c["ext_qd"])
+        ctx.synchronize()
+        launches = B.launch_count() - before
+        if fusion and c["kernel"] == 3 and c["input"].shape[-1] % 16 == 0:
+            assert launches <= 2, "%s: expected the fused kernel (+ border table), saw %d launches" % (name, launches)
+        got = host(y)
+        if c["activation"] in ("relu", "linear"):
+            if out_dtype == torch.int8:
+                assert np.array_equal(got, c["output"]), "%s: %d of %d int8 outputs differ" % (name, int(np.sum(got != c["output"])), got.size)
+            else:
+                assert np.array_equal(got.view(np.uint32), c["output"].view(np.uint32)), name
+        else:
+            diff = np.abs(got.astype(np.int32) - c["output"].astype(np.int32))
+            assert diff.max() <= 1 and np.mean(diff != 0) <= 0.01, "%s: max step %d, %.4f differ" % (name, diff.max(), np.mean(diff != 0))
+    ctx.set_fusion(True)
+
+
+def test_int8_fused_and_eager_outputs_are_identical(ctx):
+    """One requantisation formula on every path: the fused kernel's fast path (cout a multiple of 16, aligned rows), its general
+    path (a column tail; an output tensor that does not start on a 16-byte boundary) and the three eager kernels give the same
+    int8 bits, with ReLU and a residual input."""
+    from minml_b200 import layers as L
+    r = np.random.default_rng(77)
+    for (b, h, w, cin, cout), offset in (((3, 9, 10, 64, 128), 0), ((3, 9, 10, 64, 104), 0), ((2, 8, 8, 128, 128), 8), ((2, 8, 8, 32, 40), 4)):
+        q = r.integers(-127, 128, (cout, 3, 3, cin), dtype=np.int8)
+        cs = r.uniform(2e-4, 6e-4, cout).astype(np.float32)
+        qb = (r.standard_normal(cout) * 0.3).astype(np.float32)
+        xq = dev(r.integers(-128, 128, (b, h, w, cin), dtype=np.int8))
+        extq = dev(r.integers(-128, 128, (b, h, w, cout), dtype=np.int8))
+        conv = L.QuantizedConv2D(ctx, q, cs, qb, (0.02, 0.5), (0.031, 1.7), "relu", torch.int8)
+        ws = L.Workspace()
+        ws.reserve(conv.workspace_bytes(xq.shape))
+        outs = []
+        for fusion in (True, False):
+            ctx.set_fusion(fusion)
+            flat = torch.zeros(b * h * w * cout + 64, device="cuda", dtype=torch.int8)
+            y = flat[offset:offset + b * h * w * cout].view(b, h, w, cout)
+            conv.forward([xq, extq], y, ws, (0.027, -0.4))
+            ctx.synchronize()
+            outs.append(host(y).copy())
+        ctx.set_fusion(True)
+        assert len(np.unique(outs[0])) > 50
+        assert np.array_equal(outs[0], outs[1]), "cout %d offset %d: %d differ" % (cout, offset, int(np.sum(outs[0] != outs[1])))
+
+
 def test_int8_accumulators_fused_path_bit_exact(ctx, oracle):
     """With a requantisation that is the identity on integers (scale 1, shift 0, fp32 out) the fused kernel's output IS the int32 accumulator."""
     from minml_b200 import layers as L
@@ -270,3 +335,138 @@ def test_trunk_step_replayed_as_cuda_graph(ctx, oracle):
     weights16 = {k: v.astype(np.float16).astype(np.float32) for k, v in weights.items()}
     want_p, want_v = oracle_trunk(oracle, weights16, x2, blocks)
     assert max_rel_err(host(results[1][0]), want_p) <= FP16_REL and max_rel_err(host(results[1][1]), want_v) <= FP16_REL
+
+
+# ------------------------------------------------------------------------------------------- snapshot semantics, aliasing, threads
+def test_fused_path_uses_a_snapshot_of_the_weights(ctx, oracle):
+    """In the reference the transformed matrices are a snapshot of the weights at transform time.  The fused kernel reads raw
+    weights, so the library keeps its own copy made by cuda_winograd_weight_transform: overwriting (or freeing) the host's
+    weight tensor afterwards must not change the result, with fusion on exactly as with fusion off."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    x, wt, bias, ext = _case(501, 3, 10, 11, 64, 64)
+    conv = L.Conv2D(ctx, wt, bias, "relu", torch.float16)
+    ws = L.Workspace(ctx)
+    ws.reserve(conv.workspace_bytes(x.shape))
+    xd, extd = dev(x, torch.float16), dev(ext, torch.float16)
+    want = oracle.conv2d(host(xd), host(conv.weights), host(conv.bias), host(extd), "relu")
+    outs = {}
+    for fusion in (True, False):
+        ctx.set_fusion(fusion)
+        y = torch.zeros((3, 10, 11, 64), device="cuda", dtype=torch.float16)
+        conv.forward([xd, extd], y, ws)  # first call: transforms the weights (and takes the snapshot)
+        ctx.synchronize()
+        conv.weights.normal_()  # the host reuses the raw weight tensor for something else
+        torch.cuda.synchronize()
+        before = B.launch_count()
+        y.zero_()
+        conv.forward([xd, extd], y, ws)
+        ctx.synchronize()
+        assert B.launch_count() - before == (1 if fusion else 3)
+        outs[fusion] = host(y)
+        assert max_rel_err(outs[fusion], want) <= (FP16_REL if fusion else 2.5e-2), "fusion %s" % fusion
+        # restore for the next round: a new transform replaces the snapshot
+        conv.weights.copy_(dev(wt, torch.float16))
+        conv.transformed = None
+    ctx.set_fusion(True)
+
+
+def test_writing_into_the_transformed_weights_drops_the_snapshot(ctx, oracle):
+    """A host that loads transformed weights directly (a copy through the ABI into the matrices) makes the snapshot stale: the
+    sequence must then run on the three eager kernels, which read the matrices as they are."""
+    import ctypes
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    x, wt, bias, _ = _case(502, 2, 8, 8, 32, 32)
+    x2, wt2, _, _ = _case(503, 2, 8, 8, 32, 32)
+    conv = L.Conv2D(ctx, wt, bias, "linear", torch.float16)
+    other = L.Conv2D(ctx, wt2, bias, "linear", torch.float16)
+    ws = L.Workspace(ctx)
+    ws.reserve(conv.workspace_bytes(x.shape))
+    xd = dev(x, torch.float16)
+    y = torch.zeros((2, 8, 8, 32), device="cuda", dtype=torch.float16)
+    conv.forward([xd], y, ws)
+    other.forward([xd], y, ws)
+    ctx.synchronize()
+    nbytes = other.transformed.numel() * 2
+    B.lib.cuda_memcpy_within_device(ctx.handle, ctypes.c_void_p(conv.transformed.data_ptr()), 0, ctypes.c_void_p(other.transformed.data_ptr()), 0, nbytes)
+    before = B.launch_count()
+    conv.forward([xd], y, ws)
+    ctx.synchronize()
+    assert B.launch_count() - before == 3  # eager: the snapshot no longer describes the matrices
+    want = oracle.conv2d(host(xd), host(other.weights), host(conv.bias), None, "linear")
+    assert max_rel_err(host(y), want) <= 2.5e-2
+
+
+@pytest.mark.parametrize("fusion", [True, False])
+def test_convolution_in_place(ctx, oracle, fusion):
+    """y aliasing x: correct on the three-kernel path (the transformed input is complete before y is written); the fused kernel
+    would read neighbourhoods that other CTAs overwrite, so such calls are routed to the eager kernels, also with fusion on."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    x, wt, bias, _ = _case(504, 4, 12, 12, 64, 64)
+    conv = L.Conv2D(ctx, wt, bias, "relu", torch.float16)
+    ws = L.Workspace(ctx)
+    ws.reserve(conv.workspace_bytes(x.shape))
+    xd = dev(x, torch.float16)
+    want = oracle.conv2d(host(xd), host(conv.weights), host(conv.bias), None, "relu")
+    ctx.set_fusion(fusion)
+    conv.forward([xd], xd, ws)
+    ctx.synchronize()
+    assert max_rel_err(host(xd), want) <= 2.5e-2
+    xd2 = dev(x, torch.float16)
+    B.convolutionImplicitGemmForward(ctx, xd2, conv.weights, xd2, conv.bias, None, "relu")
+    ctx.synchronize()
+    assert max_rel_err(host(xd2), want) <= 2.5e-2
+    ctx.set_fusion(True)
+
+
+def test_two_threads_two_contexts(oracle):
+    """One context per host thread, as minml's search code runs its networks: thread A loops fused convolutions (the recorded call
+    triple) on its context while thread B allocates, fills and frees tensors through the ABI -- cuda_free and the null-context
+    memset flush EVERY context's recorded calls.  Both must see correct results throughout."""
+    import ctypes
+    import threading
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    ctx_a, ctx_b = B.Context(0), B.Context(0)
+    x, wt, bias, ext = _case(505, 2, 9, 9, 32, 32)
+    conv = L.Conv2D(ctx_a, wt, bias, "relu", torch.float16)
+    ws = L.Workspace(ctx_a)
+    ws.reserve(conv.workspace_bytes(x.shape))
+    xd, extd = dev(x, torch.float16), dev(ext, torch.float16)
+    want = oracle.conv2d(host(xd), host(conv.weights), host(conv.bias), host(extd), "relu")
+    stop = threading.Event()
+    errors = []
+
+    def allocator():
+        B.lib.cuda_malloc.restype = ctypes.c_void_p
+        try:
+            while not stop.is_set():
+                p = B.lib.cuda_malloc(0, 4096)
+                B.lib.cuda_memset(None, ctypes.c_void_p(p), 0, 4096, None, 0)  # null context: flushes every context
+                B.lib.cuda_free(ctypes.c_void_p(p))
+        except Exception as exc:  # pragma: no cover
+            errors.append(exc)
+
+    t = threading.Thread(target=allocator)
+    t.start()
+    try:
+        for i in range(200):
+            y = torch.zeros((2, 9, 9, 32), device="cuda", dtype=torch.float16)
+            conv.forward([xd, extd], y, ws)
+            ctx_a.synchronize()
+            err = max_rel_err(host(y), want)
+            assert err <= 2.5e-2, "iteration %d: %g" % (i, err)  # fused (1e-2) or, when the other thread flushed in between, eager
+    finally:
+        stop.set()
+        t.join()
+    assert errors == []
+    # and a plain GEMM on the second context still works
+    a = dev(np.random.default_rng(1).standard_normal((64, 32)).astype(np.float32), torch.float16)
+    c = torch.zeros((64, 64), device="cuda", dtype=torch.float16)
+    B.gemm(ctx_b, "n", a, "t", dev(np.eye(64, 32, dtype=np.float32), torch.float16), c)
+    ctx_b.synchronize()
+    assert np.allclose(host(c)[:, :32], host(a), atol=1e-3)
+    ctx_a.close()
+    ctx_b.close()

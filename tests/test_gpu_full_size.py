@@ -7,8 +7,10 @@ what is checked instead holds at any size:
     wherever its tile lands), which exercises the tile / cluster scheduling over the whole tensor;
   * linearity of the convolution in its input (linear activation), within the fp16 tolerance.
 
-Tolerances: fp16 max |d| / max |ref| <= 1e-2 per layer, int32 accumulators bit-exact; the 41-layer trunk accumulates fp16
-rounding layer after layer, its bound (3e-2 at the heads) is stated in the test.
+Tolerances: fp32 mean |d| <= 1e-4 (the reference's own metric and threshold); fp16 max |d| / max |ref| <= 1e-2 per layer and
+for the 21-layer trunk of config 1; int32 accumulators bit-exact.  The 41-layer trunk of config 3 is held to 2e-3 against the
+oracle chain that stores every activation in fp16 like the device does, and its distance from the pure fp32 chain is
+printed (run with -s) and bounded by what that fp16 storage alone costs the oracle, plus 2e-3.
 """
 import numpy as np
 import pytest
@@ -25,6 +27,72 @@ def _sample_items(batch):
 
 def _perm(batch, seed):
     return torch.from_numpy(np.random.default_rng(seed).permutation(batch)).cuda()
+
+
+def test_config0_layer_full_size(ctx, oracle, refcpu):
+    """Benchmark configuration 0 at its stated size: fp32, batch 64, 15x15, 128 -> 128, y = ReLU(conv + bias), through the
+    reference's own call triple and through the single-call entry; against the oracle on every item (it is small enough) and
+    against minml's CPU backend (its F(4x4,3x3) Winograd path), mean absolute difference <= 1e-4, the threshold of the
+    reference's own test of this path (test/backend/test_conv2D.cpp:580-629)."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    b, h, w, c = 64, 15, 15, 128
+    r = np.random.default_rng(1234)
+    x = r.uniform(-1, 1, (b, h, w, c)).astype(np.float32)
+    wt = (r.standard_normal((c, 3, 3, c)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    bias = (r.standard_normal(c) * 0.01).astype(np.float32)
+    want = oracle.conv2d(x, wt, bias, None, "relu")
+    assert np.mean(np.abs(want - refcpu.conv3x3_winograd(x, wt, bias, None, "relu", 4))) <= 1e-4  # oracle and reference agree here
+    conv = L.Conv2D(ctx, wt, bias, "relu", torch.float32)
+    ws = L.Workspace()
+    ws.reserve(conv.workspace_bytes(x.shape))
+    xd = torch.from_numpy(x).cuda()
+    for fusion in (True, False):
+        ctx.set_fusion(fusion)
+        y = torch.full((b, h, w, c), float("nan"), device="cuda")
+        before = B.launch_count()
+        conv.forward([xd], y, ws)
+        ctx.synchronize()
+        print("config 0, fusion %s: %d launches, mean |d| %.3g, max |d| %.3g" % (fusion, B.launch_count() - before,
+              np.mean(np.abs(host(y) - want)), np.max(np.abs(host(y) - want))))
+        assert np.mean(np.abs(host(y) - want)) <= 1e-4
+        assert np.max(np.abs(host(y) - want)) <= 1e-3
+    ctx.set_fusion(True)
+    y = torch.full((b, h, w, c), float("nan"), device="cuda")
+    B.convolutionImplicitGemmForward(ctx, xd, conv.weights, y, conv.bias, None, "relu")
+    ctx.synchronize()
+    assert np.mean(np.abs(host(y) - want)) <= 1e-4
+    perm = _perm(b, 7)
+    yp = torch.empty_like(y)
+    B.convolutionImplicitGemmForward(ctx, xd[perm].contiguous(), conv.weights, yp, conv.bias, None, "relu")
+    ctx.synchronize()
+    assert torch.equal(yp, y[perm])
+
+
+def test_config1_trunk_full_size(ctx, oracle):
+    """The whole config-1 trunk at its stated size (batch 256, 15x15, 32 planes, 10 blocks x 128 channels, fp16): batch
+    permutation bit-exact at the heads, eight sampled positions within 1e-2 of the fp32 oracle trunk."""
+    from minml_b200 import layers as L
+    b, h, w, planes, channels, blocks = 256, 15, 15, 32, 128, 10
+    weights = L.make_trunk_weights(1235, planes, channels, blocks)
+    weights16 = {k: v.astype(np.float16).astype(np.float32) for k, v in weights.items()}
+    x = (np.random.default_rng(18).random((b, h, w, planes)) < 0.3).astype(np.float32)
+    net = L.ResNetTrunk(ctx, weights, b, h, w, planes, channels, blocks)
+    packed = torch.from_numpy(pack_planes(x).view(np.int32)).cuda()
+    policy, value = net.predict(packed)
+    ctx.synchronize()
+    policy, value = policy.clone(), value.clone()
+    assert bool(torch.isfinite(policy).all()) and bool(torch.isfinite(value).all())
+    perm = _perm(b, 13)
+    policy_p, value_p = net.predict(packed[perm].contiguous())
+    ctx.synchronize()
+    assert torch.equal(policy_p, policy[perm]) and torch.equal(value_p, value[perm])
+    items = sorted(set(_sample_items(b) + [b // 4]))
+    assert len(items) >= 8
+    want_p, want_v = oracle_trunk(oracle, weights16, x[items], blocks)
+    ep, ev = max_rel_err(host(policy[items]), want_p), max_rel_err(host(value[items]), want_v)
+    print("config 1 trunk against the fp32 oracle: policy %.3g value %.3g" % (ep, ev))
+    assert ep <= FP16_REL and ev <= FP16_REL
 
 
 def test_config3_layer_full_size(ctx, oracle):
@@ -107,8 +175,10 @@ def test_config2_int8_layer_full_size(ctx, oracle):
 
 
 def test_config3_trunk_full_size(ctx, oracle):
-    """The whole config-3 trunk (20 blocks x 256 channels, batch 1024): batch permutation bit-exact at the heads, and two sampled
-    positions against the fp32 oracle trunk.  41 fp16 layers accumulate rounding: bound 3e-2 at the heads."""
+    """The whole config-3 trunk (20 blocks x 256 channels, batch 1024): batch permutation bit-exact at the heads, and eight
+    sampled positions against two oracle trunks: the one that stores every activation in fp16 as the device must (the ABI's
+    tensors are fp16) within 2e-3, and the pure fp32 one within what that storage alone costs the oracle plus 2e-3 -- so the
+    error that 41 fp16 layers accumulate is attributed to the storage format, not to the kernels."""
     from minml_b200 import layers as L
     b, h, w, planes, channels, blocks = 1024, 20, 20, 32, 256, 20
     weights = L.make_trunk_weights(1237, planes, channels, blocks)
@@ -124,10 +194,18 @@ def test_config3_trunk_full_size(ctx, oracle):
     policy_p, value_p = net.predict(packed[perm].contiguous())
     ctx.synchronize()
     assert torch.equal(policy_p, policy[perm]) and torch.equal(value_p, value[perm])
-    items = [0, b - 1]
+    items = sorted(set(_sample_items(b) + [b // 4]))
+    assert len(items) >= 8
     want_p, want_v = oracle_trunk(oracle, weights16, x[items], blocks)
-    assert max_rel_err(host(policy[items]), want_p) <= 3e-2
-    assert max_rel_err(host(value[items]), want_v) <= 3e-2
+    stored_p, stored_v = oracle_trunk(oracle, weights16, x[items], blocks, fp16_storage=True)
+    got_p, got_v = host(policy[items]), host(value[items])
+    storage_p, storage_v = max_rel_err(stored_p, want_p), max_rel_err(stored_v, want_v)  # what fp16 activations cost the oracle itself
+    ep, ev = max_rel_err(got_p, want_p), max_rel_err(got_v, want_v)
+    sp, sv = max_rel_err(got_p, stored_p), max_rel_err(got_v, stored_v)
+    print("config 3 trunk, %d positions: against the fp32 oracle policy %.3g value %.3g; against the oracle with fp16 activations "
+          "policy %.3g value %.3g; fp16 storage alone costs the oracle policy %.3g value %.3g" % (len(items), ep, ev, sp, sv, storage_p, storage_v))
+    assert sp <= 2e-3 and sv <= 2e-3
+    assert ep <= storage_p + 2e-3 and ev <= storage_v + 2e-3
 
 
 def test_config4_block_full_size(ctx, oracle):

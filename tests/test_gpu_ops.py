@@ -256,13 +256,13 @@ def test_empty_tensors_launch_nothing_and_record_no_error(ctx):
 
 
 def test_kernel_bench_tool_runs_and_reports_every_kernel():
-    """The per-kernel timing tool (python -m minml_b200.kernel_bench) at the smallest configuration: one JSON line per kernel,
+    """The per-kernel timing tool (python kernel_bench.py) at the smallest configuration: one JSON line per kernel,
     finite positive times, fractions of the peaks in range."""
     import json
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    out = subprocess.run([sys.executable, "-m", "minml_b200.kernel_bench", "--config", "c1", "--reps", "2"], cwd=root, capture_output=True,
+    out = subprocess.run([sys.executable, os.path.join(root, "kernel_bench.py"), "--config", "c1", "--reps", "2"], cwd=root, capture_output=True,
                          text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
     records = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]

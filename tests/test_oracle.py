@@ -170,6 +170,33 @@ def test_int8_conv_self_consistency(oracle):
     assert np.max(np.abs(y8b.astype(np.int32) - y8.astype(np.int32))) <= 1  # (x - z) / s  versus  x * (1/s) - z/s
 
 
+def test_int8_conv_bit_for_bit_against_the_reference_layer(oracle):
+    """The restatement of the integer convolution against the outputs of minml's own Conv2D on Device::cpu() (the scalar loop
+    of src/layers/Conv2D.cpp:240-308 after Layer::setupQuantization), committed as tests/golden/int8_conv_cases.bin: quantised
+    weights, channel scales, absorbed bias, int8 and fp32 outputs are all equal bit for bit -- 3x3 and 1x1, zero and non-zero
+    quantised zeros (padding), with and without a residual input, every activation the loop handles."""
+    from tests.util import load_int8_conv_cases
+    cases = load_int8_conv_cases()
+    assert sorted(cases) == ["k1_sigmoid_ext_i8", "k3_linear_f32", "k3_linear_f32_c128", "k3_relu_ext_i8", "k3_relu_ext_i8_c128",
+                             "k3_relu_ext_i8_c32", "k3_relu_min_i8", "k3_tanh_sym_i8"]
+    assert [cases[n]["input_zero"] for n in sorted(cases)] == [-7, 55, 55, -37, -128, -37, -128, 0]
+    for name, c in cases.items():
+        if c["raw_weights"] is not None:  # the wide cases keep only the quantised parameters
+            from minml_b200.networks import quantize_weights  # the numpy restatement the int8 trunk is built with
+            for fn in (oracle.quantize_weights, quantize_weights):
+                q, cs, qb = fn(c["raw_weights"], c["raw_bias"], *c["in_qd"])
+                assert np.array_equal(q, c["weights"]), name
+                assert np.array_equal(cs.view(np.uint32), c["channel_scales"].view(np.uint32)), name
+                assert np.array_equal(qb.view(np.uint32), c["bias"].view(np.uint32)), name
+        y8, yf, _ = oracle.conv2d_int8(c["input"], c["weights"], c["channel_scales"], c["bias"], c["input_zero"], c["out_qd"], c["activation"],
+                                       c["ext"], c["ext_qd"])
+        if c["output"].dtype == np.int8:
+            assert np.array_equal(y8, c["output"]), "%s: %d of %d int8 outputs differ" % (name, int(np.sum(y8 != c["output"])), y8.size)
+            assert len(np.unique(y8)) > 20  # not saturated: the comparison means something
+        else:
+            assert np.array_equal(yf.view(np.uint32), c["output"].view(np.uint32)), name
+
+
 def test_quantize_weights(oracle):
     r = rng(5)
     w = (r.standard_normal((8, 3, 3, 4)) * 0.2).astype(np.float32)

@@ -2,6 +2,10 @@
 import numpy as np
 import torch
 
+from minml_b200.synthetic import pack_planes  # noqa: F401  (the tests import it from here)
+from tests.util_cpu import (forward_loaded_network_on_cpu, load_int8_conv_cases, oracle_hybrid, oracle_quantized_trunk,  # noqa: F401
+                            oracle_trunk)
+
 
 def dev(a, dtype=None):
     t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
@@ -31,108 +35,3 @@ def max_rel_err(got, want):
 FP32_TOL = 1e-4   # mean absolute difference, as the reference's fp32 tests use
 FP16_REL = 1e-2
 INT8_REL = 2e-2
-
-
-def oracle_trunk(oracle, weights, x, blocks):
-    """fp32 forward of the ResNet trunk topology with the oracle's direct convolution: (policy [b,h,w,1], value [b,3])."""
-    a = oracle.conv2d(x, weights["stem_w"], weights["stem_b"], None, "relu")
-    for i in range(blocks):
-        t = oracle.conv2d(a, weights["b%d_w1" % i], weights["b%d_b1" % i], None, "relu")
-        a = oracle.conv2d(t, weights["b%d_w2" % i], weights["b%d_b2" % i], a, "relu")
-    policy = oracle.conv2d(a, weights["policy_w"], weights["policy_b"], None, "linear")
-    pooled = oracle.global_average_pooling(a)
-    value = oracle.add_bias_act(oracle.gemm("n", pooled, "t", weights["value_w"]), weights["value_b"], "linear")
-    return policy, value
-
-
-def oracle_quantized_trunk(oracle, weights, x01, blocks, transforms):
-    """The int8 trunk (minml_b200.networks.QuantizedTrunk) layer by layer on the oracle's integer convolution.
-    `transforms[t]` is the per-tensor (scale, shift) of tensor t (stem output, then two per block), or a bare scale (shift 0)."""
-    qd = [t if isinstance(t, tuple) else (t, 0.0) for t in transforms]
-
-    def zero_of(t):  # the int8 value that dequantises to 0, as layers.QuantizedConv2D computes it
-        return int(np.clip(np.round(-np.float32(t[1]) / np.float32(t[0])), -128, 127))
-
-    def qconv(xq, wn, bn, t_in, t_out, ext=None, t_ext=(1.0, 0.0)):
-        q, cs, qb = oracle.quantize_weights(weights[wn], weights[bn], t_in[0], t_in[1])
-        return oracle.conv2d_int8(xq, q, cs, qb, zero_of(t_in), t_out, "relu", ext, t_ext)
-    a, _, _ = qconv(x01.astype(np.int8), "stem_w", "stem_b", (1.0, 0.0), qd[0])
-    real = None
-    for i in range(blocks):
-        t_in, t_mid, t_out = qd[2 * i], qd[1 + 2 * i], qd[2 + 2 * i]
-        t, _, _ = qconv(a, "b%d_w1" % i, "b%d_b1" % i, t_in, t_mid)
-        a, real, _ = qconv(t, "b%d_w2" % i, "b%d_b2" % i, t_mid, t_out, a, t_in)
-    real = real.astype(np.float16).astype(np.float32)  # the last block hands fp16 to the heads
-    policy = oracle.conv2d(real, weights["policy_w"], weights["policy_b"], None, "linear")
-    pooled = oracle.global_average_pooling(real)
-    value = oracle.add_bias_act(oracle.gemm("n", pooled, "t", weights["value_w"]), weights["value_b"], "linear")
-    return policy, value
-
-
-def pack_planes(x01):
-    """[..., c] array of {0, 1} -> uint32 words [..., ceil(c / 32)], channel j in bit j % 32 of word j // 32."""
-    c = x01.shape[-1]
-    words = (c + 31) // 32
-    out = np.zeros(x01.shape[:-1] + (words,), np.uint32)
-    for j in range(c):
-        out[..., j // 32] |= (x01[..., j].astype(np.uint32) & 1) << np.uint32(j % 32)
-    return out
-
-
-def oracle_hybrid(oracle, w, x, heads):
-    """fp32 forward of the conv + attention block (same topology as minml_b200.layers.HybridBlock)."""
-    def conv1x1(t, wn, bn, ext=None, act="linear"):
-        b, h, ww, c = t.shape
-        out = oracle.gemm("n", t.reshape(-1, c), "t", w[wn].reshape(w[wn].shape[0], -1))
-        if ext is not None:
-            out = out + ext.reshape(out.shape)
-        return oracle.add_bias_act(out, w[bn], act).reshape(b, h, ww, -1)
-    t1 = oracle.conv2d(x, w["c1_w"], w["c1_b"], None, "relu")
-    a = oracle.conv2d(t1, w["c2_w"], w["c2_b"], x, "relu")
-    n1 = oracle.layernorm(a, w["ln1_g"], w["ln1_b"])
-    att = oracle.mha_forward(conv1x1(n1, "qkv_w", "qkv_b"), heads, w["table"])
-    a2 = conv1x1(att, "proj_w", "proj_b", a)
-    n2 = oracle.layernorm(a2, w["ln2_g"], w["ln2_b"])
-    return conv1x1(conv1x1(n2, "ffn1_w", "ffn1_b", None, "relu"), "ffn2_w", "ffn2_b", a2)
-
-
-def forward_loaded_network_on_cpu(oracle, description, blob, x):
-    """Runs a network file (minml_b200.checkpoint's description + blob) through the CPU oracle, node by node; returns the
-    output nodes' values. Only the layer kinds of the convolution path."""
-    from minml_b200 import checkpoint as C
-    values = []
-    nodes = C.nodes_of(description)
-    for node in nodes:
-        layer, ins = node["layer"], node["input_nodes"]
-        kind, act = layer["name"], layer["nonlinearity"]
-        w, b = C.read_tensor(layer.get("weights"), blob), C.read_tensor(layer.get("bias"), blob)
-        if kind == "Input":
-            y = x
-        elif kind == "Conv2D":
-            y = oracle.conv2d(values[ins[0]], w, b if b is not None else np.zeros(w.shape[0], np.float32), None, act)
-        elif kind == "BatchNormalization":
-            y = oracle.batchnorm_inference(values[ins[0]], w, b, C.read_tensor(layer["avg_var"], blob), act)
-        elif kind == "Add":
-            y = oracle.add_bias_act(values[ins[0]] + values[ins[1]], np.zeros(values[ins[0]].shape[-1], np.float32), act)
-        elif kind == "GlobalAveragePooling":
-            y = oracle.global_average_pooling(values[ins[0]])
-        elif kind == "Dense":
-            rows = values[ins[0]].reshape(values[ins[0]].shape[0], -1)
-            y = oracle.add_bias_act(oracle.gemm("n", rows, "t", w), b if b is not None else np.zeros(w.shape[0], np.float32), act)
-        elif kind == "Softmax":
-            y = oracle.softmax(values[ins[0]].reshape(values[ins[0]].shape[0], -1))
-        elif kind == "DepthwiseConv2D":
-            y = oracle.depthwise_conv(values[ins[0]], w, b)
-        elif kind == "RMSNormalization":
-            y = oracle.rmsnorm(values[ins[0]], w)
-        elif kind == "ChannelScaling":
-            y = oracle.channel_scaling(values[ins[0]], values[ins[1]])
-        elif kind == "SpaceToDepth":
-            h, wd = values[ins[0]].shape[1:3]
-            y = oracle.space_to_depth(values[ins[0]], (-(-h // int(layer["patch_size_h"])), -(-wd // int(layer["patch_size_w"]))))
-        elif kind == "DepthToSpace":
-            y = oracle.depth_to_space(values[ins[0]], tuple(int(v) for v in layer["output_shape"]))
-        else:
-            raise NotImplementedError(kind)
-        values.append(np.asarray(y, np.float32))
-    return [values[i] for i, n in enumerate(nodes) if n["is_output_node"]]
