@@ -51,9 +51,9 @@ extern "C"
 		// in place (y overlapping x) only the Winograd path below is correct: V is complete before y is written, whereas the fused
 		// kernel reads the 3x3 neighbourhood of positions that other CTAs are writing
 		const bool in_place = ranges_overlap(input, volume(x) * size_of(dtype), output, volume(y) * size_of(dtype));
-		if (!in_place && conv_fused_supported(x, w, y, act))
+		if (!in_place && conv_fused_supported(context, x, w, y, act))
 		{
-			conv_fused_run(context, x, w, bias, add, y, act);
+			conv_fused_run(context, x, w, bias, add, y, act, false);
 			return;
 		}
 		/* Winograd through the scratch workspace: U | V | M */

@@ -8,13 +8,18 @@
 namespace mb200
 {
 	/* True when an input tensor can be consumed by the fused 3x3 kernel (dtype, channel count, alignment). */
-	bool conv_fused_input_supported(const mlTensor_t &x);
+	bool conv_fused_input_supported(mlContext_t ctx, const mlTensor_t &x);
 	/* True when a raw weight tensor [cout, 3, 3, cin] can be the B operand of the fused kernel (dtype, channel count). */
 	bool conv_fused_weights_supported(const mlTensor_t &w);
 	/* True when y = act(conv3x3(x, w) + bias + ext) can run as the fused kernel. */
-	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act);
+	bool conv_fused_supported(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act);
+	/* `prepared` = w.data points at what conv_fused_prepare_weights wrote (the library's snapshot), not at the host's raw tensor */
 	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
-			mlActivationType_t act);
+			mlActivationType_t act, bool prepared);
+	/* The form in which the fused kernel wants a layer's weights kept: a plain copy for fp16, two planes (w rounded to TF32, and the
+	 * remainder) for fp32.  `prepared` must hold conv_fused_weight_bytes(w); the work is queued on the context's stream. */
+	size_t conv_fused_weight_bytes(const mlTensor_t &w);
+	bool conv_fused_prepare_weights(mlContext_t ctx, const mlTensor_t &w, void *prepared);
 } /* namespace mb200 */
 
 namespace mb200

@@ -4,6 +4,12 @@
  *      y = epilogue( conv3x3(x, w) ),  stride 1, "same" padding, NHWC, w [cout, 3, 3, cin]
  *      fp16:  epilogue = act(acc + bias + ext)                       fp32 accumulation, fp16 out
  *      int8:  epilogue = requantise(act(acc * scale[c] + shift[c] + dequant(ext)))   exact int32 accumulation
+ *      fp32:  epilogue = act(acc + bias + ext)                       fp32 in and out; the products run on the TF32 tensor cores, either
+ *             as one TF32 product (when the host allowed TF32 on the context, cuda_enable_tf32) or, by default, at fp32 accuracy
+ *             as three TF32 products of split operands, x * w ~ xh * wh + xh * wl + xl * wh (error analysis in gemm_tc.cu): the
+ *             weights arrive already split into two planes [2, cout, 9 cin] (made once per layer, at weight-transform time); of the
+ *             activations the tensor core itself takes the upper 19 bits (xh = x truncated to TF32), so the split warps only have
+ *             to write xl = x - xh next to the landed tile
  *
  * It is the single-kernel replacement for the two three-call sequences minml's Conv2D::forward issues
  * (Winograd: src/layers/Conv2D.cpp:365-377; int8: src/layers/Conv2D.cpp:214-239) and the body of
@@ -64,7 +70,8 @@ namespace mb200
 		struct Roles
 		{
 				static constexpr int epi_warps = (KIND == 1 && TMA_A) ? 16 : 8;
-				static constexpr int threads = (TMA_A ? (2 + epi_warps) : 16) * 32;
+				static constexpr int split_warps = (KIND == 3) ? 4 : 0; // fp32 at full accuracy: warps that write the lo part of the landed A tile
+				static constexpr int threads = (TMA_A ? (2 + epi_warps + split_warps) : 16) * 32;
 				static constexpr int staging_bytes = (KIND == 0) ? 8 * 32 * 80 : 0; // only the fp16 epilogue stages rows in shared memory
 		};
 		constexpr int NUM_PRODUCERS = 128;
@@ -85,12 +92,19 @@ namespace mb200
 		struct Cfg
 		{
 				static constexpr int a_stage_bytes = A_STAGE_BYTES * MT;
-				static constexpr int b_stage_bytes = BN / CTAS * 128;
+				static constexpr int b_planes = (KIND == 3) ? 2 : 1; // KIND 3: the hi and the lo plane of the weight slice, one after the other
+				static constexpr int b_stage_bytes = BN / CTAS * 128 * b_planes;
 				// The two operand rings are sized separately: the gathered A slices (cp.async, many small requests) need more
 				// slices in flight to cover their latency than the weight slices that one TMA request fetches.
-				static constexpr int a_stages = (MT == 2) ? 4 : (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
+				static constexpr bool split = (KIND == 3);
+				static constexpr int a_stages = split ? 3 : (MT == 2) ? 4 : (CTAS == 2) ? ((BN == 256) ? 6 : 8) : (TMA_A ? ((BN == 256) ? 4 : 6) : 6);
 				static constexpr int b_stages = TMA_A ? a_stages : ((BN == 256) ? 3 : 6);
-				static constexpr int smem_bytes = a_stages * a_stage_bytes + b_stages * b_stage_bytes + Roles<KIND, TMA_A>::staging_bytes + 1024;
+				// KIND 3: the lo part of a slice's A tile lives in a short ring of its own, from the split to the end of that slice's products
+				static constexpr int lo_stages = split ? 2 : 0;
+				static constexpr int lo_ring = (lo_stages > 0) ? lo_stages : 1; // divisor that is never zero
+				static constexpr int lo_bytes = a_stage_bytes;
+				static_assert(!split || BN == 128, "the split-fp32 variant is built for 128-column tiles");
+				static constexpr int smem_bytes = a_stages * a_stage_bytes + b_stages * b_stage_bytes + lo_stages * lo_bytes + Roles<KIND, TMA_A>::staging_bytes + 1024;
 				static constexpr int tmem_columns = 2 * BN * MT;
 				static_assert(tmem_columns <= 512 && smem_bytes <= 227 * 1024, "tile configuration exceeds the SM");
 		};
@@ -99,8 +113,8 @@ namespace mb200
 		{
 				const void *x;
 				void *y;
-				const void *bias; // fp16 [cout] (fp16 kind)
-				const void *ext; // fp16 or int8 [b, h, w, cout]
+				const void *bias; // fp16 / fp32 [cout] (floating-point kinds)
+				const void *ext; // fp16, fp32 or int8 [b, h, w, cout]
 				int batch, height, width, cin, cout;
 				int M, K;
 				int act;
@@ -123,12 +137,27 @@ namespace mb200
 				uint64_t empty_a[MAX_STAGES];
 				uint64_t full_b[MAX_STAGES];
 				uint64_t empty_b[MAX_STAGES];
+				uint64_t split[MAX_STAGES]; // KIND 3: the stage's hi and lo tiles are written
+				uint64_t lo_empty[2]; // KIND 3: the products that read this lo tile are done
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
 				int abort_flag;
 		};
 
+		/* Weight planes of the split-fp32 kernel: planes[0] = w rounded to the nearest TF32 number (13 low mantissa bits clear),
+		 * planes[1] = w - planes[0], exact in fp32 (gemm_tc.cu has the error analysis). */
+		__global__ void __launch_bounds__(256) kernel_split_weight_planes(float *__restrict__ planes, const float *__restrict__ w, long long elements)
+		{
+			const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+			for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < elements; i += stride)
+			{
+				const uint32_t x = __float_as_uint(w[i]);
+				const uint32_t hi = (x + 0x1000u) & 0xFFFFE000u;
+				planes[i] = __uint_as_float(hi);
+				planes[elements + i] = __uint_as_float(x) - __uint_as_float(hi);
+			}
+		}
 		__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes)
 		{
 			asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -160,17 +189,20 @@ namespace mb200
 		{
 			static_assert(CTAS == 1 || TMA_A, "the paired kernel fetches both operands by TMA");
 			static_assert(MT == 1 || (TMA_A && CTAS == 1), "two row tiles per CTA: TMA operands, single CTAs");
+			static_assert(KIND < 2 || (TMA_A && CTAS == 1 && MT == 1), "fp32: TMA operands, single CTAs, one row tile");
 			using C = Cfg<KIND, BN, TMA_A, CTAS, MT>;
 			constexpr int EPI_WARPS = Roles<KIND, TMA_A>::epi_warps;
 			constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
-			constexpr int ES = (KIND == 0) ? 2 : 1; // operand element size
+			constexpr int ES = (KIND == 0) ? 2 : (KIND == 1) ? 1 : 4; // operand element size
+			constexpr int SPLIT_WARPS = Roles<KIND, TMA_A>::split_warps;
 			constexpr int CHUNK_ELEMS = 16 / ES;
 			extern __shared__ uint8_t smem_raw[];
 			__shared__ ConvBarriers bars;
 
 			const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 			const uint32_t b_base = smem_base + C::a_stages * C::a_stage_bytes;
-			const uint32_t epi_base = b_base + C::b_stages * C::b_stage_bytes;
+			const uint32_t lo_base = b_base + C::b_stages * C::b_stage_bytes;
+			const uint32_t epi_base = lo_base + C::lo_stages * C::lo_bytes;
 			const int warp = threadIdx.x / 32;
 			const int lane = threadIdx.x % 32;
 
@@ -195,9 +227,11 @@ namespace mb200
 				{
 					mbar_init(smem_u32(&bars.full_b[s]), 1);
 					mbar_init(smem_u32(&bars.empty_b[s]), 1);
+					mbar_init(smem_u32(&bars.split[s]), SPLIT_WARPS > 0 ? SPLIT_WARPS : 1);
 				}
 				for (int a = 0; a < 2; a++)
 				{
+					mbar_init(smem_u32(&bars.lo_empty[a]), 1);
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
 					mbar_init(smem_u32(&bars.tmem_empty[a]), EPI_WARPS * CTAS);
 				}
@@ -276,6 +310,8 @@ namespace mb200
 											static_cast<uint16_t>(tap % 3), static_cast<uint16_t>(tap / 3));
 							}
 							tma_load_3d(b_base + s * C::b_stage_bytes, &map_w, full, kb * (128 / ES), nt * BN, 0);
+							if (C::split) // the lo plane of the same weight slice
+								tma_load_3d(b_base + s * C::b_stage_bytes + BN * 128, &map_w, full, kb * (128 / ES), nt * BN, 1);
 						}
 					}
 				}
@@ -286,7 +322,8 @@ namespace mb200
 				if (leader && elect_one())
 				{ // in a pair only the even CTA issues; its instructions drive the tensor cores of both SMs
 					const uint32_t idesc = (CTAS == 2) ? ((KIND == 0) ? make_idesc_f16_pair(BN) : make_idesc_i8_pair(BN))
-							: ((KIND == 0) ? make_idesc_f16(BN) : make_idesc_i8(BN));
+							: ((KIND == 0) ? make_idesc_f16(BN) : (KIND == 1) ? make_idesc_i8(BN) : make_idesc_tf32(BN));
+					uint64_t *const ready_b = C::split ? bars.split : bars.full_b; // what the tensor core may read
 					uint32_t it = 0, local_tile = 0;
 					bool ok = true;
 					for (int unit = first_unit; unit < total_units && ok; unit += unit_step, local_tile++)
@@ -300,15 +337,15 @@ namespace mb200
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
 							const int sa = it % C::a_stages, sb = it % C::b_stages;
-							if (!mbar_wait(smem_u32(&bars.full_b[sb]), (it / C::b_stages) & 1u, abort_flag)
+							if (!mbar_wait(smem_u32(&ready_b[sb]), (it / C::b_stages) & 1u, abort_flag)
 									|| (!TMA_A && !mbar_wait(smem_u32(&bars.full_a[sa]), (it / C::a_stages) & 1u, abort_flag)))
 							{
 								ok = false;
 								break;
 							}
 							tcgen05_fence_after();
-							if (!TMA_A)
-								fence_proxy_async_smem(); // the A slice was written through the generic proxy by other threads
+							if (!TMA_A || C::split)
+								fence_proxy_async_smem(); // the slice was written through the generic proxy by other threads
 							const uint64_t desc_a = make_desc_k_sw128(smem_base + sa * C::a_stage_bytes);
 							const uint64_t desc_b = make_desc_k_sw128(b_base + sb * C::b_stage_bytes);
 							if (CTAS == 2)
@@ -329,6 +366,18 @@ namespace mb200
 #pragma unroll
 									for (int k = 0; k < 4; k++)
 										mma_ss<KIND>(tmem_d + BN, desc_a1 + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+								}
+								if (C::split)
+								{ // x * w = (xh + xl) * (wh + wl) ~ xh * wh + xh * wl + xl * wh  (desc_a names the raw tile: the tensor core reads xh from it)
+									const uint64_t lo_a = make_desc_k_sw128(lo_base + (it % C::lo_ring) * C::lo_bytes);
+									const uint64_t lo_b = make_desc_k_sw128(b_base + sb * C::b_stage_bytes + BN * 128);
+#pragma unroll
+									for (int k = 0; k < 4; k++)
+										mma_ss<KIND>(tmem_d, desc_a + 2 * k, lo_b + 2 * k, idesc, 1u);
+#pragma unroll
+									for (int k = 0; k < 4; k++)
+										mma_ss<KIND>(tmem_d, lo_a + 2 * k, desc_b + 2 * k, idesc, 1u);
+									mma_commit(smem_u32(&bars.lo_empty[it % C::lo_ring]));
 								}
 								if (!TMA_A)
 									mma_commit(smem_u32(&bars.empty_a[sa]));
@@ -531,6 +580,53 @@ namespace mb200
 						if (!row_ok)
 							continue;
 						float v[32];
+						if (KIND >= 2)
+						{ /* fp32 in and out: the lane owns 32 consecutive floats (one 128-byte line) of its row */
+#pragma unroll
+							for (int j = 0; j < 32; j++)
+								v[j] = __uint_as_float(r[j]);
+							const float *bp = (p.bias != nullptr) ? reinterpret_cast<const float*>(p.bias) + n0 : nullptr;
+							const float *ep = (p.ext != nullptr) ? reinterpret_cast<const float*>(p.ext) + off + n0 : nullptr;
+							float *dp = reinterpret_cast<float*>(p.y) + off + n0;
+							const bool vec = n_valid == 32 && (p.cout % 4) == 0 && aligned_to_16(p.y) && (bp == nullptr || aligned_to_16(p.bias))
+									&& (ep == nullptr || aligned_to_16(p.ext));
+							if (vec)
+							{
+#pragma unroll
+								for (int j4 = 0; j4 < 8; j4++)
+								{
+									float4 t = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+									if (bp != nullptr)
+									{
+										const float4 b4 = reinterpret_cast<const float4*>(bp)[j4];
+										t.x += b4.x; t.y += b4.y; t.z += b4.z; t.w += b4.w;
+									}
+									if (ep != nullptr)
+									{
+										const float4 e4 = reinterpret_cast<const float4*>(ep)[j4];
+										t.x += e4.x; t.y += e4.y; t.z += e4.z; t.w += e4.w;
+									}
+									v[4 * j4] = t.x; v[4 * j4 + 1] = t.y; v[4 * j4 + 2] = t.z; v[4 * j4 + 3] = t.w;
+								}
+								activate32(v, p.act);
+#pragma unroll
+								for (int j4 = 0; j4 < 8; j4++)
+									reinterpret_cast<float4*>(dp)[j4] = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										v[j] += (bp != nullptr ? bp[j] : 0.0f) + (ep != nullptr ? ep[j] : 0.0f);
+								activate32(v, p.act);
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (j < n_valid)
+										dp[j] = v[j];
+							}
+							continue;
+						}
 						if (KIND == 0)
 						{
 #pragma unroll
@@ -660,6 +756,46 @@ namespace mb200
 							mbar_arrive(smem_u32(&bars.tmem_empty[buf]));
 					}
 				}
+			}
+			else if (C::split && warp >= 2 + EPI_WARPS)
+			{ /* ------------------------------------------------------------ split warps (fp32 at full accuracy): x -> hi (in place) and lo */
+				const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
+				constexpr int SPLIT_THREADS = (SPLIT_WARPS > 0 ? SPLIT_WARPS : 1) * 32;
+				uint32_t it = 0;
+				bool ok = true;
+				for (int unit = first_unit; unit < total_units && ok; unit += unit_step)
+					for (int kb = 0; kb < k_blocks; kb++, it++)
+					{
+						const int s = it % C::b_stages;
+						if (!mbar_wait(smem_u32(&bars.lo_empty[it % C::lo_ring]), ((it / C::lo_ring) & 1u) ^ 1u, abort_flag)
+								|| !mbar_wait(smem_u32(&bars.full_b[s]), (it / C::b_stages) & 1u, abort_flag))
+						{
+							ok = false;
+							break;
+						}
+						// elementwise, so it keeps whatever swizzled layout the copy engine wrote: xl = x - (x truncated to TF32), exact in fp32
+						const uint32_t raw_tile = smem_base + s * C::a_stage_bytes;
+						const uint32_t lo_tile = lo_base + (it % C::lo_ring) * C::lo_bytes;
+						constexpr int PER_THREAD = C::a_stage_bytes / 16 / SPLIT_THREADS;
+						uint4 x[PER_THREAD];
+#pragma unroll
+						for (int u = 0; u < PER_THREAD; u++)
+							x[u] = ld_shared_v4(raw_tile + (t + u * SPLIT_THREADS) * 16);
+#pragma unroll
+						for (int u = 0; u < PER_THREAD; u++)
+						{
+							uint4 l;
+							l.x = __float_as_uint(__uint_as_float(x[u].x) - __uint_as_float(x[u].x & 0xFFFFE000u));
+							l.y = __float_as_uint(__uint_as_float(x[u].y) - __uint_as_float(x[u].y & 0xFFFFE000u));
+							l.z = __float_as_uint(__uint_as_float(x[u].z) - __uint_as_float(x[u].z & 0xFFFFE000u));
+							l.w = __float_as_uint(__uint_as_float(x[u].w) - __uint_as_float(x[u].w & 0xFFFFE000u));
+							st_shared_v4(lo_tile + (t + u * SPLIT_THREADS) * 16, l);
+						}
+						fence_proxy_async_smem(); // plain stores -> visible to the tensor core's reads
+						__syncwarp();
+						if (lane == 0)
+							mbar_arrive(smem_u32(&bars.split[s]));
+					}
 			}
 			else if (!TMA_A && (warp == 10 || warp == 11 || warp == 14 || warp == 15))
 			{ /* ------------------------------------------------------------ A-operand gather */
@@ -835,7 +971,7 @@ namespace mb200
 
 		bool shape_ok(int kind, const mlTensor_t &x, int cout, const void *w)
 		{
-			const int chunk = (kind == 0) ? 8 : 16;
+			const int chunk = (kind == 0) ? 8 : (kind == 1) ? 16 : 32; // fp32: copy-engine operand path only, 128 bytes of channels per slice
 			if (x.rank != 4 || x.dim[3] % chunk != 0)
 				return false;
 			if (!aligned_to(x.data, 16) || !aligned_to(w, 16))
@@ -872,7 +1008,7 @@ namespace mb200
 				record_error(ctx, "cuTensorMapEncodeIm2col is not available from the driver");
 				return false;
 			}
-			const int es = (kind == 0) ? 2 : 1;
+			const int es = (kind == 0) ? 2 : (kind == 1) ? 1 : 4;
 			const cuuint64_t dims[4] = { static_cast<cuuint64_t>(x.dim[3]), static_cast<cuuint64_t>(x.dim[2]), static_cast<cuuint64_t>(x.dim[1]),
 					static_cast<cuuint64_t>(x.dim[0]) };
 			const cuuint64_t strides[3] = { static_cast<cuuint64_t>(x.dim[3]) * es, static_cast<cuuint64_t>(x.dim[3]) * es * x.dim[2],
@@ -880,7 +1016,7 @@ namespace mb200
 			const int lower[2] = { -1, -1 };
 			const int upper[2] = { -1, -1 };
 			const cuuint32_t traversal[4] = { 1, 1, 1, 1 };
-			const CUresult status = fn(map, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, x.data, dims, strides,
+			const CUresult status = fn(map, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : (kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32), 4, x.data, dims, strides,
 					lower, upper, static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(BM), traversal, CU_TENSOR_MAP_INTERLEAVE_NONE,
 					CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 			if (status != CUDA_SUCCESS)
@@ -927,9 +1063,10 @@ namespace mb200
 			}
 		}
 
+		/* kind 3 expects `w` to be the two planes [2, cout, 9 cin] written by kernel_split_weight_planes */
 		bool run(mlContext_t ctx, int kind, const mlTensor_t &x, const void *w, int cout, ConvParams p)
 		{
-			const int es = (kind == 0) ? 2 : 1;
+			const int es = (kind == 0) ? 2 : (kind == 1) ? 1 : 4;
 			p.x = x.data;
 			p.batch = x.dim[0];
 			p.height = x.dim[1];
@@ -941,7 +1078,7 @@ namespace mb200
 			p.status = get(ctx)->dev_status;
 			p.by_board = FastDiv(static_cast<uint32_t>(p.height) * p.width);
 			p.by_width = FastDiv(static_cast<uint32_t>(p.width));
-			const int bn = (cout > 128) ? 256 : 128;
+			const int bn = (cout > 128 && kind != 3) ? 256 : 128;
 			/* A operand by im2col TMA when each 128-byte K slice stays inside one tap and the padding value is zero */
 			static const bool force_gather = env_flag("MINML_B200_CONV_GATHER"); // measurement switches: each forces the slower variant
 			static const bool force_single = env_flag("MINML_B200_CONV_SINGLE_CTA");
@@ -959,18 +1096,26 @@ namespace mb200
 			// Pairs pay off where the operand fetch is the limit (256-column tiles: 0.383 -> 0.353 ms on the 256 -> 256 layer); with
 			// 128-column tiles the epilogue is, and coupling two CTAs' accumulator hand-offs costs more than it saves (measured).
 			static const bool force_pair = env_flag("MINML_B200_CONV_PAIR");
-			const bool pair = tma_a && !force_single && (bn == 256 || force_pair) && p.M > BM && get(ctx)->sm_count >= 2;
+			const bool pair = kind < 2 && tma_a && !force_single && (bn == 256 || force_pair) && p.M > BM && get(ctx)->sm_count >= 2;
 			CUtensorMap map_w;
-			const uint64_t dims[3] = { static_cast<uint64_t>(p.K), static_cast<uint64_t>(cout), 1 };
+			const uint64_t dims[3] = { static_cast<uint64_t>(p.K), static_cast<uint64_t>(cout), static_cast<uint64_t>(kind == 3 ? 2 : 1) };
 			const uint64_t strides[2] = { static_cast<uint64_t>(p.K) * es, static_cast<uint64_t>(p.K) * es * cout };
 			const uint32_t box[3] = { static_cast<uint32_t>(128 / es), static_cast<uint32_t>(pair ? bn / 2 : bn), 1 };
-			if (!encode_tensor_map(ctx, &map_w, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box,
-					CU_TENSOR_MAP_SWIZZLE_128B))
+			if (!encode_tensor_map(ctx, &map_w, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : (kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32),
+					3, w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
 				return false;
 			CUtensorMap map_x;
 			std::memset(&map_x, 0, sizeof(map_x));
 			if (tma_a && !encode_im2col_map(ctx, &map_x, kind, x))
 				return false;
+			if (kind >= 2)
+			{ // fp32: one TF32 product when the host allowed it on this context, three products of split operands otherwise
+				if (!tma_a)
+					return false;
+				if (kind == 2)
+					return bn == 256 ? launch<2, 256, true>(ctx, map_w, map_x, p) : launch<2, 128, true>(ctx, map_w, map_x, p);
+				return launch<3, 128, true>(ctx, map_w, map_x, p);
+			}
 			if (pair)
 			{
 				if (kind == 0)
@@ -993,25 +1138,64 @@ namespace mb200
 		}
 	}
 
-	bool conv_fused_input_supported(const mlTensor_t &x)
+	namespace
 	{
+		/* fp32 convolutions by the fused kernel: always with TF32 permission (one product per slice: 0.70 ms against the Winograd
+		 * path's 1.50 ms on a 1024 x 20 x 20 x 256 -> 256 layer).  At full fp32 accuracy (three products per slice, fp32 operands
+		 * streamed from L2 at twice the bytes of fp16) only for layers of up to 128 channels, where one launch measured 3 - 17 %
+		 * faster than the Winograd path's three (64 x 15 x 15: 31.8 against 38.2 us; 512 x 20 x 20: 0.288 against 0.315 ms); at 256
+		 * channels F(4x4,3x3), which does a quarter of the multiply-adds, wins (0.40 against 0.53 ms).
+		 * MINML_B200_FP32_FUSED=always|never overrides the rule (measurement switch). */
+		bool fp32_fused_wanted(mlContext_t ctx, const mlTensor_t &x, int cout)
+		{
+			static const char *mode = std::getenv("MINML_B200_FP32_FUSED");
+			if (mode != nullptr && mode[0] == 'n')
+				return false;
+			if (get(ctx)->allow_tf32 || (mode != nullptr && mode[0] == 'a'))
+				return true;
+			return x.dim[3] <= 128 && cout <= 128;
+		}
+	}
+	bool conv_fused_input_supported(mlContext_t ctx, const mlTensor_t &x)
+	{
+		if (x.dtype == DTYPE_FLOAT32)
+			return shape_ok(2, x, 1, x.data) && fp32_fused_wanted(ctx, x, 1);
 		return x.dtype == DTYPE_FLOAT16 && shape_ok(0, x, 1, x.data);
 	}
 	bool conv_fused_weights_supported(const mlTensor_t &w)
 	{
+		if (w.dtype == DTYPE_FLOAT32)
+			return w.rank == 4 && w.dim[3] % 32 == 0;
 		return w.dtype == DTYPE_FLOAT16 && w.rank == 4 && w.dim[3] % 8 == 0;
 	}
-	bool conv_fused_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act)
+	bool conv_fused_supported(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y, mlActivationType_t act)
 	{
 		(void) act;
-		if (x.dtype != DTYPE_FLOAT16 || w.dtype != DTYPE_FLOAT16 || y.dtype != DTYPE_FLOAT16)
+		if ((x.dtype != DTYPE_FLOAT16 && x.dtype != DTYPE_FLOAT32) || w.dtype != x.dtype || y.dtype != x.dtype)
 			return false;
 		if (w.rank != 4 || w.dim[1] != 3 || w.dim[2] != 3 || w.dim[3] != x.dim[3])
 			return false;
+		if (x.dtype == DTYPE_FLOAT32)
+			return shape_ok(2, x, w.dim[0], w.data) && aligned_to(y.data, 4) && fp32_fused_wanted(ctx, x, w.dim[0]);
 		return shape_ok(0, x, w.dim[0], w.data) && aligned_to(y.data, 2);
 	}
+	size_t conv_fused_weight_bytes(const mlTensor_t &w)
+	{
+		return static_cast<size_t>(volume(w)) * size_of(w.dtype) * (w.dtype == DTYPE_FLOAT32 ? 2 : 1);
+	}
+	bool conv_fused_prepare_weights(mlContext_t ctx, const mlTensor_t &w, void *prepared)
+	{
+		cudaStream_t stream = use_stream(ctx);
+		if (w.dtype != DTYPE_FLOAT32)
+			return check_cuda(ctx, cudaMemcpyAsync(prepared, w.data, conv_fused_weight_bytes(w), cudaMemcpyDeviceToDevice, stream), "weight snapshot");
+		const long long elements = volume(w);
+		const int grid = static_cast<int>(std::min<long long>((elements + 255) / 256, static_cast<long long>(get(ctx)->sm_count) * 8));
+		kernel_split_weight_planes<<<grid, 256, 0, stream>>>(reinterpret_cast<float*>(prepared), reinterpret_cast<const float*>(w.data), elements);
+		MB200_COUNT_LAUNCH();
+		return check_cuda(ctx, cudaGetLastError(), "weight planes");
+	}
 	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
-			mlActivationType_t act)
+			mlActivationType_t act, bool prepared)
 	{
 		ConvParams p;
 		std::memset(&p, 0, sizeof(p));
@@ -1019,8 +1203,17 @@ namespace mb200
 		p.bias = bias;
 		p.ext = ext;
 		p.act = act;
-		p.out_dtype = DTYPE_FLOAT16;
-		return run(ctx, 0, x, w.data, w.dim[0], p);
+		p.out_dtype = x.dtype;
+		const int kind = (x.dtype == DTYPE_FLOAT16) ? 0 : (get(ctx)->allow_tf32 ? 2 : 3);
+		const void *weights = w.data;
+		if (kind == 3 && !prepared)
+		{ // raw fp32 weights handed over per call (the single-call entry): their two planes go to the context's scratch first
+			void *planes = get_workspace(ctx, conv_fused_weight_bytes(w));
+			if (planes == nullptr || !conv_fused_prepare_weights(ctx, w, planes))
+				return false;
+			weights = planes;
+		}
+		return run(ctx, kind, x, weights, w.dim[0], p); // (kind 2 on prepared weights reads plane 0: the properly rounded TF32 values)
 	}
 
 	/* ------------------------------------------------------------------------------------------------------------

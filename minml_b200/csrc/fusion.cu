@@ -16,8 +16,8 @@
  * Snapshot semantics.  In the reference the transformed matrices U are a snapshot of the weights at transform time: the host may
  * overwrite, reuse or free the raw weight tensor afterwards and the convolution still computes with what U holds.  The fused
  * kernel works on raw weights, so cuda_winograd_weight_transform also keeps a backend-owned device copy of them (same layout,
- * [cout, 3, 3, cin], which IS the K-major B operand of the implicit GEMM) and the fused kernel reads that copy, never the host's
- * tensor.  The record is keyed by the address of U: it goes away when U is freed or when a copy / fill of the ABI writes into U
+ * [cout, 3, 3, cin], which IS the K-major B operand of the implicit GEMM; for fp32 as two planes, the TF32-rounded values and the
+ * remainders, which is what the split-fp32 kernel multiplies) and the fused kernel reads that copy, never the host's tensor.  The record is keyed by the address of U: it goes away when U is freed or when a copy / fill of the ABI writes into U
  * (the snapshot would no longer describe its contents; the sequence then runs on the three eager kernels).
  *
  * Threads.  The recorded state of a context is guarded by the context's mutex: another thread's cuda_free or null-context copy
@@ -77,7 +77,7 @@ namespace mb200
 		if (c == nullptr)
 			return;
 		const bool fusable = tile_size == 4 && !invert && w.rank == 4 && w.dim[1] == 3 && w.dim[2] == 3 && conv_fused_weights_supported(w);
-		const size_t bytes = static_cast<size_t>(volume(w)) * size_of(w.dtype);
+		const size_t bytes = conv_fused_weight_bytes(w);
 		std::lock_guard<std::mutex> lock(g_registry_mutex);
 		auto it = g_registry.find(matrices.data);
 		void *copy = nullptr;
@@ -97,7 +97,8 @@ namespace mb200
 			cudaGetLastError();
 			return; // no memory for the snapshot: the sequence stays on the eager kernels
 		}
-		if (!check_cuda(ctx, cudaMemcpyAsync(copy, w.data, bytes, cudaMemcpyDeviceToDevice, stream), "weight snapshot"))
+		(void) stream;
+		if (!conv_fused_prepare_weights(ctx, w, copy))
 		{
 			cudaFree(copy);
 			return;
@@ -141,7 +142,7 @@ namespace mb200
 		Context *c = get(ctx);
 		if (c == nullptr || !c->fusion || tile_size != 4 || matrices.dim[0] != 36)
 			return false;
-		if (!conv_fused_input_supported(x))
+		if (!conv_fused_input_supported(ctx, x))
 			return false;
 		std::lock_guard<std::recursive_mutex> lock(c->mutex);
 		c->pending.stage = 1;
@@ -190,14 +191,14 @@ namespace mb200
 		const mlTensor_t x = c->pending.x;
 		if (y.dim[0] != x.dim[0] || y.dim[1] != x.dim[1] || y.dim[2] != x.dim[2] || y.dim[3] != rec.w.dim[0])
 			return false;
-		if (!conv_fused_supported(x, rec.w, y, act))
+		if (!conv_fused_supported(ctx, x, rec.w, y, act))
 			return false;
 		// In place (y overlapping x) the three-kernel path is correct -- V is complete before y is written -- but the fused kernel
 		// reads the 3x3 neighbourhood of positions that other CTAs are writing: such a call runs on the eager kernels.
 		if (ranges_overlap(x.data, volume(x) * size_of(x.dtype), y.data, volume(y) * size_of(y.dtype)))
 			return false;
 		c->pending.stage = 0;
-		return conv_fused_run(ctx, x, rec.w, bias.data, ext.data, y, act);
+		return conv_fused_run(ctx, x, rec.w, bias.data, ext.data, y, act, true);
 	}
 	void flush_pending(mlContext_t ctx)
 	{

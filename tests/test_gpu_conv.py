@@ -470,3 +470,48 @@ def test_two_threads_two_contexts(oracle):
     assert np.allclose(host(c)[:, :32], host(a), atol=1e-3)
     ctx_a.close()
     ctx_b.close()
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+@pytest.mark.parametrize("shape", [(8, 15, 15, 128, 128), (3, 9, 11, 32, 40), (2, 20, 20, 64, 256), (1, 5, 7, 96, 300)])
+@pytest.mark.parametrize("act,use_ext", [("relu", False), ("linear", True)])
+def test_fp32_conv3x3_fused(oracle, tf32, shape, act, use_ext):
+    """fp32 3x3 layers whose channel count the copy-engine operand path takes (a multiple of 32) run as ONE kernel launched by the
+    reference's call triple: at fp32 accuracy by default (three TF32 products of split operands: mean |d| <= 1e-4, the
+    reference's threshold, and max |d| / max |ref| <= 1e-5), as one TF32 product when the host allowed TF32 on the context
+    (as cuBLAS would use it: relative error of the order of 2^-11)."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    b, h, w, cin, cout = shape
+    x, wt, bias, ext = _case(sum(shape) + 7, b, h, w, cin, cout)
+    ctx = B.Context(0)
+    ctx.enable_tf32(tf32)
+    conv = L.Conv2D(ctx, wt, bias, act, torch.float32)
+    ws = L.Workspace(ctx)
+    ws.reserve(conv.workspace_bytes(x.shape))
+    y = torch.full((b, h, w, cout), float("nan"), device="cuda")
+    inputs = [dev(x)] + ([dev(ext)] if use_ext else [])
+    conv.forward(inputs, y, ws)  # transforms the weights
+    before = B.launch_count()
+    conv.forward(inputs, y, ws)
+    ctx.synchronize()
+    mode = os.environ.get("MINML_B200_FP32_FUSED", "")[:1]
+    # without TF32 permission only layers of up to 128 channels take the fused kernel (wider ones are faster on the Winograd path)
+    fused = os.environ.get("MINML_B200_EAGER", "0")[:1] != "1" and mode != "n" and (tf32 or mode == "a" or (cin <= 128 and cout <= 128))
+    forced_eager = not fused
+    assert B.launch_count() - before == (1 if fused else 3)
+    want = oracle.conv2d(x, wt, bias, ext if use_ext else None, act)
+    if tf32 and not forced_eager:
+        assert max_rel_err(host(y), want) <= 2e-3
+    else:
+        assert mean_abs_diff(host(y), want) <= 1e-4
+        assert max_rel_err(host(y), want) <= 1e-5
+    # the single-call entry takes the same kernel
+    y2 = torch.full((b, h, w, cout), float("nan"), device="cuda")
+    B.convolutionImplicitGemmForward(ctx, inputs[0], conv.weights, y2, conv.bias, inputs[1] if use_ext else None, act)
+    ctx.synchronize()
+    if fused and not tf32:
+        assert torch.equal(y2, y)  # same kernel on the same weight planes
+    else:  # with TF32 the call triple reads weights rounded to TF32 at transform time, the single call lets the tensor core truncate them
+        assert max_rel_err(host(y2), want) <= (2e-3 if tf32 else 1e-5)
+    ctx.close()
