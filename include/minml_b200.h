@@ -243,6 +243,11 @@ void *mb200_get_stream(mlContext_t context);
  * 1: the sequence is recognised on the context and replaced by the fused kernel; the workspace is not written.
  * Default 1; the environment variable MINML_B200_EAGER=1 selects 0 at context creation. */
 void mb200_set_fusion(mlContext_t context, int enabled);
+/* Which kernel cuda_multi_head_attention_forward uses for fp16 inputs with a head dimension of 32 and up to 480 tokens:
+ * 0: the warp-level tensor-core kernel (mma.sync, scores in registers) -- the default, it measured faster (0.123 against 0.140 ms
+ *    on 256 x 225 tokens x 8 heads, 1.32 against 2.18 ms on 1024 x 400 tokens);
+ * 1: the tcgen05 kernel (scores in tensor memory).  Process-wide; the environment variable MINML_B200_MHA_TC=1 selects 1 at start. */
+void mb200_set_attention_kernel(int kernel);
 /* Library build identification: "minml_b200 <version> sm_100a". */
 const char *mb200_version(void);
 /* Failure-path self test: launches one small kernel that waits, with a limit of `polls` polls (1 .. 2^20), on a barrier that

@@ -137,6 +137,11 @@ def _last_error(handle):
     return msg.decode() if msg else None
 
 
+def set_attention_kernel(kernel):
+    """0: the warp-level tensor-core attention kernel (default); 1: the tcgen05 kernel with the scores in tensor memory."""
+    lib.mb200_set_attention_kernel(int(kernel))
+
+
 def launch_count():
     return int(lib.mb200_get_launch_count())
 

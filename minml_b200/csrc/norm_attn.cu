@@ -20,6 +20,8 @@ namespace mb200
 {
 	bool mha_forward_mma(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
 			int head_dim, int parts, int table_n, int table_pad); // attention_mma.cu
+	bool mha_forward_tc(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
+			int head_dim, int parts, int table_n, int table_pad); // attention_tc.cu
 
 	namespace
 	{
@@ -339,7 +341,11 @@ extern "C"
 			table_n = weights_shape.dim[1];
 			table_pad = weights_shape.dim[2];
 		}
-		// fp16 with a head dimension of 16, 32, 64 or 128: the tensor-core kernel; anything else: the generic kernel below
+		// fp16, head dimension 32, up to 480 tokens: the tcgen05 kernel with the scores in tensor memory; fp16 with a head dimension of
+		// 16, 32, 64 or 128: the warp-level tensor-core kernel; anything else: the generic kernel below
+		if (dtype == DTYPE_FLOAT16 && mha_forward_tc(context, output, input, table, batch, height, width, num_heads, head_dim, parts, table_n,
+				table_pad))
+			return;
 		if (dtype == DTYPE_FLOAT16 && mha_forward_mma(context, output, input, table, batch, height, width, num_heads, head_dim, parts, table_n,
 				table_pad))
 			return;

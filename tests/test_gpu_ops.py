@@ -272,3 +272,37 @@ def test_kernel_bench_tool_runs_and_reports_every_kernel():
         assert any(needle in n for n in names), needle
     for r in records:
         assert 0.0 < r["ms"] < 100.0 and 0.0 < r["hbm_frac"] < 1.5, r
+
+
+@pytest.mark.parametrize("cfg", [
+    (2, 15, 15, 8, False, None),   # config 4's shape: 225 tokens, one box of 240 keys, two CTAs per SM
+    (2, 20, 20, 4, False, None),   # 400 tokens: two boxes of 200 keys, 512 columns of tensor memory, four query tiles
+    (3, 5, 6, 2, True, None),      # q = k, 30 tokens: 32 keys, 32 columns
+    (1, 16, 16, 3, False, None),   # exactly 256 tokens
+    (2, 17, 17, 2, False, None),   # 289 tokens: two boxes of 160
+    (2, 9, 7, 4, False, 5),        # a table built for a 5 x 5 board: offsets beyond its range are clamped
+    (1, 21, 22, 1, False, None),   # 462 tokens: the most the kernel takes (480 key slots + nothing to spare)
+    (1, 1, 1, 2, False, None),     # a single token
+])
+def test_multi_head_attention_tcgen05_shapes(ctx, oracle, cfg):
+    """Head dimension 32 in fp16 -- the shapes that run on the tcgen05 kernel (scores in tensor memory) -- against the oracle, with
+    and without the relative-position table, over the token counts at which its tiling changes."""
+    from minml_b200 import backend as B
+    b, h, w, heads, symmetric, table_board = cfg
+    d = 32
+    r = np.random.default_rng(h * 100 + w)
+    parts = 2 if symmetric else 3
+    x = r.standard_normal((b, h, w, parts * heads * d)).astype(np.float16).astype(np.float32)
+    n = 2 * (table_board or max(h, w)) - 1
+    table = (r.standard_normal((heads, n, (n + 3) // 4 * 4)) * 0.5).astype(np.float16).astype(np.float32)
+    try:
+        for kernel in (1, 0):  # the tcgen05 kernel (selected explicitly) and the default warp-level kernel
+            B.set_attention_kernel(kernel)
+            for t in (table, None):
+                y = torch.full((b, h, w, heads * d), float("nan"), device="cuda", dtype=torch.float16)
+                B.multiHeadAttentionForward(ctx, dev(x, torch.float16), y, None if t is None else dev(t, torch.float16), heads, symmetric)
+                ctx.synchronize()
+                want = oracle.mha_forward(x, heads, t, symmetric)
+                assert max_rel_err(host(y), want) <= FP16_REL, "kernel %d, table %s" % (kernel, t is not None)
+    finally:
+        B.set_attention_kernel(0)
