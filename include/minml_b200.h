@@ -248,6 +248,12 @@ void mb200_set_fusion(mlContext_t context, int enabled);
  *    on 256 x 225 tokens x 8 heads, 1.32 against 2.18 ms on 1024 x 400 tokens);
  * 1: the tcgen05 kernel (scores in tensor memory).  Process-wide; the environment variable MINML_B200_MHA_TC=1 selects 1 at start. */
 void mb200_set_attention_kernel(int kernel);
+/* Tells the library that device memory in [ptr, ptr + bytes) has been given new contents (or a new owner) by something other than
+ * this ABI: what the library derived from weights lying there -- the snapshot of a layer's raw weights behind its transformed
+ * matrices, the border-correction table of an asymmetric int8 layer -- is dropped and made again on the next use.  cuda_free,
+ * cuda_memset and the cuda_memcpy_* entries do this themselves; only a host that allocates with an allocator of its own and
+ * overwrites weights in place with its own kernels needs to call it. */
+void mb200_forget_range(const void *ptr, size_t bytes);
 /* Library build identification: "minml_b200 <version> sm_100a". */
 const char *mb200_version(void);
 /* Failure-path self test: launches one small kernel that waits, with a limit of `polls` polls (1 .. 2^20), on a barrier that

@@ -10,6 +10,7 @@
  */
 #include "common.cuh"
 #include "winograd.cuh"
+#include "conv.cuh"
 
 #include <cstdarg>
 #include <cstdlib>
@@ -413,6 +414,7 @@ extern "C"
 		{
 			flush_all_pending(); // a deferred sequence may still reference this buffer
 			winograd_forget_range(ptr, allocation_size(ptr)); // a recycled address must never alias a stale weight record
+			conv_forget_range(ptr, allocation_size(ptr));
 			check_cuda(nullptr, cudaFree(ptr), "cuda_free");
 		}
 	}
@@ -436,6 +438,7 @@ extern "C"
 			flush_pending(context);
 		void *tmp_dst = reinterpret_cast<uint8_t*>(dst) + dst_offset;
 		winograd_forget_range(tmp_dst, dst_count); // transformed weights written to directly are no longer described by their snapshot
+		conv_forget_range(tmp_dst, dst_count);
 		cudaStream_t stream = use_stream(context);
 		if (src == nullptr)
 		{
@@ -479,6 +482,7 @@ extern "C"
 		void *d = reinterpret_cast<uint8_t*>(dst) + dst_offset;
 		const void *s = reinterpret_cast<const uint8_t*>(src) + src_offset;
 		winograd_forget_range(d, count);
+		conv_forget_range(d, count);
 		if (context == nullptr)
 		{
 			flush_all_pending();
@@ -497,6 +501,7 @@ extern "C"
 			return;
 		void *d = reinterpret_cast<uint8_t*>(dst) + dst_offset;
 		winograd_forget_range(d, count);
+		conv_forget_range(d, count);
 		if (context == nullptr)
 		{
 			flush_all_pending();
@@ -565,6 +570,14 @@ extern "C"
 			flush_pending(context);
 			get(context)->fusion = (enabled != 0);
 		}
+	}
+	void mb200_forget_range(const void *ptr, size_t bytes)
+	{
+		if (ptr == nullptr)
+			return;
+		flush_all_pending();
+		winograd_forget_range(ptr, bytes);
+		conv_forget_range(ptr, bytes);
 	}
 	const char* mb200_version(void)
 	{

@@ -18,6 +18,8 @@ namespace mb200
 			mlActivationType_t act, bool prepared);
 	/* The form in which the fused kernel wants a layer's weights kept: a plain copy for fp16, two planes (w rounded to TF32, and the
 	 * remainder) for fp32.  `prepared` must hold conv_fused_weight_bytes(w); the work is queued on the context's stream. */
+	/* Drops what the library derived from int8 weights lying in [ptr, ptr + bytes): they are being freed or overwritten. */
+	void conv_forget_range(const void *ptr, size_t bytes);
 	size_t conv_fused_weight_bytes(const mlTensor_t &w);
 	bool conv_fused_prepare_weights(mlContext_t ctx, const mlTensor_t &w, void *prepared);
 } /* namespace mb200 */

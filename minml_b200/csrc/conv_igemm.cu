@@ -39,8 +39,8 @@
  *   TMA_A = true   im2col-mode TMA: one request per K slice delivers 128 output positions x 128 bytes of channels of one
  *                  filter tap, zero-filled outside the image.  Needs cin * element size to be a multiple of 128 bytes.  A non-zero
  *                  int8 padding value z (the quantised zero of an asymmetric input) is made up for in the epilogue: positions on
- *                  the border get z * (sum of the weights of the taps that fell outside) from a 9 x cout table computed per call
- *                  (kernel_border_table), which keeps the int32 accumulators exact.  This is the fast path (256 -> 256 fp16:
+ *                  the border get z * (sum of the weights of the taps that fell outside) from a 9 x cout table computed once per weight
+ *                  tensor (kernel_border_table, cached_border_table), which keeps the int32 accumulators exact.  This is the fast path (256 -> 256 fp16:
  *                  1.23 PFLOP/s against 0.92 for the gather).
  *   TMA_A = false  cp.async gather of 16-byte channel chunks: any cin that is a multiple of 8 (fp16) / 16 (int8), any
  *                  int8 padding value.
@@ -51,8 +51,11 @@
 #include "tc.cuh"
 #include "epilogue.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 
 namespace mb200
 {
@@ -1064,6 +1067,52 @@ namespace mb200
 		}
 
 		/* kind 3 expects `w` to be the two planes [2, cout, 9 cin] written by kernel_split_weight_planes */
+		/* Border corrections of asymmetric int8 layers, kept per weight tensor: the table depends only on the weights and on the
+		 * padding value, so it is computed once (the first call of a layer) into memory the library owns and reused by every later
+		 * call; conv_forget_range drops an entry when the weights are freed or written to through the ABI.  A first call that
+		 * arrives while its stream is being captured into a CUDA graph may not allocate: it computes the table into the caller's
+		 * accumulator scratch, as every call did before the cache existed. */
+		struct BorderRecord
+		{
+				int *table;
+				size_t weight_bytes;
+				int pad, cin, cout, device;
+		};
+		std::mutex g_border_mutex;
+		std::map<const void*, BorderRecord> g_border_tables;
+
+		const int* cached_border_table(mlContext_t ctx, const void *w, int cin, int cout, int pad)
+		{
+			Context *c = get(ctx);
+			std::lock_guard<std::mutex> lock(g_border_mutex);
+			auto it = g_border_tables.find(w);
+			if (it != g_border_tables.end())
+			{
+				const BorderRecord &rec = it->second;
+				if (rec.pad == pad && rec.cin == cin && rec.cout == cout && rec.device == c->device)
+					return rec.table;
+				cudaFree(rec.table); // the same address now holds other weights, or the layer is used with another zero point
+				g_border_tables.erase(it);
+			}
+			cudaStream_t stream = use_stream(ctx);
+			cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+			if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone)
+			{
+				cudaGetLastError();
+				return nullptr;
+			}
+			int *table = nullptr;
+			if (cudaMalloc(reinterpret_cast<void**>(&table), static_cast<size_t>(9) * cout * sizeof(int)) != cudaSuccess)
+			{
+				cudaGetLastError();
+				return nullptr;
+			}
+			kernel_border_table<<<cout, 9 * 32, 0, stream>>>(table, reinterpret_cast<const int8_t*>(w), cin, cout, pad);
+			MB200_COUNT_LAUNCH();
+			g_border_tables[w] = BorderRecord { table, static_cast<size_t>(9) * cin * cout, pad, cin, cout, c->device };
+			return table;
+		}
+
 		bool run(mlContext_t ctx, int kind, const mlTensor_t &x, const void *w, int cout, ConvParams p)
 		{
 			const int es = (kind == 0) ? 2 : (kind == 1) ? 1 : 4;
@@ -1087,9 +1136,15 @@ namespace mb200
 			const bool tma_a = (p.cin * es) % 128 == 0 && zero_fill_ok && !force_gather;
 			if (tma_a && p.pad_byte != 0)
 			{
-				kernel_border_table<<<cout, 9 * 32, 0, use_stream(ctx)>>>(const_cast<int*>(p.border), reinterpret_cast<const int8_t*>(w), p.cin, cout,
-						p.pad_byte);
-				MB200_COUNT_LAUNCH();
+				const int *cached = cached_border_table(ctx, w, p.cin, cout, p.pad_byte);
+				if (cached != nullptr)
+					p.border = cached;
+				else
+				{ // no cached table could be made (the stream is being captured, or no memory): this call's own, in the host's scratch
+					kernel_border_table<<<cout, 9 * 32, 0, use_stream(ctx)>>>(const_cast<int*>(p.border), reinterpret_cast<const int8_t*>(w), p.cin, cout,
+							p.pad_byte);
+					MB200_COUNT_LAUNCH();
+				}
 			}
 			else
 				p.border = nullptr; // the gather variant stores the padding value itself
@@ -1154,6 +1209,29 @@ namespace mb200
 			if (get(ctx)->allow_tf32 || (mode != nullptr && mode[0] == 'a'))
 				return true;
 			return x.dim[3] <= 128 && cout <= 128;
+		}
+	}
+	void conv_forget_range(const void *ptr, size_t bytes)
+	{
+		std::lock_guard<std::mutex> lock(g_border_mutex);
+		if (g_border_tables.empty())
+			return;
+		const uint8_t *lo = reinterpret_cast<const uint8_t*>(ptr);
+		const uint8_t *hi = lo + std::max<size_t>(bytes, 1);
+		for (auto it = g_border_tables.begin(); it != g_border_tables.end();)
+		{
+			const uint8_t *w = reinterpret_cast<const uint8_t*>(it->first);
+			if (w < hi && lo < w + it->second.weight_bytes)
+			{
+				int current = 0;
+				cudaGetDevice(&current);
+				cudaSetDevice(it->second.device);
+				cudaFree(it->second.table);
+				cudaSetDevice(current);
+				it = g_border_tables.erase(it);
+			}
+			else
+				++it;
 		}
 	}
 	bool conv_fused_input_supported(mlContext_t ctx, const mlTensor_t &x)

@@ -97,10 +97,16 @@ namespace mb200
 			return __fadd_rn(x, __fadd_rn(__fmul_rn(static_cast<float>(e), ext_scale), ext_shift));
 		}
 		/* Rounded but not yet saturated: the float -> int conversion saturates at the int32 range, pack_sat_s8x4 or
-		 * requant_clamp then at the int8 range, which together are the reference's clamp(round(.), -128, 127). */
+		 * requant_clamp then at the int8 range, which together are the reference's clamp(round(.), -128, 127).
+		 * Round half away from zero (std::round) is computed as trunc(y + copysign(0.49999997, y)), 0.49999997 being the
+		 * largest float below one half: three instructions instead of the eight of roundf, and the same result for EVERY
+		 * float -- checked exhaustively for |y| < 2^23 (tests/test_oracle.py samples it); beyond that y is an integer and the
+		 * addition returns it unchanged. */
 		__device__ __forceinline__ int requant_round(float x, float inv_out_scale, float inv_out_shift)
 		{
-			return __float2int_rz(roundf(__fadd_rn(__fmul_rn(x, inv_out_scale), inv_out_shift)));
+			const float y = __fadd_rn(__fmul_rn(x, inv_out_scale), inv_out_shift);
+			const float half_towards_y = __uint_as_float((__float_as_uint(y) & 0x80000000u) | 0x3EFFFFFFu);
+			return __float2int_rz(__fadd_rn(y, half_towards_y));
 		}
 		__device__ __forceinline__ int requant_clamp(int q)
 		{

@@ -101,6 +101,8 @@ class QuantizedConv2D:
         self.kernel = q_weights.shape[1]
         self.cout, self.cin = q_weights.shape[0], q_weights.shape[3]
         self.weights = torch.from_numpy(np.ascontiguousarray(q_weights)).to(ctx.device)
+        # torch's allocator hands out addresses again without the library seeing a free: whatever it cached for weights that lay here goes
+        B.lib.mb200_forget_range(B.ptr(self.weights, ctx), self.weights.numel())
         self.channel_scales = _dev(ctx, channel_scales, torch.float32)
         self.bias = _dev(ctx, q_bias, torch.float32)
         self.input_qd, self.output_qd = input_qd, output_qd

@@ -515,3 +515,35 @@ def test_fp32_conv3x3_fused(oracle, tf32, shape, act, use_ext):
     else:  # with TF32 the call triple reads weights rounded to TF32 at transform time, the single call lets the tensor core truncate them
         assert max_rel_err(host(y2), want) <= (2e-3 if tf32 else 1e-5)
     ctx.close()
+
+
+def test_border_table_of_an_asymmetric_int8_layer_is_cached(ctx, oracle):
+    """The corrections for a non-zero quantised zero depend only on the weights and the padding value: the first call of a layer
+    computes them (two launches), later calls reuse them (one launch), and telling the library that the weights changed
+    (mb200_forget_range; cuda_free and the ABI's copies do it themselves) makes the next call compute them again."""
+    from minml_b200 import backend as B
+    from minml_b200 import layers as L
+    if os.environ.get("MINML_B200_CONV_GATHER", "0")[:1] == "1" or os.environ.get("MINML_B200_EAGER", "0")[:1] == "1":
+        pytest.skip("the measurement switch in force keeps this layer off the copy-engine operand path")
+    b, h, w, cin, cout, zero = 2, 9, 9, 128, 128, -37
+    r = np.random.default_rng(5150)
+    xq = r.integers(-128, 128, (b, h, w, cin), dtype=np.int8)
+    conv = None
+    for round_index in range(2):
+        q = r.integers(-20, 21, (cout, 3, 3, cin), dtype=np.int8)
+        if conv is None:
+            conv = L.QuantizedConv2D(ctx, q, np.ones(cout, np.float32), np.zeros(cout, np.float32), (1.0, float(-zero)), (1.0, 0.0), "linear", torch.float32)
+        else:  # new weights written in place by something the library cannot see (a torch copy), then announced
+            conv.weights.copy_(torch.from_numpy(q))
+            torch.cuda.synchronize()
+            B.lib.mb200_forget_range(B.ptr(conv.weights, ctx), conv.weights.numel())
+        ws = L.Workspace(ctx)
+        ws.reserve(conv.workspace_bytes(xq.shape))
+        _, _, want_acc = oracle.conv2d_int8(xq, q, np.ones(cout, np.float32), np.zeros(cout, np.float32), zero)
+        for call, expected_launches in enumerate((2, 1, 1)):
+            y = torch.zeros((b, h, w, cout), device="cuda", dtype=torch.float32)
+            before = B.launch_count()
+            conv.forward([dev(xq)], y, ws)
+            ctx.synchronize()
+            assert B.launch_count() - before == expected_launches, "round %d call %d" % (round_index, call)
+            assert np.array_equal(host(y).astype(np.int64), want_acc.astype(np.int64))

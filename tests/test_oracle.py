@@ -337,3 +337,21 @@ def test_space_to_depth_moves_bytes_for_any_element_size(oracle):
     assert np.array_equal(deep[1, 0, 0, :3], x[1, 0, 0]) and np.array_equal(deep[1, 0, 0, 3:6], x[1, 0, 1])
     assert np.array_equal(deep[1, 0, 0, 6:9], x[1, 1, 0]) and np.array_equal(deep[0, 2, 3, 3:], np.zeros(9, np.int8))  # past both edges
     assert np.array_equal(oracle.depth_to_space(deep, (5, 7)), x)
+
+
+def test_round_half_away_from_zero_in_three_operations():
+    """The int8 kernels round with trunc(y + copysign(0.49999997, y)) instead of roundf (epilogue.cuh: requant_round).  The two agree
+    for every float -- the exhaustive check over all 2.5e9 floats with |y| < 2^23 takes a minute; here: every float around the
+    half-integers up to 130 (where the outputs saturate), the neighbours of one half, and a stride through everything else."""
+    magic = np.nextafter(np.float32(0.5), np.float32(0))
+    assert magic.view(np.uint32) == 0x3EFFFFFF
+    halves = (np.arange(0, 131, dtype=np.float32) + np.float32(0.5))
+    near = [halves.view(np.uint32).astype(np.int64) + k for k in range(-3, 4)]
+    samples = [np.concatenate(near).astype(np.uint32).view(np.float32)]
+    samples.append(np.arange(0, 150 << 23, 9973, dtype=np.uint32).view(np.float32))  # a stride through every binade below 2^23
+    samples.append(np.array([0.0, 0.49999997, 0.5, 0.50000006, 0.99999994, 1.0, 126.5, 127.49999, 127.5, 128.5, 8388607.5, 1e9], np.float32))
+    y = np.concatenate(samples)
+    y = np.concatenate([y, -y])
+    got = np.trunc(y + np.copysign(magic, y))  # float32 arithmetic, round to nearest even: what the device does
+    want = np.trunc(y.astype(np.float64) + np.copysign(0.5, y.astype(np.float64)))  # exact in double
+    assert np.array_equal(got.astype(np.float64), want)
