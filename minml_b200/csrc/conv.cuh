@@ -18,6 +18,10 @@ namespace mb200
 			mlActivationType_t act, bool prepared);
 	/* The form in which the fused kernel wants a layer's weights kept: a plain copy for fp16, two planes (w rounded to TF32, and the
 	 * remainder) for fp32.  `prepared` must hold conv_fused_weight_bytes(w); the work is queued on the context's stream. */
+	/* conv_slab.cu: the variant for fp16 layers of up to 128 channels (input band resident in shared memory, shifted operand descriptors) */
+	bool conv_slab_supported(const mlTensor_t &x, const mlTensor_t &w, const mlTensor_t &y);
+	bool conv_slab_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
+			mlActivationType_t act);
 	/* Drops what the library derived from int8 weights lying in [ptr, ptr + bytes): they are being freed or overwritten. */
 	void conv_forget_range(const void *ptr, size_t bytes);
 	size_t conv_fused_weight_bytes(const mlTensor_t &w);

@@ -1275,6 +1275,8 @@ namespace mb200
 	bool conv_fused_run(mlContext_t ctx, const mlTensor_t &x, const mlTensor_t &w, const void *bias, const void *ext, const mlTensor_t &y,
 			mlActivationType_t act, bool prepared)
 	{
+		if (conv_slab_supported(x, w, y)) // MINML_B200_CONV_SLAB=1 only: the variant with the input band resident in shared memory (conv_slab.cu)
+			return conv_slab_run(ctx, x, w, bias, ext, y, act);
 		ConvParams p;
 		std::memset(&p, 0, sizeof(p));
 		p.y = y.data;
