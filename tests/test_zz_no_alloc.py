@@ -26,7 +26,9 @@ def _call(B, ctx, fn, x, w, y, bias, add, act):
     ctx.check()
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.float16, 2.5e-2)])
+# fp32: the allocating entry point runs small layers like this one as the fused split-TF32 kernel, the no-allocation one as F(4x4,3x3)
+# Winograd; both are fp32-accurate and differ by rounding (a few 1e-6 of the largest value).  fp16: the Winograd path's bound.
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.float16, 2.5e-2)])
 def test_noalloc_matches_allocating_entry_point(ctx, oracle, dtype, tol):
     from minml_b200 import backend as B
     noalloc = B.lib.mb200_convolution_forward_noalloc
