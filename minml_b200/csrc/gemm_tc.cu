@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 namespace mb200
@@ -94,16 +95,31 @@ namespace mb200
 		 * of that slice's products, so most of shared memory stays with the copies in flight (the kernel streams fp32 operands
 		 * and is short of bytes in flight before it is short of anything else). It has no use for the epilogue staging.
 		 */
-		template<int KIND, int BN>
+		/*
+		 * RES (weight-resident): for products with a short K -- the 1x1 convolutions and dense layers of a network, K = 256 ... 512 --
+		 * a 128 x BN tile is only a few K slices, and fetching the weight tile again for every 128 rows of output made the copies
+		 * into shared memory, not HBM, the limit (l1tex 62 % of peak, tensor pipe 30 %).  Here every CTA takes a CONTIGUOUS range of
+		 * tiles ordered (batch, column tile, row tile), keeps the whole [BN, K] weight tile in shared memory for as long as
+		 * consecutive tiles share it, and streams only A through the ring.
+		 * Measured: the 36 Winograd products of a 256-channel layer 0.167 -> 0.159 ms (0.92 of the copy bandwidth), a 256 -> 1 head over
+		 * 409 600 rows 0.054 -> 0.043 ms; the 256 -> 768 / 256 / 1024 projections of 57 600 rows did not move (0.043 / 0.029 / 0.056 ms,
+		 * tensor pipe 24 %, 25 % of the issue slots, l1tex 56 %): what is left there is the epilogue's own chain per 32-column chunk --
+		 * a version that started the tensor-memory load of chunk i + 1 and the bias reads under chunk i's arithmetic measured 5 - 10 %
+		 * slower (168 registers) and was taken out again.
+		 */
+		constexpr int RESIDENT_BYTES = 128 * 1024;
+		template<int KIND, int BN, bool RES = false>
 		struct Tiling
 		{
 				static constexpr bool split = (KIND == 3);
-				static constexpr int operand_bytes = BM * BK_BYTES + BN * BK_BYTES;
-				static constexpr int stage_bytes = operand_bytes;
-				static constexpr int stages = split ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
+				static constexpr int a_bytes = BM * BK_BYTES, b_bytes = BN * BK_BYTES;
+				static constexpr int operand_bytes = a_bytes + b_bytes;
+				static constexpr int stage_bytes = RES ? a_bytes : operand_bytes;
+				static constexpr int stages = RES ? 4 : split ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
+				static constexpr int resident_offset = stages * stage_bytes;
 				static constexpr int lo_stages = split ? ((BN == 256) ? 1 : 2) : 0;
 				static constexpr int lo_ring = (lo_stages > 0) ? lo_stages : 1; // divisor that is never zero
-				static constexpr int lo_offset = stages * stage_bytes;
+				static constexpr int lo_offset = resident_offset + (RES ? RESIDENT_BYTES : 0);
 				static constexpr int staging_offset = lo_offset + lo_stages * operand_bytes;
 				static constexpr int smem_bytes = staging_offset + (split ? 0 : EPI_WARPS * epi::WARP_BYTES) + 1024;
 				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
@@ -115,6 +131,7 @@ namespace mb200
 				uint64_t empty[6];
 				uint64_t split[6]; // KIND 3: the stage's hi and lo tiles are written
 				uint64_t lo_empty[2]; // KIND 3: the products that read this lo tile are done
+				uint64_t resident_full, resident_empty; // RES: the weight tile has landed / every product that reads it is done
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
 				uint32_t tmem_base;
@@ -132,11 +149,12 @@ namespace mb200
 
 		// (requantisation arithmetic: epilogue.cuh)
 
-		template<int KIND, int BN>
+		template<int KIND, int BN, bool RES = false>
 		__global__ void __launch_bounds__(num_threads(KIND), 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
 				const __grid_constant__ CUtensorMap map_b, const GemmTcParams p)
 		{
-			using T = Tiling<KIND, BN>;
+			static_assert(!RES || KIND == 0, "the weight-resident variant is built for fp16");
+			using T = Tiling<KIND, BN, RES>;
 			extern __shared__ uint8_t smem_raw[];
 			__shared__ Barriers bars;
 
@@ -149,6 +167,25 @@ namespace mb200
 			const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * p.batch;
 			const int elems_per_kblock = (KIND == 0) ? 64 : (KIND == 1 ? 128 : 32); // 128 bytes of K per row (fp32 for KIND 2 and 3)
 			const int k_blocks = (p.K + elems_per_kblock - 1) / elems_per_kblock;
+			// Which tiles this CTA computes: every gridDim-th one, or (RES) a contiguous range, so that consecutive tiles share weights.
+			const long long per_cta = (total_tiles + gridDim.x - 1) / gridDim.x;
+			const long long tile_first = RES ? blockIdx.x * per_cta : blockIdx.x;
+			const long long tile_last = RES ? min(total_tiles, tile_first + per_cta) : total_tiles;
+			const long long tile_step = RES ? 1 : gridDim.x;
+			auto decode = [&](long long tile, int &nt, int &mt, int &b)
+			{
+				if (RES)
+				{ // row tiles fastest: a column tile's weights stay while the rows go by
+					mt = static_cast<int>(tile % m_tiles);
+					nt = static_cast<int>((tile / m_tiles) % n_tiles);
+				}
+				else
+				{
+					nt = static_cast<int>(tile % n_tiles);
+					mt = static_cast<int>((tile / n_tiles) % m_tiles);
+				}
+				b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+			};
 
 			if (threadIdx.x == 0)
 			{
@@ -164,6 +201,8 @@ namespace mb200
 					mbar_init(smem_u32(&bars.tmem_full[a]), 1);
 					mbar_init(smem_u32(&bars.tmem_empty[a]), EPI_WARPS);
 				}
+				mbar_init(smem_u32(&bars.resident_full), 1);
+				mbar_init(smem_u32(&bars.resident_empty), 1);
 				bars.abort_flag = 0;
 				fence_mbar_init();
 			}
@@ -186,11 +225,24 @@ namespace mb200
 					prefetch_tensormap(&map_b);
 					uint32_t it = 0;
 					bool ok = true;
-					for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+					long long weights_loaded = -1; // RES: which weight tile shared memory holds
+					uint32_t weight_loads = 0;
+					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step)
 					{
-						const int nt = static_cast<int>(tile % n_tiles);
-						const int mt = static_cast<int>((tile / n_tiles) % m_tiles);
-						const int b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+						int nt, mt, b;
+						decode(tile, nt, mt, b);
+						const long long weights = static_cast<long long>(p.b_broadcast ? 0 : b) * n_tiles + nt;
+						if (RES && weights != weights_loaded)
+						{ // a new weight tile: once every product on the old one is done, all its K slices in one go
+							if (!mbar_wait(smem_u32(&bars.resident_empty), (weight_loads & 1u) ^ 1u, abort_flag))
+								break;
+							const uint32_t full = smem_u32(&bars.resident_full);
+							mbar_arrive_expect_tx(full, static_cast<uint32_t>(k_blocks) * T::b_bytes);
+							for (int kb = 0; kb < k_blocks; kb++)
+								tma_load_3d(smem_base + T::resident_offset + kb * T::b_bytes, &map_b, full, kb * elems_per_kblock, nt * BN, p.b_broadcast ? 0 : b);
+							weights_loaded = weights;
+							weight_loads++;
+						}
 						for (int kb = 0; kb < k_blocks; kb++, it++)
 						{
 							const int s = it % T::stages;
@@ -201,11 +253,11 @@ namespace mb200
 								break;
 							}
 							const uint32_t full = smem_u32(&bars.full[s]);
-							mbar_arrive_expect_tx(full, T::operand_bytes);
+							mbar_arrive_expect_tx(full, T::stage_bytes);
 							const uint32_t dst_a = smem_base + s * T::stage_bytes;
-							const uint32_t dst_b = dst_a + BM * BK_BYTES;
 							tma_load_3d(dst_a, &map_a, full, kb * elems_per_kblock, mt * BM, p.a_broadcast ? 0 : b);
-							tma_load_3d(dst_b, &map_b, full, kb * elems_per_kblock, nt * BN, p.b_broadcast ? 0 : b);
+							if (!RES)
+								tma_load_3d(dst_a + T::a_bytes, &map_b, full, kb * elems_per_kblock, nt * BN, p.b_broadcast ? 0 : b);
 						}
 					}
 				}
@@ -220,8 +272,25 @@ namespace mb200
 					uint32_t it = 0;
 					uint32_t local_tile = 0;
 					bool ok = true;
-					for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local_tile++)
+					long long weights_loaded = -1;
+					uint32_t weight_loads = 0;
+					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step, local_tile++)
 					{
+						if (RES)
+						{
+							int nt, mt, b;
+							decode(tile, nt, mt, b);
+							const long long weights = static_cast<long long>(p.b_broadcast ? 0 : b) * n_tiles + nt;
+							if (weights != weights_loaded)
+							{
+								if (weight_loads > 0)
+									mma_commit(smem_u32(&bars.resident_empty)); // arrives when every product issued so far, all on the old tile, is done
+								if (!mbar_wait(smem_u32(&bars.resident_full), (weight_loads & 1u), abort_flag))
+									break;
+								weights_loaded = weights;
+								weight_loads++;
+							}
+						}
 						const uint32_t acc = local_tile & 1u;
 						const uint32_t acc_parity = ((local_tile >> 1) & 1u) ^ 1u;
 						if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_parity, abort_flag))
@@ -241,7 +310,7 @@ namespace mb200
 							if (T::split)
 								fence_proxy_async_smem(); // the hi and lo tiles were plain stores of the split warps
 							const uint32_t addr_a = smem_base + s * T::stage_bytes;
-							const uint32_t addr_b = addr_a + BM * BK_BYTES;
+							const uint32_t addr_b = RES ? smem_base + T::resident_offset + kb * T::b_bytes : addr_a + T::a_bytes;
 							const uint64_t desc_a = make_desc_k_sw128(addr_a);
 							const uint64_t desc_b = make_desc_k_sw128(addr_b);
 #pragma unroll
@@ -273,7 +342,7 @@ namespace mb200
 				const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
 				uint32_t it = 0;
 				bool ok = true;
-				for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
+				for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step)
 					for (int kb = 0; kb < k_blocks; kb++, it++)
 					{
 						const int s = it % T::stages;
@@ -325,11 +394,10 @@ namespace mb200
 				const bool rows_vectorisable = (KIND == 0) && p.out_dtype == DTYPE_FLOAT16 && aligned_to_16(p.D) && (p.ldd % 8) == 0
 						&& (p.stride_d % 8) == 0 && (!use_c || (aligned_to_16(p.C) && (p.ldc % 8) == 0 && (p.stride_c % 8) == 0));
 				uint32_t local_tile = 0;
-				for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local_tile++)
+				for (long long tile = tile_first; tile < tile_last; tile += tile_step, local_tile++)
 				{
-					const int nt = static_cast<int>(tile % n_tiles);
-					const int mt = static_cast<int>((tile / n_tiles) % m_tiles);
-					const int b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+					int nt, mt, b;
+					decode(tile, nt, mt, b);
 					const uint32_t acc = local_tile & 1u;
 					const uint32_t acc_parity = (local_tile >> 1) & 1u;
 					if (!mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag))
@@ -572,10 +640,10 @@ namespace mb200
 			}
 		}
 
-		template<int KIND, int BN>
+		template<int KIND, int BN, bool RES = false>
 		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const GemmTcParams &p, int sm_count)
 		{
-			using T = Tiling<KIND, BN>;
+			using T = Tiling<KIND, BN, RES>;
 			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
 			const int device = get(ctx)->device;
 			if (device < 0 || device >= MAX_DEVICES)
@@ -584,14 +652,14 @@ namespace mb200
 			if (!configured)
 			{
 				if (!check_cuda(ctx,
-						cudaFuncSetAttribute(kernel_gemm_tc<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::smem_bytes),
+						cudaFuncSetAttribute(kernel_gemm_tc<KIND, BN, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::smem_bytes),
 						"gemm_tc: shared memory opt-in"))
 					return false;
 				configured = true;
 			}
 			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
 			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
-			kernel_gemm_tc<KIND, BN> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, p);
+			kernel_gemm_tc<KIND, BN, RES> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, p);
 			MB200_COUNT_LAUNCH();
 			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
 		}
@@ -692,8 +760,23 @@ namespace mb200
 			return (bn == 256) ? launch<2, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<2, 128>(ctx, stream, map_a, map_b, p,
 							c->sm_count);
 		if (g.kind == 0)
+		{
+			// weight-resident variant: the whole [bn, K] weight tile fits its 128 KB, and a CTA's contiguous range of tiles stays on one
+			// weight tile for long enough to pay for the reload (MINML_B200_GEMM_RESIDENT=0: measurement switch)
+			static const bool resident_allowed = []
+			{
+				const char *e = std::getenv("MINML_B200_GEMM_RESIDENT");
+				return !(e != nullptr && e[0] == '0');
+			}();
+			const int k_blocks = (g.K + 63) / 64;
+			const long long m_tiles = (g.M + BM - 1) / BM;
+			const bool resident = resident_allowed && static_cast<long long>(k_blocks) * bn * BK_BYTES <= RESIDENT_BYTES && m_tiles >= 8;
+			if (resident)
+				return (bn == 256) ? launch<0, 256, true>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128, true>(ctx, stream, map_a, map_b,
+								p, c->sm_count);
 			return (bn == 256) ? launch<0, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128>(ctx, stream, map_a, map_b, p,
 							c->sm_count);
+		}
 		else
 			return (bn == 256) ? launch<1, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<1, 128>(ctx, stream, map_a, map_b, p,
 							c->sm_count);
