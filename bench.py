@@ -483,8 +483,11 @@ def measure(args, cfg, replicas, steps, sample_clocks=True):
 
     # End to end through the C ABI with host buffers.  Two contexts (two streams, two copies of the network) take the steps in
     # turn, so that the copies of one step overlap the arithmetic of the other; the caller collects the result of step i when it
-    # comes back to that context for step i + 2, i.e. every step's result is waited for inside the timed region.
-    pipes = [pipe] if args.no_overlap else [pipe, Pipe(args, cfg, local, replicas.input_seed(SEED), torch, B, L)]
+    # comes back to that context for step i + 2 (or + 3), i.e. every step's result is waited for inside the timed region.
+    # (a step that moves tens of megabytes each way over PCIe -- the token tensors of the conv + attention block -- gets a third
+    # context, so that one step's copy-in, another's arithmetic and a third's copy-out run at the same time: the link is full duplex)
+    n_pipes = 1 if args.no_overlap else (3 if pipe.h2d + pipe.d2h > (8 << 20) else 2)
+    pipes = [pipe] + [Pipe(args, cfg, local, replicas.input_seed(SEED), torch, B, L) for _ in range(n_pipes - 1)]
     for p in pipes:
         p.step_from_host()
         p.ctx.synchronize()
@@ -529,7 +532,7 @@ def measure(args, cfg, replicas, steps, sample_clocks=True):
             "config": {"workload": cfg["label"], "batch_per_gpu": batch, "global_batch": batch * world, "parallelism": "dp%d replicas" % world,
                        "conv3x3": "three kernels per layer (fusion off)" if args.eager else "fused (one kernel per layer where the fused kernel takes the shape)",
                        "launch": pipe.note,
-                       "e2e_overlap": "two contexts alternate steps (copies of one overlap the arithmetic of the other)" if len(pipes) == 2 else "none",
+                       "e2e_overlap": "%d contexts take the steps in turn (copies of one overlap the arithmetic of the others)" % len(pipes) if len(pipes) > 1 else "none",
                        "l2": l2_note(batch * cfg["height"] * cfg["width"] * cfg["channels"] * elem / 1e6)},
             "algorithmic_tflops": value * fpp / 1e12,
             "frac_of_nominal_dense_peak": value * fpp / world / {"int8_trunk": 4.5e15, "layer_fp32": 1.125e15 / 3}.get(kind, 2.25e15),

@@ -1133,7 +1133,7 @@ namespace mb200
 			static const bool force_single = env_flag("MINML_B200_CONV_SINGLE_CTA");
 			// (int8 with a non-zero padding value: still by TMA when the caller supplied room for the border corrections)
 			const bool zero_fill_ok = p.pad_byte == 0 || (kind == 1 && p.border != nullptr && p.height >= 2 && p.width >= 2);
-			const bool tma_a = (p.cin * es) % 128 == 0 && zero_fill_ok && !force_gather;
+			const bool tma_a = (p.cin * es) % 128 == 0 && zero_fill_ok && (!force_gather || kind >= 2); // (fp32 has the copy-engine path only)
 			if (tma_a && p.pad_byte != 0)
 			{
 				const int *cached = cached_border_table(ctx, w, p.cin, cout, p.pad_byte);

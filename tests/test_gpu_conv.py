@@ -501,8 +501,8 @@ def test_fp32_conv3x3_fused(oracle, tf32, shape, act, use_ext):
     forced_eager = not fused
     assert B.launch_count() - before == (1 if fused else 3)
     want = oracle.conv2d(x, wt, bias, ext if use_ext else None, act)
-    if tf32 and not forced_eager:
-        assert max_rel_err(host(y), want) <= 2e-3
+    if tf32:  # one TF32 product per slice when fused; the Winograd path with TF32 products otherwise (F(4x4,3x3) amplifies the 2^-11)
+        assert max_rel_err(host(y), want) <= (2e-3 if fused else 3e-2)
     else:
         assert mean_abs_diff(host(y), want) <= 1e-4
         assert max_rel_err(host(y), want) <= 1e-5
@@ -513,7 +513,7 @@ def test_fp32_conv3x3_fused(oracle, tf32, shape, act, use_ext):
     if fused and not tf32:
         assert torch.equal(y2, y)  # same kernel on the same weight planes
     else:  # with TF32 the call triple reads weights rounded to TF32 at transform time, the single call lets the tensor core truncate them
-        assert max_rel_err(host(y2), want) <= (2e-3 if tf32 else 1e-5)
+        assert max_rel_err(host(y2), want) <= ((2e-3 if fused else 3e-2) if tf32 else 1e-5)
     ctx.close()
 
 
