@@ -243,10 +243,15 @@ void *mb200_get_stream(mlContext_t context);
  * 1: the sequence is recognised on the context and replaced by the fused kernel; the workspace is not written.
  * Default 1; the environment variable MINML_B200_EAGER=1 selects 0 at context creation. */
 void mb200_set_fusion(mlContext_t context, int enabled);
-/* Which kernel cuda_multi_head_attention_forward uses for fp16 inputs with a head dimension of 32 and up to 480 tokens:
- * 0: the warp-level tensor-core kernel (mma.sync, scores in registers) -- the default, it measured faster (0.123 against 0.140 ms
- *    on 256 x 225 tokens x 8 heads, 1.32 against 2.18 ms on 1024 x 400 tokens);
- * 1: the tcgen05 kernel (scores in tensor memory).  Process-wide; the environment variable MINML_B200_MHA_TC=1 selects 1 at start. */
+/* Which kernel cuda_multi_head_attention_forward uses for fp16 inputs with a head dimension of 32:
+ * 0: by shape (default) -- the persistent warp-specialised tcgen05 kernel (scores and probabilities in tensor memory) for boards of
+ *    up to 256 tokens whose relative offsets stay inside the bias table, the warp-level tensor-core kernel (mma.sync, scores in
+ *    registers) for everything else.  Measured on 256 x 225 tokens x 8 heads: 0.083 ms against 0.123 ms;
+ * 1: tcgen05 wherever a tcgen05 kernel takes the shape (adds the one-CTA-per-head kernel for 257 .. 462 tokens and clamped offsets,
+ *    which measured slower than the warp-level kernel: 2.18 against 1.32 ms on 1024 x 400 tokens);
+ * 2: the one-CTA-per-head tcgen05 kernel wherever it takes the shape (up to 462 tokens);
+ * 3: never a tcgen05 kernel.
+ * Process-wide; the environment variable MINML_B200_MHA_KERNEL=0..3 selects at start. */
 void mb200_set_attention_kernel(int kernel);
 /* Tells the library that device memory in [ptr, ptr + bytes) has been given new contents (or a new owner) by something other than
  * this ABI: what the library derived from weights lying there -- the snapshot of a layer's raw weights behind its transformed

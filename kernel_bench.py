@@ -193,10 +193,11 @@ def main():
     t = h * w
     add("multi_head_attention_forward (8 heads, rel-pos bias)", lambda: B.multiHeadAttentionForward(ctx, qkv, att, table, heads), 4 * act_bytes,
         4.0 * b * heads * t * t * (c // heads))
-    if c // heads == 32 and t <= 462:  # the tcgen05 variant (scores in tensor memory), selectable; the line above is the default kernel
-        B.set_attention_kernel(1)
-        add("multi_head_attention_forward, tcgen05 variant (8 heads, rel-pos bias)", lambda: B.multiHeadAttentionForward(ctx, qkv, att, table, heads),
-            4 * act_bytes, 4.0 * b * heads * t * t * (c // heads))
+    if c // heads == 32 and t <= 462:  # the kernels the default chooses between, each forced
+        for kernel, name in ((1, "tcgen05 wherever possible"), (2, "tcgen05 with one CTA per (head, item)"), (3, "warp-level mma.sync kernel")):
+            B.set_attention_kernel(kernel)
+            add("multi_head_attention_forward, %s (8 heads, rel-pos bias)" % name, lambda: B.multiHeadAttentionForward(ctx, qkv, att, table, heads),
+                4 * act_bytes, 4.0 * b * heads * t * t * (c // heads))
         B.set_attention_kernel(0)
 
     # ---- layers next to the convolution path: batch norm at inference, depthwise 7x7 (fp16 and int8), channel scaling

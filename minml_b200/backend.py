@@ -138,7 +138,8 @@ def _last_error(handle):
 
 
 def set_attention_kernel(kernel):
-    """0: the warp-level tensor-core attention kernel (default); 1: the tcgen05 kernel with the scores in tensor memory."""
+    """Attention kernel for fp16, head dimension 32.  0: by shape (default: the persistent tcgen05 kernel up to 256 tokens, else the
+    warp-level kernel); 1: tcgen05 wherever possible; 2: the one-CTA-per-head tcgen05 kernel; 3: never tcgen05."""
     lib.mb200_set_attention_kernel(int(kernel))
 
 

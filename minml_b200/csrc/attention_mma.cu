@@ -9,10 +9,10 @@
  * One CTA per (head, batch item) stages K and V of that head in shared memory once; each of its 4 warps owns one or two tiles
  * of 16 queries at a time and walks the keys in blocks of 32 or 64 with a running maximum and sum, keeping S, P and O in
  * registers (head dimensions up to 32: two tiles, 32 keys; larger ones: one tile, 64 keys).
- * Tokens here are at most a few hundred (a 20x20 board has 400) with head dimensions of 16-128.  A tcgen05 version with the
- * scores in tensor memory exists for head dimension 32 (attention_tc.cu); measured on the benchmark shapes it is 14 % (225
- * tokens) to 65 % (400 tokens) slower than this kernel, whose warps run independently of one another and keep P in the
- * accumulator registers it came from, so this one is the default.
+ * Tokens here are at most a few hundred (a 20x20 board has 400) with head dimensions of 16-128.  For head dimension 32 and boards
+ * of up to 256 tokens the persistent tcgen05 kernel (attention_ws.cu) is the default: 0.083 ms against this kernel's 0.123 ms on
+ * 256 x 225 tokens x 8 heads.  This kernel takes every other fp16 case; on 1024 x 400 tokens it measured 1.32 ms against the
+ * 2.18 ms of the one-CTA-per-head tcgen05 kernel (attention_tc.cu).
  */
 #include "common.cuh"
 

@@ -7,26 +7,26 @@
  * Replaces the batched GEMM -> softmax kernel -> batched GEMM sequence of the reference
  * (src/backend/cuda/kernels/attention.cu:494-568), whose [b, heads, T, T] score tensor never exists here.
  *
- * One CTA of 256 threads per (head, batch item); two CTAs share an SM when the board has up to 256 tokens, so one's softmax
- * overlaps the other's copies and products.  Per tile of 128 queries:
- *   1. Q (128 x 64 bytes) and K (N x 64 bytes, N = tokens rounded up to 16) arrive by TMA in the 64-byte-swizzled K-major layout;
- *      V is read with plain loads and written transposed (V^T: 32 rows of N keys, the K-major B operand of the second product);
+ * One CTA of 256 threads per (head, batch item); two CTAs share an SM when the board has up to 256 tokens.  This is the simple form of
+ * the tcgen05 path: boards of up to 256 tokens go to the persistent warp-specialised kernel (attention_ws.cu) by default, and this
+ * kernel runs only when selected (mb200_set_attention_kernel 1 or 2), where it also takes 257 .. 462 tokens and tables whose
+ * offsets need clamping.  Per tile of 128 queries:
+ *   1. Q (128 x 64 bytes), K and V (N x 64 bytes each, N = tokens rounded up to 16) arrive by TMA in the 64-byte-swizzled layout;
+ *      V stays as it landed: [key][d] is the MN-major B operand of the second product;
  *   2. S = Q K^T: one tcgen05.mma (two for more than 256 keys) of M = 128 into N columns of tensor memory;
  *   3. softmax straight from tensor memory, two threads per query row, each with half of the key columns (a tensor-memory lane is
- *      a row, so row maxima and sums need one exchange through shared memory and no shuffles): pass 1 adds scale and relative-position bias, writes the biased scores back to tensor
- *      memory and keeps the maximum; pass 2 exponentiates, sums, and writes P as fp16 into shared memory in the 128-byte-swizzled
- *      K-major layout the tensor core reads;
- *   4. O = P V^T^T: tcgen05.mma of M = 128, N = 32 over the keys, into the first 32 columns (the scores are dead by then);
+ *      a row, so row maxima and sums need one exchange through shared memory and no shuffles): pass 1 adds scale and
+ *      relative-position bias, writes the biased scores back to tensor memory and keeps the maximum; pass 2 exponentiates, sums,
+ *      and writes P as fp16 into shared memory in the 128-byte-swizzled K-major layout the tensor core reads;
+ *   4. O = P V: tcgen05.mma of M = 128, N = 32 over the keys, into the first 32 columns (the scores are dead by then);
  *   5. each thread reads its half of its row of O, divides by the row sum and stores 32 bytes.
- * Measured against the warp-level kernel (attention_mma.cu) on a B200: 256 x 225 tokens x 8 heads 0.140 ms against 0.123 ms, 1024 x 400
- * tokens 2.18 ms against 1.32 ms.  Both spend their time on the softmax arithmetic (scale, table lookup, maximum, exponential, sum:
- * about eight instructions per score here), not on the products, and this kernel's phases -- copy, product, softmax, product, store --
- * run one after the other inside a CTA with at most two CTAs per SM to overlap them (64 KB of P per tile), where the warp-level
- * kernel has twenty independent warps per SM.  So this kernel is kept selectable (mb200_set_attention_kernel, MINML_B200_MHA_TC=1)
- * and the warp-level kernel stays the default.
+ * Measured against the warp-level kernel (attention_mma.cu) on a B200: 256 x 225 tokens x 8 heads 0.128 ms against 0.123 ms, 1024 x 400
+ * tokens 2.18 ms against 1.32 ms: its phases -- copy, product, softmax, product, store -- run one after the other inside a CTA with
+ * at most two CTAs per SM to overlap them, where the warp-level kernel has sixteen independent warps per SM.  The persistent kernel
+ * removes that serialisation (0.083 ms on the first shape).
  * All tcgen05.mma are issued by thread 0; every wait is bounded (tc.cuh) and a timeout sets the context's status word.
  * Keys beyond the last token (the TMA box runs into the next batch item, or past the end of the tensor where it is filled
- * with zeros) get P = 0 and V^T = 0; query rows beyond it are computed and never stored.
+ * with zeros) get P = 0 and their rows of V are cleared; query rows beyond it are computed and never stored.
  */
 #include "common.cuh"
 #include "tc.cuh"
@@ -47,7 +47,6 @@ namespace mb200
 		constexpr int D = 32; // head dimension
 		constexpr int QM = 128; // queries per tile = tensor-memory lanes
 		constexpr int NT = 256; // threads: two per query row, each with half of the key columns (a warp reaches the lanes 32 * (warp % 4) ...)
-		constexpr float LOG2E = 1.4426950408889634f;
 
 		struct MhaTcParams
 		{
@@ -67,67 +66,6 @@ namespace mb200
 				int abort_flag;
 				float row_max[2][QM], row_sum[2][QM]; // the two column halves of a row exchange their maximum and their sum here
 		};
-
-		__device__ __forceinline__ float exp2_approx(float x)
-		{
-			float y;
-			asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-			return y;
-		}
-		/* K-major operand with 64-byte rows and the 64-byte swizzle: 8-row groups 512 bytes apart */
-		__device__ __forceinline__ uint64_t make_desc_k_sw64(uint32_t smem_addr)
-		{
-			uint64_t desc = 0;
-			desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-			desc |= static_cast<uint64_t>(1) << 16;
-			desc |= static_cast<uint64_t>(512 >> 4) << 32;
-			desc |= static_cast<uint64_t>(1) << 46;
-			desc |= static_cast<uint64_t>(4) << 61;
-			return desc;
-		}
-		__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
-		{
-			asm volatile(
-					"tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-					"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-					"%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-					:: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-					"r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
-					"r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
-					"r"(r[30]), "r"(r[31]) : "memory");
-		}
-		__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[32])
-		{
-			asm volatile(
-					"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-					"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-					:: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-					"r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-		}
-		__device__ __forceinline__ void tmem_wait_st()
-		{
-			asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-		}
-		/* 32 (or, for the last chunk of a row, 16) columns of this thread's lane */
-		__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[32], bool wide)
-		{
-			if (wide)
-				tmem_ld_32x32(taddr, r);
-			else
-			{
-				uint32_t h[16];
-				tmem_ld_32x16(taddr, h);
-#pragma unroll
-				for (int i = 0; i < 16; i++)
-					r[i] = h[i];
-			}
-			tmem_wait_ld();
-		}
-		__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
-		{
-			const __half2 h = __floats2half2_rn(lo, hi);
-			return *reinterpret_cast<const uint32_t*>(&h);
-		}
 
 		__global__ void __launch_bounds__(NT) kernel_mha_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
 				const MhaTcParams p)
@@ -177,9 +115,12 @@ namespace mb200
 			{ // K (all boxes) and the first Q tile
 				prefetch_tensormap(&map_q);
 				prefetch_tensormap(&map_k);
-				mbar_arrive_expect_tx(smem_u32(&bars.tma_k), static_cast<uint32_t>(keys) * 64u);
+				mbar_arrive_expect_tx(smem_u32(&bars.tma_k), static_cast<uint32_t>(keys) * 128u);
 				for (int i = 0; i < p.boxes; i++)
+				{
 					tma_load_3d(s_k + i * p.box_rows * 64, &map_k, smem_u32(&bars.tma_k), k_col, static_cast<int>(row0) + i * p.box_rows, 0);
+					tma_load_3d(s_vt + i * p.box_rows * 64, &map_k, smem_u32(&bars.tma_k), v_col, static_cast<int>(row0) + i * p.box_rows, 0);
+				}
 				mbar_arrive_expect_tx(smem_u32(&bars.tma_q), QM * 64u);
 				tma_load_3d(s_q, &map_q, smem_u32(&bars.tma_q), q_col, static_cast<int>(row0), 0);
 			}
@@ -197,28 +138,13 @@ namespace mb200
 				const int t = min(i, tokens - 1);
 				spos[i] = linear_bias ? (t / p.width) * p.table_pad + (t % p.width) : (((t / p.width) << 16) | (t % p.width));
 			}
-			{
-				const __half *vbase = p.input + row0 * stride + v_col;
-				for (int key = tid; key < key_tiles * 64; key += NT)
-				{
-					uint4 v[4];
-#pragma unroll
-					for (int c = 0; c < 4; c++)
-						v[c] = (key < tokens) ? *reinterpret_cast<const uint4*>(vbase + static_cast<long long>(key) * stride + c * 8) : make_uint4(0, 0, 0, 0);
-					const __half *vh = reinterpret_cast<const __half*>(v);
-					// element (d, key) of V^T: tile key / 64, row d (128-byte pitch), 16-byte chunk (key % 64) / 8 swizzled by the row
-					const uint32_t tile = s_vt + (key / 64) * 4096;
-					const int chunk = (key % 64) / 8, within = (key % 8) * 2;
-#pragma unroll
-					for (int d = 0; d < D; d++)
-					{
-						const uint32_t dst = tile + d * 128 + ((chunk ^ (d & 7)) * 16) + within;
-						asm volatile("st.shared.b16 [%0], %1;" :: "r"(dst), "h"(__half_as_ushort(vh[d])) : "memory");
-					}
-				}
-			}
-			fence_proxy_async_smem(); // V^T was written with plain stores; the tensor core reads it through the async proxy
-			__syncthreads();
+			// V arrives beside K; its rows beyond the last token belong to the next batch item (or are the copy's zero fill): cleared, so
+			// that nothing of them reaches this item's output even if they hold infinities
+			bool v_ok = mbar_wait(smem_u32(&bars.tma_k), 0, abort_flag);
+			for (int i = tid; i < (keys - tokens) * 4; i += NT)
+				st_shared_v4(s_vt + (tokens + i / 4) * 64 + (i % 4) * 16, make_uint4(0, 0, 0, 0));
+			fence_proxy_async_smem(); // plain stores; the tensor core reads V through the async proxy
+			v_ok = __syncthreads_and(v_ok ? 1 : 0) != 0;
 
 			const float scale = rsqrtf(static_cast<float>(D)) * LOG2E; // exp(x) = 2^(x log2 e)
 			const int q_tiles = (tokens + QM - 1) / QM;
@@ -229,9 +155,9 @@ namespace mb200
 			const int n_chunks = (keys + 31) / 32, all_chunks = key_tiles * 2, split = (n_chunks + 1) / 2;
 			const int chunk_begin = half == 0 ? 0 : split, chunk_end = half == 0 ? split : all_chunks;
 			uint32_t mma_phase = 0;
-			bool ok = true;
+			bool ok = v_ok;
 
-			for (int qt = 0; qt < q_tiles; qt++)
+			for (int qt = 0; qt < (ok ? q_tiles : 0); qt++)
 			{
 				/* ---- S = Q K^T */
 				if (tid == 0 && ok)
@@ -383,12 +309,12 @@ namespace mb200
 				if (tid == 0)
 				{
 					tcgen05_fence_after();
-					const uint32_t idesc = make_idesc_f16(D);
+					const uint32_t idesc = make_idesc_f16(D) | (1u << 16); // B = V as stored: [key][d], MN-major
 					const int k_steps = keys / 16;
 					for (int ks = 0; ks < k_steps; ks++)
 					{ // 16 keys = 32 bytes of the 128-byte slice per instruction
 						const uint64_t desc_a = make_desc_k_sw128(s_p + (ks / 4) * 16384) + 2 * (ks % 4);
-						const uint64_t desc_b = make_desc_k_sw128(s_vt + (ks / 4) * 4096) + 2 * (ks % 4);
+						const uint64_t desc_b = make_desc_mn_sw64(s_vt + ks * 1024);
 						mma_ss<0>(tmem_base, desc_a, desc_b, idesc, ks > 0 ? 1u : 0u);
 					}
 					mma_commit(smem_u32(&bars.mma));
@@ -440,24 +366,30 @@ namespace mb200
 			}
 		}
 
-		/* 0 = warp-level kernel (default), 1 = this kernel; MINML_B200_MHA_TC=1 at start, mb200_set_attention_kernel at run time */
+		/* 0 = by shape (the persistent tcgen05 kernel where it applies, else the warp-level kernel), 1 = tcgen05 wherever one of the two
+		 * tcgen05 kernels takes the shape, 2 = this kernel wherever it takes the shape, 3 = never tcgen05; MINML_B200_MHA_KERNEL=0..3 at
+		 * start, mb200_set_attention_kernel at run time */
 		std::atomic<int> g_attention_kernel { []
 		{
-			const char *e = std::getenv("MINML_B200_MHA_TC");
-			return (e != nullptr && e[0] == '1') ? 1 : 0;
+			const char *e = std::getenv("MINML_B200_MHA_KERNEL");
+			return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 0;
 		}() };
 	}
 
 	void g_attention_kernel_store(int kernel)
 	{
-		g_attention_kernel.store(kernel == 1 ? 1 : 0);
+		g_attention_kernel.store((kernel >= 0 && kernel <= 3) ? kernel : 0);
 	}
-	/* Returns false when the shape is outside what this kernel handles, or when it is not the selected one (the caller then uses the
-	 * warp-level kernel). */
+	bool mha_forward_ws(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
+			int head_dim, int parts, int table_n, int table_pad);
+	/* The tcgen05 kernels, as selected.  Returns false when neither is to run (the caller then uses the warp-level kernel). */
 	bool mha_forward_tc(mlContext_t ctx, void *output, const void *input, const void *table, int batch, int height, int width, int heads,
 			int head_dim, int parts, int table_n, int table_pad)
 	{
-		if (g_attention_kernel.load() != 1 || head_dim != D || height >= 32768 || width >= 32768 || batch > 65535 || heads > 65535)
+		const int selected = g_attention_kernel.load();
+		if (selected <= 1 && mha_forward_ws(ctx, output, input, table, batch, height, width, heads, head_dim, parts, table_n, table_pad))
+			return true;
+		if (selected == 0 || selected == 3 || head_dim != D || height >= 32768 || width >= 32768 || batch > 65535 || heads > 65535)
 			return false;
 		const int channels = parts * heads * D;
 		const long long rows = static_cast<long long>(batch) * height * width;

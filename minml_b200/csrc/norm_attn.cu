@@ -341,8 +341,8 @@ extern "C"
 			table_n = weights_shape.dim[1];
 			table_pad = weights_shape.dim[2];
 		}
-		// fp16, head dimension 32, up to 480 tokens: the tcgen05 kernel with the scores in tensor memory; fp16 with a head dimension of
-		// 16, 32, 64 or 128: the warp-level tensor-core kernel; anything else: the generic kernel below
+		// fp16, head dimension 32: the tcgen05 kernels as selected (by default the persistent one for boards of up to 256 tokens); fp16 with
+		// a head dimension of 16, 32, 64 or 128: the warp-level tensor-core kernel; anything else: the generic kernel below
 		if (dtype == DTYPE_FLOAT16 && mha_forward_tc(context, output, input, table, batch, height, width, num_heads, head_dim, parts, table_n,
 				table_pad))
 			return;

@@ -9,6 +9,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <cstdint>
 
 namespace mb200
@@ -77,6 +78,39 @@ namespace mb200
 		__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
 		{
 			return mbar_wait_limited(bar, parity, abort_flag, SPIN_LIMIT);
+		}
+
+		/* Wait that leaves most of the issue slots to the other warps: after a few immediate polls the thread sleeps `sleep_ns` between
+		 * polls.  The bound is a time, two seconds of the global timer, checked every 256 polls together with the abort flag. */
+		__device__ __forceinline__ uint64_t global_timer_ns()
+		{
+			uint64_t t;
+			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+			return t;
+		}
+		__device__ __forceinline__ bool mbar_wait_sleeping(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t sleep_ns)
+		{
+#pragma unroll 1
+			for (int it = 0; it < 8; ++it)
+				if (mbar_try_wait(bar, parity))
+					return true;
+			const uint64_t start = global_timer_ns();
+#pragma unroll 1
+			for (uint32_t it = 1;; ++it)
+			{
+				__nanosleep(sleep_ns);
+				if (mbar_try_wait(bar, parity))
+					return true;
+				if ((it & 255u) == 0u)
+				{
+					if (*abort_flag != 0)
+						return false;
+					if (global_timer_ns() - start > 2000000000ull)
+						break;
+				}
+			}
+			*abort_flag = 1;
+			return false;
 		}
 
 		/* ---------------------------------------------------------------- TMA */
@@ -210,6 +244,16 @@ namespace mb200
 						"tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
 						"}\n" :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 		}
+		/* A from tensor memory (128 lanes = rows; a 32-bit column holds two consecutive 16-bit elements along K), B from shared memory */
+		__device__ __forceinline__ void mma_ts_f16(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+		{
+			asm volatile(
+					"{\n\t"
+					".reg .pred p;\n\t"
+					"setp.ne.b32 p, %4, 0;\n\t"
+					"tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+					"}\n" :: "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+		}
 		/* The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has completed. */
 		__device__ __forceinline__ void mma_commit(uint32_t bar)
 		{
@@ -317,6 +361,100 @@ namespace mb200
 		__host__ __device__ constexpr uint32_t make_idesc_i8_pair(int n)
 		{
 			return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+		}
+
+		/* ---------------------------------------------------------------- pieces of the attention kernels */
+		constexpr float LOG2E = 1.4426950408889634f;
+		__device__ __forceinline__ float exp2_approx(float x)
+		{
+			float y;
+			asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+			return y;
+		}
+		/* K-major operand with 64-byte rows and the 64-byte swizzle: 8-row groups 512 bytes apart */
+		__device__ __forceinline__ uint64_t make_desc_k_sw64(uint32_t smem_addr)
+		{
+			uint64_t desc = 0;
+			desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+			desc |= static_cast<uint64_t>(1) << 16;
+			desc |= static_cast<uint64_t>(512 >> 4) << 32;
+			desc |= static_cast<uint64_t>(1) << 46;
+			desc |= static_cast<uint64_t>(4) << 61;
+			return desc;
+		}
+		/* MN-major operand of up to 32 fp16 along MN (one 64-byte row per K index, 64-byte swizzle): 8-row groups along K 512 bytes apart */
+		__device__ __forceinline__ uint64_t make_desc_mn_sw64(uint32_t smem_addr)
+		{
+			uint64_t desc = 0;
+			desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+			desc |= static_cast<uint64_t>(512 >> 4) << 16;
+			desc |= static_cast<uint64_t>(512 >> 4) << 32;
+			desc |= static_cast<uint64_t>(1) << 46;
+			desc |= static_cast<uint64_t>(4) << 61;
+			return desc;
+		}
+		__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
+		{
+			asm volatile(
+					"tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+					"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+					"%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+					:: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+					"r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+					"r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+					"r"(r[30]), "r"(r[31]) : "memory");
+		}
+		__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[32])
+		{
+			asm volatile(
+					"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+					"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+					:: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+					"r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+		}
+		__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16])
+		{
+			asm volatile(
+					"tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+					"{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+					:: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+					"r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+		}
+		__device__ __forceinline__ void tmem_wait_st()
+		{
+			asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+		}
+		/* 32 (or, for the last chunk of a row, 16) columns of this thread's lane */
+		__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[32], bool wide)
+		{
+			if (wide)
+				tmem_ld_32x32(taddr, r);
+			else
+			{
+				uint32_t h[16];
+				tmem_ld_32x16(taddr, h);
+#pragma unroll
+				for (int i = 0; i < 16; i++)
+					r[i] = h[i];
+			}
+			tmem_wait_ld();
+		}
+		__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+		{
+			const __half2 h = __floats2half2_rn(lo, hi);
+			return *reinterpret_cast<const uint32_t*>(&h);
+		}
+		__device__ __forceinline__ float max3(float a, float b, float c)
+		{
+			float d;
+			asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+			return d;
+		}
+		__device__ __forceinline__ float ld_shared_f32(uint32_t addr)
+		{
+			float v;
+			asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+			return v;
 		}
 	} /* namespace tc */
 

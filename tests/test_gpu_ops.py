@@ -283,6 +283,9 @@ def test_kernel_bench_tool_runs_and_reports_every_kernel():
     (2, 9, 7, 4, False, 5),        # a table built for a 5 x 5 board: offsets beyond its range are clamped
     (1, 21, 22, 1, False, None),   # 462 tokens: the most the kernel takes (480 key slots + nothing to spare)
     (1, 1, 1, 2, False, None),     # a single token
+    (40, 15, 15, 8, False, None),  # 320 (head, item) pairs: more than one per CTA of the persistent kernel, both of its groups at work
+    (170, 5, 6, 2, True, None),    # 340 pairs of one query tile each, q = k
+    (37, 12, 13, 5, False, None),  # 185 pairs of 156 tokens (160 keys: a last chunk of 32), ranges of one and two pairs per CTA
 ])
 def test_multi_head_attention_tcgen05_shapes(ctx, oracle, cfg):
     """Head dimension 32 in fp16 -- the shapes that run on the tcgen05 kernel (scores in tensor memory) -- against the oracle, with
@@ -296,7 +299,7 @@ def test_multi_head_attention_tcgen05_shapes(ctx, oracle, cfg):
     n = 2 * (table_board or max(h, w)) - 1
     table = (r.standard_normal((heads, n, (n + 3) // 4 * 4)) * 0.5).astype(np.float16).astype(np.float32)
     try:
-        for kernel in (1, 0):  # the tcgen05 kernel (selected explicitly) and the default warp-level kernel
+        for kernel in (0, 1, 2, 3):  # by shape, tcgen05 wherever possible, tcgen05 with one CTA per pair, never tcgen05
             B.set_attention_kernel(kernel)
             for t in (table, None):
                 y = torch.full((b, h, w, heads * d), float("nan"), device="cuda", dtype=torch.float16)
