@@ -100,28 +100,33 @@ namespace mb200
 		 * a 128 x BN tile is only a few K slices, and fetching the weight tile again for every 128 rows of output made the copies
 		 * into shared memory, not HBM, the limit (l1tex 62 % of peak, tensor pipe 30 %).  Here every CTA takes a CONTIGUOUS range of
 		 * tiles ordered (batch, column tile, row tile), keeps the whole [BN, K] weight tile in shared memory for as long as
-		 * consecutive tiles share it, and streams only A through the ring.
-		 * Measured: the 36 Winograd products of a 256-channel layer 0.167 -> 0.159 ms (0.92 of the copy bandwidth), a 256 -> 1 head over
-		 * 409 600 rows 0.054 -> 0.043 ms; the 256 -> 768 / 256 / 1024 projections of 57 600 rows did not move (0.043 / 0.029 / 0.056 ms,
-		 * tensor pipe 24 %, 25 % of the issue slots, l1tex 56 %): what is left there is the epilogue's own chain per 32-column chunk --
-		 * a version that started the tensor-memory load of chunk i + 1 and the bias reads under chunk i's arithmetic measured 5 - 10 %
-		 * slower (168 registers) and was taken out again.
+		 * consecutive tiles share it, streams only A through the ring, and moves C and D as 32 x 32 boxes through tensor maps (see the
+		 * epilogue below).  What bounds these products on a B200 is then the write path: a kernel that only writes reaches 3.4 TB/s on
+		 * 88 MB and 2.6 TB/s on 30 MB (about half of the copy bandwidth, which counts a read and a write), and in steady state this
+		 * kernel writes its 64 KB of D per tile at 3.3 TB/s chip-wide; start-up (the 128 KB of weights, the first A slices: 3 us) and
+		 * the uneven last tiles make up the rest of a 40 us product.
+		 * Measured, 57 600 rows, K = 256 (before -> after the box epilogue): N = 768 0.043 -> 0.040 ms (its 88 MB of D alone take
+		 * 0.026 ms to write), N = 256 with a residual 0.031 -> 0.025 ms, N = 1024 with ReLU 0.055 -> 0.052 ms; the 36 Winograd products
+		 * of a 256-channel layer 0.167 -> 0.159 ms with the resident weights alone (0.92 of the copy bandwidth).
 		 */
 		constexpr int RESIDENT_BYTES = 128 * 1024;
-		template<int KIND, int BN, bool RES = false>
+		template<int KIND, int BN, bool RES = false, bool BOX = false>
 		struct Tiling
 		{
 				static constexpr bool split = (KIND == 3);
 				static constexpr int a_bytes = BM * BK_BYTES, b_bytes = BN * BK_BYTES;
 				static constexpr int operand_bytes = a_bytes + b_bytes;
 				static constexpr int stage_bytes = RES ? a_bytes : operand_bytes;
-				static constexpr int stages = RES ? 4 : split ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
+				static constexpr int stages = RES ? (BOX ? 3 : 4) : split ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
 				static constexpr int resident_offset = stages * stage_bytes;
 				static constexpr int lo_stages = split ? ((BN == 256) ? 1 : 2) : 0;
 				static constexpr int lo_ring = (lo_stages > 0) ? lo_stages : 1; // divisor that is never zero
 				static constexpr int lo_offset = resident_offset + (RES ? RESIDENT_BYTES : 0);
 				static constexpr int staging_offset = lo_offset + lo_stages * operand_bytes;
-				static constexpr int smem_bytes = staging_offset + (split ? 0 : EPI_WARPS * epi::WARP_BYTES) + 1024;
+				static constexpr int box_bytes = 32 * 64; // RES: a 32-row x 32-column fp16 box of C or D, 64-byte swizzle
+				static constexpr int boxes = 3; // per epilogue warp: D of two chunks in flight, C of the next chunk
+				static constexpr int staging_bytes = split ? 0 : BOX ? EPI_WARPS * boxes * box_bytes : EPI_WARPS * epi::WARP_BYTES;
+				static constexpr int smem_bytes = staging_offset + staging_bytes + 1024;
 				static constexpr int tmem_columns = 2 * BN; // two accumulator buffers
 		};
 
@@ -134,6 +139,7 @@ namespace mb200
 				uint64_t resident_full, resident_empty; // RES: the weight tile has landed / every product that reads it is done
 				uint64_t tmem_full[2];
 				uint64_t tmem_empty[2];
+				uint64_t c_full[EPI_WARPS][3]; // RES: the box of C has landed (one ring of three per epilogue warp)
 				uint32_t tmem_base;
 				int abort_flag;
 		};
@@ -149,12 +155,14 @@ namespace mb200
 
 		// (requantisation arithmetic: epilogue.cuh)
 
-		template<int KIND, int BN, bool RES = false>
+		template<int KIND, int BN, bool RES = false, bool BOX = false>
 		__global__ void __launch_bounds__(num_threads(KIND), 1) kernel_gemm_tc(const __grid_constant__ CUtensorMap map_a,
-				const __grid_constant__ CUtensorMap map_b, const GemmTcParams p)
+				const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_d,
+				const GemmTcParams p)
 		{
 			static_assert(!RES || KIND == 0, "the weight-resident variant is built for fp16");
-			using T = Tiling<KIND, BN, RES>;
+			static_assert(!BOX || RES, "the box epilogue belongs to the weight-resident variant");
+			using T = Tiling<KIND, BN, RES, BOX>;
 			extern __shared__ uint8_t smem_raw[];
 			__shared__ Barriers bars;
 
@@ -172,19 +180,62 @@ namespace mb200
 			const long long tile_first = RES ? blockIdx.x * per_cta : blockIdx.x;
 			const long long tile_last = RES ? min(total_tiles, tile_first + per_cta) : total_tiles;
 			const long long tile_step = RES ? 1 : gridDim.x;
-			auto decode = [&](long long tile, int &nt, int &mt, int &b)
+			// Position of a tile -- column tile, row tile, batch item -- kept by increments: every role walks the same sequence, and a
+			// 64-bit division per tile and role was a tenth of a short-K tile's time.
+			struct Walk
 			{
+					int nt, mt, b;
+			};
+			const long long per_item = static_cast<long long>(n_tiles) * m_tiles;
+			const int step_b = static_cast<int>(tile_step / per_item), step_rest = static_cast<int>(tile_step % per_item);
+			const int step_mt = RES ? 0 : step_rest / n_tiles, step_nt = RES ? 0 : step_rest % n_tiles;
+			auto start = [&]() -> Walk
+			{
+				Walk w;
+				const long long rest = tile_first % per_item;
+				w.b = static_cast<int>(tile_first / per_item);
 				if (RES)
 				{ // row tiles fastest: a column tile's weights stay while the rows go by
-					mt = static_cast<int>(tile % m_tiles);
-					nt = static_cast<int>((tile / m_tiles) % n_tiles);
+					w.mt = static_cast<int>(rest % m_tiles);
+					w.nt = static_cast<int>(rest / m_tiles);
 				}
 				else
 				{
-					nt = static_cast<int>(tile % n_tiles);
-					mt = static_cast<int>((tile / n_tiles) % m_tiles);
+					w.nt = static_cast<int>(rest % n_tiles);
+					w.mt = static_cast<int>(rest / n_tiles);
 				}
-				b = static_cast<int>(tile / (static_cast<long long>(n_tiles) * m_tiles));
+				return w;
+			};
+			auto advance = [&](Walk &w)
+			{
+				if (RES)
+				{ // one tile on
+					if (++w.mt == m_tiles)
+					{
+						w.mt = 0;
+						if (++w.nt == n_tiles)
+						{
+							w.nt = 0;
+							w.b++;
+						}
+					}
+				}
+				else
+				{ // gridDim.x tiles on
+					w.nt += step_nt;
+					if (w.nt >= n_tiles)
+					{
+						w.nt -= n_tiles;
+						w.mt++;
+					}
+					w.mt += step_mt;
+					if (w.mt >= m_tiles)
+					{
+						w.mt -= m_tiles;
+						w.b++;
+					}
+					w.b += step_b;
+				}
 			};
 
 			if (threadIdx.x == 0)
@@ -203,6 +254,9 @@ namespace mb200
 				}
 				mbar_init(smem_u32(&bars.resident_full), 1);
 				mbar_init(smem_u32(&bars.resident_empty), 1);
+				for (int e = 0; e < EPI_WARPS; e++)
+					for (int k = 0; k < 3; k++)
+						mbar_init(smem_u32(&bars.c_full[e][k]), 1);
 				bars.abort_flag = 0;
 				fence_mbar_init();
 			}
@@ -227,10 +281,10 @@ namespace mb200
 					bool ok = true;
 					long long weights_loaded = -1; // RES: which weight tile shared memory holds
 					uint32_t weight_loads = 0;
-					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step)
+					Walk w = start();
+					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step, advance(w))
 					{
-						int nt, mt, b;
-						decode(tile, nt, mt, b);
+						const int nt = w.nt, mt = w.mt, b = w.b;
 						const long long weights = static_cast<long long>(p.b_broadcast ? 0 : b) * n_tiles + nt;
 						if (RES && weights != weights_loaded)
 						{ // a new weight tile: once every product on the old one is done, all its K slices in one go
@@ -274,12 +328,12 @@ namespace mb200
 					bool ok = true;
 					long long weights_loaded = -1;
 					uint32_t weight_loads = 0;
-					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step, local_tile++)
+					Walk w = start();
+					for (long long tile = tile_first; tile < tile_last && ok; tile += tile_step, local_tile++, advance(w))
 					{
 						if (RES)
 						{
-							int nt, mt, b;
-							decode(tile, nt, mt, b);
+							const int nt = w.nt, b = w.b;
 							const long long weights = static_cast<long long>(p.b_broadcast ? 0 : b) * n_tiles + nt;
 							if (weights != weights_loaded)
 							{
@@ -383,6 +437,156 @@ namespace mb200
 							mbar_arrive(smem_u32(&bars.split[s]));
 					}
 			}
+			else if (BOX)
+			{ /* ------------------------------------------------------------ box epilogue of the weight-resident variant
+			   * fp16 D (and C) whose rows start on 16-byte boundaries, which the host checks before it picks this epilogue.  A tile of
+			   * a short-K product is a few K slices, so the epilogue sets the pace; here it is kept to what only it can do:
+			   *   - chunks of 32 columns with the next chunk's tcgen05.ld in flight under the arithmetic of the current one, and the
+			   *     accumulator buffer handed back as soon as the tile's last chunk is in registers;
+			   *   - C arrives and D leaves as 32 x 32 boxes through TMA (64-byte swizzle, so that a lane's 64-byte row goes in and out
+			   *     of shared memory without bank conflicts): no cooperative re-layout, no per-row address arithmetic, tails clipped
+			   *     by the tensor map.  Three boxes per warp rotate: chunk n's D leaves from box n % 3 while chunk n + 1's C lands
+			   *     in box (n + 1) % 3, which chunk n - 2's store has finished reading (cp.async.bulk.wait_group.read 1). */
+				const int e = warp - 2; // epilogue warp
+				const int q = warp % 4; // tensor-memory lane quarter this warp may read
+				const int col_part = e / 4; // which half of the tile's columns
+				constexpr int NCH = BN / 64; // chunks of 32 columns per warp and tile
+				const uint32_t boxes = smem_base + T::staging_offset + e * T::boxes * T::box_bytes;
+				const bool use_c = p.beta != 0.0f && p.C != nullptr;
+				// a lane's row inside a box: four 16-byte pieces, piece k at (k ^ ((lane >> 1) & 3))
+				uint32_t piece[4];
+#pragma unroll
+				for (int k = 0; k < 4; k++)
+					piece[k] = lane * 64 + ((k ^ ((lane >> 1) & 3)) * 16);
+				auto active_chunks = [&](const Walk &w) -> int
+				{ // of this warp in tile w: chunks whose first column exists
+					const int n_valid_tile = min(BN, p.N - w.nt * BN);
+					return max(0, min(NCH, (n_valid_tile - col_part * (BN / 2) + 31) / 32));
+				};
+				auto issue_c = [&](const Walk &w, int i, uint32_t n)
+				{ // lane 0: chunk i of tile w is this warp's n-th chunk
+					const uint32_t bar = smem_u32(&bars.c_full[e][n % 3]);
+					mbar_arrive_expect_tx(bar, T::box_bytes);
+					tma_load_3d(boxes + (n % 3) * T::box_bytes, &map_c, bar, w.nt * BN + col_part * (BN / 2) + i * 32, w.mt * BM + q * 32, w.b);
+				};
+				uint32_t local_tile = 0, n = 0, c_issued = 0; // chunks done, boxes of C asked for (both warp-uniform)
+				Walk w = start();
+				for (long long tile = tile_first; tile < tile_last; tile += tile_step, local_tile++, advance(w))
+				{
+					Walk next = w;
+					advance(next);
+					const bool has_next = tile + tile_step < tile_last;
+					const int chunks = active_chunks(w);
+					if (use_c && chunks > 0 && c_issued == n)
+					{ // nothing asked for this tile's first chunk yet (the first tile, or a tile after one without chunks for this warp)
+						if (lane == 0)
+						{
+							bulk_wait_group_read<1>();
+							issue_c(w, 0, n);
+						}
+						c_issued++;
+					}
+					const uint32_t acc = local_tile & 1u;
+					const uint32_t acc_parity = (local_tile >> 1) & 1u;
+					if (!mbar_wait_sleeping(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag, 20u))
+						break;
+					tcgen05_fence_after();
+					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + col_part * (BN / 2);
+					uint32_t r[2][32];
+					if (chunks > 0)
+						tmem_ld_32x32(taddr, r[0]);
+					bool ok = true;
+#pragma unroll
+					for (int i = 0; i < NCH; i++)
+					{
+						if (i >= chunks)
+							break; // warp-uniform
+						tmem_wait_ld();
+						if (i + 1 < chunks)
+							tmem_ld_32x32(taddr + (i + 1) * 32, r[(i + 1) & 1]);
+						else
+						{ // the tile's accumulators are all in registers: the issue warp may have the buffer back
+							tcgen05_fence_before();
+							__syncwarp();
+							if (lane == 0)
+								mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
+						}
+						// the box after this chunk's is free once chunk n - 2's store has read it; C of the next chunk goes there
+						const bool more_here = i + 1 < chunks;
+						const bool more_next = !more_here && has_next && active_chunks(next) > 0;
+						if (lane == 0)
+						{
+							bulk_wait_group_read<1>();
+							if (use_c && c_issued == n + 1 && (more_here || more_next))
+								issue_c(more_here ? w : next, more_here ? i + 1 : 0, n + 1);
+						}
+						if (use_c && c_issued == n + 1 && (more_here || more_next))
+							c_issued++;
+						__syncwarp();
+
+						const int n0 = w.nt * BN + col_part * (BN / 2) + i * 32;
+						const uint32_t box = boxes + (n % 3) * T::box_bytes;
+						float v[32];
+						const uint32_t (&ri)[32] = r[i & 1];
+#pragma unroll
+						for (int j = 0; j < 32; j++)
+							v[j] = __uint_as_float(ri[j]) * p.alpha;
+						if (use_c)
+						{
+							if (!mbar_wait_sleeping(smem_u32(&bars.c_full[e][n % 3]), (n / 3) & 1u, abort_flag, 20u))
+							{
+								ok = false;
+								break;
+							}
+#pragma unroll
+							for (int k = 0; k < 4; k++)
+								add_half8(v + 8 * k, ld_shared_v4(box + piece[k]), p.beta);
+							__syncwarp(); // every lane has read its row of C before D goes into the same box
+						}
+						if (p.bias != nullptr)
+						{
+							const __half *bs = reinterpret_cast<const __half*>(p.bias) + n0;
+							if (n0 + 32 <= p.N && aligned_to_16(bs))
+							{
+#pragma unroll
+								for (int k = 0; k < 4; k++)
+									add_half8(v + 8 * k, reinterpret_cast<const uint4*>(bs)[k]);
+							}
+							else
+							{
+#pragma unroll
+								for (int j = 0; j < 32; j++)
+									if (n0 + j < p.N)
+										v[j] += __half2float(bs[j]);
+							}
+						}
+						activate32(v, p.act);
+#pragma unroll
+						for (int k = 0; k < 4; k++)
+							st_shared_v4(box + piece[k], pack_half8(v + 8 * k));
+						fence_proxy_async_smem(); // plain stores, read by the copy engine
+						__syncwarp();
+						if (lane == 0)
+						{
+							tma_store_3d(&map_d, box, n0, w.mt * BM + q * 32, w.b);
+							bulk_commit_group();
+						}
+						n++;
+					}
+					if (!ok)
+						break;
+					if (chunks == 0)
+					{ // nothing of this tile is this warp's: hand the buffer back
+						tcgen05_fence_before();
+						__syncwarp();
+						if (lane == 0)
+							mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
+					}
+				}
+				if (lane == 0)
+					bulk_wait_group_read<0>(); // shared memory stays until the last store has read it
+				__syncwarp();
+			}
 			else
 			{ /* ------------------------------------------------------------ epilogue */
 				const int q = warp % 4; // tensor-memory lane quarter this warp may read
@@ -394,10 +598,10 @@ namespace mb200
 				const bool rows_vectorisable = (KIND == 0) && p.out_dtype == DTYPE_FLOAT16 && aligned_to_16(p.D) && (p.ldd % 8) == 0
 						&& (p.stride_d % 8) == 0 && (!use_c || (aligned_to_16(p.C) && (p.ldc % 8) == 0 && (p.stride_c % 8) == 0));
 				uint32_t local_tile = 0;
-				for (long long tile = tile_first; tile < tile_last; tile += tile_step, local_tile++)
+				Walk w = start();
+				for (long long tile = tile_first; tile < tile_last; tile += tile_step, local_tile++, advance(w))
 				{
-					int nt, mt, b;
-					decode(tile, nt, mt, b);
+					const int nt = w.nt, mt = w.mt, b = w.b;
 					const uint32_t acc = local_tile & 1u;
 					const uint32_t acc_parity = (local_tile >> 1) & 1u;
 					if (!mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag))
@@ -640,10 +844,11 @@ namespace mb200
 			}
 		}
 
-		template<int KIND, int BN, bool RES = false>
-		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const GemmTcParams &p, int sm_count)
+		template<int KIND, int BN, bool RES = false, bool BOX = false>
+		bool launch(mlContext_t ctx, cudaStream_t stream, const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_c,
+				const CUtensorMap &map_d, const GemmTcParams &p, int sm_count)
 		{
-			using T = Tiling<KIND, BN, RES>;
+			using T = Tiling<KIND, BN, RES, BOX>;
 			static bool configured_on[MAX_DEVICES] = { false }; // the opt-in is a per-device attribute of the kernel
 			const int device = get(ctx)->device;
 			if (device < 0 || device >= MAX_DEVICES)
@@ -652,14 +857,14 @@ namespace mb200
 			if (!configured)
 			{
 				if (!check_cuda(ctx,
-						cudaFuncSetAttribute(kernel_gemm_tc<KIND, BN, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::smem_bytes),
+						cudaFuncSetAttribute(kernel_gemm_tc<KIND, BN, RES, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::smem_bytes),
 						"gemm_tc: shared memory opt-in"))
 					return false;
 				configured = true;
 			}
 			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
 			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
-			kernel_gemm_tc<KIND, BN, RES> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, p);
+			kernel_gemm_tc<KIND, BN, RES, BOX> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, map_c, map_d, p);
 			MB200_COUNT_LAUNCH();
 			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
 		}
@@ -755,14 +960,16 @@ namespace mb200
 		c->kernels_with_waits = true;
 
 		if (g.kind == 3)
-			return launch<3, 128>(ctx, stream, map_a, map_b, p, c->sm_count);
+			return launch<3, 128>(ctx, stream, map_a, map_b, map_a, map_a, p, c->sm_count);
 		if (g.kind == 2)
-			return (bn == 256) ? launch<2, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<2, 128>(ctx, stream, map_a, map_b, p,
+			return (bn == 256) ? launch<2, 256>(ctx, stream, map_a, map_b, map_a, map_a, p, c->sm_count) : launch<2, 128>(ctx, stream, map_a, map_b, map_a, map_a, p,
 							c->sm_count);
+		CUtensorMap map_c = map_a, map_d = map_a; // read only by the weight-resident variant
 		if (g.kind == 0)
 		{
 			// weight-resident variant: the whole [bn, K] weight tile fits its 128 KB, and a CTA's contiguous range of tiles stays on one
-			// weight tile for long enough to pay for the reload (MINML_B200_GEMM_RESIDENT=0: measurement switch)
+			// weight tile for long enough to pay for the reload (MINML_B200_GEMM_RESIDENT=0: measurement switch); with the box epilogue
+			// when D (and C) are fp16 with 16-byte aligned rows
 			static const bool resident_allowed = []
 			{
 				const char *e = std::getenv("MINML_B200_GEMM_RESIDENT");
@@ -770,15 +977,36 @@ namespace mb200
 			}();
 			const int k_blocks = (g.K + 63) / 64;
 			const long long m_tiles = (g.M + BM - 1) / BM;
+			const bool use_c = g.beta != 0.0f && g.C != nullptr;
+			const bool boxes_ok = g.out_dtype == DTYPE_FLOAT16 && aligned_to(g.D, 16) && g.ldd % 8 == 0 && (g.batch == 1 || g.stride_d % 8 == 0)
+					&& (!use_c || (aligned_to(g.C, 16) && g.ldc % 8 == 0 && (g.batch == 1 || g.stride_c % 8 == 0)));
 			const bool resident = resident_allowed && static_cast<long long>(k_blocks) * bn * BK_BYTES <= RESIDENT_BYTES && m_tiles >= 8;
+			if (resident && !boxes_ok)
+				return (bn == 256) ? launch<0, 256, true>(ctx, stream, map_a, map_b, map_c, map_d, p, c->sm_count) : launch<0, 128, true>(ctx, stream,
+								map_a, map_b, map_c, map_d, p, c->sm_count);
 			if (resident)
-				return (bn == 256) ? launch<0, 256, true>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128, true>(ctx, stream, map_a, map_b,
-								p, c->sm_count);
-			return (bn == 256) ? launch<0, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<0, 128>(ctx, stream, map_a, map_b, p,
-							c->sm_count);
+			{
+				const uint64_t dims[3] = { static_cast<uint64_t>(g.N), static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.batch) };
+				const uint32_t box[3] = { 32, 32, 1 };
+				const uint64_t strides_d[2] = { static_cast<uint64_t>(g.ldd) * 2, g.batch == 1 ? static_cast<uint64_t>(g.ldd) * 2 * g.M
+						: static_cast<uint64_t>(g.stride_d) * 2 };
+				if (!encode_tensor_map(ctx, &map_d, dt, 3, g.D, dims, strides_d, box, CU_TENSOR_MAP_SWIZZLE_64B))
+					return false;
+				if (use_c)
+				{
+					const uint64_t strides_c[2] = { static_cast<uint64_t>(g.ldc) * 2, g.batch == 1 ? static_cast<uint64_t>(g.ldc) * 2 * g.M
+							: static_cast<uint64_t>(g.stride_c) * 2 };
+					if (!encode_tensor_map(ctx, &map_c, dt, 3, g.C, dims, strides_c, box, CU_TENSOR_MAP_SWIZZLE_64B))
+						return false;
+				}
+				return (bn == 256) ? launch<0, 256, true, true>(ctx, stream, map_a, map_b, map_c, map_d, p, c->sm_count) : launch<0, 128, true, true>(ctx,
+								stream, map_a, map_b, map_c, map_d, p, c->sm_count);
+			}
+			return (bn == 256) ? launch<0, 256>(ctx, stream, map_a, map_b, map_c, map_d, p, c->sm_count) : launch<0, 128>(ctx, stream, map_a, map_b,
+							map_c, map_d, p, c->sm_count);
 		}
 		else
-			return (bn == 256) ? launch<1, 256>(ctx, stream, map_a, map_b, p, c->sm_count) : launch<1, 128>(ctx, stream, map_a, map_b, p,
+			return (bn == 256) ? launch<1, 256>(ctx, stream, map_a, map_b, map_c, map_d, p, c->sm_count) : launch<1, 128>(ctx, stream, map_a, map_b, map_c, map_d, p,
 							c->sm_count);
 	}
 } /* namespace mb200 */

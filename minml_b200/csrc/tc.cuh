@@ -130,6 +130,23 @@ namespace mb200
 					"cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
 					:: "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 		}
+		/* Store of a shared-memory box to global memory through a tensor map; completion is tracked by the thread's bulk groups. */
+		__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2)
+		{
+			asm volatile(
+					"cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+					:: "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+		}
+		__device__ __forceinline__ void bulk_commit_group()
+		{
+			asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+		}
+		/* Returns once all but the newest PENDING bulk groups of this thread have finished READING shared memory. */
+		template<int PENDING>
+		__device__ __forceinline__ void bulk_wait_group_read()
+		{
+			asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(PENDING) : "memory");
+		}
 		/* Makes generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05.mma operand reads). */
 		__device__ __forceinline__ void fence_proxy_async_smem()
 		{

@@ -117,7 +117,11 @@ def test_int8_k_not_multiple_of_16_uses_generic_engine(ctx, oracle):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
-@pytest.mark.parametrize("shape", [(23, 29, 37), (450, 128, 64), (225, 3, 128), (400, 1, 256)])
+@pytest.mark.parametrize("shape", [(23, 29, 37), (450, 128, 64), (225, 3, 128), (400, 1, 256),
+                                   # many rows and a short K: in fp16 the weight-resident variant, whose epilogue moves C and D as boxes
+                                   # through tensor maps -- column tails (200 = 6 x 32 + 8, 72, 264 = 256 + 8), row tails, 128- and
+                                   # 256-wide tiles; 100 columns make rows that do not start on 16 bytes (the general variant)
+                                   (1100, 200, 256), (1333, 72, 192), (1024, 264, 256), (2000, 100, 128)])
 @pytest.mark.parametrize("act", ["linear", "relu", "sigmoid"])
 def test_gemm_ex_bias_residual_activation(ctx, oracle, dtype, shape, act):
     # D = act(alpha * A B^T + beta * C + bias): 1x1 convolutions and dense layers (src/core/math.cpp:682-702)
