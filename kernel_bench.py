@@ -108,6 +108,12 @@ def main():
     add("winograd_input_transform", lambda: B.winogradInputTransform(ctx, wt.shape, x, v, 4), act_bytes + mat_bytes)
     add("gemm_batched 36 x [tiles,c] x [c,c]^T", lambda: B.gemmBatched(ctx, "n", v, "t", conv.transformed, m), 2 * mat_bytes + 36 * c * c * 2,
         2.0 * 36 * tiles * c * c)
+    # the two products of the backward pass, whose operands the tensor core reads MN-major: dV = dM x U ('n','n'), dU = dM^T x V ('t','n')
+    du = torch.empty((36, c, c), device="cuda", dtype=f16)
+    add("gemm_batched 36 x [tiles,c] x [c,c] ('n','n', backward)", lambda: B.gemmBatched(ctx, "n", m, "n", conv.transformed, v),
+        2 * mat_bytes + 36 * c * c * 2, 2.0 * 36 * tiles * c * c)
+    add("gemm_batched 36 x [tiles,c]^T x [tiles,c] ('t','n', weight update)", lambda: B.gemmBatched(ctx, "t", m, "n", v, du),
+        2 * mat_bytes + 36 * c * c * 2, 2.0 * 36 * tiles * c * c)
     add("winograd_output_transform (+bias+residual+relu)", lambda: B.winogradOutputTransform(ctx, wt.shape, m, y, conv.bias, res, "relu", 4),
         mat_bytes + 2 * act_bytes)
     add("winograd_weight_transform", lambda: B.winogradWeightTransform(ctx, conv.weights, conv.transformed, False, 4), (9 + 36) * c * c * 2)

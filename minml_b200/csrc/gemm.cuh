@@ -15,6 +15,9 @@ namespace mb200
 			int kind = 0; // 0: fp16 operands, fp32 accumulation; 1: int8 operands, int32 accumulation; 2: fp32 operands read as tf32;
 			// 3: fp32 operands split into two tf32 terms each (three tensor-core products, close to fp32 accuracy)
 			int M = 0, N = 0, K = 0, batch = 1;
+			// Storage of the operands: A as [M, K] (false) or [K, M] (true: 't' on A); B as [N, K] (false: 't' on B) or [K, N] (true).
+			// The transposed forms reach the tensor core as MN-major operands (kinds 0, 2, 3).
+			bool a_mn = false, b_mn = false;
 			const void *A = nullptr;
 			int lda = 0;
 			long long stride_a = 0;
@@ -43,6 +46,7 @@ namespace mb200
 	struct GemmTcParams
 	{
 			int M, N, K, batch;
+			int a_mn, b_mn;
 			int a_broadcast, b_broadcast;
 			void *D;
 			int ldd;

@@ -96,7 +96,10 @@ namespace
 		static const bool fp32_simt = std::getenv("MINML_B200_FP32_SIMT") != nullptr && std::getenv("MINML_B200_FP32_SIMT")[0] == '1';
 		const bool fp32 = A.dtype == DTYPE_FLOAT32 && D.dtype == DTYPE_FLOAT32;
 		const bool tf32 = fp32 && get(ctx)->allow_tf32;
-		if (!ta && tb && (A.dtype == DTYPE_FLOAT16 || A.dtype == DTYPE_INT8 || tf32 || (fp32 && !fp32_simt)))
+		// the tensor-core engine takes every transposition of fp16 and fp32 operands ('t' on A and 'n' on B as MN-major operands); int8
+		// products only in the 'n','t' form
+		if ((A.dtype == DTYPE_FLOAT16 || (A.dtype == DTYPE_INT8 && !ta && tb) || tf32 || (fp32 && !fp32_simt)) && A.dtype == B.dtype
+				&& (D.dtype == DTYPE_FLOAT16 || D.dtype == DTYPE_FLOAT32 || D.dtype == DTYPE_INT32))
 		{
 			GemmTcProblem g;
 			g.kind = (A.dtype == DTYPE_FLOAT16) ? 0 : (A.dtype == DTYPE_INT8 ? 1 : (tf32 ? 2 : 3));
@@ -104,6 +107,8 @@ namespace
 			g.N = cols;
 			g.K = K;
 			g.batch = batch;
+			g.a_mn = ta;
+			g.b_mn = !tb;
 			g.A = A.data;
 			g.lda = A.cols;
 			g.stride_a = A.batch_stride;

@@ -1,7 +1,7 @@
 /*
  * gemm_simt.cu -- generic CUDA-core GEMM: every transposition, any shape or alignment, fp16 / fp32 / fp64 and
  * int8 -> int32.  It is the engine behind the GEMM entry points whenever the tensor-core kernel does not apply
- * (fp32 and fp64 data, 'n','n' / 't','n' / 't','t' products, operands that TMA cannot address).  The reference
+ * (fp64 data, transposed int8 products, operands that TMA cannot address: rows that do not start on 16 bytes).  The reference
  * sends all of these to cuBLAS (src/backend/cuda/gemms.cpp:99-407).
  *
  * 64 x 64 output tile per CTA, 16 x 16 threads with a 4 x 4 register tile each, K staged through shared memory
@@ -142,8 +142,8 @@ namespace mb200
 
 		/* fp32 x fp32 -> fp32 on the CUDA cores: 128 x 128 output tile per CTA, K in steps of 16, 8 x 8 outputs per thread read from
 		 * shared memory as 16-byte vectors, the next K step prefetched into registers while the current one is multiplied.  The generic
-		 * kernel above covers every other type and any alignment; this one serves the fp32 products of a host that keeps TF32 off
-		 * (Winograd products 'n','t' of fp32 networks, and the 'n','n' / 't','n' products of the backward pass).
+		 * kernel above covers every other type and any alignment; this one serves fp32 products whose rows are 16-byte aligned when
+		 * the tensor-core engine is switched off for them (MINML_B200_FP32_SIMT=1) or cannot address them.
 		 * TA: A is stored [K, rows] (op 't'); TB: B is stored [cols, K] (op 't').  Needs 16-byte aligned operands and leading
 		 * dimensions that are multiples of 4. */
 		constexpr int FM = 128, FN = 128, FK = 16;

@@ -1,10 +1,11 @@
 /*
- * gemm_tc.cu -- the tensor-core GEMM of the backend: D[b] = epilogue(alpha * A[b] * B[b]^T + beta * C[b]).
+ * gemm_tc.cu -- the tensor-core GEMM of the backend: D[b] = epilogue(alpha * op(A[b]) * op(B[b]) + beta * C[b]).
  *
  * Serves every 'n','t' matrix product of the inference path (reference call sites: the 36 batched Winograd
  * products of Conv2D::forward, src/layers/Conv2D.cpp:371; 1x1 convolutions and dense layers through gemm_ex,
- * src/core/math.cpp:682-702; the int8 -> int32 product of the quantised path, src/layers/Conv2D.cpp:232),
- * which the reference sends to cuBLAS (src/backend/cuda/gemms.cpp:99-259).
+ * src/core/math.cpp:682-702; the int8 -> int32 product of the quantised path, src/layers/Conv2D.cpp:232) and,
+ * for fp16 and fp32 operands, the other transpositions (the 'n','n' and 't','n' products of Conv2D::backward,
+ * src/layers/Conv2D.cpp:383-448), which the reference sends to cuBLAS (src/backend/cuda/gemms.cpp:99-259).
  *
  * Design (one CTA per SM, persistent over output tiles of 128 x BN):
  *   warp 0      TMA producer: A and B tiles (128 bytes of K per row, 128B swizzle) into a ring of shared-memory stages
@@ -13,7 +14,12 @@
  *               fp32 / s32 accumulators, alpha/beta/bias/activation or requantisation.  fp16 results (and the fp16 C operand)
  *               are staged through shared memory so that one global access covers 8 rows x 64 contiguous bytes.  Two
  *               accumulator buffers in tensor memory let the epilogue of tile i overlap the main loop of tile i+1.
- * Both operands are K-major (row-major A[M,K] and B[N,K]); K tails and M/N tails are zero-filled by TMA.
+ * An operand stored [rows, K] ('n' on A, 't' on B) is K-major for the tensor core; one stored [K, rows] ('t' on A, 'n' on B) is
+ * fetched in boxes of [K slice x 128 bytes of rows] and read as an MN-major operand (descriptor strides and, for 32-bit
+ * elements, the swizzle in 32-byte pieces: make_desc_mn_sw128 in tc.cuh).  8-bit operands are K-major only.  K tails and M/N
+ * tails are zero-filled by TMA.  Measured on the 36 batched products of a 256-channel layer over 25 600 tiles, fp16:
+ * 'n','t' 0.159 ms, 'n','n' 0.166 ms, 't','n' 0.168 ms (0.87 - 0.92 of the copy bandwidth; the CUDA-core engine that served the
+ * transposed forms before reached 41 TFLOP/s against 720 here).
  */
 #include "common.cuh"
 #include "tc.cuh"
@@ -173,7 +179,8 @@ namespace mb200
 			const int m_tiles = (p.M + BM - 1) / BM;
 			const int n_tiles = (p.N + BN - 1) / BN;
 			const long long total_tiles = static_cast<long long>(m_tiles) * n_tiles * p.batch;
-			const int elems_per_kblock = (KIND == 0) ? 64 : (KIND == 1 ? 128 : 32); // 128 bytes of K per row (fp32 for KIND 2 and 3)
+			constexpr int ES = (KIND == 0) ? 2 : (KIND == 1 ? 1 : 4); // operand element size
+			const int elems_per_kblock = 128 / ES; // 128 bytes of K per row (or, MN-major, 128 bytes of rows per K index)
 			const int k_blocks = (p.K + elems_per_kblock - 1) / elems_per_kblock;
 			// Which tiles this CTA computes: every gridDim-th one, or (RES) a contiguous range, so that consecutive tiles share weights.
 			const long long per_cta = (total_tiles + gridDim.x - 1) / gridDim.x;
@@ -309,8 +316,25 @@ namespace mb200
 							const uint32_t full = smem_u32(&bars.full[s]);
 							mbar_arrive_expect_tx(full, T::stage_bytes);
 							const uint32_t dst_a = smem_base + s * T::stage_bytes;
-							tma_load_3d(dst_a, &map_a, full, kb * elems_per_kblock, mt * BM, p.a_broadcast ? 0 : b);
-							if (!RES)
+							// K-major operand: one box of [rows x 128 bytes of K]; MN-major operand (stored [K, rows]): one box of
+							// [K slice x 128 bytes of rows] per 128 bytes of rows, one after the other
+							if (!RES && p.a_mn)
+							{
+#pragma unroll
+								for (int j = 0; j < BM * ES / 128; j++)
+									tma_load_3d(dst_a + j * (T::a_bytes / (BM * ES / 128)), &map_a, full, mt * BM + j * elems_per_kblock, kb * elems_per_kblock,
+											p.a_broadcast ? 0 : b);
+							}
+							else
+								tma_load_3d(dst_a, &map_a, full, kb * elems_per_kblock, mt * BM, p.a_broadcast ? 0 : b);
+							if (!RES && p.b_mn)
+							{
+#pragma unroll
+								for (int j = 0; j < BN * ES / 128; j++)
+									tma_load_3d(dst_a + T::a_bytes + j * (T::b_bytes / (BN * ES / 128)), &map_b, full, nt * BN + j * elems_per_kblock,
+											kb * elems_per_kblock, p.b_broadcast ? 0 : b);
+							}
+							else if (!RES)
 								tma_load_3d(dst_a + T::a_bytes, &map_b, full, kb * elems_per_kblock, nt * BN, p.b_broadcast ? 0 : b);
 						}
 					}
@@ -321,7 +345,12 @@ namespace mb200
 			{ /* ------------------------------------------- MMA issuer */
 				if (elect_one())
 				{
-					const uint32_t idesc = (KIND == 0) ? make_idesc_f16(BN) : (KIND == 1 ? make_idesc_i8(BN) : make_idesc_tf32(BN));
+					const uint32_t idesc = ((KIND == 0) ? make_idesc_f16(BN) : (KIND == 1 ? make_idesc_i8(BN) : make_idesc_tf32(BN)))
+							| (p.a_mn ? (1u << 15) : 0u) | (p.b_mn ? (1u << 16) : 0u);
+					// descriptor step per instruction (in 16-byte units): 32 bytes along K for a K-major operand, one instruction's K indices
+					// (16 fp16 or 8 fp32) times 128 bytes for an MN-major one
+					const uint32_t step_a = p.a_mn ? (32 / ES) * 128 / 16 : 2, step_b = p.b_mn ? (32 / ES) * 128 / 16 : 2;
+					const uint32_t block_a = T::a_bytes / (BM * ES / 128), block_b = T::b_bytes / (BN * ES / 128);
 					uint64_t *const ready = T::split ? bars.split : bars.full; // what the tensor core may read
 					uint32_t it = 0;
 					uint32_t local_tile = 0;
@@ -365,22 +394,22 @@ namespace mb200
 								fence_proxy_async_smem(); // the hi and lo tiles were plain stores of the split warps
 							const uint32_t addr_a = smem_base + s * T::stage_bytes;
 							const uint32_t addr_b = RES ? smem_base + T::resident_offset + kb * T::b_bytes : addr_a + T::a_bytes;
-							const uint64_t desc_a = make_desc_k_sw128(addr_a);
-							const uint64_t desc_b = make_desc_k_sw128(addr_b);
+							const uint64_t desc_a = p.a_mn ? make_desc_mn_sw128(addr_a, block_a, KIND >= 2) : make_desc_k_sw128(addr_a);
+							const uint64_t desc_b = p.b_mn ? make_desc_mn_sw128(addr_b, block_b, KIND >= 2) : make_desc_k_sw128(addr_b);
 #pragma unroll
-							for (int k = 0; k < 4; k++) // 4 x 32 bytes of K per stage; +2 in descriptor units of 16 bytes
-								mma_ss<KIND>(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+							for (int k = 0; k < 4; k++) // 4 instructions per stage: 32 bytes of K each
+								mma_ss<KIND>(tmem_d, desc_a + step_a * k, desc_b + step_b * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
 							if (T::split)
 							{
 								const uint32_t lo = smem_base + T::lo_offset + (it % T::lo_ring) * T::operand_bytes;
-								const uint64_t lo_a = make_desc_k_sw128(lo);
-								const uint64_t lo_b = make_desc_k_sw128(lo + BM * BK_BYTES);
+								const uint64_t lo_a = p.a_mn ? make_desc_mn_sw128(lo, block_a, KIND >= 2) : make_desc_k_sw128(lo);
+								const uint64_t lo_b = p.b_mn ? make_desc_mn_sw128(lo + BM * BK_BYTES, block_b, KIND >= 2) : make_desc_k_sw128(lo + BM * BK_BYTES);
 #pragma unroll
 								for (int k = 0; k < 4; k++)
-									mma_ss<KIND>(tmem_d, desc_a + 2 * k, lo_b + 2 * k, idesc, 1u);
+									mma_ss<KIND>(tmem_d, desc_a + step_a * k, lo_b + step_b * k, idesc, 1u);
 #pragma unroll
 								for (int k = 0; k < 4; k++)
-									mma_ss<KIND>(tmem_d, lo_a + 2 * k, desc_b + 2 * k, idesc, 1u);
+									mma_ss<KIND>(tmem_d, lo_a + step_a * k, desc_b + step_b * k, idesc, 1u);
 								mma_commit(smem_u32(&bars.lo_empty[it % T::lo_ring]));
 							}
 							mma_commit(smem_u32(&bars.empty[s]));
@@ -874,6 +903,8 @@ namespace mb200
 	{
 		if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0)
 			return false;
+		if (g.kind == 1 && (g.a_mn || g.b_mn))
+			return false; // 8-bit operands are K-major only
 		const int elem = (g.kind == 0) ? 2 : (g.kind == 1 ? 1 : 4);
 		// TMA: 16-byte aligned bases and row strides
 		if (!aligned_to(g.A, 16) || !aligned_to(g.B, 16))
@@ -912,30 +943,28 @@ namespace mb200
 		const bool a_bcast = (g.batch > 1 && g.stride_a == 0);
 		const bool b_bcast = (g.batch > 1 && g.stride_b == 0);
 		CUtensorMap map_a, map_b;
+		// an operand stored [rows, K] is fetched in boxes of [rows of the tile x 128 bytes of K]; one stored [K, rows] (MN-major for the
+		// tensor core) in boxes of [one K slice x 128 bytes of rows]
+		auto encode_operand = [&](CUtensorMap *map, const void *base, bool mn, int rows, int tile_rows, int ld, long long stride, bool bcast) -> bool
 		{
-			const uint64_t dims[3] = { static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.M), static_cast<uint64_t>(
-					(a_bcast || g.batch == 1) ? 1 : g.batch) };
-			const uint64_t strides[2] = { static_cast<uint64_t>(g.lda) * elem, (a_bcast || g.batch == 1) ? static_cast<uint64_t>(g.lda) * elem
-					* g.M : static_cast<uint64_t>(g.stride_a) * elem };
-			const uint32_t box[3] = { box_k, static_cast<uint32_t>(BM), 1 };
-			if (!encode_tensor_map(ctx, &map_a, dt, 3, g.A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-				return false;
-		}
-		{
-			const uint64_t dims[3] = { static_cast<uint64_t>(g.K), static_cast<uint64_t>(g.N), static_cast<uint64_t>(
-					(b_bcast || g.batch == 1) ? 1 : g.batch) };
-			const uint64_t strides[2] = { static_cast<uint64_t>(g.ldb) * elem, (b_bcast || g.batch == 1) ? static_cast<uint64_t>(g.ldb) * elem
-					* g.N : static_cast<uint64_t>(g.stride_b) * elem };
-			const uint32_t box[3] = { box_k, static_cast<uint32_t>(bn), 1 };
-			if (!encode_tensor_map(ctx, &map_b, dt, 3, g.B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-				return false;
-		}
+			const uint64_t inner = static_cast<uint64_t>(mn ? rows : g.K), outer = static_cast<uint64_t>(mn ? g.K : rows);
+			const uint64_t dims[3] = { inner, outer, static_cast<uint64_t>((bcast || g.batch == 1) ? 1 : g.batch) };
+			const uint64_t strides[2] = { static_cast<uint64_t>(ld) * elem, (bcast || g.batch == 1) ? static_cast<uint64_t>(ld) * elem * outer
+					: static_cast<uint64_t>(stride) * elem };
+			const uint32_t box[3] = { box_k, mn ? box_k : static_cast<uint32_t>(tile_rows), 1 };
+			// 32-bit elements in this order need the swizzle in 32-byte pieces
+			return encode_tensor_map(ctx, map, dt, 3, base, dims, strides, box, (mn && elem == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+		};
+		if (!encode_operand(&map_a, g.A, g.a_mn, g.M, BM, g.lda, g.stride_a, a_bcast) || !encode_operand(&map_b, g.B, g.b_mn, g.N, bn, g.ldb, g.stride_b, b_bcast))
+			return false;
 		GemmTcParams p;
 		std::memset(&p, 0, sizeof(p));
 		p.M = g.M;
 		p.N = g.N;
 		p.K = g.K;
 		p.batch = g.batch;
+		p.a_mn = g.a_mn ? 1 : 0;
+		p.b_mn = g.b_mn ? 1 : 0;
 		p.a_broadcast = a_bcast ? 1 : 0;
 		p.b_broadcast = b_bcast ? 1 : 0;
 		p.D = g.D;
@@ -980,7 +1009,7 @@ namespace mb200
 			const bool use_c = g.beta != 0.0f && g.C != nullptr;
 			const bool boxes_ok = g.out_dtype == DTYPE_FLOAT16 && aligned_to(g.D, 16) && g.ldd % 8 == 0 && (g.batch == 1 || g.stride_d % 8 == 0)
 					&& (!use_c || (aligned_to(g.C, 16) && g.ldc % 8 == 0 && (g.batch == 1 || g.stride_c % 8 == 0)));
-			const bool resident = resident_allowed && static_cast<long long>(k_blocks) * bn * BK_BYTES <= RESIDENT_BYTES && m_tiles >= 8;
+			const bool resident = resident_allowed && !g.a_mn && !g.b_mn && static_cast<long long>(k_blocks) * bn * BK_BYTES <= RESIDENT_BYTES && m_tiles >= 8;
 			if (resident && !boxes_ok)
 				return (bn == 256) ? launch<0, 256, true>(ctx, stream, map_a, map_b, map_c, map_d, p, c->sm_count) : launch<0, 128, true>(ctx, stream,
 								map_a, map_b, map_c, map_d, p, c->sm_count);

@@ -222,7 +222,22 @@ namespace mb200
 			desc |= static_cast<uint64_t>(2) << 61;
 			return desc;
 		}
-		/* Instruction descriptors: D fp32 <- fp16 x fp16, and D s32 <- s8 x s8; both operands K-major, M = 128. */
+		/* MN-major operand, 128-byte swizzle: rows of 128 bytes along M (or N), one row per K index; 8 K indices form a 1024-byte group
+		 * (stride byte offset); `block_bytes` (leading byte offset) separates the blocks of 128 bytes along M (or N).
+		 * `atom_32b`: 32-bit elements in this order: the swizzle moves 32-byte pieces and repeats every 4 rows (the copy engine writes it
+		 * with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), so a group is 4 K indices, 512 bytes (found by trying the combinations of layout
+		 * code, copy swizzle and stride against an exact integer product: this is the one that gives it). */
+		__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t block_bytes, bool atom_32b = false)
+		{
+			uint64_t desc = 0;
+			desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+			desc |= static_cast<uint64_t>(block_bytes >> 4) << 16;
+			desc |= static_cast<uint64_t>((atom_32b ? 512 : 1024) >> 4) << 32;
+			desc |= static_cast<uint64_t>(1) << 46;
+			desc |= static_cast<uint64_t>(atom_32b ? 1 : 2) << 61;
+			return desc;
+		}
+		/* Instruction descriptors: D fp32 <- fp16 x fp16, and D s32 <- s8 x s8; M = 128; operands K-major unless bit 15 (A) / 16 (B) is set. */
 		__host__ __device__ constexpr uint32_t make_idesc_f16(int n)
 		{
 			return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);

@@ -36,6 +36,46 @@ def test_gemm_all_transpositions(ctx, oracle, dtype, ops):
     assert torch.equal(cd, cd2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("ops", [("n", "n"), ("t", "n"), ("t", "t"), ("n", "t")])
+@pytest.mark.parametrize("shape", [(256, 256, 256), (136, 264, 200), (1000, 72, 136), (64, 520, 96), (8, 8, 8)])
+def test_every_transposition_on_the_tensor_cores(ctx, oracle, dtype, ops, shape):
+    """'t' on A and 'n' on B reach the tensor core as MN-major operands (the backward products of the training path,
+    src/backend/cuda/gemms.cpp:183-259): row counts that are multiples of 8 (16-byte rows in either storage order), ragged against
+    the 128 x 256 tile and the 64-element K slice in every dimension; batched with beta; fp32 both as split operands and as TF32."""
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(m + 3 * n + 7 * k + ord(ops[0]) + 2 * ord(ops[1]))
+    batch = 3
+    a = r.uniform(-1, 1, (batch, k, m) if ops[0] == "t" else (batch, m, k)).astype(np.float32)
+    b = r.uniform(-1, 1, (batch, n, k) if ops[1] == "t" else (batch, k, n)).astype(np.float32)
+    c = r.uniform(-1, 1, (batch, m, n)).astype(np.float32)
+    if dtype == torch.float16:
+        a, b, c = [t.astype(np.float16).astype(np.float32) for t in (a, b, c)]
+    before = B.launch_count()
+    for tf32 in ((False, True) if dtype == torch.float32 else (False,)):
+        ctx.enable_tf32(tf32)
+        try:
+            cd = dev(c, dtype)
+            B.gemmBatched(ctx, ops[0], dev(a, dtype), ops[1], dev(b, dtype), cd, 0.5, 0.25)
+            ctx.synchronize()
+            c1 = dev(c[0], dtype)
+            B.gemm(ctx, ops[0], dev(a[0], dtype), ops[1], dev(b[0], dtype), c1, 0.5, 0.25)
+            ctx.synchronize()
+        finally:
+            ctx.enable_tf32(False)
+        for i in range(batch):
+            want = oracle.gemm(ops[0], a[i], ops[1], b[i], c[i], 0.5, 0.25)
+            if dtype == torch.float16:
+                assert max_rel_err(host(cd)[i], want) <= FP16_REL
+            elif tf32:
+                assert max_rel_err(host(cd)[i], want) <= 2e-3
+            else:
+                assert mean_abs_diff(host(cd)[i], want) <= FP32_TOL
+        assert torch.equal(c1, cd[0])
+    assert B.launch_count() - before == (4 if dtype == torch.float32 else 2)  # one kernel per product: nothing ran as copy + generic engine + second pass
+
+
 # (M, N, K): aligned, ragged in every dimension, K not a multiple of the 64-element stage, N beyond one tile, tiny
 TC_SHAPES = [(256, 256, 256), (300, 72, 40), (129, 130, 72), (1000, 384, 136), (5, 3, 8), (128, 1, 128), (64, 3, 256), (4096, 128, 128)]
 
