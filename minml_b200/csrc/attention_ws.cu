@@ -368,7 +368,7 @@ namespace mb200
 						}
 						loaded_head = head;
 						mbar_arrive(smem_u32(&bar.table_ready));
-						ok = mbar_wait_sleeping(smem_u32(&bar.table_ready), table_count & 1u, abort_flag, 20u);
+						ok = mbar_wait_warp(smem_u32(&bar.table_ready), table_count & 1u, abort_flag, 20u);
 						table_count++;
 						if (!ok)
 							break;
@@ -376,7 +376,7 @@ namespace mb200
 					for (int qt = 0; qt < q_tiles; qt++, tile_count++)
 					{
 						WS_TRACE(0);
-						ok = mbar_wait_sleeping(smem_u32(&bar.s_full), tile_count & 1u, abort_flag, 20u);
+						ok = mbar_wait_warp(smem_u32(&bar.s_full), tile_count & 1u, abort_flag, 20u);
 						if (!ok)
 							break;
 						tcgen05_fence_after();
@@ -404,7 +404,7 @@ namespace mb200
 						{
 							sh.row_max[g][half][row_in_tile] = my_max;
 							mbar_arrive(smem_u32(&bar.exchange));
-							ok = mbar_wait_sleeping(smem_u32(&bar.exchange), tile_count & 1u, abort_flag, 20u);
+							ok = mbar_wait_warp(smem_u32(&bar.exchange), tile_count & 1u, abort_flag, 20u);
 							if (!ok)
 								break;
 #pragma unroll
@@ -415,7 +415,7 @@ namespace mb200
 							const uint32_t awaited = (g == 0) ? tile_count - 1u : tile_count; // which of the other group's tiles (0 - 1 wraps: none)
 							if (awaited < other_tiles)
 							{
-								ok = mbar_wait_sleeping(smem_u32(&other.pass2_done), awaited & 1u, abort_flag, 20u);
+								ok = mbar_wait_warp(smem_u32(&other.pass2_done), awaited & 1u, abort_flag, 20u);
 								if (!ok)
 									break;
 							}
@@ -440,7 +440,7 @@ namespace mb200
 						if (qt == 0 && keys > tokens)
 						{ // V's rows beyond the last token belong to the next batch item (or are the copy's zero fill): cleared, so that
 						  // nothing of them reaches this item's output even if they hold infinities
-							ok = mbar_wait_sleeping(smem_u32(&bar.v_full), item_count & 1u, abort_flag, 20u);
+							ok = mbar_wait_warp(smem_u32(&bar.v_full), item_count & 1u, abort_flag, 20u);
 							if (!ok)
 								break;
 							for (int i = gt; i < (keys - tokens) * 4; i += GT)
@@ -451,7 +451,7 @@ namespace mb200
 						mbar_arrive(smem_u32(&bar.p_full));
 						WS_TRACE(4);
 
-						ok = mbar_wait_sleeping(smem_u32(&bar.o_full), tile_count & 1u, abort_flag, 20u);
+						ok = mbar_wait_warp(smem_u32(&bar.o_full), tile_count & 1u, abort_flag, 20u);
 						if (!ok)
 							break;
 						tcgen05_fence_after();

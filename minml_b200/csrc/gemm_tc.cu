@@ -517,7 +517,7 @@ namespace mb200
 					}
 					const uint32_t acc = local_tile & 1u;
 					const uint32_t acc_parity = (local_tile >> 1) & 1u;
-					if (!mbar_wait_sleeping(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag, 20u))
+					if (!mbar_wait_warp(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag, 20u))
 						break;
 					tcgen05_fence_after();
 					const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + col_part * (BN / 2);
@@ -562,7 +562,7 @@ namespace mb200
 							v[j] = __uint_as_float(ri[j]) * p.alpha;
 						if (use_c)
 						{
-							if (!mbar_wait_sleeping(smem_u32(&bars.c_full[e][n % 3]), (n / 3) & 1u, abort_flag, 20u))
+							if (!mbar_wait_warp(smem_u32(&bars.c_full[e][n % 3]), (n / 3) & 1u, abort_flag, 20u))
 							{
 								ok = false;
 								break;

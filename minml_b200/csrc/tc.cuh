@@ -113,6 +113,13 @@ namespace mb200
 			return false;
 		}
 
+		/* The same for a whole warp, with an outcome all its lanes share: what follows such a wait are warp-wide tensor-memory
+		 * instructions, which a warp split by a timeout on some of its lanes must not reach. */
+		__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t sleep_ns)
+		{
+			return __all_sync(0xFFFFFFFFu, mbar_wait_sleeping(bar, parity, abort_flag, sleep_ns) ? 1 : 0) != 0;
+		}
+
 		/* ---------------------------------------------------------------- TMA */
 		__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
 		{
