@@ -188,6 +188,22 @@ def test_gemm_ex_bias_residual_activation(ctx, oracle, dtype, shape, act):
             assert mean_abs_diff(host(d), want) <= FP32_TOL
 
 
+@pytest.mark.parametrize("shape", [(1100, 200, 256), (2048, 256, 128), (1333, 72, 192)])
+def test_weight_resident_variant_in_place(ctx, oracle, shape):
+    """C = alpha A B^T + beta C with C read and written in place, on shapes that take the weight-resident variant: its epilogue
+    fetches the box of C for the next chunk while the box of D of the current one is on its way out."""
+    from minml_b200 import backend as B
+    m, n, k = shape
+    r = np.random.default_rng(m + n + k)
+    a = r.uniform(-1, 1, (m, k)).astype(np.float16).astype(np.float32)
+    b = (r.standard_normal((n, k)) * 0.1).astype(np.float16).astype(np.float32)
+    c = r.uniform(-1, 1, (m, n)).astype(np.float16).astype(np.float32)
+    cd = dev(c, torch.float16)
+    B.gemm(ctx, "n", dev(a, torch.float16), "t", dev(b, torch.float16), cd, 0.75, 0.5)
+    ctx.synchronize()
+    assert max_rel_err(host(cd), oracle.gemm("n", a, "t", b, c, 0.75, 0.5)) <= FP16_REL
+
+
 def test_shape_mismatch_is_reported(ctx):
     from minml_b200 import backend as B
     with pytest.raises(B.BackendError):

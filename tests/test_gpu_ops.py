@@ -286,6 +286,8 @@ def test_kernel_bench_tool_runs_and_reports_every_kernel():
     (40, 15, 15, 8, False, None),  # 320 (head, item) pairs: more than one per CTA of the persistent kernel, both of its groups at work
     (170, 5, 6, 2, True, None),    # 340 pairs of one query tile each, q = k
     (37, 12, 13, 5, False, None),  # 185 pairs of 156 tokens (160 keys: a last chunk of 32), ranges of one and two pairs per CTA
+    (3, 5, 6, 2, False, 15),       # a table built for a 15 x 15 board on a 5 x 6 one: the kernel copies the window of offsets it can reach
+    (2, 15, 15, 8, False, 20),     # the same on the benchmark's board (table of 39 x 39 entries)
 ])
 def test_multi_head_attention_tcgen05_shapes(ctx, oracle, cfg):
     """Head dimension 32 in fp16 -- the shapes that run on the tcgen05 kernel (scores in tensor memory) -- against the oracle, with
