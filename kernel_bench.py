@@ -178,6 +178,8 @@ def main():
     qconv = L.QuantizedConv2D(ctx, qw, np.full(c, 1e-4, np.float32), np.zeros(c, np.float32), (0.02, 0.0), (0.05, 0.0), "relu", torch.int8)
     qws = L.Workspace()
     qws.reserve(qconv.workspace_bytes(xq.shape))
+    add("conv3x3 fused (int8, requantise+relu, no residual)", lambda: qconv.forward([xq], yq, qws), 2 * rows * c + 9 * c * c,
+        2.0 * rows * 9 * c * c)
     add("conv3x3 fused (int8, requantise+residual+relu)", lambda: qconv.forward([xq, extq], yq, qws, (0.03, 0.0)), 3 * rows * c + 9 * c * c,
         2.0 * rows * 9 * c * c, note="tensor_frac is against the bf16 peak; the int8 peak is twice that")
     ctx.set_fusion(False)

@@ -246,6 +246,16 @@ namespace mb200
 				tmem_alloc(smem_u32(&bars.tmem_base), C::tmem_columns);
 				tmem_relinquish();
 			}
+			// int8: per-channel scales and shifts in shared memory for the life of the CTA instead of sixteen 16-byte global reads per lane and
+			// 32-column chunk (measured 1.5 - 3.5 %: 0.0461 -> 0.0445 ms on 512 x 20 x 20 x 128, 0.195 -> 0.192 ms on 1024 x 20 x 20 x 256)
+			__shared__ __align__(16) float qs_s[KIND == 1 ? 512 : 4], qh_s[KIND == 1 ? 512 : 4];
+			const bool q_staged = KIND == 1 && p.scales != nullptr && p.shifts != nullptr && p.cout <= 512;
+			if (q_staged)
+				for (int i = threadIdx.x; i < p.cout; i += blockDim.x)
+				{
+					qs_s[i] = p.scales[i];
+					qh_s[i] = p.shifts[i];
+				}
 			tcgen05_fence_before();
 			if (CTAS == 2)
 				cluster_sync(); // the peer's barriers exist before anything signals them
@@ -548,8 +558,8 @@ namespace mb200
 						   * operation and without fused multiply-adds (epilogue.cuh: requant_real, requant_add_ext, requant_round) */
 							if (!row_ok)
 								continue;
-							const float4 *sp = reinterpret_cast<const float4*>(p.scales + n0);
-							const float4 *hp = reinterpret_cast<const float4*>(p.shifts + n0);
+							const float4 *sp = reinterpret_cast<const float4*>((q_staged ? qs_s : p.scales) + n0);
+							const float4 *hp = reinterpret_cast<const float4*>((q_staged ? qh_s : p.shifts) + n0);
 							const bool relu = p.act == ACTIVATION_RELU;
 							const bool other_act = p.act == ACTIVATION_SIGMOID || p.act == ACTIVATION_TANH;
 							uint32_t packed[8];
