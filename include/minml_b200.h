@@ -266,6 +266,12 @@ const char *mb200_version(void);
  * cuda_synchronize_with_context records the same sticky error a tensor-core kernel whose wait ran out would produce.  The
  * context stays usable.  Nothing in the call can hang. */
 void mb200_selftest_bounded_wait(mlContext_t context, int polls);
+/* Measurement: cycles per tcgen05.mma (kind::f16, M = 128, K = 16, N = n in {16, 32, 64, 128, 256}) when one thread issues 2 000 of
+ * them back to back on one SM from a loop with nothing else in it, A from shared memory (0) or tensor memory (1).  Synchronous;
+ * returns a negative number on error.  What it reads is the slower of the tensor core and the issuing thread: at N = 128 and 256
+ * the figures (64, 128 on a B200) are the tensor core's peak rate; the 46 - 50 cycles at N <= 64 are an upper bound of the
+ * instruction's cost, possibly the issue loop's own. */
+double mb200_probe_mma_cycles(mlContext_t context, int n, int a_in_tensor_memory);
 
 /* No counterpart in the reference.
  * y = act(conv3x3(x, w) + bias + add) by F(4x4,3x3) Winograd, for callers that must never allocate device memory: a

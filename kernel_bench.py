@@ -208,6 +208,12 @@ def main():
                 4 * act_bytes, 4.0 * b * heads * t * t * (c // heads))
         B.set_attention_kernel(0)
 
+    # ---- what one tensor-core instruction costs by N (one SM, 2 000 instructions back to back): the basis of the tile-shape notes
+    if not args.only or "tcgen05.mma" in args.only:
+        cycles = {str(nn): [round(B.lib.mb200_probe_mma_cycles(ctx.handle, nn, a), 1) for a in (0, 1)] for nn in (16, 32, 64, 128, 256)}
+        ctx.check()
+        print(json.dumps({"probe": "tcgen05.mma cycles (kind::f16, M = 128, K = 16) by N: [A in shared memory, A in tensor memory]", "cycles": cycles}), flush=True)
+
     # ---- layers next to the convolution path: batch norm at inference, depthwise 7x7 (fp16 and int8), channel scaling
     avg_var = torch.cat([torch.randn(1, c, device="cuda"), torch.rand(1, c, device="cuda") + 0.5]).contiguous()
     add("batchnorm_inference (+relu)", lambda: B.batchnormInference(ctx, x, y, gamma, beta, avg_var, "relu"), 2 * act_bytes)

@@ -255,6 +255,20 @@ def test_empty_tensors_launch_nothing_and_record_no_error(ctx):
     assert B.launch_count() == before
 
 
+def test_mma_cost_probe(ctx):
+    """The probe behind the tile-shape notes: an N = 256 instruction takes the 128 cycles the peak rate implies, and N = 32 is far from
+    a quarter of N = 128 (there is a floor), whichever memory A comes from."""
+    from minml_b200 import backend as B
+    c256 = B.lib.mb200_probe_mma_cycles(ctx.handle, 256, 0)
+    c128 = B.lib.mb200_probe_mma_cycles(ctx.handle, 128, 1)
+    c32 = B.lib.mb200_probe_mma_cycles(ctx.handle, 32, 1)
+    ctx.check()
+    assert 115.0 <= c256 <= 145.0 and 57.0 <= c128 <= 75.0 and 30.0 <= c32 <= 64.0, (c256, c128, c32)
+    assert B.lib.mb200_probe_mma_cycles(ctx.handle, 48, 0) < 0  # only the five sizes it was built for
+    with pytest.raises(B.BackendError):
+        ctx.check()  # (reported on the context, and cleared by the report)
+
+
 def test_kernel_bench_tool_runs_and_reports_every_kernel():
     """The per-kernel timing tool (python kernel_bench.py) at the smallest configuration: one JSON line per kernel,
     finite positive times, fractions of the peaks in range."""
