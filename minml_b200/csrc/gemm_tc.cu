@@ -107,12 +107,13 @@ namespace mb200
 		 * into shared memory, not HBM, the limit (l1tex 62 % of peak, tensor pipe 30 %).  Here every CTA takes a CONTIGUOUS range of
 		 * tiles ordered (batch, column tile, row tile), keeps the whole [BN, K] weight tile in shared memory for as long as
 		 * consecutive tiles share it, streams only A through the ring, and moves C and D as 32 x 32 boxes through tensor maps (see the
-		 * epilogue below).  What bounds these products on a B200 is then the write path: a kernel that only writes reaches 3.4 TB/s on
-		 * 88 MB and 2.6 TB/s on 30 MB (about half of the copy bandwidth, which counts a read and a write), and in steady state this
-		 * kernel writes its 64 KB of D per tile at 3.3 TB/s chip-wide; start-up (the 128 KB of weights, the first A slices: 3 us) and
-		 * the uneven last tiles make up the rest of a 40 us product.
-		 * Measured, 57 600 rows, K = 256 (before -> after the box epilogue): N = 768 0.043 -> 0.040 ms (its 88 MB of D alone take
-		 * 0.026 ms to write), N = 256 with a residual 0.031 -> 0.025 ms, N = 1024 with ReLU 0.055 -> 0.052 ms; the 36 Winograd products
+		 * epilogue below).  What paces these products is still the epilogue of each SM, not a chip-wide limit: the same product on 135,
+		 * 74 and 37 CTAs takes 0.040, 0.063 and 0.110 ms, i.e. 3.6, 3.1 and 2.9 us per 128 x 256 tile and CTA -- were the memory system the
+		 * limit, half the CTAs would have finished in nearly the same time.  (That a tile's 64 KB of D every 5 000 cycles on 135 SMs
+		 * comes to the 3.3 TB/s a write-only kernel reaches on this GPU is a coincidence that was first read as the cause.)  About a
+		 * fifth of the tile time at full occupancy is contention; the rest is the chain of a 32-column chunk, 1 100 - 1 200 cycles
+		 * against 512 of tensor work.
+		 * Measured, 57 600 rows, K = 256 (before -> after the box epilogue): N = 768 0.043 -> 0.040 ms, N = 256 with a residual 0.031 -> 0.025 ms, N = 1024 with ReLU 0.055 -> 0.052 ms; the 36 Winograd products
 		 * of a 256-channel layer 0.167 -> 0.159 ms with the resident weights alone (0.92 of the copy bandwidth).
 		 */
 		constexpr int RESIDENT_BYTES = 128 * 1024;
@@ -892,7 +893,9 @@ namespace mb200
 				configured = true;
 			}
 			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
-			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+			int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+			if (std::getenv("MINML_B200_GEMM_GRID") != nullptr) // (temporary: experiment)
+				grid = std::min(grid, std::atoi(std::getenv("MINML_B200_GEMM_GRID")));
 			kernel_gemm_tc<KIND, BN, RES, BOX> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, map_c, map_d, p);
 			MB200_COUNT_LAUNCH();
 			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
