@@ -893,9 +893,7 @@ namespace mb200
 				configured = true;
 			}
 			const long long tiles = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
-			int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
-			if (std::getenv("MINML_B200_GEMM_GRID") != nullptr) // (temporary: experiment)
-				grid = std::min(grid, std::atoi(std::getenv("MINML_B200_GEMM_GRID")));
+			const int grid = static_cast<int>(std::min<long long>(tiles, sm_count));
 			kernel_gemm_tc<KIND, BN, RES, BOX> <<<grid, num_threads(KIND), T::smem_bytes, stream>>>(map_a, map_b, map_c, map_d, p);
 			MB200_COUNT_LAUNCH();
 			return check_cuda(ctx, cudaGetLastError(), "gemm_tc launch");
