@@ -279,7 +279,11 @@ def test_kernel_bench_tool_runs_and_reports_every_kernel():
     out = subprocess.run([sys.executable, os.path.join(root, "kernel_bench.py"), "--config", "c1", "--reps", "2"], cwd=root, capture_output=True,
                          text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
-    records = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    lines = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    probes = [r for r in lines if "probe" in r]  # (the tcgen05.mma cost table: one line, no kernel of the path)
+    assert len(probes) == 1 and set(probes[0]["cycles"]) == {"16", "32", "64", "128", "256"}
+    records = [r for r in lines if "kernel" in r]
+    assert len(records) + len(probes) == len(lines)
     names = [r["kernel"] for r in records]
     assert len(records) >= 30 and len(set(names)) == len(names)
     for needle in ("conv3x3 fused (fp16", "conv3x3 fused (int8", "gemm_batched", "multi_head_attention", "depthwise_conv_forward", "rmsnorm"):
