@@ -422,7 +422,7 @@ namespace mb200
 				{
 					const int nt = unit % n_tiles;
 					const uint32_t buf = local_tile & 1u;
-					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), (local_tile >> 1) & 1u, abort_flag))
+					if (!mbar_wait_all_lanes(smem_u32(&bars.tmem_full[buf]), (local_tile >> 1) & 1u, abort_flag))
 						break;
 					tcgen05_fence_after();
 					const int col_begin = col_part * COLS_PER_WARP;

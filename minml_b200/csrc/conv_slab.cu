@@ -220,7 +220,7 @@ namespace mb200
 				{
 					const int image = unit / p.bands_per_image, band = unit % p.bands_per_image;
 					const uint32_t buf = local & 1u;
-					if (!mbar_wait(smem_u32(&bars.tmem_full[buf]), (local >> 1) & 1u, abort_flag))
+					if (!mbar_wait_all_lanes(smem_u32(&bars.tmem_full[buf]), (local >> 1) & 1u, abort_flag))
 						break;
 					tcgen05_fence_after();
 					const int h0 = band * p.band_rows;

@@ -634,7 +634,7 @@ namespace mb200
 					const int nt = w.nt, mt = w.mt, b = w.b;
 					const uint32_t acc = local_tile & 1u;
 					const uint32_t acc_parity = (local_tile >> 1) & 1u;
-					if (!mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag))
+					if (!mbar_wait_all_lanes(smem_u32(&bars.tmem_full[acc]), acc_parity, abort_flag))
 						break;
 					tcgen05_fence_after();
 

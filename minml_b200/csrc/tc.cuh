@@ -113,6 +113,11 @@ namespace mb200
 			return false;
 		}
 
+		/* mbar_wait for a whole warp, with an outcome all its lanes share (see mbar_wait_warp below for why) */
+		__device__ __forceinline__ bool mbar_wait_all_lanes(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+		{
+			return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
+		}
 		/* The same for a whole warp, with an outcome all its lanes share: what follows such a wait are warp-wide tensor-memory
 		 * instructions, which a warp split by a timeout on some of its lanes must not reach. */
 		__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t sleep_ns)
