@@ -113,7 +113,9 @@ namespace mb200
 		 * comes to the 3.3 TB/s a write-only kernel reaches on this GPU is a coincidence that was first read as the cause.)  About a
 		 * fifth of the tile time at full occupancy is contention; the rest is the chain of a 32-column chunk, 1 100 - 1 200 cycles
 		 * against 512 of tensor work.
-		 * Measured, 57 600 rows, K = 256 (before -> after the box epilogue): N = 768 0.043 -> 0.040 ms, N = 256 with a residual 0.031 -> 0.025 ms, N = 1024 with ReLU 0.055 -> 0.052 ms; the 36 Winograd products
+		 * Measured, 57 600 rows, K = 256 (staged epilogue -> box epilogue -> its chunk loop unrolled by two instead of whole, which took
+		 * the kernel's instruction-fetch stalls down: ncu had one stalled warp per issued instruction on `no instruction`): N = 768 0.043 ->
+		 * 0.040 -> 0.037 ms, N = 256 with a residual 0.031 -> 0.025 -> 0.023 ms, N = 1024 with ReLU 0.055 -> 0.052 -> 0.049 ms; the 36 Winograd products
 		 * of a 256-channel layer 0.167 -> 0.159 ms with the resident weights alone (0.92 of the copy bandwidth).
 		 */
 		constexpr int RESIDENT_BYTES = 128 * 1024;
@@ -526,14 +528,19 @@ namespace mb200
 					if (chunks > 0)
 						tmem_ld_32x32(taddr, r[0]);
 					bool ok = true;
+					// two chunks per trip of the loop (one per register buffer): the four-chunk body unrolled whole was 16 KB of code, and the
+					// kernel's warps stood one cycle per issued instruction waiting for instructions
+#pragma unroll 1
+					for (int ip = 0; ip < NCH && ok; ip += 2)
 #pragma unroll
-					for (int i = 0; i < NCH; i++)
+					for (int j = 0; j < 2; j++)
 					{
+						const int i = ip + j;
 						if (i >= chunks)
 							break; // warp-uniform
 						tmem_wait_ld();
 						if (i + 1 < chunks)
-							tmem_ld_32x32(taddr + (i + 1) * 32, r[(i + 1) & 1]);
+							tmem_ld_32x32(taddr + (i + 1) * 32, r[(j + 1) & 1]);
 						else
 						{ // the tile's accumulators are all in registers: the issue warp may have the buffer back
 							tcgen05_fence_before();
@@ -557,7 +564,7 @@ namespace mb200
 						const int n0 = w.nt * BN + col_part * (BN / 2) + i * 32;
 						const uint32_t box = boxes + (n % 3) * T::box_bytes;
 						float v[32];
-						const uint32_t (&ri)[32] = r[i & 1];
+						const uint32_t (&ri)[32] = r[j];
 #pragma unroll
 						for (int j = 0; j < 32; j++)
 							v[j] = __uint_as_float(ri[j]) * p.alpha;
