@@ -528,8 +528,8 @@ namespace mb200
 					if (chunks > 0)
 						tmem_ld_32x32(taddr, r[0]);
 					bool ok = true;
-					// two chunks per trip of the loop (one per register buffer): the four-chunk body unrolled whole was 16 KB of code, and the
-					// kernel's warps stood one cycle per issued instruction waiting for instructions
+					// two chunks per trip of the loop (one per register buffer): the four-chunk body unrolled whole was twice the code, and ncu had the
+					// kernel's warps stalled on instruction fetch (`no instruction`) once per issued instruction
 #pragma unroll 1
 					for (int ip = 0; ip < NCH && ok; ip += 2)
 #pragma unroll
